@@ -1,0 +1,456 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a built on tcgen05.mma with TMEM
+// accumulators and TMA-fed shared-memory operand rings.
+//
+//   D[M,N] = alpha * (A · B^T) + beta * Cin        (bf16 in, fp32 accumulate, bf16 out)
+//
+// Either operand may be K-major ([rows, K], the nn.Linear forward form) or MN-major
+// ([K, rows], which is what dgrad and wgrad see), so forward, dgrad and wgrad all run
+// on the same kernel without a transpose pass.  Two grouped forms serve the MoE
+// experts: "M-grouped" (each 128-row tile of A multiplies its own expert's B) and
+// "K-grouped" (each expert's output is reduced over its own token range).
+//
+// CTA layout (192 threads, one CTA per SM):
+//   warp 0   : TMA producer (one lane)        -> full[stage]
+//   warp 1   : tcgen05.mma issuer (one lane)  -> empty[stage], tmem_full[acc]; owns TMEM alloc
+//   warps 2-5: epilogue: tcgen05.ld -> scale/add -> swizzled smem staging -> TMA store
+// Two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1.
+//
+// The role the reference gives to cuBLAS through torch.nn.functional.linear
+// (test/fsdp/bench_fsdp2_compare.py:456-483 builds its blocks from nn.Linear) is what
+// this kernel takes over.
+#include "common.cuh"
+#include <cuda.h>
+#include <cstdio>
+#include <mutex>
+
+namespace mfsdp {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int kGemmThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr int kChunkBytes = 8192;      // one 64-wide MN chunk x 64 k-rows of bf16
+constexpr int kEpiBufBytes = BM * 128; // 128 rows x 64 bf16
+
+struct GemmArgs {
+  int M, N, K;
+  int tiles_m, tiles_n;
+  float alpha, beta;
+  const __nv_bfloat16* cin;
+  long long ldcin;
+  int* status;
+  int group_mode;            // 0 dense, 1 M-grouped, 2 K-grouped
+  const int* tile_group;     // mode 1: group id per M tile (-1 = tile has no rows)
+  const int* group_offsets;  // mode 2: [G+1] offsets along the reduce dimension
+  int b_group_stride;        // mode 1: rows added to B's row coordinate per group
+  int tiles_m_per_group;     // mode 2
+  int m_per_group;           // mode 2
+};
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 2 * kEpiBufBytes + 1024 + 256;
+};
+
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+struct TileCoord {
+  int m0, n0;        // element offsets into the (per-group) output
+  int out_row0;      // row of D this tile starts at
+  int a_row_k0;      // first reduce index
+  int nkb;           // number of 64-wide reduce blocks
+  int b_row_off;     // mode 1: offset added to B's row coordinate
+  bool skip;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, int tile) {
+  // Grouped rasterisation: 8 M-tiles share each sweep over N so that the CTAs running
+  // at the same time reuse A and B tiles out of L2.
+  constexpr int kGroupM = 8;
+  const int per_group = kGroupM * p.tiles_n;
+  const int gid = tile / per_group;
+  const int first_m = gid * kGroupM;
+  const int gsz = min(p.tiles_m - first_m, kGroupM);
+  const int tm = first_m + (tile % per_group) % gsz;
+  const int tn = (tile % per_group) / gsz;
+  TileCoord c;
+  c.skip = false;
+  c.n0 = tn;  // scaled by the caller's BN
+  c.b_row_off = 0;
+  c.a_row_k0 = 0;
+  c.nkb = (p.K + BK - 1) / BK;
+  if (p.group_mode == 0) {
+    c.m0 = tm * BM;
+    c.out_row0 = c.m0;
+  } else if (p.group_mode == 1) {
+    c.m0 = tm * BM;
+    c.out_row0 = c.m0;
+    const int g = p.tile_group[tm];
+    if (g < 0) c.skip = true;
+    c.b_row_off = (g < 0 ? 0 : g) * p.b_group_stride;
+  } else {
+    const int g = tm / p.tiles_m_per_group;
+    c.m0 = (tm % p.tiles_m_per_group) * BM;
+    c.out_row0 = g * p.m_per_group + c.m0;
+    const int k_lo = p.group_offsets[g], k_hi = p.group_offsets[g + 1];
+    c.a_row_k0 = k_lo;
+    c.nkb = (k_hi - k_lo + BK - 1) / BK;
+  }
+  return c;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
+                         const __grid_constant__ CUtensorMap tma_b,
+                         const __grid_constant__ CUtensorMap tma_d, const GemmArgs p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int kStages = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* epi_base = smem + kStages * Cfg::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_base + 2 * kEpiBufBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kStages;
+  uint64_t* tfull_bar = bars + 2 * kStages;
+  uint64_t* tempty_bar = bars + 2 * kStages + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&tfull_bar[b]), 1);
+      mbar_init(smem_u32(&tempty_bar[b]), kEpiThreads);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+    tma_prefetch_desc(&tma_d);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_tiles = p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        TileCoord c = decode_tile(p, tile);
+        if (c.skip) continue;
+        const int n0 = c.n0 * BN;
+        for (int kb = 0; kb < c.nkb; ++kb, ++it) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+          if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, p.status, abort_flag)) { ok = false; break; }
+          const uint32_t fb = smem_u32(&full_bar[s]);
+          mbar_arrive_expect_tx(fb, Cfg::kStageBytes);
+          const uint32_t a_dst = smem_u32(smem + s * Cfg::kStageBytes);
+          const uint32_t b_dst = a_dst + Cfg::kABytes;
+          const int k0 = c.a_row_k0 + kb * BK;
+          if (!A_MN) {
+            tma_load_2d(a_dst, &tma_a, fb, k0, c.m0);
+          } else {
+            tma_load_2d(a_dst, &tma_a, fb, c.m0, k0);
+            tma_load_2d(a_dst + kChunkBytes, &tma_a, fb, c.m0 + 64, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d(b_dst, &tma_b, fb, k0, n0 + c.b_row_off);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(b_dst + j * kChunkBytes, &tma_b, fb, n0 + 64 * j, k0 + c.b_row_off);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      uint32_t it = 0, lt = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        TileCoord c = decode_tile(p, tile);
+        if (c.skip) continue;
+        const uint32_t acc = lt & 1, aph = (lt >> 1) & 1;
+        if (!mbar_wait(smem_u32(&tempty_bar[acc]), aph ^ 1, p.status, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < c.nkb; ++kb, ++it) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+          if (!mbar_wait(smem_u32(&full_bar[s]), ph, p.status, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(smem + s * Cfg::kStageBytes);
+          const uint32_t b_base = a_base + Cfg::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = A_MN ? make_smem_desc_sw128(a_base + k * 2048, kChunkBytes, 1024)
+                                        : make_smem_desc_sw128(a_base + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc_sw128(b_base + k * 2048, kChunkBytes, 1024)
+                                        : make_smem_desc_sw128(b_base + k * 32, 16, 1024);
+            umma_f16_ss(tmem_d, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&empty_bar[s]));
+        }
+        if (!ok) break;
+        umma_commit(smem_u32(&tfull_bar[acc]));
+        ++lt;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;                // TMEM lane quarter this warp may read
+    const int row_in_tile = q * 32 + lane;
+    const int epi_tid = threadIdx.x - 64;
+    uint32_t lt = 0, store_cnt = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      TileCoord c = decode_tile(p, tile);
+      if (c.skip) continue;
+      const int n0 = c.n0 * BN;
+      const uint32_t acc = lt & 1, aph = (lt >> 1) & 1;
+      mbar_wait(smem_u32(&tfull_bar[acc]), aph, p.status, abort_flag);
+      epi_bar_sync();
+      if (*abort_flag) break;
+      tc_fence_after();
+      const long long grow = (long long)c.out_row0 + row_in_tile;
+      const bool row_ok = (p.group_mode == 2) ? (c.m0 + row_in_tile < p.m_per_group)
+                                              : (c.m0 + row_in_tile < p.M);
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 64; ++ch) {
+        const int ncol0 = n0 + ch * 64;
+        if (ncol0 >= p.N) break;
+        const uint32_t buf = store_cnt & 1;
+        uint8_t* ebuf = epi_base + buf * kEpiBufBytes;
+        if (epi_tid == 0) tma_store_wait_read<1>();
+        epi_bar_sync();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[32];
+          if (c.nkb > 0) {
+            tmem_ld_32x32b_x32(tmem_base + acc * BN + ((uint32_t)(q * 32) << 16) + ch * 64 + h * 32, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0u;
+          }
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = p.alpha * __uint_as_float(r[j]);
+          if (p.cin != nullptr && p.beta != 0.f && row_ok) {
+            const __nv_bfloat16* crow = p.cin + grow * p.ldcin + ncol0 + h * 32;
+#pragma unroll
+            for (int g8 = 0; g8 < 4; ++g8) {
+              const int col = ncol0 + h * 32 + g8 * 8;
+              if (col + 8 <= p.N && ((reinterpret_cast<uintptr_t>(crow + g8 * 8) & 15) == 0)) {
+                const uint4 u = *reinterpret_cast<const uint4*>(crow + g8 * 8);
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 f = unpack_bf16x2(w[e]);
+                  v[g8 * 8 + 2 * e] += p.beta * f.x;
+                  v[g8 * 8 + 2 * e + 1] += p.beta * f.y;
+                }
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  if (col + e < p.N) v[g8 * 8 + e] += p.beta * __bfloat162float(crow[g8 * 8 + e]);
+              }
+            }
+          }
+#pragma unroll
+          for (int g8 = 0; g8 < 4; ++g8) {
+            uint4 o;
+            o.x = pack_bf16x2(v[g8 * 8 + 0], v[g8 * 8 + 1]);
+            o.y = pack_bf16x2(v[g8 * 8 + 2], v[g8 * 8 + 3]);
+            o.z = pack_bf16x2(v[g8 * 8 + 4], v[g8 * 8 + 5]);
+            o.w = pack_bf16x2(v[g8 * 8 + 6], v[g8 * 8 + 7]);
+            const int chunk = h * 4 + g8;
+            const int phys = chunk ^ (row_in_tile & 7);
+            *reinterpret_cast<uint4*>(ebuf + row_in_tile * 128 + phys * 16) = o;
+          }
+        }
+        fence_proxy_async_smem();
+        epi_bar_sync();
+        if (epi_tid == 0) {
+          tma_store_2d(&tma_d, smem_u32(ebuf), ncol0, c.out_row0);
+          tma_store_commit();
+        }
+        ++store_cnt;
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&tempty_bar[acc]));
+      ++lt;
+    }
+    if (epi_tid == 0) tma_store_wait_all<0>();
+  }
+
+  // ---------------------------------------------------------------- teardown
+  if (*abort_flag) __nanosleep(1000000);  // let TMA copies in flight land before the CTA exits
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// rows x cols row-major bf16 tensor (row stride `ld` elements); box = box_rows x 64 cols.
+int make_tmap_bf16_2d(CUtensorMap* map, const void* base, long long rows, long long cols,
+                      long long ld, int box_rows, int box_cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
+                       const GemmArgs& args, int grid, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  static bool attr_set = false;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN>;
+  if (!attr_set) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, td, args);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace mfsdp
+
+using namespace mfsdp;
+
+// Returns 0 on success, a CUDA / driver error code otherwise, or -2 for a bad argument.
+// Layout contract (all bf16, strides in elements, 16-byte aligned bases and row pitches):
+//   a_mn_major = 0: A is [M, K];   1: A is [K, M]
+//   b_mn_major = 0: B is [N, K];   1: B is [K, N]
+//   D, Cin are [M, N].
+// group_mode 1 (M-grouped): A/D rows are grouped in 128-row tiles, tile_group[t] names the
+//   group of M-tile t; B holds num_groups matrices stacked along its row dimension.
+// group_mode 2 (K-grouped): both operands are MN-major and stacked along the reduce
+//   dimension; group g reduces rows [group_offsets[g], group_offsets[g+1]) and writes
+//   D rows [g*M, (g+1)*M).  M must be a multiple of 128 and offsets multiples of 64.
+MFSDP_API int mfsdp_gemm_bf16(const void* A, const void* B, void* D, const void* Cin, int M, int N,
+                              int K, long long lda, long long ldb, long long ldd, long long ldcin,
+                              int a_mn_major, int b_mn_major, float alpha, float beta,
+                              int group_mode, const int* tile_group, const int* group_offsets,
+                              int num_groups, long long k_total, int* status, int num_sms,
+                              int force_bn, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K < 0) return -2;
+  if ((lda % 8) || (ldb % 8) || (ldd % 8)) return -2;
+  if (((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)D & 15)) return -2;
+  if (group_mode == 2 && (!a_mn_major || !b_mn_major || (M % BM) != 0)) return -2;
+  if (group_mode != 0 && num_groups <= 0) return -2;
+
+  GemmArgs args{};
+  args.M = M; args.N = N; args.K = K;
+  args.alpha = alpha; args.beta = beta;
+  args.cin = reinterpret_cast<const __nv_bfloat16*>(Cin);
+  args.ldcin = ldcin;
+  args.status = status;
+  args.group_mode = group_mode;
+  args.tile_group = tile_group;
+  args.group_offsets = group_offsets;
+  args.m_per_group = M;
+  args.tiles_m_per_group = (M + BM - 1) / BM;
+
+  const int tiles_m_base = (M + BM - 1) / BM;
+  args.tiles_m = (group_mode == 2) ? tiles_m_base * num_groups : tiles_m_base;
+
+  // Tile width: 256 keeps the tensor pipe fed per shared-memory byte; 128 wins when it
+  // fills the last wave better.
+  int bn = 256;
+  if (force_bn == 128 || force_bn == 256) {
+    bn = force_bn;
+  } else if (N <= 128) {
+    bn = 128;
+  } else {
+    auto eff = [&](int b) {
+      const long long t = (long long)args.tiles_m * ((N + b - 1) / b);
+      const long long waves = (t + num_sms - 1) / num_sms;
+      const double padded_n = (double)((N + b - 1) / b) * b;
+      return ((double)t / (double)(waves * num_sms)) * ((double)N / padded_n) *
+             (b == 256 ? 1.0 : 0.88);
+    };
+    bn = eff(256) >= eff(128) ? 256 : 128;
+  }
+  args.tiles_n = (N + bn - 1) / bn;
+  args.b_group_stride = (group_mode == 1) ? (b_mn_major ? K : N) : 0;
+
+  // Tensor maps.
+  CUtensorMap ta, tb, td;
+  int rc;
+  const long long red = (group_mode == 2) ? k_total : K;
+  if (!a_mn_major) rc = make_tmap_bf16_2d(&ta, A, M, red, lda, BM, 64);
+  else             rc = make_tmap_bf16_2d(&ta, A, red, M, lda, BK, 64);
+  if (rc) return rc;
+  const long long b_groups = (group_mode == 1) ? num_groups : 1;
+  if (!b_mn_major) rc = make_tmap_bf16_2d(&tb, B, (long long)N * b_groups, red, ldb, bn, 64);
+  else             rc = make_tmap_bf16_2d(&tb, B, red * b_groups, N, ldb, BK, 64);
+  if (rc) return rc;
+  const long long d_rows = (group_mode == 2) ? (long long)M * num_groups : M;
+  rc = make_tmap_bf16_2d(&td, D, d_rows, N, ldd, BM, 64);
+  if (rc) return rc;
+
+  const int total = args.tiles_m * args.tiles_n;
+  const int grid = total < num_sms ? total : num_sms;
+#define MFSDP_LAUNCH(BN_)                                                                   \
+  (a_mn_major ? (b_mn_major ? launch_gemm<BN_, true, true>(ta, tb, td, args, grid, stream)  \
+                            : launch_gemm<BN_, true, false>(ta, tb, td, args, grid, stream)) \
+              : (b_mn_major ? launch_gemm<BN_, false, true>(ta, tb, td, args, grid, stream) \
+                            : launch_gemm<BN_, false, false>(ta, tb, td, args, grid, stream)))
+  return bn == 256 ? MFSDP_LAUNCH(256) : MFSDP_LAUNCH(128);
+#undef MFSDP_LAUNCH
+}
