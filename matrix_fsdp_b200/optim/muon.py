@@ -1,0 +1,158 @@
+"""Muon for whole-matrix owners: momentum + Nesterov, quintic Newton-Schulz, decoupled decay.
+
+Update rule (identical to ``torch.optim.Muon``, ``torch/optim/_muon.py:276-310``)::
+
+    buf  <- lerp(buf, g, 1 - mu);  u <- nesterov ? lerp(g, buf, mu) : buf
+    X    <- bf16(u) (transposed if rows > cols);  X <- X / max(||X||_F, eps)
+    k times:  A = X Xᵀ;  B = b A + c A A;  X = a X + B X
+    p    <- p (1 - lr wd) - adjust(lr, shape) * X
+
+On CUDA each Newton-Schulz product runs on the tcgen05 GEMM with the polynomial folded into
+the epilogue (``alpha * acc + beta * C``), so an iteration is three kernels with no separate
+axpy, and tall matrices are handled by switching operand majors instead of transposing.  The
+element-wise stages (momentum/Nesterov + Frobenius norm, scaling, parameter update + bf16 emit)
+are single fused kernels.  The reference delegates all of this to ``torch.optim.Muon``
+(``matrix_fsdp/optim/wrapper.py:416-429``), i.e. 15 cuBLAS ``addmm`` calls per matrix.
+"""
+from __future__ import annotations
+
+import math
+from collections.abc import Iterable
+
+import torch
+from torch.optim import Optimizer
+
+DEFAULT_NS_COEFFICIENTS = (3.4445, -4.7750, 2.0315)
+DEFAULT_MUON_ADJUST_LR_FN = "match_rms_adamw"
+EPS = 1e-7
+
+
+def adjust_lr(lr: float, adjust_lr_fn: str | None, shape) -> float:
+    a, b = int(shape[0]), int(shape[1])
+    if adjust_lr_fn is None or adjust_lr_fn == "original":
+        return lr * math.sqrt(max(1.0, a / b))
+    if adjust_lr_fn == "match_rms_adamw":
+        return lr * 0.2 * math.sqrt(max(a, b))
+    raise ValueError(f"Unknown adjust_lr_fn={adjust_lr_fn!r}; expected 'original' or 'match_rms_adamw'.")
+
+
+def newton_schulz_reference(u: torch.Tensor, coefficients=DEFAULT_NS_COEFFICIENTS, steps: int = 5,
+                            eps: float = EPS) -> torch.Tensor:
+    """Plain torch implementation (CPU path and test oracle)."""
+    a, b, c = coefficients
+    x = u.bfloat16()
+    tall = x.size(0) > x.size(1)
+    if tall:
+        x = x.T
+    x = x / x.norm().clamp(min=eps)
+    for _ in range(steps):
+        g = x @ x.T
+        bm = torch.addmm(g, g, g, beta=b, alpha=c)
+        x = torch.addmm(x, bm, x, beta=a)
+    return x.T if tall else x
+
+
+def newton_schulz_sm100(x: torch.Tensor, coefficients=DEFAULT_NS_COEFFICIENTS, steps: int = 5) -> torch.Tensor:
+    """Newton-Schulz on an already normalised bf16 ``[rows, cols]`` matrix with tcgen05 GEMMs.
+
+    Works in the matrix's own orientation: for tall matrices the Gram matrix is ``XᵀX`` and the
+    update is ``X <- a X + X B`` (``B`` is symmetric), so nothing is ever transposed in memory.
+    """
+    from ..ops import kernels as K
+
+    a, b, c = coefficients
+    rows, cols = x.shape
+    tall = rows > cols
+    n = cols if tall else rows
+    gram = torch.empty((n, n), dtype=torch.bfloat16, device=x.device)
+    poly = torch.empty_like(gram)
+    nxt = torch.empty_like(x)
+    for _ in range(steps):
+        if tall:
+            K.gemm(x, x, a_mn_major=True, b_mn_major=True, out=gram)            # XᵀX
+            K.gemm(gram, gram, out=poly, cin=gram, alpha=c, beta=b)             # bA + cAA
+            K.gemm(x, poly, out=nxt, cin=x, alpha=1.0, beta=a)                  # aX + X B
+        else:
+            K.gemm(x, x, out=gram)                                              # XXᵀ
+            K.gemm(gram, gram, out=poly, cin=gram, alpha=c, beta=b)
+            K.gemm(poly, x, b_mn_major=True, out=nxt, cin=x, alpha=1.0, beta=a)  # aX + B X
+        x, nxt = nxt, x
+    return x
+
+
+def _use_kernels(t: torch.Tensor) -> bool:
+    if t.device.type != "cuda":
+        return False
+    from ..ops import lib
+
+    if lib.disabled_by_env():
+        return False
+    lib.load(required=True)
+    rows, cols = t.shape
+    return rows % 8 == 0 and cols % 8 == 0
+
+
+class MatrixMuon(Optimizer):
+    """Muon over 2-D parameters that this rank owns whole (matrix-owner layouts)."""
+
+    def __init__(self, params: Iterable, *, lr: float = 1e-3, weight_decay: float = 0.1, momentum: float = 0.95,
+                 nesterov: bool = True, ns_coefficients=DEFAULT_NS_COEFFICIENTS, eps: float = EPS, ns_steps: int = 5,
+                 adjust_lr_fn: str | None = None, low_precision_of=None) -> None:
+        if lr < 0 or momentum < 0 or weight_decay < 0:
+            raise ValueError("invalid Muon hyper-parameters")
+        if adjust_lr_fn not in (None, "original", "match_rms_adamw"):
+            raise ValueError(f"Unknown adjust_lr_fn={adjust_lr_fn!r}.")
+        super().__init__(params, dict(lr=lr, weight_decay=weight_decay, momentum=momentum, nesterov=nesterov,
+                                      ns_coefficients=tuple(ns_coefficients), eps=eps, ns_steps=ns_steps,
+                                      adjust_lr_fn=adjust_lr_fn))
+        # optional callable param -> bf16 tensor to refresh after the update (all-gather source)
+        self._low_precision_of = low_precision_of
+        self.grad_scale = 1.0
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            for p in group["params"]:
+                if p.grad is None or p.numel() == 0:
+                    continue
+                if p.ndim != 2:
+                    raise ValueError("Muon only supports 2D parameters; route the rest to AdamW.")
+                self._step_one(p, group)
+        return loss
+
+    def _step_one(self, p: torch.Tensor, group: dict) -> None:
+        st = self.state[p]
+        if "momentum_buffer" not in st:
+            st["momentum_buffer"] = torch.zeros_like(p, dtype=torch.float32 if p.dtype == torch.float32 else p.dtype)
+        buf = st["momentum_buffer"]
+        lr, wd, mu = float(group["lr"]), group["weight_decay"], group["momentum"]
+        alr = adjust_lr(lr, group["adjust_lr_fn"], p.shape)
+        lp = self._low_precision_of(p) if self._low_precision_of is not None else None
+        g = p.grad
+        if _use_kernels(p) and p.dtype == torch.float32 and buf.dtype == torch.float32 and g.is_contiguous():
+            from ..ops import kernels as K
+
+            u = torch.empty(p.shape, dtype=torch.bfloat16, device=p.device)
+            ss = torch.zeros(1, dtype=torch.float32, device=p.device)
+            K.muon_momentum(buf.view(-1), g.reshape(-1), u.view(-1), ss, mu, float(self.grad_scale), group["nesterov"])
+            K.muon_normalize_(u.view(-1), ss, group["eps"])
+            o = newton_schulz_sm100(u, group["ns_coefficients"], group["ns_steps"])
+            K.muon_apply_(p.data.view(-1), o.reshape(-1), p.shape[0], p.shape[1], False, lr, wd, alr,
+                          p_lp=lp.view(-1) if lp is not None and lp.dtype == torch.bfloat16 else None)
+            if lp is not None and lp.dtype != torch.bfloat16:
+                lp.copy_(p.data)
+            return
+        gf = g.to(buf.dtype)
+        if self.grad_scale != 1.0:
+            gf = gf * self.grad_scale
+        buf.lerp_(gf, 1 - mu)
+        update = gf.lerp(buf, mu) if group["nesterov"] else buf
+        o = newton_schulz_reference(update, group["ns_coefficients"], group["ns_steps"], group["eps"])
+        p.data.mul_(1 - lr * wd)
+        p.data.add_(o.to(p.dtype), alpha=-alr)
+        if lp is not None:
+            lp.copy_(p.data)

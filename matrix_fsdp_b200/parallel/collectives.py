@@ -1,0 +1,294 @@
+"""Segment collectives over ``torch.distributed`` (NCCL or Gloo) with async handles.
+
+These are the portable transport: they serve CPU/Gloo runs, multi-node NCCL runs and act
+as the functional baseline for the peer-memory kernels in
+:mod:`matrix_fsdp_b200.parallel.peer`.  Every function also has a single-rank branch
+(``group is None``) that degenerates to local copies so the whole lifecycle runs in one
+process.
+
+Async pattern: when a CUDA ``stream`` is given the blocking collective is enqueued on that
+stream (after it has waited for the caller's stream) and the handle's ``wait()`` makes the
+current stream wait for the recorded event; without a stream the ``async_op`` work handle
+is kept.  Parity: ``matrix_fsdp/runtime/collectives.py:26-1046``.
+"""
+from __future__ import annotations
+
+import os
+from collections.abc import Sequence
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+from ..core.layout import LayoutSegment, rank_segments_are_rank_contiguous_chunks
+
+VALIDATE_SIGNATURE_ENV = "MFSDP_VALIDATE_OWNER_COLLECTIVE_SIGNATURE"
+
+
+class MatrixCollectiveHandle:
+    """Completion handle of one enqueued collective (or a batch of them)."""
+
+    def __init__(self, works=(), event=None, post=None, info: dict | None = None) -> None:
+        self._works = [w for w in works if w is not None]
+        self._event = event
+        self._post = post
+        self.info = info or {}
+        self.done = False
+
+    def wait(self) -> None:
+        if self.done:
+            return
+        for w in self._works:
+            w.wait()
+        if self._event is not None:
+            torch.cuda.current_stream().wait_event(self._event)
+        if self._post is not None:
+            self._post()
+        self.done = True
+
+    def is_completed(self) -> bool:
+        if self.done:
+            return True
+        if self._event is not None:
+            return self._event.query()
+        return all(w.is_completed() for w in self._works)
+
+
+class MatrixTensorCollectiveHandle(MatrixCollectiveHandle):
+    """Handle that also names the tensor the collective produces."""
+
+    def __init__(self, tensor: torch.Tensor, **kw) -> None:
+        super().__init__(**kw)
+        self.tensor = tensor
+
+
+def _world(group) -> int:
+    return 1 if group is None else dist.get_world_size(group)
+
+
+def _rank(group) -> int:
+    return 0 if group is None else dist.get_rank(group)
+
+
+def _run(fn, *, stream, info) -> MatrixCollectiveHandle:
+    """Run ``fn`` (which issues blocking collectives) on ``stream`` and return its handle."""
+    if stream is not None:
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            fn()
+            ev = torch.cuda.Event()
+            ev.record(stream)
+        info["sync_mode"] = "stream_event"
+        return MatrixCollectiveHandle(event=ev, info=info)
+    fn()
+    info["sync_mode"] = "blocking"
+    return MatrixCollectiveHandle(info=info)
+
+
+@dataclass
+class SegmentTables:
+    """Everything a transport needs about one unit's layout, precomputed once."""
+
+    total_numel: int
+    world_size: int
+    rank: int
+    rank_segments: tuple[tuple[LayoutSegment, ...], ...]
+    shard_sizes: tuple[int, ...]
+    max_shard: int = 0
+    equal_contiguous: bool = False
+    rank_contiguous: bool = False
+    signature: tuple = field(default=(), repr=False)
+
+    @classmethod
+    def build(cls, total_numel: int, rank_segments: Sequence[Sequence[LayoutSegment]], rank: int) -> "SegmentTables":
+        segs = tuple(tuple(s for s in rs if s.numel > 0) for rs in rank_segments)
+        sizes = tuple(sum(s.numel for s in rs) for rs in segs)
+        contiguous = rank_segments_are_rank_contiguous_chunks(segs)
+        equal = contiguous and len(set(sizes)) == 1 and sizes[0] * len(sizes) == total_numel
+        sig = (total_numel, tuple(tuple((s.global_start, s.global_end, s.local_start) for s in rs) for rs in segs))
+        return cls(int(total_numel), len(segs), int(rank), segs, sizes, max(sizes, default=0), equal, contiguous, sig)
+
+    @property
+    def my_segments(self) -> tuple[LayoutSegment, ...]:
+        return self.rank_segments[self.rank]
+
+
+def validate_layout_signature(tables: SegmentTables, group) -> None:
+    """Debug aid: all ranks must agree on the layout before issuing per-owner collectives."""
+    if group is None or os.environ.get(VALIDATE_SIGNATURE_ENV, "0") in ("", "0"):
+        return
+    sigs: list = [None] * _world(group)
+    dist.all_gather_object(sigs, hash(tables.signature), group=group)
+    if len(set(sigs)) != 1:
+        raise RuntimeError(f"Layout signature differs across ranks: {sigs}")
+
+
+# --------------------------------------------------------------------------- local copies
+def scatter_local_segments(shard: torch.Tensor, full: torch.Tensor, segments: Sequence[LayoutSegment]) -> None:
+    """``full[g0:g1] = shard[l0:l1]`` for every segment."""
+    for s in segments:
+        full[s.global_start:s.global_end].copy_(shard[s.local_start:s.local_end])
+
+
+def gather_local_segments(full: torch.Tensor, shard: torch.Tensor, segments: Sequence[LayoutSegment]) -> None:
+    """``shard[l0:l1] = full[g0:g1]`` for every segment."""
+    for s in segments:
+        shard[s.local_start:s.local_end].copy_(full[s.global_start:s.global_end])
+
+
+# --------------------------------------------------------------------------- all-gather
+def all_gather_equal_1d_into_async(shard: torch.Tensor, full: torch.Tensor, group, *, stream=None) -> MatrixCollectiveHandle:
+    """Equal rank-ordered shards straight into the full buffer (no staging)."""
+    info = {"kind": "all_gather", "impl": "all_gather_into_tensor", "bytes": full.numel() * full.element_size(), "count": 1}
+    if group is None:
+        full.copy_(shard)
+        return MatrixCollectiveHandle(info={**info, "impl": "local_copy", "sync_mode": "local"})
+    return _run(lambda: dist.all_gather_into_tensor(full, shard, group=group), stream=stream, info=info)
+
+
+def all_gather_matrix_1d_into_async(shard: torch.Tensor, full: torch.Tensor, tables: SegmentTables, group, *,
+                                    stream=None, workspace: torch.Tensor | None = None) -> MatrixCollectiveHandle:
+    """Uneven layouts: pad shards to the largest, gather, then unpad into the full buffer."""
+    W, mx = tables.world_size, tables.max_shard
+    info = {"kind": "all_gather", "impl": "padded_all_gather", "bytes": W * mx * full.element_size(), "count": 1}
+    if group is None:
+        scatter_local_segments(shard, full, tables.my_segments)
+        return MatrixCollectiveHandle(info={**info, "impl": "local_copy", "sync_mode": "local"})
+
+    def body():
+        ws = workspace if workspace is not None else torch.empty(W * mx, dtype=full.dtype, device=full.device)
+        send = ws.new_zeros(mx) if shard.numel() != mx else shard
+        if shard.numel() != mx:
+            send[: shard.numel()].copy_(shard)
+        dist.all_gather_into_tensor(ws[: W * mx], send, group=group)
+        for r in range(W):
+            scatter_local_segments(ws[r * mx:(r + 1) * mx], full, tables.rank_segments[r])
+
+    return _run(body, stream=stream, info=info)
+
+
+def broadcast_rank_segments_1d_into_async(shard: torch.Tensor, full: torch.Tensor, tables: SegmentTables, group, *,
+                                          stream=None) -> MatrixCollectiveHandle:
+    """Owner broadcast: every rank broadcasts its packed shard; receivers scatter it into place."""
+    W = tables.world_size
+    info = {"kind": "all_gather", "impl": "owner_broadcast", "bytes": full.numel() * full.element_size(),
+            "count": sum(1 for s in tables.shard_sizes if s)}
+    if group is None:
+        scatter_local_segments(shard, full, tables.my_segments)
+        return MatrixCollectiveHandle(info={**info, "impl": "local_copy", "sync_mode": "local"})
+    validate_layout_signature(tables, group)
+
+    def body():
+        for r in range(W):
+            n = tables.shard_sizes[r]
+            if n == 0:
+                continue
+            contiguous_one = len(tables.rank_segments[r]) == 1
+            if contiguous_one:
+                seg = tables.rank_segments[r][0]
+                view = full[seg.global_start:seg.global_end]
+                if r == tables.rank:
+                    view.copy_(shard[:n])
+                dist.broadcast(view, src=dist.get_global_rank(group, r), group=group)
+            else:
+                buf = shard[:n] if r == tables.rank else torch.empty(n, dtype=full.dtype, device=full.device)
+                dist.broadcast(buf, src=dist.get_global_rank(group, r), group=group)
+                scatter_local_segments(buf, full, tables.rank_segments[r])
+
+    return _run(body, stream=stream, info=info)
+
+
+def all_gatherv_rank_segments_1d_into_async(shard: torch.Tensor, full: torch.Tensor, tables: SegmentTables, group, *,
+                                            stream=None, impl: str = "auto",
+                                            workspace: torch.Tensor | None = None) -> MatrixCollectiveHandle:
+    """Dispatch on layout shape: equal chunks, padded gather, or owner broadcast."""
+    if tables.equal_contiguous and impl in ("auto", "equal"):
+        return all_gather_equal_1d_into_async(shard, full, group, stream=stream)
+    if impl in ("owner_broadcast", "broadcast"):
+        return broadcast_rank_segments_1d_into_async(shard, full, tables, group, stream=stream)
+    return all_gather_matrix_1d_into_async(shard, full, tables, group, stream=stream, workspace=workspace)
+
+
+# --------------------------------------------------------------------------- reduce-scatter
+def pack_rank_major_padded(full_grad: torch.Tensor, tables: SegmentTables, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``[W, max_shard]`` reduce-scatter input: row r is rank r's packed shard, zero padded."""
+    W, mx = tables.world_size, tables.max_shard
+    if out is None:
+        out = torch.zeros(W * mx, dtype=full_grad.dtype, device=full_grad.device)
+    else:
+        out.zero_()
+    for r in range(W):
+        gather_local_segments(full_grad, out[r * mx:(r + 1) * mx], tables.rank_segments[r])
+    return out
+
+
+def reduce_scatter_padded_rank_chunks_1d_async(full_grad: torch.Tensor, out_shard: torch.Tensor,
+                                               tables: SegmentTables, group, *, scale: float | None = None,
+                                               stream=None, workspace: torch.Tensor | None = None,
+                                               ) -> MatrixCollectiveHandle:
+    """Sum over ranks of each rank's segments, result on the owning rank, then ``* scale``."""
+    W, mx = tables.world_size, tables.max_shard
+    n_local = tables.shard_sizes[tables.rank]
+    info = {"kind": "reduce_scatter", "impl": "padded_reduce_scatter", "bytes": W * mx * full_grad.element_size(), "count": 1}
+    if group is None:
+        gather_local_segments(full_grad, out_shard, tables.my_segments)
+        if scale is not None and scale != 1.0:
+            out_shard.mul_(scale)
+        return MatrixCollectiveHandle(info={**info, "impl": "local_copy", "sync_mode": "local"})
+
+    def body():
+        if tables.equal_contiguous and out_shard.dtype == full_grad.dtype:
+            dist.reduce_scatter_tensor(out_shard[:n_local], full_grad, group=group)
+            info["impl"] = "reduce_scatter_tensor"
+        else:
+            packed = pack_rank_major_padded(full_grad, tables, workspace)
+            recv = torch.empty(mx, dtype=full_grad.dtype, device=full_grad.device)
+            dist.reduce_scatter_tensor(recv, packed[: W * mx], group=group)
+            out_shard[:n_local].copy_(recv[:n_local])
+        if scale is not None and scale != 1.0:
+            out_shard[:n_local].mul_(scale)
+
+    return _run(body, stream=stream, info=info)
+
+
+def reduce_owner_rank_chunks_1d_async(full_grad: torch.Tensor, out_shard: torch.Tensor, tables: SegmentTables, group, *,
+                                      scale: float | None = None, stream=None) -> MatrixCollectiveHandle:
+    """One ``reduce`` per owner rank (no padding); the owner keeps its packed result."""
+    W = tables.world_size
+    info = {"kind": "reduce_scatter", "impl": "owner_reduce", "bytes": full_grad.numel() * full_grad.element_size(),
+            "count": sum(1 for s in tables.shard_sizes if s)}
+    if group is None:
+        return reduce_scatter_padded_rank_chunks_1d_async(full_grad, out_shard, tables, None, scale=scale)
+    validate_layout_signature(tables, group)
+
+    def body():
+        for r in range(W):
+            n = tables.shard_sizes[r]
+            if n == 0:
+                continue
+            buf = torch.empty(n, dtype=full_grad.dtype, device=full_grad.device)
+            gather_local_segments(full_grad, buf, tables.rank_segments[r])
+            dist.reduce(buf, dst=dist.get_global_rank(group, r), group=group)
+            if r == tables.rank:
+                out_shard[:n].copy_(buf)
+                if scale is not None and scale != 1.0:
+                    out_shard[:n].mul_(scale)
+
+    return _run(body, stream=stream, info=info)
+
+
+def reduce_scatterv_owner_rank_chunks_1d_async(full_grad, out_shard, tables, group, *, scale=None, stream=None,
+                                               impl: str = "auto", workspace=None) -> MatrixCollectiveHandle:
+    if impl in ("owner_reduce", "reduce", "native_reduce"):
+        return reduce_owner_rank_chunks_1d_async(full_grad, out_shard, tables, group, scale=scale, stream=stream)
+    return reduce_scatter_padded_rank_chunks_1d_async(full_grad, out_shard, tables, group, scale=scale,
+                                                      stream=stream, workspace=workspace)
+
+
+def all_reduce_full_grad(tensor: torch.Tensor, group, *, scale: float | None = None) -> torch.Tensor:
+    """In-place sum over ``group`` (HSDP replicate step and diagnostics), then ``* scale``."""
+    if group is not None and _world(group) > 1:
+        dist.all_reduce(tensor, group=group)
+    if scale is not None and scale != 1.0:
+        tensor.mul_(scale)
+    return tensor

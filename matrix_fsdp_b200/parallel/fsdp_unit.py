@@ -1,0 +1,622 @@
+"""``MatrixFSDPParamGroup``: lifecycle engine of one FSDP unit (one ``fully_shard`` call).
+
+States and transitions::
+
+    SHARDED --unshard--> UNSHARDED --post-forward reshard--> FORWARD_RESHARDED
+       ^                     |                                     |
+       |                     +<-------- pre-backward unshard <-----+
+       +---- finalize backward (collect grads, reshard, reduce-scatter) ----+
+
+Hooks: a forward pre-hook (unshard + wait + prefetch the next unit), a forward hook (register
+pre-backward tensor hooks on the outputs, reshard), a post-accumulate-grad hook per parameter
+(count gradients; the last one finalises the unit) and an end-of-backward engine callback that
+finalises units whose parameters did not all receive gradients.  Forwards that run *inside* a
+backward pass (activation-checkpoint recompute) find the unit already UNSHARDED and skip all
+of this.
+
+Parity: ``matrix_fsdp/runtime/fsdp_unit.py:63-1773``.
+"""
+from __future__ import annotations
+
+import time
+import weakref
+from collections.abc import Callable, Mapping
+from enum import Enum
+from typing import Any
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from ..core.layout import MatrixGroupLayout, ShardPlan
+from ..core.managed_param import ManagedParamRegistry, ParamShardHint
+from ..core.mesh import ResolvedGroups, resolve_groups
+from ..core.mixed_precision import (cast_floating_tensors, mixed_precision_policy_metadata, offload_policy_metadata,
+                                    validate_offload_policy_for_device)
+from ..planning.layout_validator import flat_reorder_order, validate_group_layout, validate_runtime_layout
+from ..planning.planner import contiguous_even_plan
+from ..planning.planner_eval import PlannerResult, call_group_planner, planner_result_from_output
+from ..planning.shard_hint import build_shard_hints
+from .flat_buffer import MatrixFlatBuffer
+from .hooks import ForwardBackwardContext, register_pre_backward_hooks
+from .runtime_event import RuntimeEvent, RuntimeUnitMetadata, next_event_sequence, next_runtime_param_group_id
+from .transport import make_transport
+
+
+class FSDPLifecycleState(str, Enum):
+    SHARDED = "sharded"
+    UNSHARDED = "unsharded"
+    FORWARD_RESHARDED = "forward_resharded"
+
+
+FSDPRuntimeState = FSDPLifecycleState
+
+_ALLOWED = {
+    (FSDPLifecycleState.SHARDED, FSDPLifecycleState.UNSHARDED),
+    (FSDPLifecycleState.UNSHARDED, FSDPLifecycleState.FORWARD_RESHARDED),
+    (FSDPLifecycleState.UNSHARDED, FSDPLifecycleState.SHARDED),
+    (FSDPLifecycleState.FORWARD_RESHARDED, FSDPLifecycleState.UNSHARDED),
+    (FSDPLifecycleState.FORWARD_RESHARDED, FSDPLifecycleState.SHARDED),
+}
+
+
+def _in_backward() -> bool:
+    try:
+        return torch._C._current_graph_task_id() != -1
+    except Exception:  # pragma: no cover
+        return False
+
+
+class MatrixFSDPNoSync:
+    """Context manager deferring gradient reduction of a set of units (gradient accumulation)."""
+
+    def __init__(self, units) -> None:
+        self.units = list(units)
+        self._prev: list[bool] = []
+
+    def __enter__(self):
+        self._prev = [u.defer_backward_reduce for u in self.units]
+        for u in self.units:
+            u.defer_backward_reduce = True
+            u.in_no_sync = True
+        return self
+
+    def __exit__(self, *exc):
+        for u, prev in zip(self.units, self._prev):
+            u.defer_backward_reduce = prev
+            u.in_no_sync = False
+        return False
+
+
+class MatrixFSDPParamGroup:
+    def __init__(self, module: nn.Module, *, mesh=None, dp_shard_mesh_dim=None, dp_replicate_mesh_dim=None,
+                 planner: Callable[[int, int], ShardPlan] | None = None, group_planner=None, layout_planner=None,
+                 shard_hints: Mapping[str, ParamShardHint] | None = None, ignored_params=None,
+                 auto_shard_hints: bool = False, divide_grads_by_world: bool = True,
+                 reshard_after_forward: bool | int = True, forward_prefetch: bool = True,
+                 backward_prefetch: bool = True, finalize_after_backward: bool = True, mp_policy=None,
+                 offload_policy=None, param_gather_strategy: str = "auto",
+                 matrix_collective_backend: str = "owner_broadcast",
+                 backward_reduce_strategy: str = "bucket_reduce_scatter", runtime_layout_policy: str = "auto",
+                 runtime_trace_enabled: bool = True, use_saved_tensor_hooks: bool = False,
+                 use_zero_copy_grad_bucket: bool = False, shrink_full_param_storage_after_backward: bool = True,
+                 allow_shared_params: bool = False, transport=None, use_world_without_mesh: bool = True) -> None:
+        if isinstance(reshard_after_forward, bool):
+            self.reshard_after_forward = reshard_after_forward
+        elif isinstance(reshard_after_forward, int):
+            if reshard_after_forward <= 1:
+                raise ValueError("reshard_after_forward as an int must be a non-trivial divisor of the shard "
+                                 f"world size, got {reshard_after_forward}.")
+            raise NotImplementedError("reshard_after_forward=int (resharding to a smaller subgroup) is not supported; "
+                                      "pass a bool.")
+        else:
+            raise TypeError("reshard_after_forward must be a bool.")
+        valid_reduce = {"bucket_reduce_scatter", "flat", "per_param", "per_param_allreduce"}
+        if backward_reduce_strategy not in valid_reduce:
+            raise ValueError(f"Unknown backward_reduce_strategy={backward_reduce_strategy!r}; "
+                             f"expected one of {sorted(valid_reduce)}.")
+        if runtime_layout_policy not in ("auto", "matrix_shard", "segment_runtime", "flat_reorder"):
+            raise ValueError(f"Unknown runtime_layout_policy={runtime_layout_policy!r}.")
+        self.module = module
+        self.mesh = mesh
+        self.groups: ResolvedGroups = resolve_groups(mesh, dp_shard_mesh_dim, dp_replicate_mesh_dim,
+                                                     use_world_without_mesh=use_world_without_mesh)
+        self.rank, self.world_size = self.groups.shard_rank, self.groups.shard_world
+        self.replicate_rank, self.replicate_world_size = self.groups.replicate_rank, self.groups.replicate_world
+        self.planner, self.group_planner, self.layout_planner = planner, group_planner, layout_planner
+        self.shard_hints = shard_hints
+        self.ignored_params = ignored_params
+        self.auto_shard_hints = auto_shard_hints
+        self.divide_grads_by_world = divide_grads_by_world
+        self.forward_prefetch, self.backward_prefetch = forward_prefetch, backward_prefetch
+        self.finalize_after_backward = finalize_after_backward
+        self.mp_policy, self.offload_policy = mp_policy, offload_policy
+        self.param_gather_strategy = param_gather_strategy
+        self.matrix_collective_backend = matrix_collective_backend
+        self.backward_reduce_strategy = backward_reduce_strategy
+        self.runtime_layout_policy = runtime_layout_policy
+        self.runtime_trace_enabled = runtime_trace_enabled
+        self.use_saved_tensor_hooks = use_saved_tensor_hooks
+        self.use_zero_copy_grad_bucket = use_zero_copy_grad_bucket
+        self.shrink_full_param_storage_after_backward = shrink_full_param_storage_after_backward
+        self.allow_shared_params = allow_shared_params
+        self._transport_override = transport
+
+        self.metadata = RuntimeUnitMetadata(next_runtime_param_group_id(), 0, 0)
+        self.metadata = RuntimeUnitMetadata(self.metadata.runtime_param_group_id, self.metadata.runtime_param_group_id,
+                                            self.metadata.runtime_param_group_id)
+        self.name = self.metadata.name
+        self.state = FSDPLifecycleState.SHARDED
+        self.runtime_events: list[RuntimeEvent] = []
+        self.scheduler = None
+        self.all_gather_stream = None
+        self.reduce_scatter_stream = None
+        self.defer_backward_reduce = False
+        self.in_no_sync = False
+        self.finalized_after_backward = False
+        self.has_accumulated_grads = False
+        self.forward_count_since_backward = 0
+        self.used_in_forward = False
+        self.unshard_prefetched = False
+        self._grads_seen: set[str] = set()
+        self._direct_written: set[str] = set()
+        self._pre_backward_done = False
+        self._backward_callback_queued = False
+        self._hook_handles: list = []
+        self._initialized = False
+        self.planner_result: PlannerResult | None = None
+        self.registry: ManagedParamRegistry | None = None
+        self.flat_buffer: MatrixFlatBuffer | None = None
+        self.runtime_mode = "unknown"
+
+    # ------------------------------------------------------------------ init
+    def init(self) -> "MatrixFSDPParamGroup":
+        if self._initialized:
+            return self
+        module = self.module
+        if getattr(module, "_matrix_fsdp_param_group", None) is not None:
+            raise ValueError("This module is already managed by an FSDP unit.")
+        ignored = set(self.ignored_params or ())
+        # parameters already managed by nested units stay with them
+        nested = {id(p) for p in module.parameters() if getattr(p, "_matrix_fsdp_param_group_ref", None) is not None}
+        ignored |= {p for p in module.parameters() if id(p) in nested}
+        hints = self.shard_hints
+        if hints is None and self.auto_shard_hints:
+            hints = build_shard_hints(module)
+        if hints is not None:
+            keep = {fqn for fqn, p in module.named_parameters() if p not in ignored}
+            hints = {k: v for k, v in hints.items() if k in keep}
+        registry = ManagedParamRegistry.from_module(module, shard_hints=hints, ignored_params=ignored,
+                                                    allow_shared=self.allow_shared_params)
+        if len(registry) == 0:
+            raise ValueError("fully_shard needs a module with at least one parameter that is not ignored.")
+        frozen = [mp.fqn for mp in registry if not mp.param.requires_grad]
+        if frozen:
+            raise ValueError(f"Managed parameters must require grad; frozen parameters: {', '.join(frozen)}. "
+                             "Pass them through ignored_params.")
+        device = registry[0].device
+        if self.offload_policy is not None:
+            validate_offload_policy_for_device(self.offload_policy, device)
+        self.registry = registry
+
+        result = self._plan(registry)
+        compat = validate_runtime_layout(
+            result.layout, registry.params, self.world_size,
+            allow_segment_runtime=self.runtime_layout_policy in ("auto", "segment_runtime"),
+            allow_flat_reorder=self.runtime_layout_policy in ("auto", "flat_reorder"))
+        if self.runtime_layout_policy == "matrix_shard" and compat.mode != "matrix_shard":
+            raise ValueError(f"MatrixFSDP runtime cannot execute planner layout. Reason: {compat.reason}.")
+        if compat.mode == "flat_reorder" or (self.runtime_layout_policy == "flat_reorder" and compat.mode != "matrix_shard"):
+            result = self._flat_reorder(registry, result)
+            compat = validate_runtime_layout(result.layout, registry.params, self.world_size)
+        self.planner_result = result
+        self.runtime_mode = compat.mode
+        validate_group_layout(result.layout, registry.params, self.world_size)
+
+        if device.type == "cuda":
+            self.all_gather_stream = torch.cuda.Stream(device=device, priority=-1)
+            self.reduce_scatter_stream = torch.cuda.Stream(device=device, priority=-1)
+        transport = self._transport_override or make_transport(self.groups.shard_group, self.world_size, device)
+        mp = self.mp_policy
+        self.flat_buffer = MatrixFlatBuffer(
+            registry, result.layout, rank=self.rank, world_size=self.world_size, transport=transport,
+            replicate_group=self.groups.replicate_group, replicate_world_size=self.replicate_world_size,
+            param_dtype=getattr(mp, "param_dtype", None), reduce_dtype=getattr(mp, "reduce_dtype", None),
+            divide_grads_by_world=self.divide_grads_by_world, unit_key=self.name)
+        self.flat_buffer.use_local_shards()
+
+        ref = weakref.ref(self)
+        for mpm in registry:
+            mpm.param._matrix_fsdp_param_group_ref = ref
+            mpm.param._matrix_fsdp_fqn = mpm.fqn
+        module._matrix_fsdp_param_group = self
+        self._register_hooks()
+        self._initialized = True
+        self._record("init", reason=f"planner={result.name}")
+        return self
+
+    def _plan(self, registry: ManagedParamRegistry) -> PlannerResult:
+        params, world = registry.params, self.world_size
+        chosen = self.group_planner or self.layout_planner
+        if chosen is not None:
+            return call_group_planner(chosen, params, world,
+                                      shard_mesh_dim=self.groups.metadata.shard_mesh_dim if self.groups.metadata else None)
+        if self.planner is not None:
+            plan = self.planner(registry.total_numel, world)
+            return planner_result_from_output(getattr(self.planner, "__name__", "planner"), plan, params, world)
+        return planner_result_from_output("contiguous_even_plan", contiguous_even_plan(registry.total_numel, world),
+                                          params, world)
+
+    def _flat_reorder(self, registry: ManagedParamRegistry, result: PlannerResult) -> PlannerResult:
+        """Re-lay the flat space rank-major so a whole-param owner layout becomes rank-contiguous."""
+        order = flat_reorder_order(result.layout)
+        owners = {fqn: result.layout.owner_ranks(fqn)[0] for fqn in order}
+        registry.reassign_offsets(order)
+        from ..core.layout import LayoutSegment
+
+        per_rank: list[list] = [[] for _ in range(self.world_size)]
+        cursor = [0] * self.world_size
+        for mp in registry.params:
+            r = owners[mp.fqn]
+            per_rank[r].append(LayoutSegment(mp.offset, mp.end, cursor[r]))
+            cursor[r] += mp.numel
+        from ..core.layout import coalesce_segments
+
+        layout = MatrixGroupLayout.from_rank_segments(registry.total_numel, [coalesce_segments(s) for s in per_rank],
+                                                      registry.params)
+        return planner_result_from_output(result.name, layout, registry.params, self.world_size, policy=result.policy,
+                                          weights=result.cost_weights)
+
+    def _register_hooks(self) -> None:
+        m = self.module
+        self._hook_handles.append(m.register_forward_pre_hook(self._pre_forward, with_kwargs=True, prepend=True))
+        self._hook_handles.append(m.register_forward_hook(self._post_forward, prepend=False))
+        for mp in self.registry:
+            self._hook_handles.append(mp.param.register_post_accumulate_grad_hook(self._make_grad_hook(mp.fqn)))
+
+    # ------------------------------------------------------------------ events
+    def _record(self, name: str, *, start: float | None = None, handle=None, **kw) -> None:
+        if not self.runtime_trace_enabled:
+            return
+        dur = (time.perf_counter() - start) * 1e3 if start is not None else 0.0
+        info = getattr(handle, "info", None) or {}
+        snap = self.flat_buffer.memory_snapshot() if self.flat_buffer is not None else {}
+        sched = self.scheduler
+        self.runtime_events.append(RuntimeEvent(
+            name=name, unit=self.name, sequence=next_event_sequence(), lifecycle_state=self.state.value,
+            duration_ms=dur, collective_kind=info.get("kind"), collective_backend=info.get("backend"),
+            collective_impl=info.get("impl"), collective_bytes=int(info.get("bytes", 0)),
+            collective_count=int(info.get("count", 0)), collective_sync_mode=info.get("sync_mode"),
+            workspace_numel=int(info.get("workspace_numel", 0)), workspace_reused=bool(info.get("workspace_reused", False)),
+            materialization=info.get("materialization"),
+            full_param_buffer_numel=snap.get("full_param_buffer_numel", 0),
+            full_param_buffer_bytes=snap.get("full_param_buffer_bytes", 0),
+            grad_bucket_numel=snap.get("grad_bucket_numel", 0), grad_bucket_bytes=snap.get("grad_bucket_bytes", 0),
+            local_grad_shard_numel=snap.get("local_grad_shard_numel", 0),
+            local_grad_shard_bytes=snap.get("local_grad_shard_bytes", 0),
+            active_full_param_buffers=sched.active_full_param_buffers() if sched is not None else 0,
+            pending_reduce_scatter_count=sched.pending_reduce_count() if sched is not None else
+            int(self.flat_buffer is not None and self.flat_buffer.pending_reduce is not None),
+            **kw))
+
+    def clear_runtime_events(self) -> None:
+        self.runtime_events.clear()
+
+    # ------------------------------------------------------------------ state machine
+    def _transition(self, new: FSDPLifecycleState) -> None:
+        if new == self.state:
+            return
+        if (self.state, new) not in _ALLOWED:
+            raise RuntimeError(f"{self.name}: illegal lifecycle transition {self.state.value} -> {new.value}.")
+        self.state = new
+
+    def _check_invariants(self) -> None:
+        fb = self.flat_buffer
+        if self.state == FSDPLifecycleState.UNSHARDED:
+            if not fb.full_materialized:
+                raise RuntimeError(f"{self.name}: UNSHARDED without a materialised full buffer.")
+        else:
+            if fb.params_use_full:
+                raise RuntimeError(f"{self.name}: {self.state.value} but parameters still view the full buffer.")
+
+    # ------------------------------------------------------------------ unshard / reshard
+    def start_unshard(self, reason: str = "manual") -> None:
+        if self.flat_buffer.pending_gather is not None or self.state == FSDPLifecycleState.UNSHARDED:
+            return
+        t0 = time.perf_counter()
+        if self.scheduler is not None:
+            self.scheduler.wait_for_post_optimizer_event_before_all_gather(self)
+            self.scheduler.note_unshard_started(self)
+        h = self.flat_buffer.start_all_gather_full_params(stream=self.all_gather_stream)
+        self.unshard_prefetched = reason.endswith("prefetch")
+        self._record(f"start_unshard:{reason}", start=t0, handle=h, reason=reason, prefetched=self.unshard_prefetched)
+
+    def wait_unshard(self, reason: str = "manual") -> None:
+        t0 = time.perf_counter()
+        if self.state == FSDPLifecycleState.UNSHARDED:
+            return
+        if self.flat_buffer.pending_gather is None:
+            self.start_unshard(reason)
+        h = self.flat_buffer.wait_all_gather()
+        self.flat_buffer.use_full_param_buffer()
+        self._transition(FSDPLifecycleState.UNSHARDED)
+        self._record(f"wait_unshard:{reason}", start=t0, handle=h, reason=reason)
+        self._record("unshard", reason=reason, prefetched=self.unshard_prefetched)
+
+    def unshard(self, reason: str = "manual") -> "MatrixFSDPParamGroup":
+        self.start_unshard(reason)
+        self.wait_unshard(reason)
+        return self
+
+    def reshard(self, reason: str = "manual", *, to: FSDPLifecycleState = FSDPLifecycleState.SHARDED) -> None:
+        if self.state != FSDPLifecycleState.UNSHARDED and self.flat_buffer.pending_gather is None:
+            if to == FSDPLifecycleState.SHARDED and self.state == FSDPLifecycleState.FORWARD_RESHARDED:
+                self._transition(to)
+            return
+        t0 = time.perf_counter()
+        self.flat_buffer.use_local_shards()
+        self.flat_buffer.clear_full_params()
+        if self.state == FSDPLifecycleState.UNSHARDED:
+            self._transition(to)
+        if self.scheduler is not None:
+            self.scheduler.note_resharded(self)
+        self._record(reason if reason.startswith("reshard") else f"reshard:{reason}", start=t0, reason=reason)
+
+    def discard_unused_prefetch(self) -> None:
+        """Drop a gather that was prefetched but never consumed by a forward/backward."""
+        if self.flat_buffer.pending_gather is not None and self.state != FSDPLifecycleState.UNSHARDED:
+            self.flat_buffer.wait_all_gather()
+            self.flat_buffer.clear_full_params()
+            if self.scheduler is not None:
+                self.scheduler.note_resharded(self)
+            self._record("discard_unused_prefetch")
+
+    # ------------------------------------------------------------------ forward hooks
+    def _pre_forward(self, module, args, kwargs):
+        if _in_backward() and self.state == FSDPLifecycleState.UNSHARDED:
+            self._record("pre_forward_recompute_skip", recompute=True)
+            return None
+        grad_mode = torch.is_grad_enabled()
+        if self.state == FSDPLifecycleState.FORWARD_RESHARDED and grad_mode and not _in_backward():
+            raise RuntimeError(
+                f"{self.name}: another forward before the backward of the previous one; multiple forwards before "
+                "a backward need reshard_after_forward=False.")
+        if self.finalized_after_backward and self.flat_buffer.pending_reduce is not None and self.scheduler is None:
+            self.wait_post_backward_reduce()
+        t0 = time.perf_counter()
+        self._record("pre_forward")
+        self.flat_buffer.stash_local_grads_for_accumulation()
+        self.used_in_forward = True
+        self.finalized_after_backward = False
+        self.start_unshard("pre_forward")
+        self.wait_unshard("pre_forward")
+        if self.scheduler is not None:
+            self.scheduler.on_pre_forward(self)
+        mp = self.mp_policy
+        if mp is not None and getattr(mp, "cast_forward_inputs", False) and mp.param_dtype is not None:
+            args = cast_floating_tensors(args, mp.param_dtype)
+            kwargs = cast_floating_tensors(kwargs, mp.param_dtype)
+            return args, kwargs
+        del t0
+        return None
+
+    def _post_forward(self, module, args, output):
+        if _in_backward() and self._pre_backward_done and self.state == FSDPLifecycleState.UNSHARDED:
+            self._record("post_forward_recompute_skip", recompute=True)
+            return output
+        grad_mode = torch.is_grad_enabled()
+        mp = self.mp_policy
+        if mp is not None and getattr(mp, "output_dtype", None) is not None:
+            output = cast_floating_tensors(output, mp.output_dtype)
+        hooks = 0
+        if grad_mode:
+            ctx = ForwardBackwardContext(self._pre_backward_unshard)
+            hooks = register_pre_backward_hooks(output, ctx)
+            self.forward_count_since_backward += 1
+        if self.reshard_after_forward:
+            self.reshard("reshard_after_forward",
+                         to=FSDPLifecycleState.FORWARD_RESHARDED if (grad_mode and hooks) else FSDPLifecycleState.SHARDED)
+        elif not (grad_mode and hooks) and not self._keep_unsharded_in_eval():
+            self.reshard("reshard_after_forward", to=FSDPLifecycleState.SHARDED)
+        if self.scheduler is not None:
+            self.scheduler.record_post_forward(self)
+        self._record("post_forward", extra={"hooks": hooks})
+        return output
+
+    def _keep_unsharded_in_eval(self) -> bool:
+        return not self.reshard_after_forward
+
+    # ------------------------------------------------------------------ backward
+    def _pre_backward_unshard(self) -> None:
+        if self._pre_backward_done and self.state == FSDPLifecycleState.UNSHARDED:
+            return
+        self._record("pre_backward_unshard")
+        self._pre_backward_done = True
+        self._queue_backward_callback()
+        self.start_unshard("pre_backward")
+        self.wait_unshard("pre_backward")
+        if self._wants_direct_grad_writes():
+            self.flat_buffer.prepare_grad_bucket()
+        if self.scheduler is not None:
+            self.scheduler.on_pre_backward(self)
+
+    def _wants_direct_grad_writes(self) -> bool:
+        return bool(getattr(self.module, "_mfsdp_direct_grad", False))
+
+    def grad_target(self, fqn: str) -> tuple[torch.Tensor, bool]:
+        """Bucket view an op may write this parameter's gradient into, and whether to accumulate."""
+        mp = self.registry.param(fqn)
+        self.flat_buffer.prepare_grad_bucket()
+        view = self.flat_buffer.bucket.buffer[mp.offset:mp.end].view(mp.shape)
+        accumulate = self.has_accumulated_grads or fqn in self._direct_written
+        return view, accumulate
+
+    def mark_grad_written(self, fqn: str) -> None:
+        """An op wrote (or accumulated) this parameter's gradient straight into the bucket."""
+        self._direct_written.add(fqn)
+        self._on_grad(fqn)
+
+    def _queue_backward_callback(self) -> None:
+        if self._backward_callback_queued:
+            return
+        try:
+            torch.autograd.Variable._execution_engine.queue_callback(self._end_of_backward)
+            self._backward_callback_queued = True
+        except Exception:  # not inside a backward pass
+            self._backward_callback_queued = False
+
+    def _make_grad_hook(self, fqn: str):
+        def hook(param):
+            self._on_grad(fqn)
+        return hook
+
+    def _on_grad(self, fqn: str) -> None:
+        if self.state != FSDPLifecycleState.UNSHARDED:
+            return
+        self._grads_seen.add(fqn)
+        if len(self._grads_seen) >= len(self.registry) and self.finalize_after_backward:
+            self.finalize_backward("all_grads_ready")
+
+    def _end_of_backward(self) -> None:
+        self._backward_callback_queued = False
+        if self.state == FSDPLifecycleState.UNSHARDED and self._pre_backward_done:
+            self.finalize_backward("end_of_backward")
+        elif self.state == FSDPLifecycleState.FORWARD_RESHARDED:
+            # forward ran but no gradient reached this unit's outputs
+            self._transition(FSDPLifecycleState.SHARDED)
+            self.forward_count_since_backward = 0
+
+    def finalize_backward(self, reason: str = "manual") -> None:
+        if self.state != FSDPLifecycleState.UNSHARDED:
+            return
+        t0 = time.perf_counter()
+        fb = self.flat_buffer
+        any_grad = bool(self._direct_written) or any(mp.param.grad is not None for mp in self.registry)
+        how = None
+        if any_grad or self.has_accumulated_grads:
+            how = fb.collect_param_grads(accumulate=self.has_accumulated_grads, written_direct=self._direct_written)
+        self.reshard("reshard_after_backward", to=FSDPLifecycleState.SHARDED)
+        self._grads_seen.clear()
+        self._direct_written = set()
+        self._pre_backward_done = False
+        self.forward_count_since_backward = 0
+        self.finalized_after_backward = True
+        self._record("finalize_backward", start=t0, reason=reason, extra={"copy_in": how})
+        if not (any_grad or self.has_accumulated_grads):
+            return
+        if self.defer_backward_reduce:
+            self.has_accumulated_grads = True
+            self._record("defer_backward_reduce")
+            return
+        self._start_reduce()
+
+    def _start_reduce(self) -> None:
+        t0 = time.perf_counter()
+        if self.scheduler is not None:
+            self.scheduler.before_backward_reduce(self)
+        if self.backward_reduce_strategy == "per_param_allreduce":
+            h = self._reduce_by_allreduce()
+        else:
+            h = self.flat_buffer.start_reduce_grad_bucket_to_local_shard(stream=self.reduce_scatter_stream)
+        self.has_accumulated_grads = False
+        self._record("start_reduce_scatter", start=t0, handle=h)
+        if self.scheduler is not None:
+            self.scheduler.after_backward_reduce_started(self)
+        else:
+            self.wait_post_backward_reduce()
+
+    def _reduce_by_allreduce(self):
+        """Diagnostic strategy: all-reduce the whole bucket, then keep the owned slice."""
+        from .collectives import MatrixCollectiveHandle, gather_local_segments
+
+        fb = self.flat_buffer
+        buf = fb.bucket.ensure()
+        fb.transport.all_reduce(buf, self.groups.shard_group)
+        if self.replicate_world_size > 1:
+            fb.transport.all_reduce(buf, self.groups.replicate_group)
+        out = fb._ensure_local_grad_shard()
+        tmp = torch.empty(fb.local_numel, dtype=buf.dtype, device=buf.device)
+        gather_local_segments(buf, tmp, fb.tables.my_segments)
+        out.copy_(tmp)
+        out.mul_(fb.grad_scale())
+        h = MatrixCollectiveHandle(info={"kind": "all_reduce", "impl": "per_param_allreduce", "backend": fb.transport.kind,
+                                         "bytes": buf.numel() * buf.element_size(), "count": 1, "sync_mode": "blocking"})
+        fb.pending_reduce = h
+        return h
+
+    def wait_post_backward_reduce(self) -> None:
+        fb = self.flat_buffer
+        if fb.pending_reduce is None:
+            return
+        t0 = time.perf_counter()
+        h = fb.wait_reduce()
+        fb.release_grad_bucket()
+        fb.use_local_grad_shard()
+        self._record("wait_reduce_scatter", start=t0, handle=h)
+
+    def flush_deferred_reduce(self) -> None:
+        """Reduce gradients accumulated under ``no_sync`` (used when stepping after accumulation)."""
+        if self.has_accumulated_grads and self.state == FSDPLifecycleState.SHARDED:
+            self._start_reduce()
+
+    # ------------------------------------------------------------------ optimizer interplay
+    def assert_optimizer_ready(self) -> None:
+        if self.in_no_sync:
+            raise RuntimeError(f"{self.name}: optimizer step / zero_grad inside no_sync() is not allowed.")
+        if self.state != FSDPLifecycleState.SHARDED:
+            raise RuntimeError(f"{self.name}: optimizer step needs every unit SHARDED, found {self.state.value}.")
+        if self.flat_buffer.pending_reduce is not None or self.flat_buffer.pending_gather is not None:
+            raise RuntimeError(f"{self.name}: collectives still in flight at optimizer step.")
+
+    def prepare_for_optimizer_step(self) -> None:
+        if self.in_no_sync:
+            raise RuntimeError(f"{self.name}: optimizer step / zero_grad inside no_sync() is not allowed.")
+        if self.state == FSDPLifecycleState.UNSHARDED and self._pre_backward_done:
+            self.finalize_backward("optimizer_step_straggler")
+        elif self.state == FSDPLifecycleState.FORWARD_RESHARDED:
+            self._transition(FSDPLifecycleState.SHARDED)
+            self.forward_count_since_backward = 0
+        elif self.state == FSDPLifecycleState.UNSHARDED:
+            self.reshard("reshard_before_optimizer")
+        self.discard_unused_prefetch()
+        self.flush_deferred_reduce()
+        self.wait_post_backward_reduce()
+        self.used_in_forward = False
+
+    def no_sync(self) -> MatrixFSDPNoSync:
+        return MatrixFSDPNoSync([self])
+
+    # ------------------------------------------------------------------ introspection
+    @property
+    def layout(self) -> MatrixGroupLayout:
+        return self.planner_result.layout
+
+    def owner_ranks(self, fqn: str) -> tuple[int, ...]:
+        return self.layout.owner_ranks(fqn)
+
+    def params_for_rank(self, rank: int | None = None) -> tuple[str, ...]:
+        return self.layout.params_for_rank(self.rank if rank is None else rank)
+
+    def rank_segments_for_param(self, fqn: str, rank: int | None = None):
+        return self.layout.rank_segments_for_param(self.rank if rank is None else rank, fqn)
+
+    def managed_params(self):
+        return self.registry.params
+
+    def state_dict(self) -> dict[str, Any]:
+        """Debug dictionary of this unit's sharded state (metadata plus the local shard tensor)."""
+        fb = self.flat_buffer
+        return {
+            "name": self.name, "rank": self.rank, "world_size": self.world_size,
+            "replicate_rank": self.replicate_rank, "replicate_world_size": self.replicate_world_size,
+            "state": self.state.value, "runtime_mode": self.runtime_mode, "total_numel": fb.total_numel,
+            "shard_sizes": self.layout.shard_sizes,
+            "local_segments": tuple((s.global_start, s.global_end, s.local_start) for s in fb.tables.my_segments),
+            "param_fqns": self.registry.fqns, "param_shard": fb.local_shard,
+            "planner": self.planner_result.name, "policy": self.planner_result.policy,
+            "mp_policy": mixed_precision_policy_metadata(self.mp_policy),
+            "offload_policy": offload_policy_metadata(self.offload_policy),
+        }
+
+    def full_param_storage_nbytes(self) -> int:
+        return self.flat_buffer.full_storage_nbytes()

@@ -1,0 +1,345 @@
+"""Cross-unit scheduler: prefetch windows, in-flight caps, pending reduce queue, stream sharing.
+
+One scheduler serves all units of a model.  It
+
+* orders units (construction order = ``param_group_N`` id) and records the order in which their
+  forwards *finish*, because backward prefetch walks that recorded order in reverse;
+* issues forward prefetches (``max_forward_prefetch_units`` ahead, bounded by
+  ``max_unsharded_prefetch_units`` and the active-full-buffer caps) and backward prefetches
+  (at ``pre_backward`` or right after the previous unit resharded);
+* bounds the number of reduce-scatters in flight (``max_pending_backward_reduces``) and drains
+  them before the optimizer step;
+* makes the all-gather stream wait for the optimizer's writes (post-optimizer event);
+* shares one all-gather and one reduce-scatter stream across units and keeps counters.
+
+Parity: ``matrix_fsdp/runtime/scheduler.py:28-1238``.  The ordered owner-prefetch queue and the
+per-iteration barrier of the reference exist to keep NCCL point-to-point calls in the same
+order on every rank (``scheduler.py:331-364,1019-1029``); the peer transport's pulls are
+one-sided, so no cross-rank ordering is needed and neither mechanism exists here.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import asdict, dataclass, field
+from enum import Enum
+
+import torch
+import torch.distributed as dist
+
+from .buffer_pool import FullParamBufferPool
+
+DEFAULT_MAX_UNSHARDED_PREFETCH_UNITS = 1
+
+
+class BackwardPrefetchTiming(str, Enum):
+    PRE_BACKWARD = "pre_backward"
+    POST_RESHARD = "post_reshard"
+
+
+class PrefetchPolicy(str, Enum):
+    STATIC = "static"
+    ADAPTIVE = "adaptive"
+    PROFILE_GUIDED = "profile_guided"
+
+
+@dataclass
+class PrefetchProfileResult:
+    forward_prefetch_units: int
+    backward_prefetch_units: int
+    samples: int
+    mean_unshard_wait_ms: float
+
+
+@dataclass
+class MatrixFSDPSchedulerConfig:
+    max_unsharded_prefetch_units: int = DEFAULT_MAX_UNSHARDED_PREFETCH_UNITS
+    max_forward_prefetch_units: int | None = None
+    max_backward_prefetch_units: int | None = None
+    backward_prefetch_timing: str = "pre_backward"
+    prefetch_policy: str = "static"
+    max_cached_full_param_buffers_per_key: int = 2
+    max_cached_workspaces_per_key: int = 1
+    max_active_full_param_buffers: int | None = None
+    max_active_full_param_numel: int | None = None
+    max_active_full_param_memory_mb: float | None = None
+    max_pending_backward_reduces: int = 1
+    owner_backward_prefetch_with_pending_reduce: str = "auto"
+    trim_cuda_cache: bool = False
+    cuda_cache_trim_threshold_mb: float = 1024.0
+    validate_unit_order: bool = False
+
+    def __post_init__(self) -> None:
+        if self.max_unsharded_prefetch_units < 0:
+            raise ValueError("max_unsharded_prefetch_units must be >= 0")
+        BackwardPrefetchTiming(self.backward_prefetch_timing)
+        PrefetchPolicy(self.prefetch_policy)
+        if self.max_pending_backward_reduces < 0:
+            raise ValueError("max_pending_backward_reduces must be >= 0")
+
+
+SCHEDULER_KWARGS = tuple(MatrixFSDPSchedulerConfig.__dataclass_fields__) + (
+    "scheduler_config", "max_cached_full_param_buffers_per_key", "max_cached_workspaces_per_key")
+
+
+@dataclass
+class SchedulerCounters:
+    forward_prefetch_issued: int = 0
+    backward_prefetch_issued: int = 0
+    prefetch_blocked_by_budget: int = 0
+    prefetch_blocked_by_caps: int = 0
+    prefetch_deferred_pending_reduce: int = 0
+    unshard_waits: int = 0
+    reduce_waits: int = 0
+    post_optimizer_waits: int = 0
+    high_water_active_full_param_buffers: int = 0
+    high_water_active_full_param_bytes: int = 0
+    iterations: int = 0
+    cache_trims: int = 0
+
+    def as_dict(self) -> dict[str, int]:
+        return asdict(self)
+
+
+@dataclass
+class MatrixFSDPCommContext:
+    """Streams and pools shared by every unit under one scheduler."""
+
+    all_gather_stream: object = None
+    reduce_scatter_stream: object = None
+    full_param_pool: FullParamBufferPool = field(default_factory=FullParamBufferPool)
+
+
+class MatrixFSDPScheduler:
+    def __init__(self, units, config: MatrixFSDPSchedulerConfig | None = None, **overrides) -> None:
+        cfg = config or MatrixFSDPSchedulerConfig()
+        for k, v in overrides.items():
+            if v is None and k not in ("max_forward_prefetch_units", "max_backward_prefetch_units"):
+                continue
+            if not hasattr(cfg, k):
+                raise TypeError(f"Unknown scheduler option {k!r}.")
+            setattr(cfg, k, v)
+        cfg.__post_init__()
+        self.config = cfg
+        self.units = sorted(list(units), key=lambda u: u.metadata.runtime_param_group_id)
+        if not self.units:
+            raise ValueError("MatrixFSDPScheduler needs at least one unit.")
+        self._index = {id(u): i for i, u in enumerate(self.units)}
+        self.counters = SchedulerCounters()
+        self.post_forward_order: list = []
+        self._active: dict[int, object] = {}
+        self._pending_reduces: list = []
+        self._post_optimizer_event = None
+        self._waited_post_optimizer: set[int] = set()
+        self.comm = MatrixFSDPCommContext(full_param_pool=FullParamBufferPool(cfg.max_cached_full_param_buffers_per_key))
+        first = self.units[0]
+        self.comm.all_gather_stream = first.all_gather_stream
+        self.comm.reduce_scatter_stream = first.reduce_scatter_stream
+        for u in self.units:
+            old = getattr(u, "scheduler", None)
+            u.scheduler = self
+            u.all_gather_stream = self.comm.all_gather_stream
+            u.reduce_scatter_stream = self.comm.reduce_scatter_stream
+            del old
+        if cfg.validate_unit_order:
+            self.validate_unit_order()
+
+    # ------------------------------------------------------------------ limits
+    def _fwd_budget(self) -> int:
+        c = self.config
+        n = c.max_unsharded_prefetch_units if c.max_forward_prefetch_units is None else c.max_forward_prefetch_units
+        return min(n, c.max_unsharded_prefetch_units) if c.max_forward_prefetch_units is None else n
+
+    def _bwd_budget(self) -> int:
+        c = self.config
+        return c.max_unsharded_prefetch_units if c.max_backward_prefetch_units is None else c.max_backward_prefetch_units
+
+    def active_full_param_buffers(self) -> int:
+        return len(self._active)
+
+    def active_full_param_numel(self) -> int:
+        return sum(u.flat_buffer.total_numel for u in self._active.values() if not u.flat_buffer.full_aliases_shard)
+
+    def active_full_param_bytes(self) -> int:
+        return sum(u.flat_buffer.total_numel * u.flat_buffer.full_buffer.element_size()
+                   for u in self._active.values() if not u.flat_buffer.full_aliases_shard)
+
+    def pending_reduce_count(self) -> int:
+        return len(self._pending_reduces)
+
+    def _caps_allow(self, unit) -> bool:
+        c = self.config
+        if c.max_active_full_param_buffers is not None and len(self._active) + 1 > c.max_active_full_param_buffers:
+            return False
+        extra = 0 if unit.flat_buffer.full_aliases_shard else unit.flat_buffer.total_numel
+        if c.max_active_full_param_numel is not None and self.active_full_param_numel() + extra > c.max_active_full_param_numel:
+            return False
+        if c.max_active_full_param_memory_mb is not None:
+            nbytes = self.active_full_param_bytes() + extra * unit.flat_buffer.full_buffer.element_size()
+            if nbytes > c.max_active_full_param_memory_mb * 2 ** 20:
+                return False
+        return True
+
+    def note_unshard_started(self, unit) -> None:
+        self._active[id(unit)] = unit
+        ctr = self.counters
+        ctr.high_water_active_full_param_buffers = max(ctr.high_water_active_full_param_buffers, len(self._active))
+        ctr.high_water_active_full_param_bytes = max(ctr.high_water_active_full_param_bytes,
+                                                     self.active_full_param_bytes())
+
+    def note_resharded(self, unit) -> None:
+        self._active.pop(id(unit), None)
+        if self.config.backward_prefetch_timing == "post_reshard" and unit.finalized_after_backward is False \
+                and unit._pre_backward_done:
+            self._prefetch_backward(unit, reason="post_reshard_prefetch")
+
+    # ------------------------------------------------------------------ forward
+    def on_pre_forward(self, unit) -> None:
+        self.counters.unshard_waits += 1
+        if not unit.forward_prefetch:
+            return
+        i = self._index[id(unit)]
+        budget = self._fwd_budget()
+        issued = 0
+        for nxt in self.units[i + 1:]:
+            if issued >= budget:
+                if budget == 0:
+                    self.counters.prefetch_blocked_by_budget += 1
+                break
+            if nxt.state.value != "sharded" or nxt.flat_buffer.pending_gather is not None:
+                issued += 1 if nxt.flat_buffer.pending_gather is not None else 0
+                continue
+            if not self._caps_allow(nxt):
+                self.counters.prefetch_blocked_by_caps += 1
+                break
+            nxt._record("forward_prefetch", reason=f"from={unit.name}")
+            nxt.start_unshard("forward_prefetch")
+            self.counters.forward_prefetch_issued += 1
+            issued += 1
+
+    def record_post_forward(self, unit) -> None:
+        if torch.is_grad_enabled():
+            if unit in self.post_forward_order:
+                self.post_forward_order.remove(unit)
+            self.post_forward_order.append(unit)
+
+    # ------------------------------------------------------------------ backward
+    def on_pre_backward(self, unit) -> None:
+        if self.config.backward_prefetch_timing == "pre_backward":
+            self._prefetch_backward(unit, reason="backward_prefetch")
+
+    def _prefetch_backward(self, unit, *, reason: str) -> None:
+        if not unit.backward_prefetch or unit not in self.post_forward_order:
+            return
+        pos = self.post_forward_order.index(unit)
+        budget = self._bwd_budget()
+        issued = 0
+        for prev in reversed(self.post_forward_order[:pos]):
+            if issued >= budget:
+                break
+            if prev.state.value != "forward_resharded" or prev.flat_buffer.pending_gather is not None:
+                continue
+            if self._pending_reduces and self.config.owner_backward_prefetch_with_pending_reduce == "never":
+                self.counters.prefetch_deferred_pending_reduce += 1
+                break
+            if not self._caps_allow(prev):
+                self.counters.prefetch_blocked_by_caps += 1
+                break
+            prev._record("backward_prefetch", reason=f"from={unit.name}")
+            prev.start_unshard(reason)
+            self.counters.backward_prefetch_issued += 1
+            issued += 1
+
+    def before_backward_reduce(self, unit) -> None:
+        """Bound the reduce-scatters in flight before a new one starts."""
+        limit = self.config.max_pending_backward_reduces
+        while len(self._pending_reduces) > max(limit - 1, 0) and self._pending_reduces:
+            oldest = self._pending_reduces.pop(0)
+            self.counters.reduce_waits += 1
+            oldest.wait_post_backward_reduce()
+
+    def after_backward_reduce_started(self, unit) -> None:
+        if self.config.max_pending_backward_reduces == 0:
+            unit.wait_post_backward_reduce()
+            return
+        self._pending_reduces.append(unit)
+
+    def wait_pending_backward_reduce(self) -> None:
+        while self._pending_reduces:
+            u = self._pending_reduces.pop(0)
+            self.counters.reduce_waits += 1
+            u.wait_post_backward_reduce()
+
+    # ------------------------------------------------------------------ optimizer boundary
+    def prepare_optimizer_step(self) -> None:
+        for u in self.units:
+            if u.in_no_sync:
+                raise RuntimeError(f"{u.name}: optimizer step / zero_grad inside no_sync() is not allowed.")
+        self.wait_pending_backward_reduce()
+        for u in self.units:
+            u.prepare_for_optimizer_step()
+        self.wait_pending_backward_reduce()
+        for u in self.units:
+            u.assert_optimizer_ready()
+        self.finish_backward_iteration()
+
+    def finish_backward_iteration(self) -> None:
+        self.post_forward_order.clear()
+        self.counters.iterations += 1
+
+    def record_post_optimizer_event(self) -> None:
+        dev = self.units[0].flat_buffer.device
+        if dev.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(dev))
+            self._post_optimizer_event = ev
+            self._waited_post_optimizer.clear()
+        self.maybe_trim_cuda_cache()
+
+    def wait_for_post_optimizer_event_before_all_gather(self, unit) -> None:
+        ev = self._post_optimizer_event
+        if ev is None or self.comm.all_gather_stream is None:
+            return
+        if 0 not in self._waited_post_optimizer:
+            self.comm.all_gather_stream.wait_event(ev)
+            self._waited_post_optimizer.add(0)
+            self.counters.post_optimizer_waits += 1
+
+    def maybe_trim_cuda_cache(self) -> None:
+        c = self.config
+        if not c.trim_cuda_cache or not torch.cuda.is_available():
+            return
+        reserved = torch.cuda.memory_reserved()
+        allocated = torch.cuda.memory_allocated()
+        if (reserved - allocated) > c.cuda_cache_trim_threshold_mb * 2 ** 20:
+            torch.cuda.empty_cache()
+            self.counters.cache_trims += 1
+
+    # ------------------------------------------------------------------ policies / diagnostics
+    def tune_prefetch(self, result: PrefetchProfileResult) -> None:
+        """Apply a profile-guided prefetch depth (``prefetch_policy="profile_guided"``)."""
+        self.config.max_forward_prefetch_units = result.forward_prefetch_units
+        self.config.max_backward_prefetch_units = result.backward_prefetch_units
+
+    def adapt_prefetch(self, mean_unshard_wait_ms: float, *, threshold_ms: float = 0.05) -> None:
+        """``prefetch_policy="adaptive"``: deepen prefetch while waits are visible, within the budget."""
+        if self.config.prefetch_policy != "adaptive":
+            return
+        cur = self._fwd_budget()
+        if mean_unshard_wait_ms > threshold_ms and cur < max(2, self.config.max_unsharded_prefetch_units):
+            self.config.max_forward_prefetch_units = cur + 1
+            self.config.max_backward_prefetch_units = self._bwd_budget() + 1
+
+    def validate_unit_order(self) -> None:
+        """All ranks must have built the same units in the same order."""
+        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+            return
+        sig = tuple((u.name, u.flat_buffer.total_numel) for u in self.units)
+        sigs: list = [None] * dist.get_world_size()
+        dist.all_gather_object(sigs, sig)
+        if any(s != sig for s in sigs):
+            raise RuntimeError(f"FSDP unit order differs across ranks: {sigs}")
+
+    def summary(self) -> dict[str, object]:
+        return {"num_units": len(self.units), "config": asdict(self.config), "counters": self.counters.as_dict(),
+                "pool": self.comm.full_param_pool.stats.as_dict(), "pending_reduces": len(self._pending_reduces),
+                "active_full_param_buffers": len(self._active)}

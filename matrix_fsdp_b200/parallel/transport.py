@@ -1,0 +1,133 @@
+"""Transports: how a unit's shards and gradients move between ranks.
+
+A transport owns the *data plane* of one shard group.  The flat-buffer runtime only ever
+calls ``gather`` (shards → full parameters), ``reduce`` (full gradients → owned shard of the
+mean) and the two allocation hooks, so the same lifecycle code runs on:
+
+* :class:`LocalTransport`      – one rank: copies (or pure aliasing);
+* :class:`TorchDistTransport`  – NCCL / Gloo collectives (portable baseline, CPU tests);
+* ``PeerTransport`` (:mod:`matrix_fsdp_b200.parallel.peer`) – hand-written sm_100a kernels
+  that pull peer shards / reduce peer gradients over NVLink from IPC-mapped memory.
+
+The reference hard-wires ``torch.distributed`` calls into its flat buffer
+(``matrix_fsdp/runtime/flat_buffer.py:304-382,629-818``) and selects implementations through
+environment variables (``kernels/custom_collectives.py:24-52``); here that choice is one
+object picked at construction.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from .collectives import (MatrixCollectiveHandle, SegmentTables, all_gatherv_rank_segments_1d_into_async,
+                          all_reduce_full_grad, gather_local_segments,
+                          reduce_scatterv_owner_rank_chunks_1d_async, scatter_local_segments)
+from .workspace_cache import CommWorkspaceCache
+
+GATHER_IMPL_ENV = "MFSDP_ALLGATHERV_IMPL"
+REDUCE_IMPL_ENV = "MFSDP_REDUCE_SCATTERV_IMPL"
+TRANSPORT_ENV = "MFSDP_TRANSPORT"
+
+
+class LocalTransport:
+    kind = "local"
+    needs_symmetric_buffers = False
+    accumulates_fp32 = True   # a single rank only copies; copy_ converts dtypes on the way
+
+    def __init__(self) -> None:
+        self.group = None
+
+    def alloc_persistent(self, numel: int, dtype: torch.dtype, device: torch.device, tag: str = "") -> torch.Tensor:
+        return torch.empty(numel, dtype=dtype, device=device)
+
+    def acquire_grad_buffer(self, unit_key, numel: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+        return torch.empty(numel, dtype=dtype, device=device)
+
+    def release_grad_buffer(self, unit_key, buf: torch.Tensor) -> None:
+        pass
+
+    def gather(self, shard, full, tables: SegmentTables, *, stream=None, unit_key=None) -> MatrixCollectiveHandle:
+        scatter_local_segments(shard, full, tables.my_segments)
+        return MatrixCollectiveHandle(info={"kind": "all_gather", "impl": "local_copy", "backend": self.kind,
+                                            "bytes": full.numel() * full.element_size(), "count": 0,
+                                            "sync_mode": "local"})
+
+    def reduce(self, full_grad, out_shard, tables: SegmentTables, *, scale=None, stream=None,
+               unit_key=None) -> MatrixCollectiveHandle:
+        gather_local_segments(full_grad, out_shard, tables.my_segments)
+        if scale is not None and scale != 1.0:
+            out_shard.mul_(scale)
+        return MatrixCollectiveHandle(info={"kind": "reduce_scatter", "impl": "local_copy", "backend": self.kind,
+                                            "bytes": 0, "count": 0, "sync_mode": "local"})
+
+    def all_reduce(self, tensor, group, *, scale=None):
+        return all_reduce_full_grad(tensor, group, scale=scale)
+
+
+class TorchDistTransport(LocalTransport):
+    kind = "torch_dist"
+    accumulates_fp32 = False  # library collectives reduce in the dtype of the buffer they are given
+
+    def __init__(self, group, *, gather_impl: str | None = None, reduce_impl: str | None = None,
+                 workspace_cache: CommWorkspaceCache | None = None) -> None:
+        super().__init__()
+        self.group = group
+        self.gather_impl = gather_impl or os.environ.get(GATHER_IMPL_ENV, "auto")
+        self.reduce_impl = reduce_impl or os.environ.get(REDUCE_IMPL_ENV, "auto")
+        self.workspace_cache = workspace_cache or CommWorkspaceCache(max_cached_per_key=1)
+
+    def _workspace(self, tables: SegmentTables, like: torch.Tensor):
+        if tables.equal_contiguous:
+            return None
+        return self.workspace_cache.lease(tables.world_size * tables.max_shard, like.dtype, like.device)
+
+    def gather(self, shard, full, tables, *, stream=None, unit_key=None):
+        lease = self._workspace(tables, full) if self.gather_impl not in ("owner_broadcast", "broadcast") else None
+        h = all_gatherv_rank_segments_1d_into_async(shard, full, tables, self.group, stream=stream,
+                                                    impl=self.gather_impl,
+                                                    workspace=lease.tensor if lease else None)
+        h.info["backend"] = self.kind
+        if lease is not None:
+            h.info["workspace_numel"] = lease.tensor.numel()
+            h.info["workspace_reused"] = lease.reused
+            prev = h._post
+            h._post = (lambda: (prev() if prev else None, lease.release()))
+        return h
+
+    def reduce(self, full_grad, out_shard, tables, *, scale=None, stream=None, unit_key=None):
+        lease = self._workspace(tables, full_grad) if self.reduce_impl not in ("owner_reduce", "reduce") else None
+        h = reduce_scatterv_owner_rank_chunks_1d_async(full_grad, out_shard, tables, self.group, scale=scale,
+                                                       stream=stream, impl=self.reduce_impl,
+                                                       workspace=lease.tensor if lease else None)
+        h.info["backend"] = self.kind
+        if lease is not None:
+            h.info["workspace_numel"] = lease.tensor.numel()
+            h.info["workspace_reused"] = lease.reused
+            prev = h._post
+            h._post = (lambda: (prev() if prev else None, lease.release()))
+        return h
+
+
+def make_transport(group, world_size: int, device: torch.device, *, prefer: str | None = None):
+    """Pick the transport for a shard group.
+
+    ``prefer``: ``"peer"`` | ``"torch_dist"`` | ``None`` (auto: peer kernels on CUDA when every
+    rank of the group sits on this node and the IPC mapping succeeds, else torch.distributed).
+    """
+    if world_size <= 1 or group is None:
+        return LocalTransport()
+    prefer = prefer or os.environ.get(TRANSPORT_ENV, "auto")
+    if device.type == "cuda" and prefer in ("auto", "peer"):
+        try:
+            from .peer import PeerTransport
+
+            t = PeerTransport.create(group, device)
+            if t is not None:
+                return t
+            if prefer == "peer":
+                raise RuntimeError("peer transport requested but unavailable")
+        except Exception:
+            if prefer == "peer":
+                raise
+    return TorchDistTransport(group)
