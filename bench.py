@@ -1,0 +1,315 @@
+"""Headline benchmark: sharded training step of a Llama-style decoder, tokens/s per box.
+
+    python bench.py --gpus N --steps K --warmup W [--impl ours|reference] [--config 2|3|tiny]
+
+Default config is BASELINE config 2: AdamW, dp_shard = N, bf16 parameters and compute with fp32
+master weights and optimizer state, 8 layers, hidden 2048, 16 heads x 128, SwiGLU 5504, vocab
+32000, micro-batch 4 x seq 1024 per GPU (weak scaling), synthetic uniform token ids, random
+N(0, 0.02) weights.  For N > 1 launch under ``torch.distributed.run``.
+
+Rank 0 prints one JSON line.  ``value`` is device-timed (CUDA events around exactly K steps,
+barrier + synchronize on both sides, max over ranks) with the step inputs already on the device.
+``e2e`` is the same metric through the user-facing ``train_step`` call, whose timed region
+includes the host→device copy of every step's batch from pinned memory and the device→host read
+of the loss.
+
+``--impl reference`` runs the unmodified reference package (installed under ``baseline/_ref``)
+through its public ``fully_shard`` / ``configure_optimizer`` on a stock-PyTorch model of the same
+architecture (``baseline/ref_llama.py``).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CONFIGS = {
+    "2": dict(model="llama-8L-h2048-ffn5504-v32000", vocab_size=32000, hidden=2048, n_layers=8, n_heads=16,
+              head_dim=128, ffn=5504, micro_batch=4, seq_len=1024, optimizer="adamw", ac=False,
+              lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1),
+    "3": dict(model="llama-32L-h4096-ffn11008-v32000", vocab_size=32000, hidden=4096, n_layers=32, n_heads=32,
+              head_dim=128, ffn=11008, micro_batch=1, seq_len=4096, optimizer="mixed_muon_adamw", ac=True,
+              lr=0.02, betas=(0.9, 0.95), weight_decay=0.1),
+    "tiny": dict(model="llama-2L-h256-ffn688-v1024", vocab_size=1024, hidden=256, n_layers=2, n_heads=2,
+                 head_dim=128, ffn=688, micro_batch=2, seq_len=128, optimizer="adamw", ac=False,
+                 lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1),
+}
+
+
+# ------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+        self._thread = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+
+        def pump():
+            for line in self.proc.stdout:
+                self.lines.append(line.strip())
+
+        self._thread = threading.Thread(target=pump, daemon=True)
+        self._thread.start()
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                 parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------ builders
+def build_ours(cfg: dict, device, mesh, world: int):
+    from torch.distributed.fsdp import MixedPrecisionPolicy
+
+    from matrix_fsdp_b200.models.llama import LlamaConfig, LlamaModel, shard_llama
+    from matrix_fsdp_b200.optim import configure_optimizer
+
+    mcfg = LlamaConfig(vocab_size=cfg["vocab_size"], hidden=cfg["hidden"], n_layers=cfg["n_layers"],
+                       n_heads=cfg["n_heads"], head_dim=cfg["head_dim"], ffn=cfg["ffn"],
+                       activation_checkpointing=cfg["ac"], max_seq_len=cfg["seq_len"])
+    torch.manual_seed(0)
+    model = LlamaModel(mcfg).to(device)
+    model.loss_is_final = True
+    mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16)
+    policy = "mixed_muon_adamw" if cfg["optimizer"] == "mixed_muon_adamw" else None
+    shard_llama(model, mesh=mesh, mp_policy=mp, optimizer_policy=policy)
+    if cfg["optimizer"] == "adamw":
+        opt = configure_optimizer(model, "adamw", lr=cfg["lr"], betas=cfg["betas"], weight_decay=cfg["weight_decay"])
+    else:
+        opt = configure_optimizer(model, "mixed_muon_adamw", muon_lr=cfg["lr"], adamw_lr=3e-4,
+                                  adamw_betas=cfg["betas"], weight_decay=cfg["weight_decay"], muon_momentum=0.95,
+                                  muon_ns_steps=5, muon_adjust_lr_fn="original")
+    from matrix_fsdp_b200.parallel.unit_collection import collect_param_groups
+
+    for u in collect_param_groups(model):
+        u.runtime_trace_enabled = False
+    return model, opt
+
+
+def build_reference(cfg: dict, device, mesh, world: int):
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "matrix_fsdp")):
+        raise FileNotFoundError("reference package is not installed under baseline/_ref")
+    sys.path.insert(0, ref_dir)
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import matrix_fsdp as R
+    from ref_llama import RefLlama
+    from torch.distributed.fsdp import MixedPrecisionPolicy
+
+    torch.manual_seed(0)
+    model = RefLlama(cfg["vocab_size"], cfg["hidden"], cfg["n_layers"], cfg["n_heads"], cfg["head_dim"], cfg["ffn"],
+                     activation_checkpointing=cfg["ac"]).to(device)
+    mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16)
+    policy = "mixed_muon_adamw" if cfg["optimizer"] == "mixed_muon_adamw" else None
+    for layer in model.layers:
+        R.fully_shard(layer, mesh=mesh, mp_policy=mp, optimizer_policy=policy)
+    R.fully_shard(model, mesh=mesh, mp_policy=mp)
+    if cfg["optimizer"] == "adamw":
+        opt = R.configure_optimizer(model, "adamw", lr=cfg["lr"], betas=cfg["betas"], weight_decay=cfg["weight_decay"])
+    else:
+        opt = R.configure_optimizer(model, "mixed_muon_adamw", muon_lr=cfg["lr"], adamw_lr=3e-4,
+                                    adamw_betas=cfg["betas"], weight_decay=cfg["weight_decay"], muon_momentum=0.95,
+                                    muon_ns_steps=5, muon_adjust_lr_fn="original")
+    for u in R.collect_param_groups(model):
+        u.runtime_trace_enabled = False
+    return model, opt
+
+
+# ------------------------------------------------------------------------------------ main
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--config", default="2", choices=sorted(CONFIGS))
+    ap.add_argument("--device", default=None)
+    args = ap.parse_args()
+    cfg = CONFIGS[args.config]
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    cuda = torch.cuda.is_available() and args.device != "cpu"
+    if args.impl == "reference" and not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "matrix_fsdp")):
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "reference package not installed under baseline/_ref"}))
+        return
+    device = torch.device("cuda", local_rank) if cuda else torch.device("cpu")
+    if cuda:
+        torch.cuda.set_device(device)
+    mesh = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl" if cuda else "gloo", device_id=device if cuda else None)
+        from torch.distributed.device_mesh import init_device_mesh
+
+        mesh = init_device_mesh("cuda" if cuda else "cpu", (world,), mesh_dim_names=("dp_shard",))
+    if args.gpus != world and rank == 0 and world > 1:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
+
+    build = build_ours if args.impl == "ours" else build_reference
+    model, opt = build(cfg, device, mesh, world)
+
+    B, S, V = cfg["micro_batch"], cfg["seq_len"], cfg["vocab_size"]
+    total_steps = args.warmup + args.steps
+    gen = torch.Generator().manual_seed(1234 + rank)
+    host = torch.randint(0, V, (2 * total_steps + 2, B, S + 1), generator=gen, dtype=torch.int64)
+    if cuda:
+        host = host.pin_memory()
+    dev_batches = host[: total_steps].to(device)
+
+    def sync():
+        if cuda:
+            torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        if cuda:
+            torch.cuda.synchronize()
+
+    def device_step(i: int):
+        batch = dev_batches[i]
+        loss = model(batch[:, :-1], batch[:, 1:])
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    def e2e_step(i: int) -> float:
+        hb = host[total_steps + i]
+        tokens = hb[:, :-1].to(device, non_blocking=True)
+        targets = hb[:, 1:].to(device, non_blocking=True)
+        loss = model(tokens, targets)
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return float(loss.item())
+
+    launches_before = 0
+    counter = None
+    if args.impl == "ours":
+        from matrix_fsdp_b200.ops import kernels as _K
+
+        counter = _K
+
+    # ---- warm-up
+    for i in range(args.warmup):
+        last = device_step(i)
+    sync()
+    if cuda:
+        torch.cuda.reset_peak_memory_stats()
+    if counter is not None:
+        launches_before = counter.launch_count()
+
+    # ---- device-timed region
+    sampler = ClockSampler(local_rank) if (cuda and rank == 0) else None
+    if sampler:
+        sampler.start()
+    if cuda:
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+    t0 = time.perf_counter()
+    for i in range(args.warmup, total_steps):
+        last = device_step(i)
+    if cuda:
+        ev1.record()
+        torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1)
+    else:
+        ms = (time.perf_counter() - t0) * 1e3
+    launches = (counter.launch_count() - launches_before) if counter is not None else 0
+    clocks = sampler.stop() if sampler else {}
+    sync()
+    final_loss = float(last.item())
+    peak_mb = torch.cuda.max_memory_allocated() / 2 ** 20 if cuda else 0.0
+
+    # ---- end-to-end region (public train_step semantics: H2D each step, D2H loss read each step)
+    for i in range(min(3, args.steps)):
+        e2e_step(i)
+    sync()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_loss = e2e_step(i)
+    if cuda:
+        torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+
+    stats = torch.tensor([ms, e2e_ms, peak_mb], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    ms, e2e_ms, peak_mb = (float(x) for x in stats.tolist())
+
+    tokens_per_step = B * S * world
+    value = tokens_per_step * args.steps / (ms / 1e3)
+    e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
+    out = {
+        "metric": "tokens_per_s_per_box", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids; random-init N(0,0.02) weights",
+        "impl": args.impl, "peak_mb": peak_mb, "final_loss": final_loss,
+        "config": {"model": cfg["model"], "global_batch": B * world, "micro_batch_per_gpu": B, "seq_len": S,
+                   "parallelism": f"dp_shard{world}", "optimizer": cfg["optimizer"],
+                   "precision": "bf16 params+compute, fp32 master weights and optimizer state",
+                   "activation_checkpointing": cfg["ac"],
+                   "l2": "no explicit flush: each step streams >1 GB of weights/activations (L2 is 126 MB)"},
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
+                "h2d_bytes_per_step": 2 * B * S * 8, "d2h_bytes_per_step": 4, "last_loss": e2e_loss},
+        "gpu_launches": launches,
+    }
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,208 @@
+"""Llama-style decoder (RMSNorm, RoPE, causal attention, SwiGLU) on the sm_100a ops.
+
+Parameters are kept as separate matrices (``wq, wk, wv, wo, w_gate, w_up, w_down``) so that a
+matrix-owner layout / Muon sees seven 2-D matrices per block; because an FSDP unit lays its
+parameters out back to back in one flat buffer, ``wq|wk|wv`` and ``w_gate|w_up`` are adjacent in
+memory and the block node multiplies them as one fused matrix.
+
+On CUDA/bf16 each block is a single autograd node (:class:`DecoderBlockFunction`); elsewhere the
+same math runs as plain PyTorch ops, which is also the reference the tests compare against.
+
+The reference has no model library; its benches use a LayerNorm/GELU toy transformer
+(``test/fsdp/bench_fsdp2_compare.py:456-514``) and a DeepSeek-style fixture
+(``test/fsdp/test_deepseek_v3_ep_train.py:354-563``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from ..ops import functional as OF
+
+
+@dataclass
+class LlamaConfig:
+    vocab_size: int = 32000
+    hidden: int = 2048
+    n_layers: int = 8
+    n_heads: int = 16
+    head_dim: int = 128
+    ffn: int = 5504
+    rope_theta: float = 10000.0
+    eps: float = 1e-5
+    tie_embeddings: bool = False
+    init_std: float = 0.02
+    activation_checkpointing: bool = False
+    max_seq_len: int = 4096
+    loss_ignore_index: int | None = None   # None: every target counts (lets the loss skip a host sync)
+
+    @staticmethod
+    def config1() -> "LlamaConfig":
+        return LlamaConfig(vocab_size=1024, hidden=256, n_layers=2, n_heads=4, head_dim=64, ffn=688,
+                           tie_embeddings=True, max_seq_len=128)
+
+    @staticmethod
+    def config2() -> "LlamaConfig":
+        return LlamaConfig(vocab_size=32000, hidden=2048, n_layers=8, n_heads=16, head_dim=128, ffn=5504)
+
+    @staticmethod
+    def config3() -> "LlamaConfig":
+        return LlamaConfig(vocab_size=32000, hidden=4096, n_layers=32, n_heads=32, head_dim=128, ffn=11008,
+                           activation_checkpointing=True)
+
+    @staticmethod
+    def config4() -> "LlamaConfig":
+        return LlamaConfig(vocab_size=32000, hidden=5120, n_layers=40, n_heads=40, head_dim=128, ffn=13824,
+                           activation_checkpointing=True)
+
+
+class RMSNorm(nn.Module):
+    is_norm_like = True
+
+    def __init__(self, dim: int, eps: float = 1e-5) -> None:
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim))
+        self.eps = eps
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return OF.rms_norm(x, self.weight, self.eps)
+
+
+class Matrix(nn.Module):
+    """A bias-free linear map holding ``weight`` [out, in]; flagged so shard-hint rules treat it as Linear."""
+
+    is_linear_like = True
+
+    def __init__(self, in_features: int, out_features: int, std: float = 0.02, is_lm_head: bool = False) -> None:
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = nn.Parameter(torch.empty(out_features, in_features))
+        self.is_lm_head = is_lm_head
+        nn.init.normal_(self.weight, mean=0.0, std=std)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return OF.linear(x, self.weight, self.weight)
+
+
+class LlamaBlock(nn.Module):
+    def __init__(self, cfg: LlamaConfig) -> None:
+        super().__init__()
+        self.cfg = cfg
+        h, f, std = cfg.hidden, cfg.ffn, cfg.init_std
+        assert cfg.n_heads * cfg.head_dim == h
+        # registration order is the flat-buffer order: keep q|k|v and gate|up adjacent
+        self.attn_norm = RMSNorm(h, cfg.eps)
+        self.wq = Matrix(h, h, std)
+        self.wk = Matrix(h, h, std)
+        self.wv = Matrix(h, h, std)
+        self.wo = Matrix(h, h, std)
+        self.mlp_norm = RMSNorm(h, cfg.eps)
+        self.w_gate = Matrix(h, f, std)
+        self.w_up = Matrix(h, f, std)
+        self.w_down = Matrix(f, h, std)
+
+    def _shape(self, batch: int, seq: int) -> OF.BlockShape:
+        c = self.cfg
+        return OF.BlockShape(batch, seq, c.hidden, c.n_heads, c.head_dim, c.ffn, c.eps, c.rope_theta)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """``x``: [B, S, H]."""
+        b, s, h = x.shape
+        c = self.cfg
+        cos, sin = OF.rope_tables(max(s, 1), c.head_dim, c.rope_theta, x.device)
+        if OF.use_native(x) and self.wq.weight.dtype == torch.bfloat16 and h % 8 == 0 and c.ffn % 8 == 0:
+            y = OF.decoder_block(x.reshape(b * s, h), self, self._shape(b, s), cos, sin,
+                                 recompute=c.activation_checkpointing and torch.is_grad_enabled())
+            return y.view(b, s, h)
+        if c.activation_checkpointing and torch.is_grad_enabled():
+            from torch.utils.checkpoint import checkpoint
+
+            return checkpoint(self._forward_reference, x, cos, sin, use_reentrant=False)
+        return self._forward_reference(x, cos, sin)
+
+    def _forward_reference(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        c = self.cfg
+        b, s, h = x.shape
+        xn = self.attn_norm(x)
+        q = F.linear(xn, self.wq.weight).view(b, s, c.n_heads, c.head_dim)
+        k = F.linear(xn, self.wk.weight).view(b, s, c.n_heads, c.head_dim)
+        v = F.linear(xn, self.wv.weight).view(b, s, c.n_heads, c.head_dim)
+        q, k = OF.apply_rope_reference(q, cos, sin), OF.apply_rope_reference(k, cos, sin)
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
+        x = x + F.linear(o.transpose(1, 2).reshape(b, s, h), self.wo.weight)
+        xn = self.mlp_norm(x)
+        hidden = F.silu(F.linear(xn, self.w_gate.weight)) * F.linear(xn, self.w_up.weight)
+        return x + F.linear(hidden, self.w_down.weight)
+
+
+class LlamaModel(nn.Module):
+    """Decoder-only LM.  ``forward(tokens, targets=None)`` returns logits or the mean CE loss."""
+
+    def __init__(self, cfg: LlamaConfig) -> None:
+        super().__init__()
+        self.cfg = cfg
+        self.embed = nn.Embedding(cfg.vocab_size, cfg.hidden)
+        nn.init.normal_(self.embed.weight, mean=0.0, std=cfg.init_std)
+        self.layers = nn.ModuleList([LlamaBlock(cfg) for _ in range(cfg.n_layers)])
+        self.final_norm = RMSNorm(cfg.hidden, cfg.eps)
+        self.lm_head = Matrix(cfg.hidden, cfg.vocab_size, cfg.init_std, is_lm_head=True)
+        if cfg.tie_embeddings:
+            self.lm_head.weight = self.embed.weight
+
+    def forward(self, tokens: torch.Tensor, targets: torch.Tensor | None = None) -> torch.Tensor:
+        x = self.embed(tokens)
+        for layer in self.layers:
+            x = layer(x)
+        x = self.final_norm(x)
+        logits = self.lm_head(x)
+        if targets is None:
+            return logits
+        n_valid = targets.numel() if self.cfg.loss_ignore_index is None else None
+        ignore = -100 if self.cfg.loss_ignore_index is None else self.cfg.loss_ignore_index
+        return OF.fused_cross_entropy(logits, targets, ignore_index=ignore, n_valid=n_valid,
+                                      unit_upstream_grad=getattr(self, "loss_is_final", False))
+
+    def num_params(self) -> int:
+        return sum(p.numel() for p in self.parameters())
+
+    def flops_per_token(self, seq_len: int) -> float:
+        """Training FLOPs per token (fwd+bwd = 3× forward), causal attention counted at half density."""
+        c = self.cfg
+        per_layer = 2 * (4 * c.hidden * c.hidden + 3 * c.hidden * c.ffn)
+        attn = 2 * 2 * seq_len * c.hidden * 0.5
+        head = 2 * c.hidden * c.vocab_size
+        return 3.0 * (c.n_layers * (per_layer + attn) + head)
+
+
+def shard_llama(model: LlamaModel, *, mesh=None, dp_mesh_dims=None, mp_policy=None, optimizer_policy=None,
+                reshard_after_forward=None, shard_root: bool = True, **kw) -> LlamaModel:
+    """``fully_shard`` every block, then the root (embedding, final norm, LM head)."""
+    from torch.distributed.fsdp import MixedPrecisionPolicy
+
+    from ..api import fully_shard, matrix_fully_shard
+
+    mp = mp_policy or MixedPrecisionPolicy()
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh, dp_mesh_dims=dp_mesh_dims, mp_policy=mp, optimizer_policy=optimizer_policy,
+                    reshard_after_forward=reshard_after_forward, **kw)
+    if shard_root:
+        hints = None
+        if optimizer_policy is not None:
+            from ..planning.shard_hint import build_shard_hints
+
+            hints = {k: v for k, v in build_shard_hints(model).items() if not k.startswith("layers.")}
+        if model.cfg.tie_embeddings or hints is not None:
+            from ..core.mesh import DataParallelMeshDims  # noqa: F401
+
+            matrix_fully_shard(model, mesh, dp_mesh_dims=dp_mesh_dims, mp_policy=mp, shard_hints=hints,
+                               auto_planner_policy="muon_shard_aware" if optimizer_policy else None,
+                               owner_assignment="role_greedy" if optimizer_policy else "rotate",
+                               reshard_after_forward=True if reshard_after_forward is None else reshard_after_forward,
+                               allow_shared_params=model.cfg.tie_embeddings)
+        else:
+            fully_shard(model, mesh=mesh, dp_mesh_dims=dp_mesh_dims, mp_policy=mp,
+                        reshard_after_forward=reshard_after_forward, **kw)
+    return model

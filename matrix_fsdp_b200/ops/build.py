@@ -79,7 +79,9 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
         objs = list(ex.map(compile_one, sources()))
-    link = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(lib_path()), *map(str, objs)]
+    # Shared cudart: inside a torch process the loader binds to the libcudart.so.12 torch already
+    # loaded, so both sides see one runtime (same per-thread current device, same primary context).
+    link = [nvcc, *ARCH_FLAGS, "-shared", "-cudart", "shared", "-o", str(lib_path()), *map(str, objs)]
     res = subprocess.run(link, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")

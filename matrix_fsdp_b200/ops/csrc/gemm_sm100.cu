@@ -389,6 +389,9 @@ MFSDP_API int mfsdp_gemm_bf16(const void* A, const void* B, void* D, const void*
                               int num_groups, long long k_total, int* status, int num_sms,
                               int force_bn, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K < 0) return -2;
+  // Tensor-map encoding is a driver call and needs a current context; a thread that has not yet
+  // made a runtime call (e.g. an autograd worker on device 0) has none until this binds it.
+  cudaFree(nullptr);
   if ((lda % 8) || (ldb % 8) || (ldd % 8)) return -2;
   if (((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)D & 15)) return -2;
   if (group_mode == 2 && (!a_mn_major || !b_mn_major || (M % BM) != 0)) return -2;

@@ -19,6 +19,10 @@ def _L():
     return _lib.load(required=True)
 
 
+def launch_count() -> int:
+    return _lib.launch_count()
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 

@@ -81,9 +81,20 @@ def available() -> bool:
     return load() is not None
 
 
+# kernels launched per launcher call (default 1); the counter feeds the benchmark's launch report
+_KERNELS_PER_CALL = {"rmsnorm_bwd": 2}
+_LAUNCH_COUNT = [0]
+
+
 def check(rc: int, what: str) -> None:
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}")
+    _LAUNCH_COUNT[0] += _KERNELS_PER_CALL.get(what, 1)
+
+
+def launch_count() -> int:
+    """Number of kernels of this library launched so far in this process."""
+    return _LAUNCH_COUNT[0]
 
 
 def disabled_by_env() -> bool:
