@@ -1,0 +1,134 @@
+"""FSDP2 / DCP-shaped state-dict facade over the sharded state.
+
+``get_model_state_dict`` / ``get_optimizer_state_dict`` / ``get_state_dict`` and their ``set_*``
+twins mirror ``torch.distributed.checkpoint.state_dict``; ``options.full_state_dict`` gathers every
+unit and returns ordinary full tensors keyed like ``module.state_dict()`` (optionally on CPU).
+``patch_model_state_dict`` / ``patch_optimizer_state_dict`` rebind ``state_dict`` /
+``load_state_dict`` on the objects themselves.
+
+Parity: ``matrix_fsdp/checkpoint/_api.py:1-277``.
+"""
+from __future__ import annotations
+
+import functools
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+from torch import nn
+
+from ..parallel.unit_collection import collect_param_groups
+from .state_dict import iter_optimizer_components, load_matrix_state_dict, matrix_state_dict
+
+
+@dataclass
+class MatrixStateDictOptions:
+    full_state_dict: bool = False
+    cpu_offload: bool = False
+    strict: bool = True
+
+
+def _opts(options) -> MatrixStateDictOptions:
+    if options is None:
+        return MatrixStateDictOptions()
+    return MatrixStateDictOptions(bool(getattr(options, "full_state_dict", False)),
+                                  bool(getattr(options, "cpu_offload", False)), bool(getattr(options, "strict", True)))
+
+
+def _full_model_state(model: nn.Module, cpu: bool) -> dict[str, torch.Tensor]:
+    units = collect_param_groups(model)
+    for u in units:
+        u.unshard("state_dict")
+    try:
+        out = {}
+        for k, v in nn.Module.state_dict(model).items():
+            t = v.detach().clone()
+            out[k] = t.cpu() if cpu else t
+    finally:
+        for u in units:
+            u.reshard("state_dict")
+    return out
+
+
+def get_model_state_dict(model: nn.Module, *, options=None) -> dict[str, Any]:
+    o = _opts(options)
+    if o.full_state_dict:
+        return _full_model_state(model, o.cpu_offload)
+    return matrix_state_dict(model, clone=True)
+
+
+def set_model_state_dict(model: nn.Module, model_state_dict, *, options=None) -> None:
+    o = _opts(options)
+    if o.full_state_dict or "units" not in model_state_dict:
+        units = collect_param_groups(model)
+        by_param = {}
+        for u in units:
+            for mp in u.registry:
+                by_param[id(mp.param)] = (u, mp)
+        with torch.no_grad():
+            for name, p in model.named_parameters(remove_duplicate=False):
+                if name not in model_state_dict:
+                    if o.strict:
+                        raise KeyError(f"missing key {name!r} in state dict")
+                    continue
+                full = model_state_dict[name]
+                hit = by_param.get(id(p))
+                if hit is None:
+                    p.data.copy_(full.to(p.device))
+                    continue
+                u, mp = hit
+                piece = u.flat_buffer.pieces.get(mp.fqn)
+                if piece is not None:
+                    src = full.reshape(-1)[piece.param_start:piece.param_start + piece.numel]
+                    u.flat_buffer.local_shard[piece.local_start:piece.local_end].copy_(src.to(u.flat_buffer.device))
+            for u in units:
+                u.flat_buffer.mark_master_updated(lp_written=False)
+            for name, b in model.named_buffers():
+                if name in model_state_dict:
+                    b.copy_(model_state_dict[name].to(b.device))
+        return
+    load_matrix_state_dict(model, model_state_dict, strict=o.strict)
+
+
+def get_optimizer_state_dict(model: nn.Module, optimizers, *, options=None) -> dict[str, Any]:
+    opts = optimizers if isinstance(optimizers, (list, tuple)) else [optimizers]
+    out: dict[str, Any] = {}
+    for i, opt in enumerate(opts):
+        comps = {name: o.state_dict() for name, o in iter_optimizer_components(opt)}
+        out[f"optimizer_{i}"] = comps
+    return out if len(opts) > 1 else out["optimizer_0"]
+
+
+def set_optimizer_state_dict(model: nn.Module, optimizers, optim_state_dict, *, options=None) -> None:
+    opts = optimizers if isinstance(optimizers, (list, tuple)) else [optimizers]
+    for i, opt in enumerate(opts):
+        sd = optim_state_dict[f"optimizer_{i}"] if len(opts) > 1 else optim_state_dict
+        for name, o in iter_optimizer_components(opt):
+            if name not in sd:
+                raise ValueError(f"missing component {name!r} in optimizer state dict")
+            o.load_state_dict(sd[name])
+
+
+def get_state_dict(model: nn.Module, optimizers, *, options=None):
+    return get_model_state_dict(model, options=options), get_optimizer_state_dict(model, optimizers, options=options)
+
+
+def set_state_dict(model: nn.Module, optimizers, *, model_state_dict, optim_state_dict, options=None) -> None:
+    set_model_state_dict(model, model_state_dict, options=options)
+    set_optimizer_state_dict(model, optimizers, optim_state_dict, options=options)
+
+
+matrix_get_state_dict = get_state_dict
+matrix_set_state_dict = set_state_dict
+
+
+def patch_model_state_dict(model: nn.Module, *, options=None) -> None:
+    model.state_dict = functools.partial(get_model_state_dict, model, options=options)  # type: ignore[assignment]
+    model.load_state_dict = lambda sd, **kw: set_model_state_dict(model, sd, options=options)  # type: ignore[assignment]
+
+
+def patch_optimizer_state_dict(model: nn.Module, *, optimizers, options=None) -> None:
+    opts = optimizers if isinstance(optimizers, (list, tuple)) else [optimizers]
+    for opt in opts:
+        opt.state_dict = functools.partial(get_optimizer_state_dict, model, opt, options=options)
+        opt.load_state_dict = functools.partial(set_optimizer_state_dict, model, opt, options=options)

@@ -142,20 +142,31 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
   for (int i = 0; i < VPT; ++i) {
     const int v = threadIdx.x + i * blockDim.x;
     if (v < nvec) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) atomicAdd(dw_acc + v * 8 + e, dwp[i][e]);
+      // one partial row per CTA in the scratch matrix [gridDim.x, H]; no atomics
+      float* dst = dw_acc + (long long)blockIdx.x * H + v * 8;
+      reinterpret_cast<float4*>(dst)[0] = make_float4(dwp[i][0], dwp[i][1], dwp[i][2], dwp[i][3]);
+      reinterpret_cast<float4*>(dst)[1] = make_float4(dwp[i][4], dwp[i][5], dwp[i][6], dwp[i][7]);
     }
   }
 }
 
-// out (bf16) = (accumulate ? out : 0) + acc (fp32)
-__global__ void f32_to_bf16_accum_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ out,
-                                         long long n, int accumulate) {
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
-       i += (long long)gridDim.x * blockDim.x) {
-    float v = acc[i];
-    if (accumulate) v += __bfloat162float(out[i]);
-    out[i] = __float2bfloat16_rn(v);
+// out[c] (bf16) = (accumulate ? out[c] : 0) + sum_r partial[r, c]; one thread per column, rows
+// strided over blockIdx.y-less 2-D thread blocks (32 columns x 8 row lanes).
+__global__ void colsum_f32_to_bf16_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
+                                          int rows, int H, int accumulate) {
+  __shared__ float tile[8][33];
+  const int col = blockIdx.x * 32 + threadIdx.x;
+  float acc = 0.f;
+  if (col < H)
+    for (int r = threadIdx.y; r < rows; r += 8) acc += partial[(long long)r * H + col];
+  tile[threadIdx.y][threadIdx.x] = acc;
+  __syncthreads();
+  if (threadIdx.y == 0 && col < H) {
+    float v = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v += tile[j][threadIdx.x];
+    if (accumulate) v += __bfloat162float(out[col]);
+    out[col] = __float2bfloat16_rn(v);
   }
 }
 
@@ -544,7 +555,11 @@ MFSDP_API int mfsdp_rmsnorm_fwd(const void* x, const void* w, void* y, float* rs
   return (int)cudaGetLastError();
 }
 
-// dw_acc: fp32 [H] scratch that must be zero on entry; dw (bf16) = (accumulate ? dw : 0) + sum.
+// Rows of CTAs used by the backward kernel (= rows of the dw scratch matrix).
+MFSDP_API int mfsdp_rmsnorm_bwd_scratch_rows(long long rows) { return (int)(rows < 148 * 4 ? rows : 148 * 4); }
+
+// dw_acc: fp32 scratch of mfsdp_rmsnorm_bwd_scratch_rows(rows) x H floats (fully overwritten, needs no
+// initialisation); dw (bf16) = (accumulate ? dw : 0) + column sums of the scratch.
 MFSDP_API int mfsdp_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
                                 const void* dres, void* dx, float* dw_acc, void* dw,
                                 int accumulate_dw, long long rows, int H, cudaStream_t st) {
@@ -559,7 +574,7 @@ MFSDP_API int mfsdp_rmsnorm_bwd(const void* dy, const void* x, const void* w, co
   else if (vpt <= 2) rmsnorm_bwd_kernel<2><<<grid, threads, 0, st>>>(DY, X, W, rstd, DR, DX, dw_acc, rows, H);
   else if (vpt <= 4) rmsnorm_bwd_kernel<4><<<grid, threads, 0, st>>>(DY, X, W, rstd, DR, DX, dw_acc, rows, H);
   else return -2;
-  if (dw) f32_to_bf16_accum_kernel<<<grid_for(H, 256), 256, 0, st>>>(dw_acc, (__nv_bfloat16*)dw, H, accumulate_dw);
+  if (dw) colsum_f32_to_bf16_kernel<<<(H + 31) / 32, dim3(32, 8), 0, st>>>(dw_acc, (__nv_bfloat16*)dw, grid, H, accumulate_dw);
   return (int)cudaGetLastError();
 }
 

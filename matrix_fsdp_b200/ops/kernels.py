@@ -175,8 +175,7 @@ def rmsnorm_bwd(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor, rstd: torch.
     x2, dy2 = x.reshape(-1, H), dy.reshape(-1, H)
     assert x2.is_contiguous() and dy2.is_contiguous()
     dx = torch.empty_like(x2)
-    acc = _scratch_f32(H, x.device, "rms_dw")
-    acc.zero_()
+    acc = _scratch_f32(min(x2.shape[0], 148 * 4) * H, x.device, "rms_dw")
     if dw_out is None:
         dw_out = torch.empty(H, dtype=torch.bfloat16, device=x.device)
         accumulate_dw = False

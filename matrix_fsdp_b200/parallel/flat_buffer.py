@@ -126,8 +126,10 @@ class MatrixFlatBuffer:
             self.full_buffer = self._gather_source_tensor()
         else:
             self.full_buffer = torch.empty(self.total_numel, dtype=self.param_dtype, device=self.device)
-            self._shrink_full()
+        # views are created while the storage exists; they stay valid across resize_(0) / resize_(n)
         self._full_views = {mp.fqn: self.full_buffer[mp.offset:mp.end].view(mp.shape) for mp in params}
+        if not self.full_aliases_shard:
+            self._shrink_full()
         self._local_views: dict[str, torch.Tensor] = {}
         self._rebuild_local_views()
         self.full_materialized = self.full_aliases_shard

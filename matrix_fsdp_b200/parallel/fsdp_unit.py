@@ -381,7 +381,11 @@ class MatrixFSDPParamGroup:
             raise RuntimeError(
                 f"{self.name}: another forward before the backward of the previous one; multiple forwards before "
                 "a backward need reshard_after_forward=False.")
-        if self.finalized_after_backward and self.flat_buffer.pending_reduce is not None and self.scheduler is None:
+        if self.flat_buffer.pending_reduce is not None:
+            # a reduction from an earlier backward has not been consumed by an optimizer step yet:
+            # finish it so its result can be folded into the next one
+            if self.scheduler is not None:
+                self.scheduler.drop_pending_reduce(self)
             self.wait_post_backward_reduce()
         t0 = time.perf_counter()
         self._record("pre_forward")

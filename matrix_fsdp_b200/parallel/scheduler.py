@@ -263,6 +263,9 @@ class MatrixFSDPScheduler:
             return
         self._pending_reduces.append(unit)
 
+    def drop_pending_reduce(self, unit) -> None:
+        self._pending_reduces = [u for u in self._pending_reduces if u is not unit]
+
     def wait_pending_backward_reduce(self) -> None:
         while self._pending_reduces:
             u = self._pending_reduces.pop(0)

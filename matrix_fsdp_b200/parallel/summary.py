@@ -1,0 +1,149 @@
+"""Human- and machine-readable summaries of units, schedulers and runtime event logs.
+
+Parity: ``matrix_fsdp/runtime/summary.py:1-893`` (``summarize_param_groups``,
+``summarize_runtime_events``, the two formatters).
+"""
+from __future__ import annotations
+
+from collections import defaultdict
+from collections.abc import Iterable
+from statistics import mean
+
+from .param_buffers import describe_unit_param_buffer
+from .runtime_event import RuntimeEvent
+from .unit_collection import collect_param_groups
+
+EVENT_CATEGORIES = {
+    "unshard": ("start_unshard", "wait_unshard", "unshard"),
+    "reshard": ("reshard",),
+    "prefetch": ("forward_prefetch", "backward_prefetch", "discard_unused_prefetch"),
+    "forward": ("pre_forward", "post_forward"),
+    "backward": ("pre_backward", "finalize_backward", "defer_backward_reduce"),
+    "reduce": ("start_reduce_scatter", "wait_reduce_scatter"),
+    "init": ("init",),
+}
+
+
+def _category(name: str) -> str:
+    base = name.split(":", 1)[0]
+    for cat, prefixes in EVENT_CATEGORIES.items():
+        if any(base.startswith(p) for p in prefixes):
+            return cat
+    return "other"
+
+
+def summarize_param_groups(module_or_units) -> list[dict[str, object]]:
+    """One dict per unit: planner, runtime mode, per-rank estimates, communication summary, memory."""
+    out = []
+    for u in collect_param_groups(module_or_units):
+        fb, res = u.flat_buffer, u.planner_result
+        desc = describe_unit_param_buffer(u)
+        comm = desc.communication_summary(
+            param_gather_strategy=u.param_gather_strategy, matrix_collective_backend=u.matrix_collective_backend,
+            can_direct_all_gather=fb.tables.equal_contiguous, transport_kind=fb.transport.kind)
+        est = res.resource_estimate
+        out.append({
+            "name": u.name, "rank": u.rank, "world_size": u.world_size,
+            "replicate_world_size": u.replicate_world_size, "state": u.state.value,
+            "planner_name": res.name, "planner_policy": res.policy, "runtime_mode": u.runtime_mode,
+            "num_params": len(u.registry), "total_numel": fb.total_numel, "local_numel": fb.local_numel,
+            "shard_sizes": res.layout.shard_sizes, "param_dtype": str(fb.param_dtype),
+            "shard_dtype": str(fb.shard_dtype), "reduce_dtype": str(fb.reduce_dtype),
+            "transport": fb.transport.kind, "communication": comm, "memory": fb.memory_snapshot(),
+            "rank_memory_bytes": est.rank_memory_bytes if est else (), "rank_comm_bytes": est.rank_comm_bytes if est else (),
+            "rank_ns_flops": est.rank_ns_flops if est else (), "planner_cost": res.cost, "warnings": res.warnings,
+            "num_events": len(u.runtime_events),
+            "scheduler": u.scheduler.summary() if u.scheduler is not None else None,
+        })
+    return out
+
+
+def format_param_group_summary(module_or_units) -> str:
+    rows = summarize_param_groups(module_or_units)
+    if not rows:
+        return "(no FSDP units)"
+    lines = []
+    for r in rows:
+        comm = r["communication"]
+        lines.append(
+            f"{r['name']}: rank {r['rank']}/{r['world_size']} state={r['state']} planner={r['planner_name']}"
+            f"({r['planner_policy']}) mode={r['runtime_mode']} params={r['num_params']} numel={r['total_numel']} "
+            f"local={r['local_numel']} transport={r['transport']} gather={comm['effective_param_gather_backend']} "
+            f"reduce={comm['effective_grad_reduce_backend']} pad_waste={comm['padding_waste_ratio']:.3f} "
+            f"owner_imbalance={comm['owner_imbalance_ratio']:.3f}")
+    sched = rows[0]["scheduler"]
+    if sched:
+        c = sched["counters"]
+        lines.append(f"scheduler: units={sched['num_units']} fwd_prefetch={c['forward_prefetch_issued']} "
+                     f"bwd_prefetch={c['backward_prefetch_issued']} reduce_waits={c['reduce_waits']} "
+                     f"high_water_full_bytes={c['high_water_active_full_param_bytes']}")
+    return "\n".join(lines)
+
+
+def _stats(values: list[float]) -> dict[str, float]:
+    if not values:
+        return {"count": 0, "total_ms": 0.0, "mean_ms": 0.0, "max_ms": 0.0}
+    return {"count": len(values), "total_ms": sum(values), "mean_ms": mean(values), "max_ms": max(values)}
+
+
+def summarize_runtime_events(module_or_units_or_events) -> dict[str, object]:
+    """Aggregate event logs per name, per category, per collective kind/impl and per unit."""
+    events: list[RuntimeEvent] = []
+    if isinstance(module_or_units_or_events, Iterable) and not hasattr(module_or_units_or_events, "modules"):
+        items = list(module_or_units_or_events)
+        if items and isinstance(items[0], RuntimeEvent):
+            events = items
+        else:
+            for u in collect_param_groups(items):
+                events.extend(u.runtime_events)
+    else:
+        for u in collect_param_groups(module_or_units_or_events):
+            events.extend(u.runtime_events)
+    events.sort(key=lambda e: e.sequence)
+    by_name, by_cat, by_unit = defaultdict(list), defaultdict(list), defaultdict(list)
+    by_coll: dict[tuple, dict] = {}
+    for e in events:
+        by_name[e.name].append(e.duration_ms)
+        by_cat[_category(e.name)].append(e.duration_ms)
+        by_unit[e.unit].append(e.duration_ms)
+        if e.collective_kind:
+            key = (e.collective_kind, e.collective_backend, e.collective_impl)
+            d = by_coll.setdefault(key, {"count": 0, "bytes": 0, "host_ms": 0.0, "collective_count": 0})
+            if e.name.startswith(("start_", "wait_")):
+                d["host_ms"] += e.duration_ms
+            if e.name.startswith("start_"):
+                d["count"] += 1
+                d["bytes"] += e.collective_bytes
+                d["collective_count"] += e.collective_count
+    return {
+        "num_events": len(events),
+        "by_name": {k: _stats(v) for k, v in by_name.items()},
+        "by_category": {k: _stats(v) for k, v in by_cat.items()},
+        "by_unit": {k: _stats(v) for k, v in by_unit.items()},
+        "by_collective": {"/".join(str(x) for x in k): v for k, v in by_coll.items()},
+        "max_active_full_param_buffers": max((e.active_full_param_buffers for e in events), default=0),
+        "max_pending_reduce_scatter": max((e.pending_reduce_scatter_count for e in events), default=0),
+        "max_grad_bucket_bytes": max((e.grad_bucket_bytes for e in events), default=0),
+        "prefetched_unshards": sum(1 for e in events if e.name == "unshard" and e.prefetched),
+        "recompute_skips": sum(1 for e in events if e.recompute),
+    }
+
+
+def format_runtime_events(module_or_units_or_events, *, limit: int | None = None) -> str:
+    s = summarize_runtime_events(module_or_units_or_events)
+    lines = [f"runtime events: {s['num_events']}"]
+    lines.append("by category:")
+    for k, v in sorted(s["by_category"].items()):
+        lines.append(f"  {k:10s} n={v['count']:5d} total={v['total_ms']:.3f}ms mean={v['mean_ms']:.4f}ms max={v['max_ms']:.3f}ms")
+    lines.append("by name:")
+    names = sorted(s["by_name"].items(), key=lambda kv: -kv[1]["total_ms"])
+    for k, v in names[: limit or len(names)]:
+        lines.append(f"  {k:34s} n={v['count']:5d} total={v['total_ms']:.3f}ms max={v['max_ms']:.3f}ms")
+    if s["by_collective"]:
+        lines.append("collectives:")
+        for k, v in s["by_collective"].items():
+            lines.append(f"  {k}: launches={v['count']} bytes={v['bytes']} host_ms={v['host_ms']:.3f}")
+    lines.append(f"max_active_full_param_buffers={s['max_active_full_param_buffers']} "
+                 f"max_pending_reduce_scatter={s['max_pending_reduce_scatter']} "
+                 f"prefetched_unshards={s['prefetched_unshards']} recompute_skips={s['recompute_skips']}")
+    return "\n".join(lines)

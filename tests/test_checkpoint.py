@@ -1,0 +1,173 @@
+"""matrix_dcp checkpoints: format, same-layout round trip, tamper detection, reshard, facade."""
+import copy
+import os
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from dist_utils import run_ranks
+from matrix_fsdp_b200 import (configure_optimizer, fully_shard, get_model_state_dict, load_matrix_dcp,
+                              load_matrix_dcp_full_state, load_matrix_state_dict, matrix_state_dict, save_matrix_dcp,
+                              set_model_state_dict)
+from matrix_fsdp_b200.api import reset_shared_owner_planners
+from matrix_fsdp_b200.checkpoint import MatrixStateDictOptions, read_global_metadata
+
+
+def _model(seed=0):
+    torch.manual_seed(seed)
+    return nn.Sequential(nn.Linear(6, 10), nn.LayerNorm(10), nn.Linear(10, 4))
+
+
+def _train(model, opt, steps=2, seed=1):
+    g = torch.Generator().manual_seed(seed)
+    for _ in range(steps):
+        model(torch.randn(3, 6, generator=g)).pow(2).mean().backward()
+        opt.step()
+        opt.zero_grad()
+
+
+def test_single_process_roundtrip_and_format():
+    reset_shared_owner_planners()
+    model = _model()
+    fully_shard(model)
+    opt = configure_optimizer(model, "adamw", lr=1e-2)
+    _train(model, opt)
+    with tempfile.TemporaryDirectory() as d:
+        save_matrix_dcp(model, d, optimizer=opt, no_dist=True)
+        assert os.path.exists(os.path.join(d, "matrix_metadata.pt"))
+        assert not [f for f in os.listdir(d) if f.startswith("matrix_metadata_rank_")]
+        payload = read_global_metadata(d)
+        assert payload["metadata"]["format"] == "matrix_dcp_global_metadata" and payload["metadata"]["ranks"] == (0,)
+        meta = payload["ranks"][0]
+        assert meta["optimizer"]["optimizer_format_version"] == 2
+        unit0 = meta["units"][0]
+        assert unit0["dcp_payload_rank"] == "rank_0" and "pieces" in unit0["params"]["0.weight"]
+        other = _model(seed=5)
+        fully_shard(other)
+        opt2 = configure_optimizer(other, "adamw", lr=1e-2)
+        load_matrix_dcp(other, d, optimizer=opt2, no_dist=True)
+        u, u2 = model._matrix_fsdp_param_group, other._matrix_fsdp_param_group
+        assert torch.equal(u.flat_buffer.local_shard, u2.flat_buffer.local_shard)
+        for (p, st), (p2, st2) in zip(opt.state.items(), opt2.state.items()):
+            assert torch.equal(st["exp_avg"], st2["exp_avg"]) and float(st["step"]) == float(st2["step"])
+        # training continues identically
+        _train(model, opt, seed=9)
+        _train(other, opt2, seed=9)
+        assert torch.equal(u.flat_buffer.local_shard, u2.flat_buffer.local_shard)
+        # tampering with structure is caught before tensors are read
+        payload["ranks"][0]["units"][0]["local_end"] = 3
+        torch.save(payload, os.path.join(d, "matrix_metadata.pt"))
+        with pytest.raises(ValueError, match="local_end"):
+            load_matrix_dcp(other, d, no_dist=True)
+
+
+def test_full_state_and_grads_and_facade():
+    model = _model()
+    ref = copy.deepcopy(model)
+    fully_shard(model)
+    model(torch.randn(2, 6)).sum().backward()
+    u = model._matrix_fsdp_param_group
+    u.prepare_for_optimizer_step()
+    with tempfile.TemporaryDirectory() as d:
+        save_matrix_dcp(model, d, full_state=True, include_grads=True, no_dist=True)
+        full = load_matrix_dcp_full_state(d)
+        assert set(full["params"]) == set(ref.state_dict())
+        for k, v in ref.state_dict().items():
+            assert torch.equal(full["params"][k], v)
+        g = u.flat_buffer.local_grad_shard.clone()
+        u.flat_buffer.local_grad_shard.zero_()
+        load_matrix_dcp(model, d, include_grads=True, no_dist=True)
+        assert torch.equal(u.flat_buffer.local_grad_shard, g)
+    sd = get_model_state_dict(model, options=MatrixStateDictOptions(full_state_dict=True, cpu_offload=True))
+    assert set(sd) == set(ref.state_dict()) and all(torch.equal(sd[k], v) for k, v in ref.state_dict().items())
+    fresh = _model(seed=3)
+    fully_shard(fresh)
+    set_model_state_dict(fresh, sd, options=MatrixStateDictOptions(full_state_dict=True))
+    assert torch.equal(fresh._matrix_fsdp_param_group.flat_buffer.local_shard, u.flat_buffer.local_shard)
+    inmem = matrix_state_dict(model)
+    fresh2 = _model(seed=4)
+    fully_shard(fresh2)
+    load_matrix_state_dict(fresh2, inmem)
+    assert torch.equal(fresh2._matrix_fsdp_param_group.flat_buffer.local_shard, u.flat_buffer.local_shard)
+
+
+def test_mixed_optimizer_components():
+    reset_shared_owner_planners()
+    model = _model()
+    fully_shard(model, optimizer_policy="mixed_muon_adamw")
+    opt = configure_optimizer(model, "mixed_muon_adamw", lr=0.01)
+    _train(model, opt)
+    with tempfile.TemporaryDirectory() as d:
+        meta = save_matrix_dcp(model, d, optimizer=opt, no_dist=True)
+        om = meta["optimizer"]
+        assert om["kind"] == "mixed_muon_adamw" and set(om["components"]) == {"muon", "adamw"}
+        entry = next(iter(om["components"]["muon"]["state"].values()))
+        assert "momentum_buffer" in entry["tensors"] and "matrix_state" in entry["tensors"]["momentum_buffer"]
+        single = configure_optimizer(model, "adamw", lr=0.01)
+        with pytest.raises(ValueError, match="unknown component"):
+            load_matrix_dcp(model, d, optimizer=single, no_dist=True)
+        reset_shared_owner_planners()
+        other = _model(seed=2)
+        fully_shard(other, optimizer_policy="mixed_muon_adamw")
+        opt2 = configure_optimizer(other, "mixed_muon_adamw", lr=0.01)
+        _train(other, opt2, steps=1)
+        load_matrix_dcp(other, d, optimizer=opt2, no_dist=True)
+        _train(model, opt, seed=4)
+        _train(other, opt2, seed=4)
+        assert torch.equal(model._matrix_fsdp_param_group.flat_buffer.local_shard,
+                           other._matrix_fsdp_param_group.flat_buffer.local_shard)
+
+
+def _save_two_rank_owner(rank, world, directory):
+    reset_shared_owner_planners()
+    model = _model()
+    fully_shard(model, optimizer_policy="mixed_muon_adamw")
+    opt = configure_optimizer(model, "mixed_muon_adamw", lr=0.01)
+    g = torch.Generator().manual_seed(11)
+    for _ in range(2):
+        model(torch.randn(3, 6, generator=g)).pow(2).mean().backward()
+        opt.step()
+        opt.zero_grad()
+    save_matrix_dcp(model, directory, optimizer=opt)
+    from matrix_fsdp_b200.checkpoint import get_model_state_dict as gms, MatrixStateDictOptions as O
+
+    full = gms(model, options=O(full_state_dict=True))
+    if rank == 0:
+        torch.save(full, os.path.join(directory, "expected_full.pt"))
+        mom = {}
+    # continue one more step for the reshard-equivalence check
+    model(torch.randn(3, 6, generator=g)).pow(2).mean().backward()
+    opt.step()
+    full2 = gms(model, options=O(full_state_dict=True))
+    if rank == 0:
+        torch.save(full2, os.path.join(directory, "expected_after.pt"))
+
+
+def test_reshard_owner_layout_two_ranks_to_one():
+    with tempfile.TemporaryDirectory() as d:
+        run_ranks(_save_two_rank_owner, 2, d)
+        payload = read_global_metadata(d)
+        assert payload["metadata"]["num_ranks"] == 2
+        reset_shared_owner_planners()
+        model = _model(seed=8)
+        fully_shard(model, optimizer_policy="mixed_muon_adamw")
+        opt = configure_optimizer(model, "mixed_muon_adamw", lr=0.01)
+        with pytest.raises(ValueError):
+            load_matrix_dcp(model, d, optimizer=opt, no_dist=True)
+        load_matrix_dcp(model, d, optimizer=opt, allow_reshard=True, no_dist=True)
+        expected = torch.load(os.path.join(d, "expected_full.pt"))
+        got = get_model_state_dict(model, options=MatrixStateDictOptions(full_state_dict=True))
+        for k, v in expected.items():
+            assert torch.equal(got[k], v), k            # bitwise
+        g = torch.Generator().manual_seed(11)
+        for _ in range(2):
+            torch.randn(3, 6, generator=g)
+        model(torch.randn(3, 6, generator=g)).pow(2).mean().backward()
+        opt.step()
+        after = torch.load(os.path.join(d, "expected_after.pt"))
+        got = get_model_state_dict(model, options=MatrixStateDictOptions(full_state_dict=True))
+        for k, v in after.items():
+            assert torch.allclose(got[k], v, atol=1e-5), k   # optimizer state came across too
