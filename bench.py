@@ -270,6 +270,12 @@ def main() -> None:
     sync()
     final_loss = float(last.item())
     peak_mb = torch.cuda.max_memory_allocated() / 2 ** 20 if cuda else 0.0
+    symmetric_mb = 0.0
+    if args.impl == "ours" and world > 1 and cuda:
+        from matrix_fsdp_b200.parallel.peer import PeerContext
+
+        symmetric_mb = PeerContext.symmetric_bytes / 2 ** 20   # cudaMalloc'd outside torch's allocator
+        peak_mb += symmetric_mb
 
     # ---- end-to-end region (public train_step semantics: H2D each step, D2H loss read each step)
     for i in range(min(3, args.steps)):
@@ -294,7 +300,7 @@ def main() -> None:
         "metric": "tokens_per_s_per_box", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids; random-init N(0,0.02) weights",
-        "impl": args.impl, "peak_mb": peak_mb, "final_loss": final_loss,
+        "impl": args.impl, "peak_mb": peak_mb, "symmetric_mb": symmetric_mb, "final_loss": final_loss,
         "config": {"model": cfg["model"], "global_batch": B * world, "micro_batch_per_gpu": B, "seq_len": S,
                    "parallelism": f"dp_shard{world}", "optimizer": cfg["optimizer"],
                    "precision": "bf16 params+compute, fp32 master weights and optimizer state",

@@ -96,7 +96,8 @@ class MatrixFlatBuffer:
             MatrixShard((0,), shard_sizes_to_matrix_local_units(layout.shard_sizes)) if compat.compatible else None)
 
         # ---- local shard: copy only the owned pieces out of the original parameters
-        self.local_shard = transport.alloc_persistent(self.local_numel, self.shard_dtype, self.device, "shard") \
+        self.local_shard = transport.alloc_persistent(self.local_numel, self.shard_dtype, self.device, "shard",
+                                                      symmetric_numel=self.tables.max_shard) \
             if not self.mixed else torch.empty(self.local_numel, dtype=self.shard_dtype, device=self.device)
         self.pieces: dict[str, LocalParamPiece] = {}
         with torch.no_grad():
@@ -114,7 +115,8 @@ class MatrixFlatBuffer:
         self.local_shard_lp: torch.Tensor | None = None
         self.lp_stale = True
         if self.mixed:
-            self.local_shard_lp = transport.alloc_persistent(self.local_numel, self.param_dtype, self.device, "shard_lp")
+            self.local_shard_lp = transport.alloc_persistent(self.local_numel, self.param_dtype, self.device, "shard_lp",
+                                                             symmetric_numel=self.tables.max_shard)
 
         # ---- aliasing: a single rank that holds the whole space in flat order needs no gather copy
         segs = self.tables.my_segments

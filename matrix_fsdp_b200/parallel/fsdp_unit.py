@@ -244,8 +244,11 @@ class MatrixFSDPParamGroup:
         if self.planner is not None:
             plan = self.planner(registry.total_numel, world)
             return planner_result_from_output(getattr(self.planner, "__name__", "planner"), plan, params, world)
-        return planner_result_from_output("contiguous_even_plan", contiguous_even_plan(registry.total_numel, world),
-                                          params, world)
+        # on CUDA every shard boundary sits on a 16-byte boundary of the bf16 wire format so the peer
+        # kernels (and TMA) can address any rank's shard with full-width vector accesses
+        align = 8 if registry[0].device.type == "cuda" and registry.total_numel >= 64 * world else 1
+        return planner_result_from_output("contiguous_even_plan",
+                                          contiguous_even_plan(registry.total_numel, world, align=align), params, world)
 
     def _flat_reorder(self, registry: ManagedParamRegistry, result: PlannerResult) -> PlannerResult:
         """Re-lay the flat space rank-major so a whole-param owner layout becomes rank-contiguous."""

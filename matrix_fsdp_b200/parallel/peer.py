@@ -1,0 +1,386 @@
+"""Peer-memory transport: FSDP collectives as hand-written kernels over IPC-mapped peer buffers.
+
+One :class:`PeerContext` per (process group, device) owns *symmetric* memory: every rank performs
+the same sequence of allocations, shares each segment through CUDA IPC, and maps all peers'
+segments once.  :class:`PeerTransport` then implements the transport interface on top of it:
+
+``gather``   publish "my shard for this unit is ready (epoch e)" → wait for every peer's flag →
+             ``ag_pull`` copies each peer's segments from its shard buffer straight into the local
+             full-parameter buffer (no padding, no staging, any layout);
+``reduce``   publish "my gradients for this unit are complete" → wait for peers →
+             ``rs_pull_reduce`` sums the owned segments across all ranks' gradient buffers in fp32,
+             applies the 1/world scale and writes the local gradient shard → publish "pulled" so
+             owners may reuse their gradient buffers.
+
+Gradient buffers come from a small ring of symmetric slots per size class; a slot is handed to the
+next unit only after every peer has published "pulled" for its previous user.  All waits are
+bounded (``MFSDP_PEER_WAIT_TIMEOUT_S``) and report through the device status word.
+
+The reference's closest analogue is its optional NCCL send/recv + per-call window registration
+path (``matrix_fsdp/kernels/native/matrix_nccl.cpp:176-395``, ``kernels/gin/native/rma_nccl.cpp:
+104-195``), which its own gap analysis lists as lacking persistent symmetric buffers
+(``docs/deepep_v2_gap_analysis.md:59-236``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+
+from ..ops import lib as _lib
+from .collectives import MatrixCollectiveHandle, SegmentTables
+from .transport import LocalTransport
+
+_u64, _vp, _i32, _i64 = C.c_ulonglong, C.c_void_p, C.c_int, C.c_longlong
+_lib.register_signatures({
+    "mfsdp_dev_malloc": [_u64, C.POINTER(C.c_void_p)],
+    "mfsdp_dev_free": [_vp],
+    "mfsdp_ipc_get_handle": [_vp, C.c_char_p],
+    "mfsdp_ipc_open_handle": [C.c_char_p, C.POINTER(C.c_void_p)],
+    "mfsdp_ipc_close_handle": [_vp],
+    "mfsdp_can_access_peer": [_i32, _i32],
+    "mfsdp_peer_signal": [C.POINTER(_u64), _i32, _u64, _vp],
+    "mfsdp_peer_wait": [_vp, _i32, _i32, _u64, _u64, _vp, _vp],
+    "mfsdp_ag_pull": [_vp, _vp, _vp, _vp, _i32, _i64, _i32, _vp],
+    "mfsdp_rs_pull_reduce": [C.POINTER(_u64), _i32, _i32, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32,
+                             C.c_float, _vp],
+})
+
+KIND_SHARD, KIND_GRAD, KIND_PULLED = 0, 1, 2
+MAX_UNITS = 2048
+SEGMENT_ENV = "MFSDP_PEER_SEGMENT_MB"
+TIMEOUT_ENV = "MFSDP_PEER_WAIT_TIMEOUT_S"
+RING_ENV = "MFSDP_PEER_GRAD_SLOTS"
+
+
+def _stream_handle(stream) -> int:
+    return (stream if stream is not None else torch.cuda.current_stream()).cuda_stream
+
+
+class SymBuffer:
+    """A symmetric allocation: the local tensor plus the address of the same bytes on every peer."""
+
+    __slots__ = ("tensor", "peer_addr", "nbytes")
+
+    def __init__(self, tensor: torch.Tensor, peer_addr: list[int], nbytes: int) -> None:
+        self.tensor, self.peer_addr, self.nbytes = tensor, peer_addr, nbytes
+
+
+class _RawDeviceMemory:
+    """Adapter exposing a raw device allocation through ``__cuda_array_interface__``."""
+
+    def __init__(self, ptr: int, nbytes: int) -> None:
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerContext:
+    symmetric_bytes = 0   # bytes of symmetric segments this process allocated (outside torch's allocator)
+
+    def __init__(self, group, device: torch.device) -> None:
+        self.group, self.device = group, device
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.lib = _lib.load(required=True)
+        self.segment_bytes = int(float(os.environ.get(SEGMENT_ENV, "512")) * 2 ** 20)
+        self._segments: list[dict] = []
+        self._opened: dict[bytes, int] = {}
+        self._by_ptr: dict[int, SymBuffer] = {}
+        self.timeout_ns = int(float(os.environ.get(TIMEOUT_ENV, "120")) * 1e9)
+        flags = self.alloc(MAX_UNITS * 3 * self.world * 8, zero=True)
+        self.flags = flags
+        self.flags_u64 = flags.tensor.view(torch.int64)
+        from ..ops import kernels
+
+        self.status = kernels.status_word(device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+
+    # ------------------------------------------------------------------ symmetric allocation
+    def _new_segment(self, min_bytes: int) -> dict:
+        nbytes = max(self.segment_bytes, (min_bytes + 4095) // 4096 * 4096)
+        raw = C.c_void_p()
+        rc = self.lib.mfsdp_dev_malloc(nbytes, C.byref(raw))
+        if rc != 0:
+            raise RuntimeError(f"cudaMalloc of a {nbytes >> 20} MiB symmetric segment failed with code {rc}")
+        t = torch.as_tensor(_RawDeviceMemory(int(raw.value), nbytes), device=self.device)
+        hbuf = C.create_string_buffer(64)
+        rc = self.lib.mfsdp_ipc_get_handle(raw, hbuf)
+        if rc != 0:
+            raise RuntimeError(f"cudaIpcGetMemHandle failed with code {rc}")
+        handle, offset = hbuf.raw, 0
+        PeerContext.symmetric_bytes += nbytes
+        gathered: list = [None] * self.world
+        dist.all_gather_object(gathered, (handle, offset, nbytes), group=self.group)
+        bases = []
+        for r, (h, off, nb) in enumerate(gathered):
+            if nb != nbytes:
+                raise RuntimeError("symmetric allocation sizes differ across ranks")
+            if r == self.rank:
+                bases.append(t.data_ptr())
+                continue
+            base = self._opened.get(h)
+            if base is None:
+                out = C.c_void_p()
+                rc = self.lib.mfsdp_ipc_open_handle(h, C.byref(out))
+                if rc != 0:
+                    raise RuntimeError(f"cudaIpcOpenMemHandle failed with code {rc}")
+                base = int(out.value)
+                self._opened[h] = base
+            bases.append(base + off)
+        seg = {"tensor": t, "bases": bases, "used": 0, "nbytes": nbytes}
+        self._segments.append(seg)
+        return seg
+
+    def alloc(self, nbytes: int, *, zero: bool = False, align: int = 256) -> SymBuffer:
+        """Collective: every rank must call with the same ``nbytes`` in the same order."""
+        nbytes = max(int(nbytes), 16)
+        seg = None
+        for s in self._segments:
+            start = (s["used"] + align - 1) // align * align
+            if start + nbytes <= s["nbytes"]:
+                seg = s
+                break
+        if seg is None:
+            seg = self._new_segment(nbytes)
+        start = (seg["used"] + align - 1) // align * align
+        seg["used"] = start + nbytes
+        view = seg["tensor"][start:start + nbytes]
+        if zero:
+            view.zero_()
+        buf = SymBuffer(view, [b + start for b in seg["bases"]], nbytes)
+        self._by_ptr[view.data_ptr()] = buf
+        return buf
+
+    def lookup(self, tensor: torch.Tensor) -> SymBuffer | None:
+        return self._by_ptr.get(tensor.data_ptr())
+
+    # ------------------------------------------------------------------ flags
+    def slot(self, unit_index: int, kind: int, src: int) -> int:
+        return (unit_index * 3 + kind) * self.world + src
+
+    def signal(self, unit_index: int, kind: int, value: int, stream) -> None:
+        """Write ``value`` into my slot of every rank's flag page (including my own)."""
+        idx = self.slot(unit_index, kind, self.rank)
+        arr = (_u64 * self.world)(*[self.flags.peer_addr[r] + idx * 8 for r in range(self.world)])
+        _lib.check(self.lib.mfsdp_peer_signal(arr, self.world, value, _stream_handle(stream)), "peer_signal")
+
+    def wait(self, unit_index: int, kind: int, value: int, stream) -> None:
+        """Wait until every rank's slot in my page reached ``value``."""
+        first = self.slot(unit_index, kind, 0)
+        _lib.check(self.lib.mfsdp_peer_wait(self.flags.tensor.data_ptr(), first, self.world, value, self.timeout_ns,
+                                            self.status.data_ptr(), _stream_handle(stream)), "peer_wait")
+
+
+class _Slot:
+    __slots__ = ("buf", "held", "last_unit", "last_epoch", "event")
+
+    def __init__(self, buf: SymBuffer) -> None:
+        self.buf, self.held, self.last_unit, self.last_epoch, self.event = buf, False, None, 0, None
+
+
+class PeerTransport(LocalTransport):
+    kind = "peer"
+    needs_symmetric_buffers = True
+    accumulates_fp32 = True
+
+    _transports: dict[tuple, "PeerTransport"] = {}
+
+    def __init__(self, ctx: PeerContext) -> None:
+        super().__init__()
+        self.ctx = ctx
+        self.group = ctx.group
+        self._unit_index: dict[str, int] = {}
+        self._epochs: dict[str, dict[str, int]] = {}
+        self._tables: dict[tuple, dict] = {}
+        self._rings: dict[int, list[_Slot]] = {}
+        self._slot_of_ptr: dict[int, _Slot] = {}
+        self.max_slots = int(os.environ.get(RING_ENV, "3"))
+        self.launches = 0
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def create(cls, group, device: torch.device) -> "PeerTransport | None":
+        if device.type != "cuda" or not _lib.available() or _lib.disabled_by_env():
+            return None
+        # one transport per (group, device): units index one shared flag page, so they must share the
+        # unit numbering, the epoch counters and the gradient-slot ring
+        key = (id(group), device.index)
+        if key in cls._transports:
+            return cls._transports[key]
+        world = dist.get_world_size(group)
+        if world > 16:
+            return None
+        hosts: list = [None] * world
+        dist.all_gather_object(hosts, (socket.gethostname(), torch.cuda.current_device()), group=group)
+        if len({h for h, _ in hosts}) != 1:
+            return None
+        lib = _lib.load(required=True)
+        me = torch.cuda.current_device()
+        ok = all(d == me or lib.mfsdp_can_access_peer(me, d) for _, d in hosts)
+        flags: list = [None] * world
+        dist.all_gather_object(flags, bool(ok), group=group)
+        if not all(flags):
+            return None
+        ctx = PeerContext(group, device)
+        transport = cls(ctx)
+        cls._transports[key] = transport
+        return transport
+
+    def _unit(self, unit_key: str) -> int:
+        idx = self._unit_index.get(unit_key)
+        if idx is None:
+            idx = len(self._unit_index)
+            if idx >= MAX_UNITS:
+                raise RuntimeError("too many FSDP units for the peer flag page")
+            self._unit_index[unit_key] = idx
+            self._epochs[unit_key] = {"shard": 0, "grad": 0}
+        return idx
+
+    # ------------------------------------------------------------------ allocation hooks
+    def alloc_persistent(self, numel: int, dtype: torch.dtype, device: torch.device, tag: str = "",
+                         symmetric_numel: int | None = None) -> torch.Tensor:
+        es = torch.empty((), dtype=dtype).element_size()
+        buf = self.ctx.alloc(max(symmetric_numel or numel, 1) * es)
+        t = buf.tensor.view(dtype)[:numel]
+        self.ctx._by_ptr[t.data_ptr()] = buf
+        return t
+
+    def acquire_grad_buffer(self, unit_key, numel: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+        es = torch.empty((), dtype=dtype).element_size()
+        nbytes = numel * es
+        ring = self._rings.setdefault(nbytes, [])
+        slot = next((s for s in ring if not s.held and s.last_unit == unit_key), None)
+        if slot is None and len(ring) < self.max_slots:
+            slot = _Slot(self.ctx.alloc(nbytes))
+            ring.append(slot)
+        if slot is None:
+            free = [s for s in ring if not s.held]
+            slot = min(free, key=lambda s: s.last_epoch) if free else None
+        if slot is None:
+            slot = _Slot(self.ctx.alloc(nbytes))
+            ring.append(slot)
+        if slot.last_unit is not None and slot.last_epoch > 0:
+            # every peer must have finished pulling the previous user's gradients out of this slot;
+            # this GPU's own pull is ordered by a stream event, so the spin only ever waits on other GPUs
+            if slot.event is not None:
+                torch.cuda.current_stream().wait_event(slot.event)
+            self.ctx.wait(self._unit(slot.last_unit), KIND_PULLED, slot.last_epoch, None)
+            self.launches += 1
+        slot.held = True
+        slot.last_unit = unit_key
+        t = slot.buf.tensor.view(dtype)[:numel]
+        self._slot_of_ptr[t.data_ptr()] = slot
+        return t
+
+    def release_grad_buffer(self, unit_key, buf: torch.Tensor) -> None:
+        slot = self._slot_of_ptr.get(buf.data_ptr())
+        if slot is not None:
+            slot.held = False
+
+    # ------------------------------------------------------------------ gather
+    def _gather_tables(self, unit_key, shard_buf: SymBuffer, tables: SegmentTables, es: int, device) -> dict:
+        key = ("ag", unit_key, shard_buf.tensor.data_ptr())
+        t = self._tables.get(key)
+        if t is None:
+            src, dst, ln = [], [], []
+            for r, segs in enumerate(tables.rank_segments):
+                for s in segs:
+                    src.append(shard_buf.peer_addr[r] + s.local_start * es)
+                    dst.append(s.global_start)
+                    ln.append(s.numel)
+            # order so that the local rank's own segments come first (they need no NVLink traffic)
+            t = {"src": torch.tensor(src, dtype=torch.int64, device=device),
+                 "dst": torch.tensor(dst, dtype=torch.int64, device=device),
+                 "len": torch.tensor(ln, dtype=torch.int64, device=device), "n": len(src), "max": max(ln, default=0)}
+            self._tables[key] = t
+        return t
+
+    def gather(self, shard, full, tables: SegmentTables, *, stream=None, unit_key=None) -> MatrixCollectiveHandle:
+        buf = self.ctx.lookup(shard)
+        if buf is None:
+            raise RuntimeError("peer gather needs a shard that lives in symmetric memory")
+        ui = self._unit(unit_key)
+        ep = self._epochs[unit_key]
+        ep["shard"] += 1
+        e = ep["shard"]
+        es = full.element_size()
+        t = self._gather_tables(unit_key, buf, tables, es, full.device)
+        cur = torch.cuda.current_stream()
+        run = stream if stream is not None else cur
+        if stream is not None:
+            stream.wait_stream(cur)
+        self.ctx.signal(ui, KIND_SHARD, e, run)
+        self.ctx.wait(ui, KIND_SHARD, e, run)
+        _lib.check(self.ctx.lib.mfsdp_ag_pull(full.data_ptr(), t["src"].data_ptr(), t["dst"].data_ptr(),
+                                              t["len"].data_ptr(), t["n"], t["max"], es, run.cuda_stream), "ag_pull")
+        self.launches += 3
+        ev = None
+        if stream is not None:
+            ev = torch.cuda.Event()
+            ev.record(stream)
+        return MatrixCollectiveHandle(event=ev, info={
+            "kind": "all_gather", "impl": "ag_pull", "backend": self.kind, "bytes": full.numel() * es, "count": 1,
+            "sync_mode": "stream_event" if stream is not None else "stream_order"})
+
+    # ------------------------------------------------------------------ reduce
+    def _reduce_tables(self, unit_key, tables: SegmentTables, device) -> dict:
+        key = ("rs", unit_key)
+        t = self._tables.get(key)
+        if t is None:
+            segs = tables.my_segments
+            t = {"g": torch.tensor([s.global_start for s in segs], dtype=torch.int64, device=device),
+                 "l": torch.tensor([s.local_start for s in segs], dtype=torch.int64, device=device),
+                 "len": torch.tensor([s.numel for s in segs], dtype=torch.int64, device=device), "n": len(segs),
+                 "max": max((s.numel for s in segs), default=0)}
+            self._tables[key] = t
+        return t
+
+    def reduce(self, full_grad, out_shard, tables: SegmentTables, *, scale=None, stream=None, unit_key=None,
+               accumulate: bool = False) -> MatrixCollectiveHandle:
+        buf = self.ctx.lookup(full_grad)
+        if buf is None:
+            raise RuntimeError("peer reduce needs a gradient buffer from acquire_grad_buffer()")
+        if full_grad.dtype not in (torch.bfloat16, torch.float32) or out_shard.dtype not in (torch.bfloat16, torch.float32):
+            raise TypeError("peer reduce supports bf16 / fp32 gradients")
+        ui = self._unit(unit_key)
+        ep = self._epochs[unit_key]
+        ep["grad"] += 1
+        e = ep["grad"]
+        slot = self._slot_of_ptr.get(full_grad.data_ptr())
+        if slot is not None:
+            slot.last_epoch = e
+        t = self._reduce_tables(unit_key, tables, full_grad.device)
+        cur = torch.cuda.current_stream()
+        run = stream if stream is not None else cur
+        if stream is not None:
+            stream.wait_stream(cur)
+        ctx = self.ctx
+        ctx.signal(ui, KIND_GRAD, e, run)
+        ctx.wait(ui, KIND_GRAD, e, run)
+        ptrs = (_u64 * ctx.world)(*buf.peer_addr)
+        _lib.check(ctx.lib.mfsdp_rs_pull_reduce(
+            ptrs, ctx.world, ctx.rank, out_shard.data_ptr(), t["g"].data_ptr(), t["l"].data_ptr(),
+            t["len"].data_ptr(), t["n"], t["max"], int(full_grad.dtype == torch.bfloat16),
+            int(out_shard.dtype == torch.bfloat16), int(accumulate), float(1.0 if scale is None else scale),
+            run.cuda_stream), "rs_pull_reduce")
+        ctx.signal(ui, KIND_PULLED, e, run)
+        self.launches += 4
+        ev = torch.cuda.Event()
+        ev.record(run)
+        if slot is not None:
+            slot.event = ev
+        if stream is None:
+            ev = None
+        return MatrixCollectiveHandle(event=ev, info={
+            "kind": "reduce_scatter", "impl": "rs_pull_reduce", "backend": self.kind,
+            "bytes": full_grad.numel() * full_grad.element_size(), "count": 1,
+            "sync_mode": "stream_event" if stream is not None else "stream_order"})
+
+    def check_health(self) -> None:
+        """Raise if any bounded wait on this device ran out (reads the status word: a device sync)."""
+        from ..ops import kernels
+
+        kernels.check_status(self.ctx.device)

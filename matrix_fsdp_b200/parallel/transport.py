@@ -38,7 +38,8 @@ class LocalTransport:
     def __init__(self) -> None:
         self.group = None
 
-    def alloc_persistent(self, numel: int, dtype: torch.dtype, device: torch.device, tag: str = "") -> torch.Tensor:
+    def alloc_persistent(self, numel: int, dtype: torch.dtype, device: torch.device, tag: str = "",
+                         symmetric_numel: int | None = None) -> torch.Tensor:
         return torch.empty(numel, dtype=dtype, device=device)
 
     def acquire_grad_buffer(self, unit_key, numel: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:

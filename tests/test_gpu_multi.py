@@ -1,0 +1,169 @@
+"""Peer-memory transport on 2+ GPUs: kernels against torch math, sharded training against NCCL path,
+and the bounded-wait status path (a flag that nothing sets)."""
+import os
+import tempfile
+import traceback
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _entry(rank, world, fn, init_file, err_dir, args):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    try:
+        dist.init_process_group("nccl", init_method=f"file://{init_file}", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", rank))
+        fn(rank, world, *args)
+        torch.cuda.synchronize()
+        dist.barrier()
+    except Exception:
+        with open(os.path.join(err_dir, f"rank{rank}.err"), "w") as f:
+            f.write(traceback.format_exc())
+        raise
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def _run(fn, world, *args):
+    import torch.multiprocessing as mp
+
+    with tempfile.TemporaryDirectory() as tmp:
+        try:
+            mp.spawn(_entry, args=(world, fn, os.path.join(tmp, "rdzv"), tmp, args), nprocs=world, join=True)
+        except Exception as exc:
+            msgs = [open(os.path.join(tmp, f)).read() for f in sorted(os.listdir(tmp)) if f.endswith(".err")]
+            raise AssertionError("\n".join(msgs) or str(exc)) from None
+
+
+def _peer_collectives(rank, world):
+    import torch.distributed as dist
+
+    from matrix_fsdp_b200.core.layout import LayoutSegment as S
+    from matrix_fsdp_b200.parallel.collectives import SegmentTables
+    from matrix_fsdp_b200.parallel.peer import PeerTransport
+
+    dev = torch.device("cuda", rank)
+    tr = PeerTransport.create(dist.group.WORLD, dev)
+    assert tr is not None, "peer transport unavailable on this box"
+    # uneven, multi-segment layout over `world` ranks; total 100_003 elements (odd, exercises scalar tails)
+    total = 100_003
+    cuts = [0] + [total * (i + 1) // (2 * world) + (7 if i % 2 else 0) for i in range(2 * world - 1)] + [total]
+    per_rank = [[] for _ in range(world)]
+    local = [0] * world
+    for i in range(2 * world):
+        r = i % world
+        per_rank[r].append(S(cuts[i], cuts[i + 1], local[r]))
+        local[r] += cuts[i + 1] - cuts[i]
+    tables = SegmentTables.build(total, per_rank, rank)
+    torch.manual_seed(0)
+    ref_full = torch.randn(total, device=dev).bfloat16()
+    shard = tr.alloc_persistent(tables.shard_sizes[rank], torch.bfloat16, dev, "shard", symmetric_numel=tables.max_shard)
+    for s in tables.my_segments:
+        shard[s.local_start:s.local_end].copy_(ref_full[s.global_start:s.global_end])
+    full = torch.full((total,), float("nan"), device=dev, dtype=torch.bfloat16)
+    side = torch.cuda.Stream()
+    for _ in range(3):   # epochs advance; repeated use must keep working
+        full.fill_(float("nan"))
+        tr.gather(shard, full, tables, stream=side, unit_key="u0").wait()
+        assert torch.equal(full, ref_full)
+    # reduce-scatter: each rank contributes rank-dependent gradients
+    for it in range(3):
+        g = tr.acquire_grad_buffer("u0", total, torch.bfloat16, dev)
+        torch.manual_seed(100 + it)
+        base = torch.randn(total, device=dev)
+        g.copy_((base * (rank + 1)).bfloat16())
+        out = torch.zeros(tables.shard_sizes[rank], device=dev)
+        tr.reduce(g, out, tables, scale=1.0 / world, stream=side, unit_key="u0").wait()
+        tr.release_grad_buffer("u0", g)
+        expect_full = sum((base * (r + 1)).bfloat16().float() for r in range(world)) / world
+        for s in tables.my_segments:
+            assert torch.allclose(out[s.local_start:s.local_end], expect_full[s.global_start:s.global_end],
+                                  atol=1e-5, rtol=1e-5)
+    tr.check_health()
+
+
+def _train(rank, world, transport_kind):
+    import torch.distributed as dist
+    from torch.distributed.fsdp import MixedPrecisionPolicy
+
+    from matrix_fsdp_b200.api import reset_shared_owner_planners
+    from matrix_fsdp_b200.models.llama import LlamaConfig, LlamaModel, shard_llama
+    from matrix_fsdp_b200.optim import configure_optimizer
+    from matrix_fsdp_b200.parallel.unit_collection import collect_param_groups
+
+    os.environ["MFSDP_TRANSPORT"] = transport_kind
+    reset_shared_owner_planners()
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=1024, hidden=256, n_layers=3, n_heads=2, head_dim=128, ffn=688)
+    model = LlamaModel(cfg).cuda()
+    shard_llama(model, mp_policy=MixedPrecisionPolicy(param_dtype=torch.bfloat16))
+    kinds = {u.flat_buffer.transport.kind for u in collect_param_groups(model)}
+    assert kinds == {transport_kind}, kinds
+    opt = configure_optimizer(model, "adamw", lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
+    g = torch.Generator().manual_seed(5 + rank)
+    losses = []
+    for _ in range(4):
+        tok = torch.randint(0, 1024, (2, 65), generator=g).cuda()
+        loss = model(tok[:, :-1], tok[:, 1:])
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        losses.append(loss.item())
+    from matrix_fsdp_b200.ops import kernels as K
+
+    K.check_status()
+    shards = torch.cat([u.flat_buffer.local_shard.float().cpu() for u in collect_param_groups(model)])
+    return losses, shards
+
+
+def _train_both(rank, world, out_dir):
+    l_peer, s_peer = _train(rank, world, "peer")
+    l_nccl, s_nccl = _train(rank, world, "torch_dist")
+    for a, b in zip(l_peer, l_nccl):
+        assert abs(a - b) < 2e-2 * abs(b), (l_peer, l_nccl)
+    rel = ((s_peer - s_nccl).norm() / s_nccl.norm()).item()
+    assert rel < 2e-3, rel
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_peer_collectives_match_torch():
+    _run(_peer_collectives, min(_ngpu(), 4))
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_sharded_training_peer_vs_nccl():
+    with tempfile.TemporaryDirectory() as d:
+        _run(_train_both, 2, d)
+
+
+def test_bounded_wait_reports_timeout_instead_of_hanging():
+    """A wait on a flag that nothing sets ends after its budget with status 2; the context stays usable."""
+    from matrix_fsdp_b200.ops import kernels as K
+    from matrix_fsdp_b200.ops import lib
+    import matrix_fsdp_b200.parallel.peer  # noqa: F401  (registers the launcher signatures)
+
+    L = lib.load(required=True)
+    flags = torch.zeros(8, dtype=torch.int64, device="cuda")
+    status = K.status_word()
+    status.zero_()
+    rc = L.mfsdp_peer_wait(flags.data_ptr(), 0, 4, 1, int(0.2e9), status.data_ptr(),
+                           torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 2
+    with pytest.raises(RuntimeError, match="peer flag wait timed out"):
+        K.check_status()
+    assert int(status.item()) == 0
+    # the device still works
+    assert torch.ones(4, device="cuda").sum().item() == 4.0
