@@ -705,3 +705,47 @@ MFSDP_API int mfsdp_cast_f32_bf16(const float* src, void* dst, long long n, cuda
   cast_f32_bf16_kernel<<<grid_for(n / 4 + 1, 256, 148 * 8), 256, 0, st>>>(src, (__nv_bfloat16*)dst, n);
   return (int)cudaGetLastError();
 }
+
+// ============================================================== allocation-free RMSNorm backward
+// Declared and documented in mfsdp_noalloc.h.  The weight-gradient partial sums go to a device
+// array that is part of the library image instead of a caller-provided buffer.  In host code the
+// array's name is only a handle for the runtime, so its device address is looked up once per device
+// with cudaGetSymbolAddress and that pointer is what the kernels receive.
+#include "mfsdp_noalloc.h"
+
+namespace mfsdp {
+static __device__ __align__(256) float g_noalloc_dw_scratch[MFSDP_NOALLOC_SCRATCH_ROWS * MFSDP_NOALLOC_MAX_HIDDEN];
+constexpr int kNoAllocMaxDevices = 64;
+static float* g_noalloc_scratch_addr[kNoAllocMaxDevices] = {nullptr};
+}  // namespace mfsdp
+
+MFSDP_API int mfsdp_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
+                                        const void* dres, void* dx, void* dw, int accumulate_dw, long long rows,
+                                        int H, cudaStream_t st) {
+  if (rows <= 0 || H <= 0 || H % 8 || H > MFSDP_NOALLOC_MAX_HIDDEN) return -2;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return -2;
+  float* scratch = g_noalloc_scratch_addr[dev];
+  if (scratch == nullptr) {
+    // set-up, once per device, with that device current
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_dw_scratch);
+    if (e != cudaSuccess) return (int)e;
+    scratch = static_cast<float*>(p);
+    g_noalloc_scratch_addr[dev] = scratch;
+  }
+  const int nvec = H / 8;
+  const int threads = 256;
+  const int vpt = (nvec + threads - 1) / threads;
+  const int grid = (int)(rows < MFSDP_NOALLOC_SCRATCH_ROWS ? rows : MFSDP_NOALLOC_SCRATCH_ROWS);
+  auto DY = (const __nv_bfloat16*)dy; auto X = (const __nv_bfloat16*)x; auto W = (const __nv_bfloat16*)w;
+  auto DR = (const __nv_bfloat16*)dres; auto DX = (__nv_bfloat16*)dx;
+  if (vpt <= 1) rmsnorm_bwd_kernel<1><<<grid, threads, 0, st>>>(DY, X, W, rstd, DR, DX, scratch, rows, H);
+  else if (vpt <= 2) rmsnorm_bwd_kernel<2><<<grid, threads, 0, st>>>(DY, X, W, rstd, DR, DX, scratch, rows, H);
+  else if (vpt <= 4) rmsnorm_bwd_kernel<4><<<grid, threads, 0, st>>>(DY, X, W, rstd, DR, DX, scratch, rows, H);
+  else return -2;
+  if (dw) colsum_f32_to_bf16_kernel<<<(H + 31) / 32, dim3(32, 8), 0, st>>>(scratch, (__nv_bfloat16*)dw, grid, H, accumulate_dw);
+  return (int)cudaGetLastError();
+}
