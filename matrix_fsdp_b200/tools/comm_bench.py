@@ -1,0 +1,111 @@
+"""Micro-benchmark of the all-gather / reduce-scatter transports.
+
+    python -m torch.distributed.run --nproc-per-node N -m matrix_fsdp_b200.tools.comm_bench \
+        --numel 50000000 --layout even|owner --iters 20
+
+Times each transport (peer kernels, NCCL equal/padded, owner broadcast) with CUDA events on the
+launching stream after warm-up, takes the max over ranks and reports logical bus bandwidth
+(bytes every rank must receive ÷ time) and the fraction of the measured NVLink peer-copy rate.
+
+Parity: ``matrix_fsdp/tools/comm_bench.py:1-224``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..core.layout import LayoutSegment
+from ..parallel.collectives import SegmentTables
+from ..parallel.transport import TorchDistTransport
+
+NVLINK_PEER_GBS = 770.0   # measured per-direction peer copy on this pool
+
+
+def make_tables(total: int, world: int, rank: int, layout: str) -> SegmentTables:
+    if layout == "even":
+        per = (total // world) // 8 * 8
+        sizes = [per] * world
+        sizes[-1] += total - per * world
+    else:  # owner-like: alternating big / small chunks
+        weights = [3 if r % 2 == 0 else 1 for r in range(world)]
+        unit = total // sum(weights) // 8 * 8
+        sizes = [w * unit for w in weights]
+        sizes[-1] += total - sum(sizes)
+    segs, cur = [], 0
+    for s in sizes:
+        segs.append((LayoutSegment(cur, cur + s, 0),))
+        cur += s
+    return SegmentTables.build(total, segs, rank)
+
+
+def time_op(fn, iters: int, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--numel", type=int, default=50_593_792)   # one Llama-2048 block
+    ap.add_argument("--layout", choices=("even", "owner"), default="even")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--out", default=None)
+    args = ap.parse_args(argv)
+    rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    world, dev = dist.get_world_size(), torch.device("cuda", rank)
+    tables = make_tables(args.numel, world, dist.get_rank(), args.layout)
+    n_local = tables.shard_sizes[dist.get_rank()]
+    results = []
+    transports = {"nccl_auto": TorchDistTransport(dist.group.WORLD),
+                  "nccl_owner_broadcast": TorchDistTransport(dist.group.WORLD, gather_impl="owner_broadcast",
+                                                             reduce_impl="owner_reduce")}
+    from ..parallel.peer import PeerTransport
+
+    peer = PeerTransport.create(dist.group.WORLD, dev)
+    if peer is not None:
+        transports = {"peer": peer, **transports}
+    full = torch.empty(args.numel, dtype=torch.bfloat16, device=dev)
+    for name, tr in transports.items():
+        shard = tr.alloc_persistent(n_local, torch.bfloat16, dev, "shard", symmetric_numel=tables.max_shard)
+        shard.normal_()
+        grad = tr.acquire_grad_buffer(f"bench_{name}", args.numel, torch.bfloat16, dev)
+        grad.normal_()
+        out = torch.empty(n_local, dtype=torch.float32 if name == "peer" else torch.bfloat16, device=dev)
+        key = f"bench_{name}"
+        ag = time_op(lambda: tr.gather(shard, full, tables, unit_key=key).wait(), args.iters)
+        rs = time_op(lambda: tr.reduce(grad, out, tables, scale=1.0 / world, unit_key=key).wait(), args.iters)
+        recv_bytes = (args.numel - n_local) * 2
+        for op, ms in (("all_gather", ag), ("reduce_scatter", rs)):
+            gbs = recv_bytes / (ms * 1e-3) / 1e9
+            results.append({"transport": name, "op": op, "ms": ms, "recv_gb_per_s": gbs,
+                            "frac_of_measured_nvlink_770": gbs / NVLINK_PEER_GBS})
+    if dist.get_rank() == 0:
+        for r in results:
+            print(json.dumps(r))
+        if args.out:
+            with open(args.out, "w") as f:
+                json.dump({"world": world, "numel": args.numel, "layout": args.layout, "results": results}, f, indent=1)
+    dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
