@@ -126,6 +126,8 @@ class MatrixFSDPScheduler:
         self._index = {id(u): i for i, u in enumerate(self.units)}
         self.counters = SchedulerCounters()
         self.post_forward_order: list = []
+        self.forward_order: list = []
+        self._pre_forward_seen: list = []
         self._active: dict[int, object] = {}
         self._pending_reduces: list = []
         self._post_optimizer_event = None
@@ -197,10 +199,15 @@ class MatrixFSDPScheduler:
         self.counters.unshard_waits += 1
         if not unit.forward_prefetch:
             return
-        i = self._index[id(unit)]
+        if unit not in self._pre_forward_seen:
+            self._pre_forward_seen.append(unit)
+        # construction order on the first iteration, afterwards the order forwards actually ran in
+        # (a root unit that wraps the blocks is built last but runs first)
+        order = self.forward_order if (self.forward_order and unit in self.forward_order) else self.units
+        i = order.index(unit)
         budget = self._fwd_budget()
         issued = 0
-        for nxt in self.units[i + 1:]:
+        for nxt in order[i + 1:]:
             if issued >= budget:
                 if budget == 0:
                     self.counters.prefetch_blocked_by_budget += 1
@@ -286,6 +293,9 @@ class MatrixFSDPScheduler:
         self.finish_backward_iteration()
 
     def finish_backward_iteration(self) -> None:
+        if self._pre_forward_seen:
+            self.forward_order = list(self._pre_forward_seen)
+        self._pre_forward_seen = []
         self.post_forward_order.clear()
         self.counters.iterations += 1
 

@@ -36,11 +36,11 @@ def _time(fns, iters: int = 20, warmup: int = 3) -> float:
     return e0.elapsed_time(e1) / iters
 
 
-def bench_gemm(small: bool):
+def bench_gemm(small: bool, shape=None):
     from ..ops import kernels as K
 
     hbm, tf, src = _peaks()
-    shapes = [(1024, 1024, 1024)] if small else [
+    shapes = [tuple(shape)] if shape else [(1024, 1024, 1024)] if small else [
         (4096, 6144, 2048), (4096, 2048, 2048), (4096, 11008, 2048), (4096, 2048, 5504), (4096, 32000, 2048),
         (8192, 8192, 8192), (4096, 12288, 4096), (4096, 4096, 11008)]
     rows = []
@@ -125,8 +125,12 @@ def main(argv=None) -> int:
     ap.add_argument("--what", choices=("gemm", "elementwise", "muon"), default="gemm")
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--out", default=None)
+    ap.add_argument("--shape", type=int, nargs=3, default=None, metavar=("M", "N", "K"))
     args = ap.parse_args(argv)
-    rows = {"gemm": bench_gemm, "elementwise": bench_elementwise, "muon": bench_muon}[args.what](args.small)
+    if args.what == "gemm":
+        rows = bench_gemm(args.small, args.shape)
+    else:
+        rows = {"elementwise": bench_elementwise, "muon": bench_muon}[args.what](args.small)
     if args.out:
         with open(args.out, "w") as f:
             json.dump(rows, f, indent=1)
