@@ -80,11 +80,13 @@ def attention_bwd(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, lse:
     _check_qkv(qkv, batch, seq, n_heads, head_dim)
     scale = 1.0 / math.sqrt(head_dim) if softmax_scale is None else float(softmax_scale)
     dout = dout.contiguous()
+    out = out if out.stride(0) == dout.stride(0) else out.contiguous()
     dqkv = torch.empty_like(qkv, memory_format=torch.contiguous_format)
+    scratch = torch.empty(2 * batch * n_heads * seq, dtype=torch.float32, device=qkv.device)
     status = K.status_word(qkv.device)
     lib = _lib.load()
     _lib.check(lib.mfsdp_attention_bwd(dout.data_ptr(), qkv.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                                       dqkv.data_ptr(), None, batch, seq, n_heads, qkv.stride(0), out.stride(0),
+                                       dqkv.data_ptr(), scratch.data_ptr(), batch, seq, n_heads, qkv.stride(0), dout.stride(0),
                                        dqkv.stride(0), scale, status.data_ptr(),
                                        torch.cuda.current_stream(qkv.device).cuda_stream),
                "mfsdp_attention_bwd")

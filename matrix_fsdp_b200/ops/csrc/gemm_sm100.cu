@@ -425,7 +425,7 @@ MFSDP_API int mfsdp_gemm_bf16(const void* A, const void* B, void* D, const void*
       const long long waves = (t + num_sms - 1) / num_sms;
       const double padded_n = (double)((N + b - 1) / b) * b;
       return ((double)t / (double)(waves * num_sms)) * ((double)N / padded_n) *
-             (b == 256 ? 1.0 : 0.88);
+             (b == 256 ? 1.0 : 0.72);
     };
     bn = eff(256) >= eff(128) ? 256 : 128;
   }

@@ -82,7 +82,7 @@ def available() -> bool:
 
 
 # kernels launched per launcher call (default 1); the counter feeds the benchmark's launch report
-_KERNELS_PER_CALL = {"rmsnorm_bwd": 2}
+_KERNELS_PER_CALL = {"rmsnorm_bwd": 2, "mfsdp_attention_bwd": 3}
 _LAUNCH_COUNT = [0]
 
 

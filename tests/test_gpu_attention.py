@@ -52,3 +52,27 @@ def test_attention_fwd_large_scores_rescale():
     ref_o, ref_lse = _ref(qkv, B, S, nH, hd)
     assert (out.float() - ref_o).abs().max().item() < 4e-2
     assert (lse - ref_lse).abs().max().item() < 5e-3
+
+
+@pytest.mark.parametrize("B,S,nH", [(1, 128, 1), (2, 256, 2), (1, 1024, 2), (2, 384, 3), (1, 200, 2)])
+def test_attention_bwd_matches_fp32(B, S, nH):
+    from matrix_fsdp_b200.ops import attention as A
+    from matrix_fsdp_b200.ops import kernels as K
+
+    assert A.bwd_available(), "attention backward kernel missing from the kernel library"
+    torch.manual_seed(2)
+    hd = 128
+    qkv = torch.randn(B * S, 3 * nH * hd, device="cuda", dtype=torch.bfloat16)
+    dout = torch.randn(B * S, nH * hd, device="cuda", dtype=torch.bfloat16)
+    out, lse = A.attention_fwd(qkv, B, S, nH, hd)
+    dqkv = A.attention_bwd(dout, qkv, out, lse, B, S, nH, hd)
+    torch.cuda.synchronize()
+    K.check_status()
+    ref_in = qkv.float().requires_grad_(True)
+    ref_o, _ = _ref(ref_in, B, S, nH, hd)
+    (ref_g,) = torch.autograd.grad(ref_o, ref_in, dout.float())
+    assert torch.isfinite(dqkv).all()
+    err = (dqkv.float() - ref_g).abs().max().item()
+    assert err < 6e-2 * max(1.0, ref_g.abs().max().item() / 4), err
+    rel = (dqkv.float() - ref_g).norm() / ref_g.norm()
+    assert rel.item() < 2e-2, rel.item()
