@@ -117,7 +117,7 @@ class MatrixMuon(Optimizer):
                 loss = closure()
         for group in self.param_groups:
             for p in group["params"]:
-                if p.grad is None or p.numel() == 0:
+                if (p.grad is None and getattr(p, "_grad_override", None) is None) or p.numel() == 0:
                     continue
                 if p.ndim != 2:
                     raise ValueError("Muon only supports 2D parameters; route the rest to AdamW.")
@@ -132,7 +132,9 @@ class MatrixMuon(Optimizer):
         lr, wd, mu = float(group["lr"]), group["weight_decay"], group["momentum"]
         alr = adjust_lr(lr, group["adjust_lr_fn"], p.shape)
         lp = self._low_precision_of(p) if self._low_precision_of is not None else None
-        g = p.grad
+        g = getattr(p, "_grad_override", None)   # a gradient kept in another dtype (expert-parallel slices)
+        if g is None:
+            g = p.grad
         if _use_kernels(p) and p.dtype == torch.float32 and buf.dtype == torch.float32 and g.is_contiguous():
             from ..ops import kernels as K
 
