@@ -42,6 +42,15 @@ CONFIGS = {
     "3": dict(model="llama-32L-h4096-ffn11008-v32000", vocab_size=32000, hidden=4096, n_layers=32, n_heads=32,
               head_dim=128, ffn=11008, micro_batch=1, seq_len=4096, optimizer="mixed_muon_adamw", ac=True,
               lr=0.02, betas=(0.9, 0.95), weight_decay=0.1),
+    "4": dict(model="llama-40L-h5120-ffn13824-v32000", vocab_size=32000, hidden=5120, n_layers=40, n_heads=40,
+              head_dim=128, ffn=13824, micro_batch=1, seq_len=4096, optimizer="mixed_muon_adamw", ac=True,
+              lr=0.02, betas=(0.9, 0.95), weight_decay=0.1, hsdp_replicate=2),
+    "5": dict(model="moe-16L-h2048-e64x1408-top6-v32000", kind="moe", vocab_size=32000, hidden=2048, n_layers=16,
+              n_heads=16, head_dim=128, n_experts=64, expert_ffn=1408, top_k=6, micro_batch=2, seq_len=4096,
+              optimizer="mixed_muon_adamw", ac=False, lr=0.02, betas=(0.9, 0.95), weight_decay=0.1),
+    "5s": dict(model="moe-4L-h1024-e16x512-top2-v8192", kind="moe", vocab_size=8192, hidden=1024, n_layers=4,
+               n_heads=8, head_dim=128, n_experts=16, expert_ffn=512, top_k=2, micro_batch=2, seq_len=1024,
+               optimizer="mixed_muon_adamw", ac=False, lr=0.02, betas=(0.9, 0.95), weight_decay=0.1),
     "tiny": dict(model="llama-2L-h256-ffn688-v1024", vocab_size=1024, hidden=256, n_layers=2, n_heads=2,
                  head_dim=128, ffn=688, micro_batch=2, seq_len=128, optimizer="adamw", ac=False,
                  lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1),
@@ -106,8 +115,33 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------ builders
+def build_ours_moe(cfg: dict, device, mesh, world: int):
+    from torch.distributed.fsdp import MixedPrecisionPolicy
+
+    from matrix_fsdp_b200.models.moe import MoEConfig, MoEModel, configure_moe_optimizer, shard_moe
+
+    mcfg = MoEConfig(vocab_size=cfg["vocab_size"], hidden=cfg["hidden"], n_layers=cfg["n_layers"],
+                     n_heads=cfg["n_heads"], head_dim=cfg["head_dim"], n_experts=cfg["n_experts"],
+                     expert_ffn=cfg["expert_ffn"], top_k=cfg["top_k"], max_seq_len=cfg["seq_len"])
+    torch.manual_seed(0)
+    model = MoEModel(mcfg, ep_group=None if world > 1 else False, device=device, dtype=torch.bfloat16).to(device)
+    shard_moe(model, mesh=mesh, mp_policy=MixedPrecisionPolicy(param_dtype=torch.bfloat16),
+              optimizer_policy="mixed_muon_adamw")
+    opt = configure_moe_optimizer(model, "mixed_muon_adamw", muon_lr=cfg["lr"], adamw_lr=3e-4,
+                                  adamw_betas=cfg["betas"], weight_decay=cfg["weight_decay"], muon_momentum=0.95,
+                                  muon_ns_steps=5, muon_adjust_lr_fn="original")
+    from matrix_fsdp_b200.parallel.unit_collection import collect_param_groups
+
+    for u in collect_param_groups(model):
+        u.runtime_trace_enabled = False
+    return model, opt
+
+
 def build_ours(cfg: dict, device, mesh, world: int):
     from torch.distributed.fsdp import MixedPrecisionPolicy
+
+    if cfg.get("kind") == "moe":
+        return build_ours_moe(cfg, device, mesh, world)
 
     from matrix_fsdp_b200.models.llama import LlamaConfig, LlamaModel, shard_llama
     from matrix_fsdp_b200.optim import configure_optimizer
@@ -192,7 +226,12 @@ def main() -> None:
         dist.init_process_group("nccl" if cuda else "gloo", device_id=device if cuda else None)
         from torch.distributed.device_mesh import init_device_mesh
 
-        mesh = init_device_mesh("cuda" if cuda else "cpu", (world,), mesh_dim_names=("dp_shard",))
+        rep = cfg.get("hsdp_replicate", 1)
+        if rep > 1 and world % rep == 0 and world > rep:
+            mesh = init_device_mesh("cuda" if cuda else "cpu", (rep, world // rep),
+                                    mesh_dim_names=("dp_replicate", "dp_shard"))
+        else:
+            mesh = init_device_mesh("cuda" if cuda else "cpu", (world,), mesh_dim_names=("dp_shard",))
     if args.gpus != world and rank == 0 and world > 1:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
 
@@ -294,6 +333,11 @@ def main() -> None:
     ms, e2e_ms, peak_mb = (float(x) for x in stats.tolist())
 
     tokens_per_step = B * S * world
+    parallelism = f"dp_shard{world}"
+    if mesh is not None and mesh.ndim == 2:
+        parallelism = f"dp_replicate{mesh.shape[0]}xdp_shard{mesh.shape[1]}"
+    if cfg.get("kind") == "moe":
+        parallelism += f"+ep{world}"
     value = tokens_per_step * args.steps / (ms / 1e3)
     e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
     out = {
@@ -302,7 +346,7 @@ def main() -> None:
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids; random-init N(0,0.02) weights",
         "impl": args.impl, "peak_mb": peak_mb, "symmetric_mb": symmetric_mb, "final_loss": final_loss,
         "config": {"model": cfg["model"], "global_batch": B * world, "micro_batch_per_gpu": B, "seq_len": S,
-                   "parallelism": f"dp_shard{world}", "optimizer": cfg["optimizer"],
+                   "parallelism": parallelism, "optimizer": cfg["optimizer"],
                    "precision": "bf16 params+compute, fp32 master weights and optimizer state",
                    "activation_checkpointing": cfg["ac"],
                    "l2": "no explicit flush: each step streams >1 GB of weights/activations (L2 is 126 MB)"},

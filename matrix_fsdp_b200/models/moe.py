@@ -63,14 +63,17 @@ class Experts(nn.Module):
         super().__init__()
         h, f = cfg.hidden, cfg.expert_ffn
         self.first_expert, self.n_local = first_expert, n_local
-        gu = torch.empty(n_local, 2 * f, h, dtype=torch.float32)
-        dn = torch.empty(n_local, h, f, dtype=torch.float32)
+        gen_dev = torch.device(device) if device is not None and torch.device(device).type == "cuda" else torch.device("cpu")
+        dt = dtype or torch.float32
+        gu = torch.empty(n_local, 2 * f, h, dtype=dt, device=gen_dev)
+        dn = torch.empty(n_local, h, f, dtype=dt, device=gen_dev)
+        g = torch.Generator(device=gen_dev)
         for el in range(n_local):
-            g = torch.Generator().manual_seed(cfg.seed * 1_000_003 + layer * 4099 + first_expert + el + 17)
-            gu[el].normal_(0.0, cfg.init_std, generator=g)
-            dn[el].normal_(0.0, cfg.init_std, generator=g)
-        self.w_gate_up = nn.Parameter(gu.to(device=device, dtype=dtype))
-        self.w_down = nn.Parameter(dn.to(device=device, dtype=dtype))
+            g.manual_seed(cfg.seed * 1_000_003 + layer * 4099 + first_expert + el + 17)
+            gu[el].copy_(torch.empty(2 * f, h, dtype=torch.float32, device=gen_dev).normal_(0.0, cfg.init_std, generator=g))
+            dn[el].copy_(torch.empty(h, f, dtype=torch.float32, device=gen_dev).normal_(0.0, cfg.init_std, generator=g))
+        self.w_gate_up = nn.Parameter(gu.to(device=device))
+        self.w_down = nn.Parameter(dn.to(device=device))
 
 
 class MoEBlock(nn.Module):

@@ -27,7 +27,7 @@ struct EpPtrs {
 };
 
 // ------------------------------------------------------------------ router
-// One warp per token.  logits: [T, E] bf16 (row stride ld).  E <= 256, multiple of 32.
+// One warp per token.  logits: [T, E] bf16 (row stride ld).  E <= 256 (lanes past E hold -inf / 0).
 template <int VPL>
 __global__ void moe_router_topk_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, int T, int E, int K,
                                        float* __restrict__ probs, int* __restrict__ topk_idx,
@@ -39,7 +39,7 @@ __global__ void moe_router_topk_kernel(const __nv_bfloat16* __restrict__ logits,
   float mx = -INFINITY;
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
-    v[i] = __bfloat162float(logits[(long long)t * ld + i * 32 + lane]);
+    v[i] = (i * 32 + lane < E) ? __bfloat162float(logits[(long long)t * ld + i * 32 + lane]) : -INFINITY;
     mx = fmaxf(mx, v[i]);
   }
   mx = warp_max(mx);
@@ -54,8 +54,12 @@ __global__ void moe_router_topk_kernel(const __nv_bfloat16* __restrict__ logits,
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     v[i] *= inv;
-    probs[(long long)t * E + i * 32 + lane] = v[i];
-    if (prob_sum) atomicAdd(&prob_sum[i * 32 + lane], v[i]);
+    if (i * 32 + lane < E) {
+      probs[(long long)t * E + i * 32 + lane] = v[i];
+      if (prob_sum) atomicAdd(&prob_sum[i * 32 + lane], v[i]);
+    } else {
+      v[i] = -2.f;   // never selected
+    }
   }
   unsigned taken = 0;
   for (int k = 0; k < K; ++k) {
@@ -96,8 +100,9 @@ __global__ void moe_router_bwd_kernel(const float* __restrict__ probs, const int
   float p[VPL], d[VPL];
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
-    p[i] = probs[(long long)t * E + i * 32 + lane];
-    d[i] = aux_grad ? aux_grad[i * 32 + lane] : 0.f;
+    const bool in = i * 32 + lane < E;
+    p[i] = in ? probs[(long long)t * E + i * 32 + lane] : 0.f;
+    d[i] = (in && aux_grad) ? aux_grad[i * 32 + lane] : 0.f;
   }
   for (int k = 0; k < K; ++k) {
     const int e = topk_idx[(long long)t * K + k];
@@ -112,7 +117,7 @@ __global__ void moe_router_bwd_kernel(const float* __restrict__ probs, const int
   dot = warp_sum(dot);
 #pragma unroll
   for (int i = 0; i < VPL; ++i)
-    dlogits[(long long)t * ld + i * 32 + lane] = __float2bfloat16(p[i] * (d[i] - dot));
+    if (i * 32 + lane < E) dlogits[(long long)t * ld + i * 32 + lane] = __float2bfloat16(p[i] * (d[i] - dot));
 }
 
 // ------------------------------------------------------------------ slots
@@ -389,10 +394,11 @@ static EpPtrs make_ptrs(const unsigned long long* addrs, int n) {
 
 MFSDP_API int mfsdp_moe_router_topk(const void* logits, long long ld, int T, int E, int K, float* probs, int* topk_idx,
                                     float* topk_w, float* prob_sum, cudaStream_t st) {
-  if (E % 32 || E > 256 || K < 1 || K > kMaxTopK || K > E) return -2;
+  if (E < 1 || E > 256 || K < 1 || K > kMaxTopK || K > E) return -2;
   const int grid = (T + 7) / 8;
   auto lg = (const __nv_bfloat16*)logits;
-  switch (E / 32) {
+  const int vpl = (E + 31) / 32;
+  switch (vpl <= 1 ? 1 : vpl <= 2 ? 2 : vpl <= 4 ? 4 : 8) {
     case 1: moe_router_topk_kernel<1><<<grid, 256, 0, st>>>(lg, ld, T, E, K, probs, topk_idx, topk_w, prob_sum); break;
     case 2: moe_router_topk_kernel<2><<<grid, 256, 0, st>>>(lg, ld, T, E, K, probs, topk_idx, topk_w, prob_sum); break;
     case 4: moe_router_topk_kernel<4><<<grid, 256, 0, st>>>(lg, ld, T, E, K, probs, topk_idx, topk_w, prob_sum); break;
@@ -404,10 +410,11 @@ MFSDP_API int mfsdp_moe_router_topk(const void* logits, long long ld, int T, int
 
 MFSDP_API int mfsdp_moe_router_bwd(const float* probs, const int* topk_idx, const float* dw, const float* aux_grad, int T,
                                    int E, int K, void* dlogits, long long ld, cudaStream_t st) {
-  if (E % 32 || E > 256 || K < 1 || K > kMaxTopK) return -2;
+  if (E < 1 || E > 256 || K < 1 || K > kMaxTopK) return -2;
   const int grid = (T + 7) / 8;
   auto dl = (__nv_bfloat16*)dlogits;
-  switch (E / 32) {
+  const int vpl = (E + 31) / 32;
+  switch (vpl <= 1 ? 1 : vpl <= 2 ? 2 : vpl <= 4 ? 4 : 8) {
     case 1: moe_router_bwd_kernel<1><<<grid, 256, 0, st>>>(probs, topk_idx, dw, aux_grad, T, E, K, dl, ld); break;
     case 2: moe_router_bwd_kernel<2><<<grid, 256, 0, st>>>(probs, topk_idx, dw, aux_grad, T, E, K, dl, ld); break;
     case 4: moe_router_bwd_kernel<4><<<grid, 256, 0, st>>>(probs, topk_idx, dw, aux_grad, T, E, K, dl, ld); break;
