@@ -178,6 +178,26 @@ def build_reference(cfg: dict, device, mesh, world: int):
     from ref_llama import RefLlama
     from torch.distributed.fsdp import MixedPrecisionPolicy
 
+    if cfg.get("kind") == "moe":
+        from ref_moe import RefCombinedOptimizer, RefMoE
+
+        torch.manual_seed(0)
+        with torch.device(device):
+            model = RefMoE(cfg["vocab_size"], cfg["hidden"], cfg["n_layers"], cfg["n_heads"], cfg["head_dim"],
+                           cfg["n_experts"], cfg["expert_ffn"], cfg["top_k"], world=world)
+        mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16)
+        for layer in model.layers:
+            R.fully_shard(layer, mesh=mesh, mp_policy=mp, optimizer_policy="mixed_muon_adamw",
+                          ignored_params=set(layer.experts.parameters()))
+        R.fully_shard(model, mesh=mesh, mp_policy=mp, ignored_params=set(model.expert_parameters()))
+        dense = R.configure_optimizer(model, "mixed_muon_adamw", muon_lr=cfg["lr"], adamw_lr=3e-4,
+                                      adamw_betas=cfg["betas"], weight_decay=cfg["weight_decay"], muon_momentum=0.95,
+                                      muon_ns_steps=5, muon_adjust_lr_fn="original")
+        experts = torch.optim.Muon(model.expert_parameters(), lr=cfg["lr"], momentum=0.95, nesterov=True, ns_steps=5,
+                                   weight_decay=cfg["weight_decay"])
+        for u in R.collect_param_groups(model):
+            u.runtime_trace_enabled = False
+        return model, RefCombinedOptimizer(dense, experts)
     torch.manual_seed(0)
     model = RefLlama(cfg["vocab_size"], cfg["hidden"], cfg["n_layers"], cfg["n_heads"], cfg["head_dim"], cfg["ffn"],
                      activation_checkpointing=cfg["ac"]).to(device)
