@@ -34,10 +34,10 @@ class RefExperts(nn.Module):
 
 
 class RefMoEBlock(nn.Module):
-    def __init__(self, hidden, n_heads, head_dim, n_experts, expert_ffn, top_k, aux_coef, eps, std, world, dtype):
+    def __init__(self, hidden, n_heads, head_dim, n_experts, expert_ffn, top_k, aux_coef, eps, std, world, dtype, ep_group=None):
         super().__init__()
         self.n_heads, self.head_dim, self.top_k, self.aux_coef = n_heads, head_dim, top_k, aux_coef
-        self.n_experts, self.world = n_experts, world
+        self.n_experts, self.world, self.ep_group = n_experts, world, ep_group
         self.attn_norm = nn.RMSNorm(hidden, eps=eps)
         self.wq = nn.Linear(hidden, hidden, bias=False)
         self.wk = nn.Linear(hidden, hidden, bias=False)
@@ -64,10 +64,10 @@ class RefMoEBlock(nn.Module):
         xs = x.index_select(0, tok)
         if W > 1:
             recv_counts = torch.empty_like(counts)
-            dist.all_to_all_single(recv_counts, counts)                     # [W * El] counts from every source
+            dist.all_to_all_single(recv_counts, counts, group=self.ep_group)                     # [W * El] counts from every source
             in_splits = counts.view(W, El).sum(1).tolist()
             out_splits = recv_counts.view(W, El).sum(1).tolist()
-            xr = _a2a(xs, out_splits, in_splits, None)
+            xr = _a2a(xs, out_splits, in_splits, self.ep_group)
             per = recv_counts.view(W, El)
             # rows arrive grouped by source rank, then by local expert: regroup by expert
             eid = torch.repeat_interleave(torch.arange(El, device=x.device).repeat(W), per.reshape(-1))
@@ -88,7 +88,7 @@ class RefMoEBlock(nn.Module):
             inv = torch.empty_like(perm)
             inv[perm] = torch.arange(perm.numel(), device=perm.device)
             yr = yr.index_select(0, inv)
-            ys = _a2a(yr, in_splits, out_splits, None)
+            ys = _a2a(yr, in_splits, out_splits, self.ep_group)
         else:
             ys = yr
         wk = w.reshape(-1).index_select(0, order).to(ys.dtype).unsqueeze(1)
@@ -110,13 +110,13 @@ class RefMoEBlock(nn.Module):
 
 class RefMoE(nn.Module):
     def __init__(self, vocab_size, hidden, n_layers, n_heads, head_dim, n_experts, expert_ffn, top_k, aux_coef=0.01,
-                 rope_theta=10000.0, eps=1e-5, init_std=0.02, world=1, expert_dtype=torch.bfloat16):
+                 rope_theta=10000.0, eps=1e-5, init_std=0.02, world=1, expert_dtype=torch.bfloat16, ep_group=None):
         super().__init__()
         self.head_dim, self.rope_theta = head_dim, rope_theta
         self.embed = nn.Embedding(vocab_size, hidden)
         nn.init.normal_(self.embed.weight, mean=0.0, std=init_std)
         self.layers = nn.ModuleList([RefMoEBlock(hidden, n_heads, head_dim, n_experts, expert_ffn, top_k, aux_coef, eps,
-                                                 init_std, world, expert_dtype) for _ in range(n_layers)])
+                                                 init_std, world, expert_dtype, ep_group) for _ in range(n_layers)])
         self.final_norm = nn.RMSNorm(hidden, eps=eps)
         self.lm_head = nn.Linear(hidden, vocab_size, bias=False)
         nn.init.normal_(self.lm_head.weight, mean=0.0, std=init_std)

@@ -150,13 +150,17 @@ def build_ours(cfg: dict, device, mesh, world: int):
                        n_heads=cfg["n_heads"], head_dim=cfg["head_dim"], ffn=cfg["ffn"],
                        activation_checkpointing=cfg["ac"], max_seq_len=cfg["seq_len"])
     torch.manual_seed(0)
-    model = LlamaModel(mcfg).to(device)
+    with torch.device(device):
+        model = LlamaModel(mcfg)
     model.loss_is_final = True
     mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16)
     policy = "mixed_muon_adamw" if cfg["optimizer"] == "mixed_muon_adamw" else None
     shard_llama(model, mesh=mesh, mp_policy=mp, optimizer_policy=policy)
     if cfg["optimizer"] == "adamw":
-        opt = configure_optimizer(model, "adamw", lr=cfg["lr"], betas=cfg["betas"], weight_decay=cfg["weight_decay"])
+        # the sharded AdamW update runs inside the gradient reduce-scatter kernel (peer transport, N > 1)
+        fused = world > 1 and os.environ.get("MFSDP_FUSED_REDUCE_UPDATE", "1") != "0"
+        opt = configure_optimizer(model, "adamw", lr=cfg["lr"], betas=cfg["betas"], weight_decay=cfg["weight_decay"],
+                                  fused_reduce_update=fused)
     else:
         opt = configure_optimizer(model, "mixed_muon_adamw", muon_lr=cfg["lr"], adamw_lr=3e-4,
                                   adamw_betas=cfg["betas"], weight_decay=cfg["weight_decay"], muon_momentum=0.95,
@@ -184,7 +188,8 @@ def build_reference(cfg: dict, device, mesh, world: int):
         torch.manual_seed(0)
         with torch.device(device):
             model = RefMoE(cfg["vocab_size"], cfg["hidden"], cfg["n_layers"], cfg["n_heads"], cfg["head_dim"],
-                           cfg["n_experts"], cfg["expert_ffn"], cfg["top_k"], world=world)
+                           cfg["n_experts"], cfg["expert_ffn"], cfg["top_k"], world=world,
+                           ep_group=dist.new_group(list(range(world))) if world > 1 else None)
         mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16)
         for layer in model.layers:
             R.fully_shard(layer, mesh=mesh, mp_policy=mp, optimizer_policy="mixed_muon_adamw",
@@ -199,8 +204,9 @@ def build_reference(cfg: dict, device, mesh, world: int):
             u.runtime_trace_enabled = False
         return model, RefCombinedOptimizer(dense, experts)
     torch.manual_seed(0)
-    model = RefLlama(cfg["vocab_size"], cfg["hidden"], cfg["n_layers"], cfg["n_heads"], cfg["head_dim"], cfg["ffn"],
-                     activation_checkpointing=cfg["ac"]).to(device)
+    with torch.device(device):
+        model = RefLlama(cfg["vocab_size"], cfg["hidden"], cfg["n_layers"], cfg["n_heads"], cfg["head_dim"], cfg["ffn"],
+                         activation_checkpointing=cfg["ac"])
     mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16)
     policy = "mixed_muon_adamw" if cfg["optimizer"] == "mixed_muon_adamw" else None
     for layer in model.layers:

@@ -184,6 +184,71 @@ __global__ void rs_pull_reduce_kernel(PeerPtrs grads, int world, int rank, TOut*
   }
 }
 
+// Reduce-scatter fused with the sharded AdamW update: the reduced gradient never touches memory.
+//   g = scale * sum_r grads_r[global_off + i]   (bf16 or fp32 in, fp32 sum, fixed rank order)
+//   p, m, v (fp32, this rank's shard) updated in place; p_lp = bf16 copy of p for the next all-gather.
+struct AdamWArgs {
+  float* p;
+  float* m;
+  float* v;
+  __nv_bfloat16* p_lp;
+  float lr, beta1, beta2, eps, weight_decay, bias1, bias2_sqrt;
+};
+
+__device__ __forceinline__ void adamw_one(float& p, float& m, float& v, float g, const AdamWArgs& a) {
+  p *= (1.f - a.lr * a.weight_decay);
+  m = a.beta1 * m + (1.f - a.beta1) * g;
+  v = a.beta2 * v + (1.f - a.beta2) * g * g;
+  p -= (a.lr / a.bias1) * (m / (sqrtf(v) / a.bias2_sqrt + a.eps));
+}
+
+template <typename TIn>
+__global__ void rs_pull_adamw_kernel(PeerPtrs grads, int world, int rank, ReduceTable tab, int nseg, float scale,
+                                     AdamWArgs a) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  for (int s = blockIdx.y; s < nseg; s += gridDim.y) {
+    const long long g0 = tab.global_off[s], l0 = tab.local_off[s], n = tab.len[s];
+    const bool aligned = ((g0 * sizeof(TIn)) % 16 == 0) && (l0 % 8 == 0);
+    const long long nvec = aligned ? n / 8 : 0;
+    for (long long i = tid; i < nvec; i += stride) {
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      for (int k = 0; k < world; ++k) {
+        const int r = (rank + k) % world;
+        float v[8];
+        load8(reinterpret_cast<const TIn*>(grads.p[r]) + g0 + i * 8, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += v[e];
+      }
+      const long long j = l0 + i * 8;
+      float pp[8], mm[8], vv[8];
+      load8(a.p + j, pp);
+      load8(a.m + j, mm);
+      load8(a.v + j, vv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) adamw_one(pp[e], mm[e], vv[e], acc[e] * scale, a);
+      store8(a.p + j, pp);
+      store8(a.m + j, mm);
+      store8(a.v + j, vv);
+      if (a.p_lp) store8(a.p_lp + j, pp);
+    }
+    for (long long i = nvec * 8 + tid; i < n; i += stride) {
+      float acc = 0.f;
+      for (int k = 0; k < world; ++k) {
+        const int r = (rank + k) % world;
+        acc += to_f(reinterpret_cast<const TIn*>(grads.p[r])[g0 + i]);
+      }
+      const long long j = l0 + i;
+      float pp = a.p[j], mm = a.m[j], vv = a.v[j];
+      adamw_one(pp, mm, vv, acc * scale, a);
+      a.p[j] = pp; a.m[j] = mm; a.v[j] = vv;
+      if (a.p_lp) a.p_lp[j] = __float2bfloat16_rn(pp);
+    }
+  }
+}
+
 static inline dim3 seg_grid(long long max_len, int per_thread, int nseg) {
   long long bx = (max_len / per_thread + 255) / 256;
   if (bx < 1) bx = 1;
@@ -280,5 +345,24 @@ MFSDP_API int mfsdp_rs_pull_reduce(const unsigned long long* grad_ptrs_host, int
   else if (!in_is_bf16 && !out_is_bf16) MFSDP_RS(float, float);
   else return -2;
 #undef MFSDP_RS
+  return (int)cudaGetLastError();
+}
+
+MFSDP_API int mfsdp_rs_pull_adamw(const unsigned long long* grad_ptrs_host, int world, int rank,
+                                  const long long* global_off, const long long* local_off, const long long* len,
+                                  int nseg, long long max_len, int in_is_bf16, float scale, float* p, float* m,
+                                  float* v, void* p_lp, float lr, float beta1, float beta2, float eps,
+                                  float weight_decay, int step, cudaStream_t st) {
+  if (nseg <= 0) return 0;
+  if (world <= 0 || world > kMaxPeers || step < 1) return -2;
+  if (((uintptr_t)p % 16) || ((uintptr_t)m % 16) || ((uintptr_t)v % 16) || ((uintptr_t)p_lp % 16)) return -2;
+  PeerPtrs pp{};
+  for (int i = 0; i < world; ++i) pp.p[i] = reinterpret_cast<const void*>(grad_ptrs_host[i]);
+  ReduceTable tab{global_off, local_off, len};
+  AdamWArgs a{p, m, v, (__nv_bfloat16*)p_lp, lr, beta1, beta2, eps, weight_decay,
+              1.f - powf(beta1, (float)step), sqrtf(1.f - powf(beta2, (float)step))};
+  const dim3 grid = seg_grid(max_len, 8, nseg);
+  if (in_is_bf16) rs_pull_adamw_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(pp, world, rank, tab, nseg, scale, a);
+  else rs_pull_adamw_kernel<float><<<grid, 256, 0, st>>>(pp, world, rank, tab, nseg, scale, a);
   return (int)cudaGetLastError();
 }

@@ -141,10 +141,29 @@ class FlatShardedAdamW(_FlatShardedBase):
     _state_names = ("exp_avg", "exp_avg_sq")
 
     def __init__(self, params: Iterable, *, units=None, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
-                 weight_decay: float = 1e-2, **_ignored) -> None:
+                 weight_decay: float = 1e-2, fused_reduce_update: bool = False, **_ignored) -> None:
         if lr < 0 or eps < 0 or not 0 <= betas[0] < 1 or not 0 <= betas[1] < 1 or weight_decay < 0:
             raise ValueError("invalid AdamW hyper-parameters")
         super().__init__(params, dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay), units)
+        # Opt-in: the update runs inside the gradient reduce-scatter kernel (peer transport), so the
+        # reduced gradient is never materialised: no gradient clipping and ``param.grad`` stays None.
+        self.fused_reduce_update = bool(fused_reduce_update)
+        if self.fused_reduce_update:
+            for us in self._unit_states.values():
+                us.unit.flat_buffer.fused_reduce_update = self._make_fused_update(us)
+
+    def _make_fused_update(self, us: _UnitState):
+        def update():
+            fb = us.unit.flat_buffer
+            if fb.local_numel == 0 or not _native(fb.device) or self.grad_scale != 1.0 or \
+                    (fb.local_shard_lp is not None and fb.local_shard_lp.dtype != torch.bfloat16):
+                return None
+            hp = self._group_of(us.unit)
+            us.step += 1
+            return dict(p=fb.local_shard, m=us.buffers["exp_avg"], v=us.buffers["exp_avg_sq"], p_lp=fb.local_shard_lp,
+                        lr=float(hp["lr"]), beta1=hp["betas"][0], beta2=hp["betas"][1], eps=hp["eps"],
+                        weight_decay=hp["weight_decay"], step=us.step)
+        return update
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -154,6 +173,15 @@ class FlatShardedAdamW(_FlatShardedBase):
                 loss = closure()
         for us in self._unit_states.values():
             unit, fb = us.unit, us.unit.flat_buffer
+            if fb.fused_update_applied:
+                # the reduce-scatter kernel already updated master, moments and the bf16 shard
+                fb.fused_update_applied = False
+                fb.mark_master_updated(lp_written=fb.local_shard_lp is not None)
+                for mp in unit.registry:
+                    st = self.state.get(mp.param)
+                    if st and "step" in st:
+                        st["step"].fill_(us.step)
+                continue
             g = self._unit_grad(unit)
             if g is None or fb.local_numel == 0:
                 continue

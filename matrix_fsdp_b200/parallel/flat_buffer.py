@@ -147,6 +147,10 @@ class MatrixFlatBuffer:
         self.grad_bucket_acquired = False
         self.accumulate_into_local_grad = False
         self.fused_optimizer_consumes_bucket = False
+        # Set by an optimizer that wants the reduce-scatter to apply its update (peer transport only):
+        # a callable returning the update arguments for this reduction, or None to reduce normally.
+        self.fused_reduce_update = None
+        self.fused_update_applied = False
 
     # ------------------------------------------------------------------ helpers
     def _bucket_dtype(self) -> torch.dtype:
@@ -335,6 +339,15 @@ class MatrixFlatBuffer:
                                              "bytes": 0, "count": 0, "sync_mode": "local"})
             self.pending_reduce = h
             return h
+        if self.fused_reduce_update is not None and self.replicate_world_size == 1 \
+                and not self.accumulate_into_local_grad and hasattr(self.transport, "reduce_update"):
+            update = self.fused_reduce_update()
+            if update is not None:
+                h = self.transport.reduce_update(src, self.tables, update, scale=scale, stream=stream,
+                                                 unit_key=self.unit_key)
+                self.fused_update_applied = True
+                self.pending_reduce = h
+                return h
         needs_cast = out.dtype != src.dtype and not getattr(self.transport, "accumulates_fp32", False)
         accumulate = self.accumulate_into_local_grad
         self.accumulate_into_local_grad = False

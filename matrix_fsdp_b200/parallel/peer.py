@@ -47,6 +47,8 @@ _lib.register_signatures({
     "mfsdp_ag_pull": [_vp, _vp, _vp, _vp, _i32, _i64, _i32, _vp],
     "mfsdp_rs_pull_reduce": [C.POINTER(_u64), _i32, _i32, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32,
                              C.c_float, _vp],
+    "mfsdp_rs_pull_adamw": [C.POINTER(_u64), _i32, _i32, _vp, _vp, _vp, _i32, _i64, _i32, C.c_float, _vp, _vp, _vp,
+                            _vp, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, _i32, _vp],
 })
 
 KIND_SHARD, KIND_GRAD, KIND_PULLED = 0, 1, 2
@@ -338,12 +340,19 @@ class PeerTransport(LocalTransport):
             self._tables[key] = t
         return t
 
+    def reduce_update(self, full_grad, tables: SegmentTables, update: dict, *, scale=None, stream=None,
+                      unit_key=None) -> MatrixCollectiveHandle:
+        """Reduce-scatter fused with the sharded AdamW update (``update``: p, m, v, p_lp tensors and
+        lr, beta1, beta2, eps, weight_decay, step); the reduced gradient is never written."""
+        return self.reduce(full_grad, None, tables, scale=scale, stream=stream, unit_key=unit_key, update=update)
+
     def reduce(self, full_grad, out_shard, tables: SegmentTables, *, scale=None, stream=None, unit_key=None,
-               accumulate: bool = False) -> MatrixCollectiveHandle:
+               accumulate: bool = False, update: dict | None = None) -> MatrixCollectiveHandle:
         buf = self.ctx.lookup(full_grad)
         if buf is None:
             raise RuntimeError("peer reduce needs a gradient buffer from acquire_grad_buffer()")
-        if full_grad.dtype not in (torch.bfloat16, torch.float32) or out_shard.dtype not in (torch.bfloat16, torch.float32):
+        if full_grad.dtype not in (torch.bfloat16, torch.float32) or \
+                (update is None and out_shard.dtype not in (torch.bfloat16, torch.float32)):
             raise TypeError("peer reduce supports bf16 / fp32 gradients")
         ui = self._unit(unit_key)
         ep = self._epochs[unit_key]
@@ -361,11 +370,20 @@ class PeerTransport(LocalTransport):
         ctx.signal(ui, KIND_GRAD, e, run)
         ctx.wait(ui, KIND_GRAD, e, run)
         ptrs = (_u64 * ctx.world)(*buf.peer_addr)
-        _lib.check(ctx.lib.mfsdp_rs_pull_reduce(
-            ptrs, ctx.world, ctx.rank, out_shard.data_ptr(), t["g"].data_ptr(), t["l"].data_ptr(),
-            t["len"].data_ptr(), t["n"], t["max"], int(full_grad.dtype == torch.bfloat16),
-            int(out_shard.dtype == torch.bfloat16), int(accumulate), float(1.0 if scale is None else scale),
-            run.cuda_stream), "rs_pull_reduce")
+        if update is not None:
+            u = update
+            _lib.check(ctx.lib.mfsdp_rs_pull_adamw(
+                ptrs, ctx.world, ctx.rank, t["g"].data_ptr(), t["l"].data_ptr(), t["len"].data_ptr(), t["n"], t["max"],
+                int(full_grad.dtype == torch.bfloat16), float(1.0 if scale is None else scale), u["p"].data_ptr(),
+                u["m"].data_ptr(), u["v"].data_ptr(), u["p_lp"].data_ptr() if u.get("p_lp") is not None else None,
+                float(u["lr"]), float(u["beta1"]), float(u["beta2"]), float(u["eps"]), float(u["weight_decay"]),
+                int(u["step"]), run.cuda_stream), "rs_pull_adamw")
+        else:
+            _lib.check(ctx.lib.mfsdp_rs_pull_reduce(
+                ptrs, ctx.world, ctx.rank, out_shard.data_ptr(), t["g"].data_ptr(), t["l"].data_ptr(),
+                t["len"].data_ptr(), t["n"], t["max"], int(full_grad.dtype == torch.bfloat16),
+                int(out_shard.dtype == torch.bfloat16), int(accumulate), float(1.0 if scale is None else scale),
+                run.cuda_stream), "rs_pull_reduce")
         ctx.signal(ui, KIND_PULLED, e, run)
         self.launches += 4
         ev = torch.cuda.Event()
@@ -375,7 +393,8 @@ class PeerTransport(LocalTransport):
         if stream is None:
             ev = None
         return MatrixCollectiveHandle(event=ev, info={
-            "kind": "reduce_scatter", "impl": "rs_pull_reduce", "backend": self.kind,
+            "kind": "reduce_scatter", "impl": "rs_pull_adamw" if update is not None else "rs_pull_reduce",
+            "backend": self.kind,
             "bytes": full_grad.numel() * full_grad.element_size(), "count": 1,
             "sync_mode": "stream_event" if stream is not None else "stream_order"})
 

@@ -93,7 +93,7 @@ def _peer_collectives(rank, world):
     tr.check_health()
 
 
-def _train(rank, world, transport_kind):
+def _train(rank, world, transport_kind, fused_update=False):
     import torch.distributed as dist
     from torch.distributed.fsdp import MixedPrecisionPolicy
 
@@ -110,7 +110,8 @@ def _train(rank, world, transport_kind):
     shard_llama(model, mp_policy=MixedPrecisionPolicy(param_dtype=torch.bfloat16))
     kinds = {u.flat_buffer.transport.kind for u in collect_param_groups(model)}
     assert kinds == {transport_kind}, kinds
-    opt = configure_optimizer(model, "adamw", lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
+    opt = configure_optimizer(model, "adamw", lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1,
+                              fused_reduce_update=fused_update)
     g = torch.Generator().manual_seed(5 + rank)
     losses = []
     for _ in range(4):
@@ -134,6 +135,11 @@ def _train_both(rank, world, out_dir):
         assert abs(a - b) < 2e-2 * abs(b), (l_peer, l_nccl)
     rel = ((s_peer - s_nccl).norm() / s_nccl.norm()).item()
     assert rel < 2e-3, rel
+    # the update applied inside the reduce-scatter kernel is the same update
+    l_fused, s_fused = _train(rank, world, "peer", fused_update=True)
+    for a, b in zip(l_fused, l_peer):
+        assert abs(a - b) < 1e-3 * abs(b), (l_fused, l_peer)
+    assert ((s_fused - s_peer).norm() / s_peer.norm()).item() < 1e-5
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
