@@ -40,6 +40,11 @@ def bwd_available() -> bool:
 
 
 def available() -> bool:
+    """Both kernels present (``MFSDP_ATTENTION=sdpa`` selects the library kernel, for A/B timing)."""
+    import os
+
+    if os.environ.get("MFSDP_ATTENTION", "native") == "sdpa":
+        return False
     return fwd_available() and bwd_available()
 
 

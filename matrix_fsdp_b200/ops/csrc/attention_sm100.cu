@@ -7,10 +7,10 @@
 //   warp 0   : TMA producer (Q once, then K/V tiles of 128 keys through a 2-stage ring)
 //   warp 1   : tcgen05.mma issuer.  S_j = Q K_j^T goes to one of two TMEM buffers so that S_{j+1} is
 //              computed while the softmax of tile j runs; O += P_j V_j accumulates in TMEM.
-//   warps 2-5: softmax.  Thread r owns query row r (the 32x32b TMEM load shape gives one row per lane,
-//              so row max / row sum need no shuffles), writes P as bf16 into a 128B-swizzled shared
-//              tile (the A operand of the second MMA) and rescales O in TMEM only when the running
-//              maximum moved by more than 2^8 (lazy rescaling).
+//   warps 2-9: softmax.  Two threads own query row r (the 32x32b TMEM load shape gives one row per
+//              lane), one per 64-key half; they exchange the half-row maximum through shared memory,
+//              write P as bf16 into a 128B-swizzled shared tile (the A operand of the second MMA) and
+//              rescale O in TMEM only when the running maximum moved by more than 2^8 (lazy rescaling).
 // Every wait is bounded; on a timeout the kernel records a status code and leaves through the normal
 // teardown.
 //
@@ -29,7 +29,7 @@ constexpr int kBq = 128;            // queries per CTA
 constexpr int kBk = 128;            // keys per iteration
 constexpr int kTileBytes = 128 * 128 * 2;   // one [128 x 128] bf16 tile = two 64-column chunks of 16 KB
 constexpr int kHalfTile = kTileBytes / 2;
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 320;          // warp 0 TMA, warp 1 MMA, warps 2-9 softmax (two per TMEM lane quadrant)
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct AttnFwdArgs {
@@ -47,11 +47,21 @@ struct AttnFwdSmem {
   static constexpr int kK = kQ + kTileBytes;            // 2 stages
   static constexpr int kV = kK + 2 * kTileBytes;        // 2 stages
   static constexpr int kP = kV + 2 * kTileBytes;
-  static constexpr int kBars = kP + kTileBytes;
+  static constexpr int kXchg = kP + kTileBytes;          // row max [2 parities][2 halves][128] + row sum [2][128]
+  static constexpr int kBars = kXchg + 3 * 1024;
   static constexpr int kBytes = kBars + 256 + 1024;
 };
 
-__device__ __forceinline__ void softmax_bar_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+__device__ __forceinline__ void softmax_bar_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
+// Barrier over the 256 softmax threads that also ORs a predicate, so that every thread takes the
+// same decision about leaving the loop after a wait ran out.
+__device__ __forceinline__ bool softmax_bar_or(bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, 2, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out) : "r"((uint32_t)pred) : "memory");
+  return out != 0;
+}
 
 // Issue the 8 k-steps of a 128x128x128 MMA whose operands are [128 x 128] bf16 tiles stored as two
 // 64-column swizzled chunks.  A K-major operand advances 32 B per k-step inside a chunk and one chunk
@@ -102,7 +112,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnFwdArgs p
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    for (int i = 0; i < 13; ++i) mbar_init(smem_u32(&bars[i]), (i == 11) ? 128 : 1);
+    for (int i = 0; i < 13; ++i) mbar_init(smem_u32(&bars[i]), (i == 11) ? 256 : 1);
     mbar_fence_init();
     tma_prefetch_desc(&tma_qkv);
   }
@@ -163,47 +173,50 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnFwdArgs p
       }
     }
   } else {
-    // ------------------------------------------------------------ softmax / epilogue (128 threads)
-    const int q = warp & 3;
+    // ------------------------------------------------------------ softmax / epilogue (256 threads)
+    const int q = warp & 3;                      // TMEM lane quadrant this warp may access
+    const int half = (warp - 2) >> 2;            // which 64 keys of the tile / which 64 columns of O
     const int r = q * 32 + lane;                 // query row inside the tile == TMEM lane
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const int qi = q0 + r;
+    float* xmax = reinterpret_cast<float*>(smem + AttnFwdSmem::kXchg);     // [parity][half][128]
+    float* xsum = xmax + 512;                                              // [half][128]
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < nkv; ++j) {
       mbar_wait(smem_u32(&s_full[j & 1]), (j >> 1) & 1, p.status, abort_flag);
-      softmax_bar_sync();
-      if (*abort_flag) { ok = false; break; }
       tc_fence_after();
-      float s[128];
+      float s[64];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t t[32];
-        tmem_ld_32x32b_x32(tmem_base + (j & 1) * 128 + lane_off + c * 32, t);
+        tmem_ld_32x32b_x32(tmem_base + (j & 1) * 128 + lane_off + half * 64 + c * 32, t);
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 32; ++e) s[c * 32 + e] = __uint_as_float(t[e]);
       }
       if (j == nkv - 1) {
-        const int kv0 = j * kBk;
+        const int kv0 = j * kBk + half * 64;
 #pragma unroll
-        for (int e = 0; e < 128; ++e)
+        for (int e = 0; e < 64; ++e)
           if (kv0 + e > qi) s[e] = -INFINITY;
       }
       float mx = s[0];
 #pragma unroll
-      for (int e = 1; e < 128; ++e) mx = fmaxf(mx, s[e]);
-      mx *= p.scale_log2;
+      for (int e = 1; e < 64; ++e) mx = fmaxf(mx, s[e]);
+      xmax[(j & 1) * 256 + half * 128 + r] = mx;
+      if (softmax_bar_or(*abort_flag != 0)) { ok = false; break; }
+      mx = fmaxf(mx, xmax[(j & 1) * 256 + (half ^ 1) * 128 + r]) * p.scale_log2;
       if (mx == -INFINITY) mx = 0.f;
-      float m_new = fmaxf(m_used, mx);
+      const float m_new = fmaxf(m_used, mx);
       const bool need = (j > 0) && (m_new - m_used > 8.f);
       const bool any_need = __any_sync(0xffffffffu, need);
       const float m_next = (j == 0 || any_need) ? m_new : m_used;
       const float factor = (j == 0) ? 0.f : exp2f(m_used - m_next);
       float sum = 0.f;
-      uint32_t pk[64];
+      uint32_t pk[32];
 #pragma unroll
-      for (int e = 0; e < 64; ++e) {
+      for (int e = 0; e < 32; ++e) {
         const float p0 = exp2f(s[2 * e] * p.scale_log2 - m_next);
         const float p1 = exp2f(s[2 * e + 1] * p.scale_log2 - m_next);
         sum += p0 + p1;
@@ -213,28 +226,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnFwdArgs p
       m_used = m_next;
       if (j > 0) {
         mbar_wait(smem_u32(pv_done), (j - 1) & 1, p.status, abort_flag);
-        softmax_bar_sync();
-        if (*abort_flag) { ok = false; break; }
         tc_fence_after();
         if (any_need) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             uint32_t t[32];
-            tmem_ld_32x32b_x32(tmem_o + lane_off + c * 32, t);
+            tmem_ld_32x32b_x32(tmem_o + lane_off + half * 64 + c * 32, t);
             tmem_ld_wait();
 #pragma unroll
             for (int e = 0; e < 32; ++e) t[e] = __float_as_uint(__uint_as_float(t[e]) * factor);
-            tmem_st_32x32b_x32(tmem_o + lane_off + c * 32, t);
+            tmem_st_32x32b_x32(tmem_o + lane_off + half * 64 + c * 32, t);
           }
           tmem_st_wait();
         }
       }
-      uint8_t* prow = smem + AttnFwdSmem::kP + r * 128;
+      uint8_t* prow = smem + AttnFwdSmem::kP + half * kHalfTile + r * 128;
 #pragma unroll
-      for (int kc = 0; kc < 16; ++kc) {
-        const int phys = (kc & 7) ^ (r & 7);
-        *reinterpret_cast<uint4*>(prow + (kc >> 3) * kHalfTile + phys * 16) =
-            make_uint4(pk[kc * 4], pk[kc * 4 + 1], pk[kc * 4 + 2], pk[kc * 4 + 3]);
+      for (int kc = 0; kc < 8; ++kc) {
+        const int phys = kc ^ (r & 7);
+        *reinterpret_cast<uint4*>(prow + phys * 16) = make_uint4(pk[kc * 4], pk[kc * 4 + 1], pk[kc * 4 + 2], pk[kc * 4 + 3]);
       }
       fence_proxy_async_smem();
       tc_fence_before();
@@ -242,18 +252,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnFwdArgs p
     }
     if (ok) {
       mbar_wait(smem_u32(pv_done), (nkv - 1) & 1, p.status, abort_flag);
-      softmax_bar_sync();
-      ok = !*abort_flag;
+      xsum[half * 128 + r] = l;
+      ok = !softmax_bar_or(*abort_flag != 0);
     }
     if (ok) {
       tc_fence_after();
+      l += xsum[(half ^ 1) * 128 + r];
       const float inv = 1.f / l;
       const bool row_ok = qi < p.S;
-      __nv_bfloat16* orow = p.out + (long long)(row_base + qi) * p.ld_out + h * kHd;
+      __nv_bfloat16* orow = p.out + (long long)(row_base + qi) * p.ld_out + h * kHd + half * 64;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t t[32];
-        tmem_ld_32x32b_x32(tmem_o + lane_off + c * 32, t);
+        tmem_ld_32x32b_x32(tmem_o + lane_off + half * 64 + c * 32, t);
         tmem_ld_wait();
         if (row_ok) {
 #pragma unroll
@@ -267,7 +278,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tma_qkv, const AttnFwdArgs p
           }
         }
       }
-      if (row_ok && p.lse) p.lse[((long long)b * p.nH + h) * p.S + qi] = (m_used + log2f(l)) * 0.6931471805599453f;
+      if (half == 0 && row_ok && p.lse) p.lse[((long long)b * p.nH + h) * p.S + qi] = (m_used + log2f(l)) * 0.6931471805599453f;
     }
   }
   if (*abort_flag) __nanosleep(1000000);
@@ -305,11 +316,13 @@ struct AttnBwdArgs {
   int* status;
 };
 
+constexpr int kBwdStages = 3;   // streamed-tile ring: deep enough to hide the TMA latency behind two tiles of work
+
 struct AttnBwdSmem {
   static constexpr int kA0 = 0;
   static constexpr int kA1 = kA0 + kTileBytes;
-  static constexpr int kB = kA1 + kTileBytes;             // 2 stages x (B0, B1)
-  static constexpr int kP = kB + 4 * kStreamBytes;        // 2 stages x (P, dS)
+  static constexpr int kB = kA1 + kTileBytes;             // kBwdStages stages x (B0, B1)
+  static constexpr int kP = kB + kBwdStages * 2 * kStreamBytes;   // 2 stages x (P, dS)
   static constexpr int kRow = kP + 4 * kPBytes;           // 2 stages x 128 floats (lse2 | delta of the streamed rows)
   static constexpr int kBars = kRow + 2 * 128 * 4;
   static constexpr int kBytes = kBars + 256 + 1024;
@@ -357,12 +370,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_qkv, const __grid_consta
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttnBwdSmem::kBars);
   uint64_t* stat_full = bars;          // [1]
-  uint64_t* b_full = bars + 1;         // [2]
-  uint64_t* stage_free = bars + 3;     // [2] streamed tiles and P/dS tiles of a stage consumed
-  uint64_t* sdp_full = bars + 5;       // [2]
-  uint64_t* p_full = bars + 7;         // [2] count 128
-  uint64_t* acc_done = bars + 9;       // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* b_full = bars + 1;         // [3]
+  uint64_t* b_empty = bars + 4;        // [3] streamed tiles of a stage consumed by both of their MMAs
+  uint64_t* sdp_full = bars + 7;       // [2]
+  uint64_t* p_full = bars + 9;         // [2] count 256
+  uint64_t* p_free = bars + 11;        // [2] P / dS tiles of a stage consumed
+  uint64_t* acc_done = bars + 13;      // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* row_vals = reinterpret_cast<float*>(smem + AttnBwdSmem::kRow);
 
@@ -379,7 +393,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_qkv, const __grid_consta
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    for (int i = 0; i < 10; ++i) mbar_init(smem_u32(&bars[i]), (i == 7 || i == 8) ? 128 : 1);
+    for (int i = 0; i < 14; ++i) mbar_init(smem_u32(&bars[i]), (i == 9 || i == 10) ? 256 : 1);
     mbar_fence_init();
     tma_prefetch_desc(&tma_qkv);
     tma_prefetch_desc(&tma_do);
@@ -407,8 +421,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_qkv, const __grid_consta
         tma_load_tile_4(sA1, &tma_qkv, smem_u32(stat_full), 2 * H + h * kHd, row_base + r0);  // V_j
       }
       for (int i = 0; i < T; ++i) {
-        const uint32_t s = i & 1, ph = (i >> 1) & 1;
-        if (!mbar_wait(smem_u32(&stage_free[s]), ph ^ 1, p.status, abort_flag)) break;
+        const uint32_t s = i % kBwdStages, ph = (i / kBwdStages) & 1;
+        if (!mbar_wait(smem_u32(&b_empty[s]), ph ^ 1, p.status, abort_flag)) break;
         mbar_arrive_expect_tx(smem_u32(&b_full[s]), 2 * kStreamBytes);
         const int row = row_base + (t_begin + i) * kBt;
         const uint32_t dst = sB + s * 2 * kStreamBytes;
@@ -433,31 +447,33 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_qkv, const __grid_consta
       }
       for (int i = 0; i < T && ok; ++i) {
         if (i + 1 < T) {
-          const uint32_t s1 = (i + 1) & 1, ph1 = ((i + 1) >> 1) & 1;
-          if (!mbar_wait(smem_u32(&b_full[s1]), ph1, p.status, abort_flag)) { ok = false; break; }
+          const uint32_t b1 = (i + 1) % kBwdStages, bph1 = ((i + 1) / kBwdStages) & 1, t1 = (i + 1) & 1;
+          if (!mbar_wait(smem_u32(&b_full[b1]), bph1, p.status, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          mma_sdp(tmem_base + s1 * 128, sA0, sB + s1 * 2 * kStreamBytes);
-          mma_sdp(tmem_base + s1 * 128 + kBt, sA1, sB + s1 * 2 * kStreamBytes + kStreamBytes);
-          umma_commit(smem_u32(&sdp_full[s1]));
+          mma_sdp(tmem_base + t1 * 128, sA0, sB + b1 * 2 * kStreamBytes);
+          mma_sdp(tmem_base + t1 * 128 + kBt, sA1, sB + b1 * 2 * kStreamBytes + kStreamBytes);
+          umma_commit(smem_u32(&sdp_full[t1]));
         }
-        const uint32_t s = i & 1, ph = (i >> 1) & 1;
+        const uint32_t s = i & 1, ph = (i >> 1) & 1, bsi = i % kBwdStages;
         if (!mbar_wait(smem_u32(&p_full[s]), ph, p.status, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t bs = sB + s * 2 * kStreamBytes, ps = sP + s * 2 * kPBytes;
+        const uint32_t bs = sB + bsi * 2 * kStreamBytes, ps = sP + s * 2 * kPBytes;
         if (!DQ) mma_acc(tmem_acc0, ps, bs + kStreamBytes, i > 0);     // dV += P^T dO_t
         mma_acc(tmem_acc1, ps + kPBytes, bs, i > 0);                   // dK += dS^T Q_t   |   dQ += dS K_t
-        umma_commit(smem_u32(&stage_free[s]));
+        umma_commit(smem_u32(&b_empty[bsi]));
+        umma_commit(smem_u32(&p_free[s]));
       }
       if (ok) umma_commit(smem_u32(acc_done));
     }
   } else {
-    const int q = warp & 3;
+    const int q = warp & 3;                      // TMEM lane quadrant this warp may access
+    const int half = (warp - 2) >> 2;            // which 32 of the 64 streamed columns this thread handles
     const int r = q * 32 + lane;                 // stationary row inside the tile == TMEM lane
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const int stat_idx = r0 + r;
     const long long vec_base = ((long long)b * p.nH + h) * p.S;
     // DQ: this thread's own row statistics.  Otherwise the streamed rows' statistics go through
-    // shared memory: thread r fetches lse2 (r < 64) or delta (r >= 64) of streamed row (r & 63).
+    // shared memory: thread r of the first half fetches lse2 (r < 64) or delta (r >= 64) of streamed row (r & 63).
     float own_lse = 0.f, own_delta = 0.f;
     if (DQ && stat_idx < p.S) {
       own_lse = p.lse2[vec_base + stat_idx];
@@ -465,52 +481,60 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_qkv, const __grid_consta
     }
     auto fetch = [&](int t) -> float {
       const int idx = t * kBt + (r & 63);
-      if (DQ || idx >= p.S) return 0.f;
+      if (DQ || half != 0 || idx >= p.S) return 0.f;
       return (r < 64) ? p.lse2[vec_base + idx] : p.delta[vec_base + idx];
     };
     float next_val = fetch(t_begin);
-    if (!DQ) row_vals[r] = next_val;
+    if (!DQ && half == 0) row_vals[r] = next_val;
     bool ok = true;
     for (int i = 0; i < T; ++i) {
       const int t = t_begin + i;
       const uint32_t s = i & 1, ph = (i >> 1) & 1;
       if (i + 1 < T) next_val = fetch(t + 1);
       mbar_wait(smem_u32(&sdp_full[s]), ph, p.status, abort_flag);
-      if (i >= 2) mbar_wait(smem_u32(&stage_free[s]), ph ^ 1, p.status, abort_flag);
-      softmax_bar_sync();
-      if (*abort_flag) { ok = false; break; }
+      if (i >= 2) mbar_wait(smem_u32(&p_free[s]), ph ^ 1, p.status, abort_flag);
+      if (softmax_bar_or(*abort_flag != 0)) { ok = false; break; }
       tc_fence_after();
       const int c0 = t * kBt;                    // first streamed index of this tile
       // mask needed when the tile touches the diagonal or the end of the sequence
       const bool need_mask = DQ ? (c0 + kBt - 1 > r0) : (c0 < r0 + 128 || c0 + kBt > p.S);
       const float* rv = row_vals + s * 128;
       uint8_t* prow = smem + AttnBwdSmem::kP + s * 2 * kPBytes + r * 128;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      {
+        const int c = half;
         uint32_t sv[32], dv[32];
         tmem_ld_32x32b_x32(tmem_base + s * 128 + lane_off + c * 32, sv);
         tmem_ld_32x32b_x32(tmem_base + s * 128 + kBt + lane_off + c * 32, dv);
         tmem_ld_wait();
         uint32_t pp[16], dd[16];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pv[2], dsv[2];
+        for (int e = 0; e < 32; e += 4) {
+          float l4[4], d4[4];
+          if (DQ) {
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = c * 32 + e + u;
-            const float l2 = DQ ? own_lse : rv[col];
-            const float dl = DQ ? own_delta : rv[64 + col];
-            float pe = exp2f(__uint_as_float(sv[e + u]) * p.scale_log2 - l2);
-            float de = pe * (__uint_as_float(dv[e + u]) - dl) * p.scale;
+            for (int u = 0; u < 4; ++u) { l4[u] = own_lse; d4[u] = own_delta; }
+          } else {
+            const float4 a = *reinterpret_cast<const float4*>(rv + c * 32 + e);
+            const float4 bq = *reinterpret_cast<const float4*>(rv + 64 + c * 32 + e);
+            l4[0] = a.x; l4[1] = a.y; l4[2] = a.z; l4[3] = a.w;
+            d4[0] = bq.x; d4[1] = bq.y; d4[2] = bq.z; d4[3] = bq.w;
+          }
+          float pv[4], dsv[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            float pe = exp2f(__uint_as_float(sv[e + u]) * p.scale_log2 - l4[u]);
+            float de = pe * (__uint_as_float(dv[e + u]) - d4[u]) * p.scale;
             if (need_mask) {
-              const int sidx = c0 + col;
+              const int sidx = c0 + c * 32 + e + u;
               const bool valid = DQ ? (sidx <= stat_idx) : (sidx >= stat_idx && sidx < p.S);
               if (!valid) { pe = 0.f; de = 0.f; }
             }
             pv[u] = pe; dsv[u] = de;
           }
           pp[e >> 1] = pack_bf16x2(pv[0], pv[1]);
+          pp[(e >> 1) + 1] = pack_bf16x2(pv[2], pv[3]);
           dd[e >> 1] = pack_bf16x2(dsv[0], dsv[1]);
+          dd[(e >> 1) + 1] = pack_bf16x2(dsv[2], dsv[3]);
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -519,27 +543,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_qkv, const __grid_consta
           *reinterpret_cast<uint4*>(prow + kPBytes + phys) = make_uint4(dd[g * 4], dd[g * 4 + 1], dd[g * 4 + 2], dd[g * 4 + 3]);
         }
       }
-      if (!DQ && i + 1 < T) row_vals[(s ^ 1) * 128 + r] = next_val;
+      if (!DQ && half == 0 && i + 1 < T) row_vals[(s ^ 1) * 128 + r] = next_val;
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(smem_u32(&p_full[s]));
     }
     if (ok) {
       mbar_wait(smem_u32(acc_done), 0, p.status, abort_flag);
-      softmax_bar_sync();
-      ok = !*abort_flag;
+      ok = !softmax_bar_or(*abort_flag != 0);
     }
     if (ok && stat_idx < p.S) {
       tc_fence_after();
       __nv_bfloat16* grow = p.dqkv + (long long)(row_base + stat_idx) * p.ld_dqkv + h * kHd;
 #pragma unroll
       for (int a = (DQ ? 1 : 0); a < 2; ++a) {
-        // acc0 = dV (columns 2H..), acc1 = dK (columns H..) or dQ (columns 0..)
-        __nv_bfloat16* dst = grow + (DQ ? 0 : (a == 0 ? 2 * H : H));
+        // acc0 = dV (columns 2H..), acc1 = dK (columns H..) or dQ (columns 0..); each half stores 64 columns
+        __nv_bfloat16* dst = grow + (DQ ? 0 : (a == 0 ? 2 * H : H)) + half * 64;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t t4[32];
-          tmem_ld_32x32b_x32((a == 0 ? tmem_acc0 : tmem_acc1) + lane_off + c * 32, t4);
+          tmem_ld_32x32b_x32((a == 0 ? tmem_acc0 : tmem_acc1) + lane_off + half * 64 + c * 32, t4);
           tmem_ld_wait();
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
