@@ -108,6 +108,12 @@ class LlamaBlock(nn.Module):
         c = self.cfg
         return OF.BlockShape(batch, seq, c.hidden, c.n_heads, c.head_dim, c.ffn, c.eps, c.rope_theta)
 
+    def mfsdp_fuses_first_gemm(self, x: torch.Tensor, *a, **k) -> bool:
+        """Asked by the FSDP unit before forward: will this call run the QKV GEMM that can take the
+        q|k|v rows of the all-gather?  (The unit's parameters are bf16 once unsharded.)"""
+        return x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3 and self.cfg.hidden % 8 == 0 \
+            and self.cfg.ffn % 8 == 0 and not OF._lib.disabled_by_env()
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """``x``: [B, S, H]."""
         b, s, h = x.shape
@@ -177,6 +183,23 @@ class LlamaModel(nn.Module):
         return 3.0 * (c.n_layers * (per_layer + attn) + head)
 
 
+def _mark_fused_first_gemm(layer: LlamaBlock) -> None:
+    """Tell the layer's FSDP unit which rows of its flat buffer (q|k|v, when adjacent) the block's first
+    GEMM reads, so a transport that can may deliver them inside that GEMM (``MFSDP_FUSED_AG_GEMM=0`` disables)."""
+    import os
+
+    unit = getattr(layer, "_matrix_fsdp_param_group", None)
+    if unit is None or os.environ.get("MFSDP_FUSED_AG_GEMM", "1") == "0":
+        return
+    by_fqn = {mp.fqn: mp for mp in unit.registry}
+    try:
+        q, k, v = (by_fqn[n] for n in ("wq.weight", "wk.weight", "wv.weight"))
+    except KeyError:
+        return
+    if q.offset + q.numel == k.offset and k.offset + k.numel == v.offset and q.offset % 8 == 0:
+        unit.fused_first_gemm_range = (q.offset, v.offset + v.numel, layer.cfg.hidden)
+
+
 def shard_llama(model: LlamaModel, *, mesh=None, dp_mesh_dims=None, mp_policy=None, optimizer_policy=None,
                 reshard_after_forward=None, shard_root: bool = True, **kw) -> LlamaModel:
     """``fully_shard`` every block, then the root (embedding, final norm, LM head)."""
@@ -188,6 +211,7 @@ def shard_llama(model: LlamaModel, *, mesh=None, dp_mesh_dims=None, mp_policy=No
     for layer in model.layers:
         fully_shard(layer, mesh=mesh, dp_mesh_dims=dp_mesh_dims, mp_policy=mp, optimizer_policy=optimizer_policy,
                     reshard_after_forward=reshard_after_forward, **kw)
+        _mark_fused_first_gemm(layer)
     if shard_root:
         hints = None
         if optimizer_policy is not None:

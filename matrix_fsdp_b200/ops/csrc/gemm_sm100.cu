@@ -46,7 +46,21 @@ struct GemmArgs {
   int b_group_stride;        // mode 1: rows added to B's row coordinate per group
   int tiles_m_per_group;     // mode 2
   int m_per_group;           // mode 2
+  // Fused all-gather (GATHER kernels only): B's rows are still on peer GPUs when the kernel starts.
+  // Four extra warps per CTA copy them into B's local buffer job by job (16-byte peer loads, local
+  // stores) and count finished jobs per B tile row-block; the TMA producer waits (bounded) until
+  // the row-block of its tile is complete before loading it.
+  const unsigned long long* ag_src;   // [njobs] peer (or local) source address
+  const unsigned long long* ag_dst;   // [njobs] destination address inside B's local buffer
+  const int* ag_bytes;                // [njobs] multiple of 16
+  const int* ag_flag;                 // [njobs] B row-block (tile column) the job belongs to
+  int ag_njobs;
+  unsigned* ag_flags;                 // [tiles_n] zero at launch
+  const int* ag_need;                 // [tiles_n] jobs per row-block
+  unsigned long long ag_budget_ns;
 };
+
+constexpr int kGatherThreads = 128;
 
 template <int BN>
 struct GemmCfg {
@@ -105,8 +119,8 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, int tile) {
   return c;
 }
 
-template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int BN, bool A_MN, bool B_MN, bool GATHER = false>
+__global__ void __launch_bounds__(GATHER ? kGemmThreads + kGatherThreads : kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
                          const __grid_constant__ CUtensorMap tma_b,
                          const __grid_constant__ CUtensorMap tma_d, const GemmArgs p) {
@@ -162,6 +176,26 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
         TileCoord c = decode_tile(p, tile);
         if (c.skip) continue;
         const int n0 = c.n0 * BN;
+        if (GATHER) {
+          // rows [n0, n0 + BN) of B must have landed in local memory (written by gather warps of
+          // any CTA through the generic proxy) before the async proxy reads them
+          const unsigned need = (unsigned)p.ag_need[c.n0];
+          const unsigned* flag = p.ag_flags + c.n0;
+          const uint64_t t0 = globaltimer_ns();
+          uint32_t spins = 0;
+          while (ld_acquire_gpu_u32(flag) < need) {
+            if ((++spins & 0xff) == 0) {
+              if (*abort_flag || globaltimer_ns() - t0 > p.ag_budget_ns) {
+                *abort_flag = 1;
+                if (p.status) atomicCAS(p.status, 0, (int)kErrPeerFlagTimeout);
+                ok = false;
+                break;
+              }
+            }
+          }
+          if (!ok) break;
+          fence_proxy_async_all();
+        }
         for (int kb = 0; kb < c.nkb; ++kb, ++it) {
           const uint32_t s = it % kStages, ph = (it / kStages) & 1;
           if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, p.status, abort_flag)) { ok = false; break; }
@@ -219,6 +253,24 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
         umma_commit(smem_u32(&tfull_bar[acc]));
         ++lt;
       }
+    }
+  } else if (GATHER && warp >= 6) {
+    // ------------------------------------------------------------ gather warps (never wait on anything)
+    const int gt = threadIdx.x - kGemmThreads;
+    for (int j = blockIdx.x; j < p.ag_njobs; j += gridDim.x) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.ag_src[j]);
+      uint4* dst = reinterpret_cast<uint4*>(p.ag_dst[j]);
+      const int nvec = p.ag_bytes[j] >> 4;
+      int i = gt;
+      for (; i + 3 * kGatherThreads < nvec; i += 4 * kGatherThreads) {
+        const uint4 a = src[i], b = src[i + kGatherThreads], c = src[i + 2 * kGatherThreads],
+                    d = src[i + 3 * kGatherThreads];
+        dst[i] = a; dst[i + kGatherThreads] = b; dst[i + 2 * kGatherThreads] = c; dst[i + 3 * kGatherThreads] = d;
+      }
+      for (; i < nvec; i += kGatherThreads) dst[i] = src[i];
+      __threadfence();
+      asm volatile("bar.sync 3, 128;" ::: "memory");
+      if (gt == 0) red_release_gpu_add_u32(p.ag_flags + p.ag_flag[j], 1u);
     }
   } else {
     // ------------------------------------------------------------ epilogue
@@ -352,19 +404,19 @@ int make_tmap_bf16_2d(CUtensorMap* map, const void* base, long long rows, long l
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool GATHER = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
                        const GemmArgs& args, int grid, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   static bool attr_set = false;
-  auto kern = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN, GATHER>;
   if (!attr_set) {
     cudaError_t e =
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, td, args);
+  kern<<<grid, GATHER ? kGemmThreads + kGatherThreads : kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, td, args);
   return (int)cudaGetLastError();
 }
 
@@ -456,4 +508,46 @@ MFSDP_API int mfsdp_gemm_bf16(const void* A, const void* B, void* D, const void*
                             : launch_gemm<BN_, false, false>(ta, tb, td, args, grid, stream)))
   return bn == 256 ? MFSDP_LAUNCH(256) : MFSDP_LAUNCH(128);
 #undef MFSDP_LAUNCH
+}
+
+// All-gather fused into the GEMM that first consumes the gathered weight:
+//   D[M,N] = alpha * A[M,K] * B[N,K]^T + beta * Cin,  B row-major and contiguous (ldb == K),
+// where (parts of) B are not in local memory yet.  `njobs` copy jobs (device tables) bring them in
+// from peer memory with plain 16-byte loads while the tensor-core tiles whose B rows already
+// arrived run; ag_flag[j] names the bn-row block of B that job j belongs to and ag_need[b] is the
+// number of jobs of block b (0 for blocks that are already local).  `flags` (tiles_n words) must be
+// zero.  Returns the tile width used through *bn_out when called with njobs < 0 (planning call).
+MFSDP_API int mfsdp_gemm_bf16_ag(const void* A, const void* B, void* D, const void* Cin, int M, int N, int K,
+                                 long long lda, long long ldd, long long ldcin, float alpha, float beta,
+                                 const unsigned long long* ag_src, const unsigned long long* ag_dst,
+                                 const int* ag_bytes, const int* ag_flag, int njobs, unsigned* flags,
+                                 const int* ag_need, int bn, unsigned long long budget_ns, int* status,
+                                 int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (bn != 128 && bn != 256) || njobs < 0) return -2;
+  cudaFree(nullptr);
+  if ((lda % 8) || (K % 8) || (ldd % 8)) return -2;
+  if (((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)D & 15)) return -2;
+  GemmArgs args{};
+  args.M = M; args.N = N; args.K = K;
+  args.alpha = alpha; args.beta = beta;
+  args.cin = (const __nv_bfloat16*)Cin; args.ldcin = ldcin;
+  args.status = status;
+  args.group_mode = 0;
+  args.m_per_group = M;
+  args.tiles_m = (M + BM - 1) / BM;
+  args.tiles_m_per_group = args.tiles_m;
+  args.tiles_n = (N + bn - 1) / bn;
+  args.ag_src = ag_src; args.ag_dst = ag_dst; args.ag_bytes = ag_bytes; args.ag_flag = ag_flag;
+  args.ag_njobs = njobs; args.ag_flags = flags; args.ag_need = ag_need; args.ag_budget_ns = budget_ns;
+  CUtensorMap ta, tb, td;
+  int rc = make_tmap_bf16_2d(&ta, A, M, K, lda, BM, 64);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tb, B, N, K, K, bn, 64);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&td, D, M, N, ldd, BM, 64);
+  if (rc) return rc;
+  const int total = args.tiles_m * args.tiles_n;
+  const int grid = total < num_sms ? total : num_sms;
+  return bn == 256 ? launch_gemm<256, false, false, true>(ta, tb, td, args, grid, stream)
+                   : launch_gemm<128, false, false, true>(ta, tb, td, args, grid, stream);
 }

@@ -294,7 +294,7 @@ class DecoderBlockFunction(torch.autograd.Function):
     def forward(ctx, x, cos, sin, bp: BlockParams, shape: BlockShape, recompute: bool, *weights):
         ctx.bp, ctx.shape, ctx.recompute = bp, shape, recompute
         x = x.contiguous()
-        acts = DecoderBlockFunction._forward_impl(x, cos, sin, weights, shape)
+        acts = DecoderBlockFunction._forward_impl(x, cos, sin, weights, shape, bp)
         out = acts["out"]
         if recompute:
             ctx.save_for_backward(x, cos, sin, *weights)
@@ -305,7 +305,7 @@ class DecoderBlockFunction(torch.autograd.Function):
         return out
 
     @staticmethod
-    def _forward_impl(x, cos, sin, weights, s: BlockShape) -> dict:
+    def _forward_impl(x, cos, sin, weights, s: BlockShape, bp: "BlockParams | None" = None) -> dict:
         from . import kernels as K
 
         wn1, wq, wk, wv, wo, wn2, wg, wu, wd = weights
@@ -313,7 +313,11 @@ class DecoderBlockFunction(torch.autograd.Function):
         xn, rstd1 = K.rmsnorm_fwd(x, wn1, s.eps)
         qkv = torch.empty((T, 3 * H), dtype=x.dtype, device=x.device)
         wqkv = _fused_weight([wq, wk, wv])
-        if wqkv is not None:
+        plan = _take_deferred_gather(bp, wqkv) if bp is not None else None
+        if plan is not None:
+            # the q|k|v rows of this unit's all-gather arrive inside this GEMM
+            K.gemm_ag(xn, wqkv, plan, out=qkv)
+        elif wqkv is not None:
             K.gemm(xn, wqkv, out=qkv)
         else:
             for i, w in enumerate((wq, wk, wv)):
@@ -385,6 +389,18 @@ class DecoderBlockFunction(torch.autograd.Function):
         del dqkv
         dx, grads[0] = _norm_bwd(dxn, x, wn1, acts["rstd1"], dx1, bp.sink(0))
         return (dx, None, None, None, None, None, *grads)
+
+
+def _take_deferred_gather(bp: "BlockParams", wqkv: torch.Tensor | None):
+    """Plan of the all-gather rows that the owning FSDP unit left to the QKV GEMM, if any."""
+    ref = getattr(bp.params[1], "_matrix_fsdp_param_group_ref", None)
+    unit = ref() if ref is not None else None
+    if unit is None or unit.flat_buffer.deferred_gather is None:
+        return None
+    if wqkv is None:
+        unit.flat_buffer.complete_deferred_gather()
+        return None
+    return unit.flat_buffer.take_deferred_gather(wqkv)
 
 
 def _norm_bwd(dy, x, w, rstd, dres, sink: GradSink):

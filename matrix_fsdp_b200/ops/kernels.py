@@ -104,6 +104,31 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     return out
 
 
+def gemm_ag(a: torch.Tensor, b: torch.Tensor, plan, *, out: torch.Tensor | None = None,
+            cin: torch.Tensor | None = None, alpha: float = 1.0, beta: float = 0.0) -> torch.Tensor:
+    """``out = alpha * a·bᵀ + beta * cin`` where rows of ``b`` ([N, K], contiguous) are still on peer GPUs.
+
+    ``plan`` (see ``parallel.peer.DeferredGather``) lists the copy jobs that bring them into ``b``'s
+    local storage; the kernel runs them on four extra warps per CTA while tiles whose rows have
+    arrived are multiplied.
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and b.is_contiguous() and a.stride(1) == 1
+    M, Kd = a.shape
+    N = b.shape[0]
+    assert b.shape[1] == Kd and b.data_ptr() == plan.b_ptr and plan.bn in (128, 256)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    plan.flags.zero_()
+    rc = _L().mfsdp_gemm_bf16_ag(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), cin.data_ptr() if cin is not None else None, M, N, Kd,
+        a.stride(0), out.stride(0), cin.stride(0) if cin is not None else 0, alpha, beta,
+        plan.src.data_ptr(), plan.dst.data_ptr(), plan.nbytes.data_ptr(), plan.flag_idx.data_ptr(), plan.njobs,
+        plan.flags.data_ptr(), plan.need.data_ptr(), plan.bn, int(plan.budget_ns),
+        status_word(a.device).data_ptr(), sm_count(a.device), _stream())
+    _lib.check(rc, "mfsdp_gemm_bf16_ag")
+    return out
+
+
 def grouped_gemm_m(a: torch.Tensor, b: torch.Tensor, tile_group: torch.Tensor, *,
                    b_mn_major: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
     """M-grouped GEMM: rows of ``a`` come in 128-row tiles, tile ``t`` uses ``b[tile_group[t]]``.

@@ -151,6 +151,7 @@ class MatrixFlatBuffer:
         # a callable returning the update arguments for this reduction, or None to reduce normally.
         self.fused_reduce_update = None
         self.fused_update_applied = False
+        self.deferred_gather = None          # plan of the all-gather rows left to the first consumer GEMM
 
     # ------------------------------------------------------------------ helpers
     def _bucket_dtype(self) -> torch.dtype:
@@ -218,7 +219,9 @@ class MatrixFlatBuffer:
                 self.local_shard_lp.copy_(self.local_shard)
             self.lp_stale = False
 
-    def start_all_gather_full_params(self, *, stream=None) -> MatrixCollectiveHandle:
+    def start_all_gather_full_params(self, *, stream=None, defer: tuple | None = None) -> MatrixCollectiveHandle:
+        """``defer`` = (lo, hi, row_len): leave that range of the full buffer to the GEMM that reads it
+        first (transports that can; the plan is then in ``self.deferred_gather``)."""
         if self.pending_gather is not None:
             return self.pending_gather
         self.refresh_low_precision_shard()
@@ -227,23 +230,51 @@ class MatrixFlatBuffer:
                                              "count": 0, "sync_mode": "local", "materialization": "alias"})
         else:
             self._materialize_full()
-            h = self.transport.gather(self._gather_source_tensor(), self.full_buffer, self.tables, stream=stream,
-                                      unit_key=self.unit_key)
+            if defer is not None and getattr(self.transport, "supports_deferred_gather", False) \
+                    and self.full_buffer.dtype == torch.bfloat16:
+                h = self.transport.gather(self._gather_source_tensor(), self.full_buffer, self.tables, stream=stream,
+                                          unit_key=self.unit_key, defer=defer)
+                self.deferred_gather = getattr(h, "deferred", None)
+            else:
+                h = self.transport.gather(self._gather_source_tensor(), self.full_buffer, self.tables, stream=stream,
+                                          unit_key=self.unit_key)
             h.info.setdefault("materialization", "storage_resize")
         self.full_materialized = True
         self.pending_gather = h
         return h
 
-    def wait_all_gather(self) -> MatrixCollectiveHandle | None:
+    def wait_all_gather(self, *, keep_deferred: bool = False) -> MatrixCollectiveHandle | None:
         h, self.pending_gather = self.pending_gather, None
         if h is not None:
             h.wait()
+        if not keep_deferred:
+            self.complete_deferred_gather()
         return h
+
+    def complete_deferred_gather(self) -> None:
+        """Nobody will fuse the deferred rows into a GEMM: copy them now (current stream)."""
+        plan, self.deferred_gather = self.deferred_gather, None
+        if plan is not None:
+            plan.complete()
+
+    def take_deferred_gather(self, weight: torch.Tensor):
+        """Hand the deferred plan to the GEMM whose B operand is exactly the deferred weight."""
+        plan = self.deferred_gather
+        if plan is None:
+            return None
+        if weight.data_ptr() != plan.b_ptr or weight.numel() != plan.hi - plan.lo or not weight.is_contiguous():
+            self.complete_deferred_gather()
+            return None
+        self.deferred_gather = None
+        return plan
 
     def clear_full_params(self) -> None:
         """Drop the unsharded storage (params must already point at local views)."""
         if self.pending_gather is not None:
             self.wait_all_gather()
+        if self.deferred_gather is not None:
+            self.deferred_gather = None
+            raise RuntimeError("rows of the all-gather were left to a fused GEMM that never ran")
         self._shrink_full()
         self.full_materialized = self.full_aliases_shard
 

@@ -136,6 +136,9 @@ class MatrixFSDPParamGroup:
         self.backward_reduce_strategy = backward_reduce_strategy
         self.runtime_layout_policy = runtime_layout_policy
         self.runtime_trace_enabled = runtime_trace_enabled
+        # (lo, hi, row_len) of the weight whose all-gather may be fused into the block's first GEMM
+        self.fused_first_gemm_range: tuple | None = None
+        self._module_fuses_first_gemm = False
         self.use_saved_tensor_hooks = use_saved_tensor_hooks
         self.use_zero_copy_grad_bucket = use_zero_copy_grad_bucket
         self.shrink_full_param_storage_after_backward = shrink_full_param_storage_after_backward
@@ -330,7 +333,11 @@ class MatrixFSDPParamGroup:
         if self.scheduler is not None:
             self.scheduler.wait_for_post_optimizer_event_before_all_gather(self)
             self.scheduler.note_unshard_started(self)
-        h = self.flat_buffer.start_all_gather_full_params(stream=self.all_gather_stream)
+        defer = None
+        if "backward" not in reason and getattr(self, "fused_first_gemm_range", None) is not None \
+                and not _in_backward() and torch.is_grad_enabled():
+            defer = self.fused_first_gemm_range
+        h = self.flat_buffer.start_all_gather_full_params(stream=self.all_gather_stream, defer=defer)
         self.unshard_prefetched = reason.endswith("prefetch")
         self._record(f"start_unshard:{reason}", start=t0, handle=h, reason=reason, prefetched=self.unshard_prefetched)
 
@@ -340,7 +347,8 @@ class MatrixFSDPParamGroup:
             return
         if self.flat_buffer.pending_gather is None:
             self.start_unshard(reason)
-        h = self.flat_buffer.wait_all_gather()
+        # rows left to the block's first GEMM stay pending only when the module said it will run that GEMM
+        h = self.flat_buffer.wait_all_gather(keep_deferred=(reason == "pre_forward" and self._module_fuses_first_gemm))
         self.flat_buffer.use_full_param_buffer()
         self._transition(FSDPLifecycleState.UNSHARDED)
         self._record(f"wait_unshard:{reason}", start=t0, handle=h, reason=reason)
@@ -395,8 +403,11 @@ class MatrixFSDPParamGroup:
         self.flat_buffer.stash_local_grads_for_accumulation()
         self.used_in_forward = True
         self.finalized_after_backward = False
+        probe = getattr(module, "mfsdp_fuses_first_gemm", None)
+        self._module_fuses_first_gemm = bool(probe(*args, **kwargs)) if probe is not None else False
         self.start_unshard("pre_forward")
         self.wait_unshard("pre_forward")
+        self._module_fuses_first_gemm = False
         if self.scheduler is not None:
             self.scheduler.on_pre_forward(self)
         mp = self.mp_policy

@@ -176,6 +176,73 @@ class PeerContext:
                                             self.status.data_ptr(), _stream_handle(stream)), "peer_wait")
 
 
+class DeferredGather:
+    """The part of a unit's all-gather that is left to the GEMM which first reads it.
+
+    ``[lo, hi)`` (elements of the full buffer) holds a row-major ``[N, K]`` weight.  The copy jobs are
+    grouped by the GEMM's ``bn``-row blocks of that weight; ``need[b]`` is the number of jobs of block b.
+    ``complete()`` performs the same copies with the plain pull kernel instead.
+    """
+
+    MAX_JOB_BYTES = 256 * 1024
+
+    def __init__(self, transport: "PeerTransport", shard_buf: SymBuffer, tables: SegmentTables, full: torch.Tensor,
+                 lo: int, hi: int, k: int) -> None:
+        es = full.element_size()
+        assert es == 2 and (hi - lo) % k == 0 and lo % 8 == 0 and k % 8 == 0
+        n = (hi - lo) // k
+        self.lo, self.hi, self.k, self.n = lo, hi, k, n
+        self.bn = 256 if n > 128 else 128
+        self.b_ptr = full.data_ptr() + lo * es
+        self.full_ptr = full.data_ptr()
+        self.budget_ns = transport.ctx.timeout_ns
+        self.lib = transport.ctx.lib
+        block = self.bn * k
+        nblocks = (n + self.bn - 1) // self.bn
+        src, dst, nbytes, flag = [], [], [], []
+        psrc, pdst, plen = [], [], []
+        need = [0] * nblocks
+        max_elems = self.MAX_JOB_BYTES // es
+        for r, segs in enumerate(tables.rank_segments):
+            for sg in segs:
+                g0, g1 = max(sg.global_start, lo), min(sg.global_start + sg.numel, hi)
+                if g0 >= g1:
+                    continue
+                psrc.append(shard_buf.peer_addr[r] + (sg.local_start + g0 - sg.global_start) * es)
+                pdst.append(g0)
+                plen.append(g1 - g0)
+                cur = g0
+                while cur < g1:
+                    b = (cur - lo) // block
+                    end = min(g1, lo + (b + 1) * block, cur + max_elems)
+                    src.append(shard_buf.peer_addr[r] + (sg.local_start + cur - sg.global_start) * es)
+                    dst.append(full.data_ptr() + cur * es)
+                    nbytes.append((end - cur) * es)
+                    flag.append(b)
+                    need[b] += 1
+                    cur = end
+        if any(x % 16 for x in src + dst + nbytes):
+            raise ValueError("deferred gather pieces are not 16-byte aligned")
+        # jobs in block order, so the tiles scheduled first find their rows first
+        order = sorted(range(len(src)), key=lambda i: flag[i])
+        dev = full.device
+        i64 = lambda xs: torch.tensor(xs, dtype=torch.int64, device=dev)          # noqa: E731
+        i32 = lambda xs: torch.tensor(xs, dtype=torch.int32, device=dev)          # noqa: E731
+        self.src, self.dst = i64([src[i] for i in order]), i64([dst[i] for i in order])
+        self.nbytes, self.flag_idx = i32([nbytes[i] for i in order]), i32([flag[i] for i in order])
+        self.njobs = len(order)
+        self.need = i32(need)
+        self.flags = torch.zeros(nblocks, dtype=torch.int32, device=dev)
+        self._plain = {"src": i64(psrc), "dst": i64(pdst), "len": i64(plen), "n": len(psrc), "max": max(plen, default=0)}
+
+    def complete(self, stream=None) -> None:
+        """Copy the deferred rows with the plain pull kernel (nobody fused them into a GEMM)."""
+        t = self._plain
+        run = stream if stream is not None else torch.cuda.current_stream()
+        _lib.check(self.lib.mfsdp_ag_pull(self.full_ptr, t["src"].data_ptr(), t["dst"].data_ptr(), t["len"].data_ptr(),
+                                          t["n"], t["max"], 2, run.cuda_stream), "ag_pull")
+
+
 class _Slot:
     __slots__ = ("buf", "held", "last_unit", "last_epoch", "event")
 
@@ -300,7 +367,35 @@ class PeerTransport(LocalTransport):
             self._tables[key] = t
         return t
 
-    def gather(self, shard, full, tables: SegmentTables, *, stream=None, unit_key=None) -> MatrixCollectiveHandle:
+    supports_deferred_gather = True
+
+    def _deferred_tables(self, unit_key, shard_buf: SymBuffer, tables: SegmentTables, full, defer) -> tuple:
+        """(plan for the deferred range, pull tables for everything else), cached per unit."""
+        lo, hi, k = defer
+        key = ("ag_defer", unit_key, shard_buf.tensor.data_ptr(), full.data_ptr(), lo, hi, k)
+        hit = self._tables.get(key)
+        if hit is None:
+            es = full.element_size()
+            plan = DeferredGather(self, shard_buf, tables, full, lo, hi, k)
+            src, dst, ln = [], [], []
+            for r, segs in enumerate(tables.rank_segments):
+                for sg in segs:
+                    g0, g1 = sg.global_start, sg.global_start + sg.numel
+                    for a, b in ((g0, min(g1, lo)), (max(g0, hi), g1)):
+                        if a < b:
+                            src.append(shard_buf.peer_addr[r] + (sg.local_start + a - g0) * es)
+                            dst.append(a)
+                            ln.append(b - a)
+            dev = full.device
+            rest = {"src": torch.tensor(src, dtype=torch.int64, device=dev),
+                    "dst": torch.tensor(dst, dtype=torch.int64, device=dev),
+                    "len": torch.tensor(ln, dtype=torch.int64, device=dev), "n": len(src), "max": max(ln, default=0)}
+            hit = (plan, rest)
+            self._tables[key] = hit
+        return hit
+
+    def gather(self, shard, full, tables: SegmentTables, *, stream=None, unit_key=None,
+               defer: tuple | None = None) -> MatrixCollectiveHandle:
         buf = self.ctx.lookup(shard)
         if buf is None:
             raise RuntimeError("peer gather needs a shard that lives in symmetric memory")
@@ -309,7 +404,11 @@ class PeerTransport(LocalTransport):
         ep["shard"] += 1
         e = ep["shard"]
         es = full.element_size()
-        t = self._gather_tables(unit_key, buf, tables, es, full.device)
+        plan = None
+        if defer is not None and es == 2:
+            plan, t = self._deferred_tables(unit_key, buf, tables, full, defer)
+        else:
+            t = self._gather_tables(unit_key, buf, tables, es, full.device)
         cur = torch.cuda.current_stream()
         run = stream if stream is not None else cur
         if stream is not None:
@@ -323,9 +422,12 @@ class PeerTransport(LocalTransport):
         if stream is not None:
             ev = torch.cuda.Event()
             ev.record(stream)
-        return MatrixCollectiveHandle(event=ev, info={
-            "kind": "all_gather", "impl": "ag_pull", "backend": self.kind, "bytes": full.numel() * es, "count": 1,
+        h = MatrixCollectiveHandle(event=ev, info={
+            "kind": "all_gather", "impl": "ag_pull+gemm" if plan is not None else "ag_pull", "backend": self.kind,
+            "bytes": full.numel() * es, "count": 1,
             "sync_mode": "stream_event" if stream is not None else "stream_order"})
+        h.deferred = plan
+        return h
 
     # ------------------------------------------------------------------ reduce
     def _reduce_tables(self, unit_key, tables: SegmentTables, device) -> dict:

@@ -29,7 +29,8 @@ def _hb_worker(rank, world, path, result_dir):
                 outcome = "left"
                 break
             time.sleep(0.4)
-            health.assert_alive()
+            if rank != 2:                                           # the rank that will crash only beats
+                health.assert_alive()
     except RankFailure as exc:
         outcome = f"detected:{sorted(exc.missing)}:{exc.reason}"
         health.leave("stopped after a peer failure")

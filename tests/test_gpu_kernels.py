@@ -244,3 +244,47 @@ def test_copy_segments_and_cast(K):
     b = torch.empty(4099, device="cuda", dtype=torch.bfloat16)
     K.cast_f32_bf16(f, b)
     assert torch.equal(b, f.bfloat16())
+
+
+def test_gemm_with_fused_gather_single_gpu():
+    """The all-gather-fused GEMM with its copy jobs reading from a second local buffer: rows of B
+    arrive through the kernel's gather warps while tiles are computed."""
+    from types import SimpleNamespace
+
+    from matrix_fsdp_b200.ops import kernels as K
+
+    torch.manual_seed(0)
+    M, N, Kd, bn = 1024, 1536, 512, 256
+    a = (torch.randn(M, Kd, device="cuda") * 0.1).bfloat16()
+    src = (torch.randn(N, Kd, device="cuda") * 0.1).bfloat16()       # stands in for the peers' shards
+    b = torch.zeros(N, Kd, device="cuda", dtype=torch.bfloat16)
+    b[:300] = src[:300]                                              # some rows are already local
+    nblocks = (N + bn - 1) // bn
+    jobs, need = [], [0] * nblocks
+    row = 300
+    while row < N:
+        blk = row // bn
+        end = min(N, (blk + 1) * bn, row + 100)
+        jobs.append((src.data_ptr() + row * Kd * 2, b.data_ptr() + row * Kd * 2, (end - row) * Kd * 2, blk))
+        need[blk] += 1
+        row = end
+    dev = "cuda"
+    plan = SimpleNamespace(
+        b_ptr=b.data_ptr(), bn=bn, njobs=len(jobs), budget_ns=int(2e9),
+        src=torch.tensor([j[0] for j in jobs], dtype=torch.int64, device=dev),
+        dst=torch.tensor([j[1] for j in jobs], dtype=torch.int64, device=dev),
+        nbytes=torch.tensor([j[2] for j in jobs], dtype=torch.int32, device=dev),
+        flag_idx=torch.tensor([j[3] for j in jobs], dtype=torch.int32, device=dev),
+        need=torch.tensor(need, dtype=torch.int32, device=dev),
+        flags=torch.zeros(nblocks, dtype=torch.int32, device=dev))
+    out = K.gemm_ag(a, b, plan)
+    torch.cuda.synchronize()
+    K.check_status()
+    assert torch.equal(b, src)
+    ref = a.float() @ src.float().t()
+    assert (out.float() - ref).abs().max().item() < 2e-2
+    # a second call with the rows in place and no jobs is a plain GEMM
+    plan.njobs, plan.need = 0, torch.zeros(nblocks, dtype=torch.int32, device=dev)
+    out2 = K.gemm_ag(a, b, plan)
+    torch.cuda.synchronize()
+    assert torch.equal(out2, out)
