@@ -18,6 +18,7 @@ Parity: ``matrix_fsdp/runtime/fsdp_unit.py:63-1773``.
 """
 from __future__ import annotations
 
+import os
 import time
 import weakref
 from collections.abc import Callable, Mapping
@@ -333,9 +334,12 @@ class MatrixFSDPParamGroup:
         if self.scheduler is not None:
             self.scheduler.wait_for_post_optimizer_event_before_all_gather(self)
             self.scheduler.note_unshard_started(self)
+        # Fuse the q|k|v rows into the block's first GEMM when the gather is on the critical path (issued by
+        # the forward that needs it); a prefetched gather is already hidden behind the previous block.
         defer = None
         if "backward" not in reason and getattr(self, "fused_first_gemm_range", None) is not None \
-                and not _in_backward() and torch.is_grad_enabled():
+                and not _in_backward() and torch.is_grad_enabled() \
+                and (not reason.endswith("prefetch") or os.environ.get("MFSDP_FUSED_AG_GEMM", "exposed") == "always"):
             defer = self.fused_first_gemm_range
         h = self.flat_buffer.start_all_gather_full_params(stream=self.all_gather_stream, defer=defer)
         self.unshard_prefetched = reason.endswith("prefetch")

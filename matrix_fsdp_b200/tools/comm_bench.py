@@ -59,12 +59,93 @@ def time_op(fn, iters: int, warmup: int = 3) -> float:
     return float(t.item())
 
 
+def fused_paths(peer, tables: SegmentTables, args, world: int, dev) -> list[dict]:
+    """Fused kernels against their unfused sequences, with roofline fractions.
+
+    AG+GEMM: the q|k|v rows ([3H, H] at element offset H of the block) arrive inside the QKV GEMM of a
+    ``tokens x H`` activation.  Roofline = max(GEMM FLOPs / sustained GEMM rate, remote bytes / link rate).
+    RS+AdamW: reduce-scatter with the sharded AdamW update applied in the same kernel.  Roofline =
+    bytes pulled over NVLink / link rate (the optimizer traffic is local HBM, an order of magnitude faster).
+    """
+    from ..ops import kernels as K
+
+    rank = dist.get_rank()
+    h, t = args.hidden, args.tokens
+    lo, hi = h, h + 3 * h * h
+    n_local = tables.shard_sizes[rank]
+    key = "bench_fused"
+    shard = peer.alloc_persistent(n_local, torch.bfloat16, dev, "shard", symmetric_numel=tables.max_shard)
+    shard.normal_(0, 0.02)
+    full = torch.empty(args.numel, dtype=torch.bfloat16, device=dev)
+    x = (torch.randn(t, h, device=dev) * 0.1).bfloat16()
+    out = torch.empty(t, 3 * h, dtype=torch.bfloat16, device=dev)
+    w = full[lo:hi].view(3 * h, h)
+    res = []
+
+    def unfused():
+        peer.gather(shard, full, tables, unit_key=key).wait()
+        K.gemm(x, w, out=out)
+
+    def fused():
+        hd = peer.gather(shard, full, tables, unit_key=key, defer=(lo, hi, h))
+        hd.wait()
+        K.gemm_ag(x, w, hd.deferred, out=out)
+
+    def gather_rest_only():
+        peer.gather(shard, full, tables, unit_key=key, defer=(lo, hi, h)).wait()
+
+    def gemm_only():
+        K.gemm(x, w, out=out)
+
+    ms_u, ms_f = time_op(unfused, args.iters), time_op(fused, args.iters)
+    ms_rest, ms_gemm = time_op(gather_rest_only, args.iters), time_op(gemm_only, args.iters)
+    flops = 2.0 * t * 3 * h * h
+    remote = sum(max(0, min(s.global_start + s.numel, hi) - max(s.global_start, lo))
+                 for r, segs in enumerate(tables.rank_segments) if r != rank for s in segs) * 2
+    roof_ms = max(flops / (args.gemm_tflops * 1e12), remote / (NVLINK_PEER_GBS * 1e9)) * 1e3
+    fused_part = ms_f - ms_rest
+    res.append({"op": "ag+gemm", "unfused_ms": ms_u, "fused_ms": ms_f, "gather_of_other_rows_ms": ms_rest,
+                "gemm_alone_ms": ms_gemm, "fused_gemm_part_ms": fused_part, "roofline_ms": roof_ms,
+                "frac_of_roofline": roof_ms / fused_part if fused_part > 0 else None,
+                "remote_mb": remote / 2 ** 20, "gflop": flops / 1e9})
+
+    grad = peer.acquire_grad_buffer(key, args.numel, torch.bfloat16, dev)
+    grad.normal_(0, 1e-3)
+    p = torch.zeros(n_local, dtype=torch.float32, device=dev)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    lp = torch.zeros(n_local, dtype=torch.bfloat16, device=dev)
+    g = torch.empty(n_local, dtype=torch.float32, device=dev)
+    hp = dict(lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1)
+    step = [0]
+
+    def rs_then_adamw():
+        step[0] += 1
+        peer.reduce(grad, g, tables, scale=1.0 / world, unit_key=key).wait()
+        K.adamw_flat_(p, m, v, g, step=step[0], p_lp=lp, **hp)
+
+    def rs_adamw_fused():
+        step[0] += 1
+        peer.reduce_update(grad, tables, dict(p=p, m=m, v=v, p_lp=lp, step=step[0], **hp), scale=1.0 / world,
+                           unit_key=key).wait()
+
+    ms_u, ms_f = time_op(rs_then_adamw, args.iters), time_op(rs_adamw_fused, args.iters)
+    pulled = (world - 1) * n_local * 2
+    roof_ms = pulled / (NVLINK_PEER_GBS * 1e9) * 1e3
+    res.append({"op": "rs+adamw", "unfused_ms": ms_u, "fused_ms": ms_f, "roofline_ms": roof_ms,
+                "frac_of_roofline": roof_ms / ms_f, "pulled_mb": pulled / 2 ** 20})
+    return res
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--numel", type=int, default=50_593_792)   # one Llama-2048 block
     ap.add_argument("--layout", choices=("even", "owner"), default="even")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--fused", action="store_true", help="also time the fused compute+collective kernels")
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--hidden", type=int, default=2048)
+    ap.add_argument("--gemm-tflops", type=float, default=1400.0, help="sustained bf16 GEMM rate used as roofline")
     args = ap.parse_args(argv)
     rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(rank)
@@ -97,6 +178,8 @@ def main(argv=None) -> int:
             gbs = recv_bytes / (ms * 1e-3) / 1e9
             results.append({"transport": name, "op": op, "ms": ms, "recv_gb_per_s": gbs,
                             "frac_of_measured_nvlink_770": gbs / NVLINK_PEER_GBS})
+    if peer is not None and args.fused:
+        results += fused_paths(peer, tables, args, world, dev)
     if dist.get_rank() == 0:
         for r in results:
             print(json.dumps(r))
