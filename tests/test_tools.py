@@ -26,3 +26,27 @@ def test_runtime_profile_single_and_two_ranks(capsys):
 def test_device_probe():
     p = device_api_probe.probe()
     assert "kernel_library_present" in p and "nccl_version" in p
+
+
+def test_planner_bench_reports_balance(capsys):
+    import json
+
+    from matrix_fsdp_b200.tools import planner_bench
+
+    assert planner_bench.main(["--hidden", "256", "--layers", "3", "--world", "2", "4", "--repeat", "1"]) == 0
+    rows = [json.loads(ln) for ln in capsys.readouterr().out.strip().splitlines()]
+    assert {r["strategy"] for r in rows} == set(planner_bench.STRATEGIES)
+    for r in rows:
+        assert r["owned_imbalance"] >= 1.0 and r["ms_per_block"] > 0
+    best = min(r["owned_imbalance"] for r in rows if r["world"] == 4)
+    assert best < 1.6
+
+
+def test_regression_package_check(capsys):
+    import json
+
+    from matrix_fsdp_b200.tools import regression
+
+    assert regression.main(["package"]) == 0
+    rec = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rec["missing_entry_points"] == [] and rec["unresolved_public_names"] == []
