@@ -234,6 +234,11 @@ def main() -> None:
     ap.add_argument("--device", default=None)
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
+    dump_after = float(os.environ.get("MFSDP_BENCH_DUMP_STACKS_AFTER_S", "0"))
+    if dump_after > 0:           # diagnose a run that stops making progress: print every thread's stack
+        import faulthandler
+
+        faulthandler.dump_traceback_later(dump_after, exit=False, file=sys.stderr)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

@@ -262,10 +262,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
       uint4* dst = reinterpret_cast<uint4*>(p.ag_dst[j]);
       const int nvec = p.ag_bytes[j] >> 4;
       int i = gt;
-      for (; i + 3 * kGatherThreads < nvec; i += 4 * kGatherThreads) {
-        const uint4 a = src[i], b = src[i + kGatherThreads], c = src[i + 2 * kGatherThreads],
-                    d = src[i + 3 * kGatherThreads];
-        dst[i] = a; dst[i + kGatherThreads] = b; dst[i + 2 * kGatherThreads] = c; dst[i + 3 * kGatherThreads] = d;
+      // 8 independent 16-byte peer loads in flight per thread to cover the NVLink latency
+      for (; i + 7 * kGatherThreads < nvec; i += 8 * kGatherThreads) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = src[i + u * kGatherThreads];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) dst[i + u * kGatherThreads] = v[u];
       }
       for (; i < nvec; i += kGatherThreads) dst[i] = src[i];
       __threadfence();

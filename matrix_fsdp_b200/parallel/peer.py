@@ -184,7 +184,7 @@ class DeferredGather:
     ``complete()`` performs the same copies with the plain pull kernel instead.
     """
 
-    MAX_JOB_BYTES = 256 * 1024
+    MAX_JOB_BYTES = 48 * 1024   # small jobs: every CTA's gather warps get work and each row block completes early
 
     def __init__(self, transport: "PeerTransport", shard_buf: SymBuffer, tables: SegmentTables, full: torch.Tensor,
                  lo: int, hi: int, k: int) -> None:
@@ -268,6 +268,7 @@ class PeerTransport(LocalTransport):
         self._slot_of_ptr: dict[int, _Slot] = {}
         self.max_slots = int(os.environ.get(RING_ENV, "3"))
         self.launches = 0
+        self._ar_state: dict[tuple, dict] = {}
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -302,7 +303,7 @@ class PeerTransport(LocalTransport):
         idx = self._unit_index.get(unit_key)
         if idx is None:
             idx = len(self._unit_index)
-            if idx >= MAX_UNITS:
+            if idx >= MAX_UNITS - 1:        # the last index belongs to the expert-parallel runtime
                 raise RuntimeError("too many FSDP units for the peer flag page")
             self._unit_index[unit_key] = idx
             self._epochs[unit_key] = {"shard": 0, "grad": 0}
@@ -428,6 +429,50 @@ class PeerTransport(LocalTransport):
             "sync_mode": "stream_event" if stream is not None else "stream_order"})
         h.deferred = plan
         return h
+
+    # ------------------------------------------------------------------ all-reduce (HSDP replicate group)
+    def all_reduce(self, tensor, group, *, scale=None):
+        """Sum ``tensor`` over ``group`` with the same pull-and-sum kernel as the reduce-scatter: every
+        rank publishes its values in a symmetric staging buffer, waits for the others and reads all of
+        them (fixed rank order, fp32 sum), writing the result back into ``tensor``.
+
+        Used for the dp_replicate step of HSDP after the dp_shard reduce-scatter (the reference runs
+        ``dist.all_reduce`` + ``div_`` synchronously there, matrix_fsdp/runtime/flat_buffer.py:1472-1480).
+        """
+        rep = PeerTransport.create(group, tensor.device) if tensor.is_cuda else None
+        if rep is None or tensor.dtype not in (torch.float32, torch.bfloat16) or not tensor.is_contiguous() \
+                or dist.get_world_size(group) == 1:
+            return super().all_reduce(tensor, group, scale=scale)
+        return rep._all_reduce_own_group(tensor, scale)
+
+    def _all_reduce_own_group(self, tensor: torch.Tensor, scale) -> None:
+        ctx = self.ctx
+        key = ("ar", tensor.numel(), tensor.dtype)   # one staging buffer per size: rounds are ordered by the flags
+        st = self._ar_state.get(key)
+        if st is None:
+            buf = ctx.alloc(tensor.numel() * tensor.element_size())
+            dev = tensor.device
+            st = {"buf": buf, "view": buf.tensor.view(tensor.dtype), "epoch": 0, "unit": self._unit(key),
+                  "g": torch.zeros(1, dtype=torch.int64, device=dev), "l": torch.zeros(1, dtype=torch.int64, device=dev),
+                  "len": torch.tensor([tensor.numel()], dtype=torch.int64, device=dev)}
+            self._ar_state[key] = st
+        run = torch.cuda.current_stream()
+        ui = st["unit"]
+        if st["epoch"] > 0:
+            ctx.wait(ui, KIND_PULLED, st["epoch"], run)          # everyone has read the previous round
+        st["epoch"] += 1
+        e = st["epoch"]
+        st["view"].copy_(tensor.view(-1))
+        ctx.signal(ui, KIND_GRAD, e, run)
+        ctx.wait(ui, KIND_GRAD, e, run)
+        ptrs = (_u64 * ctx.world)(*st["buf"].peer_addr)
+        is_bf16 = int(tensor.dtype == torch.bfloat16)
+        _lib.check(ctx.lib.mfsdp_rs_pull_reduce(
+            ptrs, ctx.world, ctx.rank, tensor.data_ptr(), st["g"].data_ptr(), st["l"].data_ptr(), st["len"].data_ptr(),
+            1, tensor.numel(), is_bf16, is_bf16, 0, float(1.0 if scale is None else scale), run.cuda_stream),
+            "rs_pull_reduce")
+        ctx.signal(ui, KIND_PULLED, e, run)
+        self.launches += 6
 
     # ------------------------------------------------------------------ reduce
     def _reduce_tables(self, unit_key, tables: SegmentTables, device) -> dict:

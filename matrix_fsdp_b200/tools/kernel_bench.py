@@ -1,6 +1,6 @@
 """Time single kernels of the library against their rooflines (one GPU).
 
-    python -m matrix_fsdp_b200.tools.kernel_bench --what gemm|elementwise|muon [--small]
+    python -m matrix_fsdp_b200.tools.kernel_bench --what gemm|elementwise|muon|attention [--small]
 
 Every number is CUDA-event timed after warm-up; between iterations the inputs rotate through enough
 distinct buffers to exceed L2.  Fractions are of the measured peaks in ``MEASURED_PEAKS.json``
@@ -120,9 +120,40 @@ def bench_muon(small: bool):
     return rows
 
 
+def bench_attention(small: bool):
+    """Causal attention forward/backward (head_dim 128) against the library SDPA kernel.
+
+    FLOPs: forward 4*B*nH*S^2*128/2 (two GEMMs, causal half); backward counted as 2.5x forward.
+    """
+    import torch.nn.functional as F
+
+    from ..ops import attention as A
+    from ..ops import kernels as K
+
+    _, tf, src = _peaks()
+    cases = [(1, 2048, 16)] if small else [(4, 1024, 16), (2, 4096, 32), (1, 8192, 32)]
+    rows = []
+    for B, S, nH in cases:
+        hd, H = 128, nH * 128
+        qkv = torch.randn(B * S, 3 * H, device="cuda", dtype=torch.bfloat16)
+        fl = 4.0 * B * nH * S * S * hd / 2 / 1e9
+        t_f = _time([lambda: A.attention_fwd(qkv, B, S, nH, hd)])
+        out, lse = A.attention_fwd(qkv, B, S, nH, hd)
+        do = torch.randn_like(out)
+        t_b = _time([lambda: A.attention_bwd(do, qkv, out, lse, B, S, nH, hd)])
+        q, k, v = (qkv[:, i * H:(i + 1) * H].view(B, S, nH, hd).transpose(1, 2) for i in range(3))
+        t_lib = _time([lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True)])
+        rows.append({"B": B, "S": S, "heads": nH, "fwd_ms": t_f, "fwd_tflops": fl / t_f, "bwd_ms": t_b,
+                     "bwd_tflops": 2.5 * fl / t_b, "sdpa_fwd_ms": t_lib, "sdpa_fwd_tflops": fl / t_lib,
+                     "fwd_frac_of_%s_peak" % src: fl / t_f / tf})
+        print(json.dumps(rows[-1]), flush=True)
+    K.check_status()
+    return rows
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", choices=("gemm", "elementwise", "muon"), default="gemm")
+    ap.add_argument("--what", choices=("gemm", "elementwise", "muon", "attention"), default="gemm")
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--out", default=None)
     ap.add_argument("--shape", type=int, nargs=3, default=None, metavar=("M", "N", "K"))
@@ -130,7 +161,7 @@ def main(argv=None) -> int:
     if args.what == "gemm":
         rows = bench_gemm(args.small, args.shape)
     else:
-        rows = {"elementwise": bench_elementwise, "muon": bench_muon}[args.what](args.small)
+        rows = {"elementwise": bench_elementwise, "muon": bench_muon, "attention": bench_attention}[args.what](args.small)
     if args.out:
         with open(args.out, "w") as f:
             json.dump(rows, f, indent=1)

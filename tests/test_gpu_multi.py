@@ -93,6 +93,28 @@ def _peer_collectives(rank, world):
     tr.check_health()
 
 
+def _peer_all_reduce(rank, world):
+    import torch.distributed as dist
+
+    from matrix_fsdp_b200.ops import kernels as K
+    from matrix_fsdp_b200.parallel.peer import PeerTransport
+
+    dev = torch.device("cuda", rank)
+    tr = PeerTransport.create(dist.group.WORLD, dev)
+    assert tr is not None
+    for rnd in range(3):                       # later rounds reuse the staging buffer
+        for dtype, n in ((torch.float32, 100_003), (torch.bfloat16, 65_536)):
+            torch.manual_seed(100 * rnd + rank)
+            t = torch.randn(n, device=dev).to(dtype)
+            ref = t.float().clone()
+            dist.all_reduce(ref)
+            tr.all_reduce(t, dist.group.WORLD, scale=1.0 / world)
+            torch.cuda.synchronize()
+            tol = 1e-5 if dtype == torch.float32 else 2e-2
+            assert (t.float() - ref / world).abs().max().item() < tol, (rnd, dtype)
+    K.check_status()
+
+
 def _train(rank, world, transport_kind, fused_update=False):
     import torch.distributed as dist
     from torch.distributed.fsdp import MixedPrecisionPolicy
@@ -145,6 +167,11 @@ def _train_both(rank, world, out_dir):
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_peer_collectives_match_torch():
     _run(_peer_collectives, min(_ngpu(), 4))
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_peer_all_reduce_matches_nccl():
+    _run(_peer_all_reduce, 2)
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
