@@ -40,7 +40,8 @@ from ..planning.planner_eval import PlannerResult, call_group_planner, planner_r
 from ..planning.shard_hint import build_shard_hints
 from .flat_buffer import MatrixFlatBuffer
 from .hooks import ForwardBackwardContext, register_pre_backward_hooks
-from .runtime_event import RuntimeEvent, RuntimeUnitMetadata, next_event_sequence, next_runtime_param_group_id
+from .runtime_event import (RuntimeEvent, RuntimeUnitMetadata, next_event_sequence, next_runtime_param_group_id,
+                            nvtx_range)
 from .transport import make_transport
 
 
@@ -341,7 +342,8 @@ class MatrixFSDPParamGroup:
                 and not _in_backward() and torch.is_grad_enabled() \
                 and (not reason.endswith("prefetch") or os.environ.get("MFSDP_FUSED_AG_GEMM", "exposed") == "always"):
             defer = self.fused_first_gemm_range
-        h = self.flat_buffer.start_all_gather_full_params(stream=self.all_gather_stream, defer=defer)
+        with nvtx_range(f"mfsdp.all_gather:{self.name}"):
+            h = self.flat_buffer.start_all_gather_full_params(stream=self.all_gather_stream, defer=defer)
         self.unshard_prefetched = reason.endswith("prefetch")
         self._record(f"start_unshard:{reason}", start=t0, handle=h, reason=reason, prefetched=self.unshard_prefetched)
 
@@ -539,7 +541,8 @@ class MatrixFSDPParamGroup:
         if self.backward_reduce_strategy == "per_param_allreduce":
             h = self._reduce_by_allreduce()
         else:
-            h = self.flat_buffer.start_reduce_grad_bucket_to_local_shard(stream=self.reduce_scatter_stream)
+            with nvtx_range(f"mfsdp.reduce_scatter:{self.name}"):
+                h = self.flat_buffer.start_reduce_grad_bucket_to_local_shard(stream=self.reduce_scatter_stream)
         self.has_accumulated_grads = False
         self._record("start_reduce_scatter", start=t0, handle=h)
         if self.scheduler is not None:

@@ -92,3 +92,38 @@ class RuntimeEvent:
 
     def as_dict(self) -> dict[str, Any]:
         return asdict(self)
+
+
+class nvtx_range:
+    """NVTX range around a runtime phase (``MFSDP_NVTX=1`` on a CUDA build; otherwise free).
+
+    The reference has no NVTX / profiler integration (its event log carries host durations only)."""
+
+    _enabled: bool | None = None
+
+    def __init__(self, name: str) -> None:
+        self.name = name
+
+    @classmethod
+    def enabled(cls) -> bool:
+        if cls._enabled is None:
+            import os
+
+            import torch
+
+            cls._enabled = os.environ.get("MFSDP_NVTX", "0") not in ("", "0") and torch.cuda.is_available()
+        return cls._enabled
+
+    def __enter__(self):
+        if self.enabled():
+            import torch
+
+            torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        if self.enabled():
+            import torch
+
+            torch.cuda.nvtx.range_pop()
+        return False
