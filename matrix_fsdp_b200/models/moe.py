@@ -224,3 +224,59 @@ def configure_moe_optimizer(model: MoEModel, optimizer: str = "mixed_muon_adamw"
         experts = ExpertParallelOptimizer(model.expert_parameters(), "adamw", lr=lr, weight_decay=weight_decay,
                                           betas=kw.get("betas", (0.9, 0.999)), eps=kw.get("eps", 1e-8))
     return CombinedOptimizer(dense, experts)
+
+
+def save_moe_checkpoint(model: MoEModel, directory: str, optimizer=None) -> None:
+    """Dense parameters (and their optimizer state) through ``save_matrix_dcp``; every EP rank adds one file
+    with the experts it owns (weights, fp32 masters and optimizer state), keyed by global expert id."""
+    import os
+
+    from ..checkpoint import save_matrix_dcp
+
+    dense_opt = getattr(optimizer, "dense", optimizer)
+    save_matrix_dcp(model, directory, optimizer=dense_opt)
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    payload = {"experts": {}, "optimizer": None}
+    for li, layer in enumerate(model.layers):
+        ex = layer.experts
+        payload["experts"][li] = {"first_expert": ex.first_expert, "w_gate_up": ex.w_gate_up.detach().cpu(),
+                                  "w_down": ex.w_down.detach().cpu()}
+    expert_opt = getattr(optimizer, "experts", None)
+    if expert_opt is not None:
+        payload["optimizer"] = _to_cpu(expert_opt.state_dict())
+    torch.save(payload, os.path.join(directory, f"experts_rank{rank}.pt"))
+    if dist.is_initialized():
+        dist.barrier()
+
+
+def load_moe_checkpoint(model: MoEModel, directory: str, optimizer=None, allow_reshard: bool = False) -> None:
+    """Inverse of :func:`save_moe_checkpoint` for the same expert-parallel size."""
+    import os
+
+    from ..checkpoint import load_matrix_dcp
+
+    dense_opt = getattr(optimizer, "dense", optimizer)
+    load_matrix_dcp(model, directory, optimizer=dense_opt, allow_reshard=allow_reshard)
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    payload = torch.load(os.path.join(directory, f"experts_rank{rank}.pt"), map_location="cpu", weights_only=False)
+    for li, layer in enumerate(model.layers):
+        rec = payload["experts"][li]
+        ex = layer.experts
+        if rec["first_expert"] != ex.first_expert or rec["w_down"].shape != ex.w_down.shape:
+            raise ValueError("expert checkpoint was written with a different expert-parallel layout")
+        with torch.no_grad():
+            ex.w_gate_up.copy_(rec["w_gate_up"])
+            ex.w_down.copy_(rec["w_down"])
+    expert_opt = getattr(optimizer, "experts", None)
+    if expert_opt is not None and payload.get("optimizer") is not None:
+        expert_opt.load_state_dict(payload["optimizer"])
+
+
+def _to_cpu(obj):
+    if isinstance(obj, torch.Tensor):
+        return obj.detach().cpu()
+    if isinstance(obj, dict):
+        return {k: _to_cpu(v) for k, v in obj.items()}
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_to_cpu(v) for v in obj)
+    return obj

@@ -25,6 +25,8 @@ from __future__ import annotations
 from collections.abc import Sequence
 from dataclasses import dataclass
 
+import os
+
 import torch
 
 from ..core.layout import LayoutSegment, MatrixGroupLayout
@@ -59,6 +61,9 @@ def _piece_shape(mp: ManagedParam, start: int, numel: int) -> tuple[int, ...]:
         if start % inner == 0 and numel % inner == 0:
             return (numel // inner, *tuple(mp.shape)[1:])
     return (numel,)
+
+
+_POISON = os.environ.get("MFSDP_DEBUG_POISON", "0") not in ("", "0")
 
 
 class MatrixFlatBuffer:
@@ -202,6 +207,10 @@ class MatrixFlatBuffer:
         st = self.full_buffer.untyped_storage()
         if st.size() != self._full_nbytes():
             st.resize_(self._full_nbytes())
+            if _POISON and self.full_buffer.is_floating_point():
+                # debug aid: a read of gathered parameters before they arrived shows up as NaN
+                # (ordered before the gather by the gather stream's wait on the current stream)
+                self.full_buffer.fill_(float("nan"))
 
     def full_storage_nbytes(self) -> int:
         return 0 if self.full_aliases_shard else self.full_buffer.untyped_storage().size()

@@ -169,6 +169,55 @@ def test_peer_collectives_match_torch():
     _run(_peer_collectives, min(_ngpu(), 4))
 
 
+def _hsdp_train(rank, world, transport_kind):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import MixedPrecisionPolicy
+
+    from matrix_fsdp_b200 import DataParallelMeshDims
+    from matrix_fsdp_b200.api import reset_shared_owner_planners
+    from matrix_fsdp_b200.models.llama import LlamaConfig, LlamaModel, shard_llama
+    from matrix_fsdp_b200.ops import kernels as K
+    from matrix_fsdp_b200.optim import configure_optimizer
+    from matrix_fsdp_b200.parallel.unit_collection import collect_param_groups
+
+    os.environ["MFSDP_TRANSPORT"] = transport_kind
+    os.environ["MFSDP_DEBUG_POISON"] = "1"
+    reset_shared_owner_planners()
+    mesh = init_device_mesh("cuda", (2, world // 2), mesh_dim_names=("dp_replicate", "dp_shard"))
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=1024, hidden=256, n_layers=2, n_heads=2, head_dim=128, ffn=688)
+    model = LlamaModel(cfg).cuda()
+    shard_llama(model, mesh=mesh, dp_mesh_dims=DataParallelMeshDims(shard="dp_shard", replicate="dp_replicate"),
+                mp_policy=MixedPrecisionPolicy(param_dtype=torch.bfloat16))
+    opt = configure_optimizer(model, "adamw", lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
+    g = torch.Generator().manual_seed(5 + rank)
+    losses = []
+    for _ in range(3):
+        tok = torch.randint(0, 1024, (2, 65), generator=g).cuda()
+        loss = model(tok[:, :-1], tok[:, 1:])
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        losses.append(loss.item())
+    K.check_status()
+    return losses, torch.cat([u.flat_buffer.local_shard.float().cpu() for u in collect_param_groups(model)])
+
+
+def _hsdp_both(rank, world):
+    l_peer, s_peer = _hsdp_train(rank, world, "peer")
+    l_nccl, s_nccl = _hsdp_train(rank, world, "torch_dist")
+    for a, b in zip(l_peer, l_nccl):
+        assert a == a and abs(a - b) < 2e-2 * abs(b), (l_peer, l_nccl)
+    assert ((s_peer - s_nccl).norm() / s_nccl.norm()).item() < 2e-3
+
+
+@pytest.mark.skipif(_ngpu() < 4, reason="needs 4 GPUs")
+def test_hsdp_2x2_peer_vs_nccl():
+    """HSDP on a 2 x 2 mesh: reduce-scatter in the shard group and all-reduce in the replicate group,
+    both through the peer kernels, against the library collectives."""
+    _run(_hsdp_both, 4)
+
+
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_peer_all_reduce_matches_nccl():
     _run(_peer_all_reduce, 2)

@@ -82,3 +82,36 @@ def _ep_worker(rank, world):
 
 def test_moe_ep_gloo_matches_single_process():
     run_ranks(_ep_worker, 2)
+
+
+def test_moe_checkpoint_roundtrip_single_process(tmp_path):
+    from matrix_fsdp_b200.models.moe import (MoEModel, configure_moe_optimizer, load_moe_checkpoint, save_moe_checkpoint,
+                                             shard_moe)
+
+    cfg = _cfg()
+    toks = _tokens()
+
+    def make():
+        torch.manual_seed(0)
+        m = MoEModel(cfg, ep_group=False)
+        shard_moe(m)
+        return m, configure_moe_optimizer(m, "adamw", lr=1e-2, betas=(0.9, 0.95))
+
+    model, opt = make()
+    for _ in range(2):
+        model(toks[:, :-1], toks[:, 1:]).backward()
+        opt.step()
+        opt.zero_grad()
+    save_moe_checkpoint(model, str(tmp_path), optimizer=opt)
+    model(toks[:, :-1], toks[:, 1:]).backward()
+    opt.step()
+    opt.zero_grad()
+    expect = model(toks[:, :-1], toks[:, 1:]).item()
+
+    model2, opt2 = make()
+    load_moe_checkpoint(model2, str(tmp_path), optimizer=opt2)
+    model2(toks[:, :-1], toks[:, 1:]).backward()
+    opt2.step()
+    opt2.zero_grad()
+    got = model2(toks[:, :-1], toks[:, 1:]).item()
+    assert abs(got - expect) < 1e-5, (got, expect)
