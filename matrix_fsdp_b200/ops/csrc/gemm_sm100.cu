@@ -46,6 +46,7 @@ struct GemmArgs {
   int b_group_stride;        // mode 1: rows added to B's row coordinate per group
   int tiles_m_per_group;     // mode 2
   int m_per_group;           // mode 2
+  int raster_group_m;        // M-tiles per rasterisation group
   // Fused all-gather (GATHER kernels only): B's rows are still on peer GPUs when the kernel starts.
   // Four extra warps per CTA copy them into B's local buffer job by job (16-byte peer loads, local
   // stores) and count finished jobs per B tile row-block; the TMA producer waits (bounded) until
@@ -85,8 +86,9 @@ struct TileCoord {
 
 __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, int tile) {
   // Grouped rasterisation: 8 M-tiles share each sweep over N so that the CTAs running
-  // at the same time reuse A and B tiles out of L2.
-  constexpr int kGroupM = 8;
+  // at the same time reuse A and B tiles out of L2.  The fused all-gather form walks all M-tiles of
+  // one B row-block before the next one, so the first wave only needs the first few row-blocks.
+  const int kGroupM = p.raster_group_m;
   const int per_group = kGroupM * p.tiles_n;
   const int gid = tile / per_group;
   const int first_m = gid * kGroupM;
@@ -459,6 +461,7 @@ MFSDP_API int mfsdp_gemm_bf16(const void* A, const void* B, void* D, const void*
   args.ldcin = ldcin;
   args.status = status;
   args.group_mode = group_mode;
+  args.raster_group_m = 8;
   args.tile_group = tile_group;
   args.group_offsets = group_offsets;
   args.m_per_group = M;
@@ -540,6 +543,7 @@ MFSDP_API int mfsdp_gemm_bf16_ag(const void* A, const void* B, void* D, const vo
   args.tiles_m = (M + BM - 1) / BM;
   args.tiles_m_per_group = args.tiles_m;
   args.tiles_n = (N + bn - 1) / bn;
+  args.raster_group_m = args.tiles_m;
   args.ag_src = ag_src; args.ag_dst = ag_dst; args.ag_bytes = ag_bytes; args.ag_flag = ag_flag;
   args.ag_njobs = njobs; args.ag_flags = flags; args.ag_need = ag_need; args.ag_budget_ns = budget_ns;
   CUtensorMap ta, tb, td;

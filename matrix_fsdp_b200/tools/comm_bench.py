@@ -102,6 +102,9 @@ def fused_paths(peer, tables: SegmentTables, args, world: int, dev) -> list[dict
     flops = 2.0 * t * 3 * h * h
     remote = sum(max(0, min(s.global_start + s.numel, hi) - max(s.global_start, lo))
                  for r, segs in enumerate(tables.rank_segments) if r != rank for s in segs) * 2
+    rt = torch.tensor([float(remote)], device=dev)
+    dist.all_reduce(rt, op=dist.ReduceOp.MAX)          # the slowest rank is the one that pulls the most
+    remote = float(rt.item())
     roof_ms = max(flops / (args.gemm_tflops * 1e12), remote / (NVLINK_PEER_GBS * 1e9)) * 1e3
     fused_part = ms_f - ms_rest
     res.append({"op": "ag+gemm", "unfused_ms": ms_u, "fused_ms": ms_f, "gather_of_other_rows_ms": ms_rest,
