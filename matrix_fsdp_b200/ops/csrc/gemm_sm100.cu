@@ -48,7 +48,7 @@ struct GemmArgs {
   int m_per_group;           // mode 2
   int raster_group_m;        // M-tiles per rasterisation group
   // Fused all-gather (GATHER kernels only): B's rows are still on peer GPUs when the kernel starts.
-  // Four extra warps per CTA copy them into B's local buffer job by job (16-byte peer loads, local
+  // Eight extra warps per CTA copy them into B's local buffer job by job (16-byte peer loads, local
   // stores) and count finished jobs per B tile row-block; the TMA producer waits (bounded) until
   // the row-block of its tile is complete before loading it.
   const unsigned long long* ag_src;   // [njobs] peer (or local) source address
@@ -61,7 +61,7 @@ struct GemmArgs {
   unsigned long long ag_budget_ns;
 };
 
-constexpr int kGatherThreads = 128;
+constexpr int kGatherThreads = 256;
 
 template <int BN>
 struct GemmCfg {
@@ -86,8 +86,7 @@ struct TileCoord {
 
 __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, int tile) {
   // Grouped rasterisation: 8 M-tiles share each sweep over N so that the CTAs running
-  // at the same time reuse A and B tiles out of L2.  The fused all-gather form walks all M-tiles of
-  // one B row-block before the next one, so the first wave only needs the first few row-blocks.
+  // at the same time reuse A and B tiles out of L2.
   const int kGroupM = p.raster_group_m;
   const int per_group = kGroupM * p.tiles_n;
   const int gid = tile / per_group;
@@ -274,7 +273,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
       }
       for (; i < nvec; i += kGatherThreads) dst[i] = src[i];
       __threadfence();
-      asm volatile("bar.sync 3, 128;" ::: "memory");
+      asm volatile("bar.sync 3, 256;" ::: "memory");
       if (gt == 0) red_release_gpu_add_u32(p.ag_flags + p.ag_flag[j], 1u);
     }
   } else {
@@ -543,7 +542,7 @@ MFSDP_API int mfsdp_gemm_bf16_ag(const void* A, const void* B, void* D, const vo
   args.tiles_m = (M + BM - 1) / BM;
   args.tiles_m_per_group = args.tiles_m;
   args.tiles_n = (N + bn - 1) / bn;
-  args.raster_group_m = args.tiles_m;
+  args.raster_group_m = 8;   // (walking a whole B row-block first measured slower: 0.193 vs 0.144 ms on 4 GPUs)
   args.ag_src = ag_src; args.ag_dst = ag_dst; args.ag_bytes = ag_bytes; args.ag_flag = ag_flag;
   args.ag_njobs = njobs; args.ag_flags = flags; args.ag_need = ag_need; args.ag_budget_ns = budget_ns;
   CUtensorMap ta, tb, td;

@@ -109,7 +109,7 @@ def gemm_ag(a: torch.Tensor, b: torch.Tensor, plan, *, out: torch.Tensor | None 
     """``out = alpha * a·bᵀ + beta * cin`` where rows of ``b`` ([N, K], contiguous) are still on peer GPUs.
 
     ``plan`` (see ``parallel.peer.DeferredGather``) lists the copy jobs that bring them into ``b``'s
-    local storage; the kernel runs them on four extra warps per CTA while tiles whose rows have
+    local storage; the kernel runs them on eight extra warps per CTA while tiles whose rows have
     arrived are multiplied.
     """
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and b.is_contiguous() and a.stride(1) == 1
