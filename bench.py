@@ -318,9 +318,17 @@ def main() -> None:
 
         counter = _K
 
-    # ---- warm-up
+    # ---- warm-up (the last warm-up step is issued on an idle device: its host time is the pure cost of
+    # enqueueing one step, which tells a launch-bound run from a device-bound one)
+    host_issue_ms = None
     for i in range(args.warmup):
-        last = device_step(i)
+        if i == args.warmup - 1 and i > 0:
+            sync()
+            t_issue = time.perf_counter()
+            last = device_step(i)
+            host_issue_ms = (time.perf_counter() - t_issue) * 1e3
+        else:
+            last = device_step(i)
     sync()
     if cuda:
         torch.cuda.reset_peak_memory_stats()
@@ -392,7 +400,7 @@ def main() -> None:
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                 "h2d_bytes_per_step": 2 * B * S * 8, "d2h_bytes_per_step": 4, "last_loss": e2e_loss},
-        "gpu_launches": launches,
+        "gpu_launches": launches, "host_issue_ms_per_step": host_issue_ms,
     }
     if rank == 0:
         print(json.dumps(out))

@@ -18,6 +18,7 @@
 // (test/fsdp/bench_fsdp2_compare.py:419,480); this file is that op written for Blackwell.
 #include "common.cuh"
 #include <cuda.h>
+#include <cstdlib>
 
 namespace mfsdp {
 
@@ -351,6 +352,17 @@ __device__ __forceinline__ void mma_sdp(uint32_t tmem_d, uint32_t a_base, uint32
     umma_f16_ss(tmem_d, ad, bd, idesc, k > 0 ? 1u : 0u);
   }
 }
+// Same product with the A operand (P or dS as packed bf16 pairs) read from tensor memory: the thread that
+// owns row r stored elements [32h, 32h+32) of its row as 16 packed columns at column offset 32h, so
+// k-step kk (16 elements) starts at column (kk >> 1) * 32 + (kk & 1) * 8.
+__device__ __forceinline__ void mma_acc_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_base, bool accumulate) {
+  constexpr uint32_t idesc = make_idesc_bf16(128, 128, false, true);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const uint64_t bd = make_smem_desc_sw128(b_base + k * 2048, 8192, 1024);
+    umma_f16_ts(tmem_d, tmem_a + (k >> 1) * 32 + (k & 1) * 8, bd, idesc, (accumulate || k > 0) ? 1u : 0u);
+  }
+}
 // D[128 x 128] (+)= P[128 x 64 (K-major)] * B[64 x 128 (rows along K, N contiguous)]
 __device__ __forceinline__ void mma_acc(uint32_t tmem_d, uint32_t p_base, uint32_t b_base, bool accumulate) {
   constexpr uint32_t idesc = make_idesc_bf16(128, 128, false, true);
@@ -362,7 +374,9 @@ __device__ __forceinline__ void mma_acc(uint32_t tmem_d, uint32_t p_base, uint32
   }
 }
 
-template <bool DQ>
+// PT: P and dS stay in tensor memory (written over the S / dP columns their thread just read) and feed
+// the accumulation MMAs from there; otherwise they go through swizzled shared tiles.
+template <bool DQ, bool PT>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_qkv, const __grid_constant__ CUtensorMap tma_do,
                 const AttnBwdArgs p) {
@@ -458,8 +472,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_qkv, const __grid_consta
         if (!mbar_wait(smem_u32(&p_full[s]), ph, p.status, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t bs = sB + bsi * 2 * kStreamBytes, ps = sP + s * 2 * kPBytes;
-        if (!DQ) mma_acc(tmem_acc0, ps, bs + kStreamBytes, i > 0);     // dV += P^T dO_t
-        mma_acc(tmem_acc1, ps + kPBytes, bs, i > 0);                   // dK += dS^T Q_t   |   dQ += dS K_t
+        if (PT) {
+          if (!DQ) mma_acc_ts(tmem_acc0, tmem_base + s * 128, bs + kStreamBytes, i > 0);
+          mma_acc_ts(tmem_acc1, tmem_base + s * 128 + kBt, bs, i > 0);
+        } else {
+          if (!DQ) mma_acc(tmem_acc0, ps, bs + kStreamBytes, i > 0);     // dV += P^T dO_t
+          mma_acc(tmem_acc1, ps + kPBytes, bs, i > 0);                   // dK += dS^T Q_t   |   dQ += dS K_t
+        }
         umma_commit(smem_u32(&b_empty[bsi]));
         umma_commit(smem_u32(&p_free[s]));
       }
@@ -492,7 +511,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_qkv, const __grid_consta
       const uint32_t s = i & 1, ph = (i >> 1) & 1;
       if (i + 1 < T) next_val = fetch(t + 1);
       mbar_wait(smem_u32(&sdp_full[s]), ph, p.status, abort_flag);
-      if (i >= 2) mbar_wait(smem_u32(&p_free[s]), ph ^ 1, p.status, abort_flag);
+      if (!PT && i >= 2) mbar_wait(smem_u32(&p_free[s]), ph ^ 1, p.status, abort_flag);
       if (softmax_bar_or(*abort_flag != 0)) { ok = false; break; }
       tc_fence_after();
       const int c0 = t * kBt;                    // first streamed index of this tile
@@ -536,15 +555,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_qkv, const __grid_consta
           dd[e >> 1] = pack_bf16x2(dsv[0], dsv[1]);
           dd[(e >> 1) + 1] = pack_bf16x2(dsv[2], dsv[3]);
         }
+        if (PT) {
+          // over the columns this thread just read: P at the start of its 32 S columns, dS likewise in dP
+          if (!DQ) tmem_st_32x32b_x16(tmem_base + s * 128 + lane_off + c * 32, pp);
+          tmem_st_32x32b_x16(tmem_base + s * 128 + kBt + lane_off + c * 32, dd);
+          tmem_st_wait();
+        } else {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int phys = ((c * 4 + g) ^ (r & 7)) * 16;
-          if (!DQ) *reinterpret_cast<uint4*>(prow + phys) = make_uint4(pp[g * 4], pp[g * 4 + 1], pp[g * 4 + 2], pp[g * 4 + 3]);
-          *reinterpret_cast<uint4*>(prow + kPBytes + phys) = make_uint4(dd[g * 4], dd[g * 4 + 1], dd[g * 4 + 2], dd[g * 4 + 3]);
+          for (int g = 0; g < 4; ++g) {
+            const int phys = ((c * 4 + g) ^ (r & 7)) * 16;
+            if (!DQ) *reinterpret_cast<uint4*>(prow + phys) = make_uint4(pp[g * 4], pp[g * 4 + 1], pp[g * 4 + 2], pp[g * 4 + 3]);
+            *reinterpret_cast<uint4*>(prow + kPBytes + phys) = make_uint4(dd[g * 4], dd[g * 4 + 1], dd[g * 4 + 2], dd[g * 4 + 3]);
+          }
         }
       }
       if (!DQ && half == 0 && i + 1 < T) row_vals[(s ^ 1) * 128 + r] = next_val;
-      fence_proxy_async_smem();
+      if (!PT) fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(smem_u32(&p_full[s]));
     }
@@ -651,9 +677,11 @@ MFSDP_API int mfsdp_attention_bwd(const void* dout, const void* qkv, const void*
   if (rc) return rc;
   static bool attr = false;
   if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnBwdSmem::kBytes);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attn_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnBwdSmem::kBytes);
+    cudaError_t e = cudaSuccess;
+    const void* kerns[4] = {(const void*)attn_bwd_kernel<false, false>, (const void*)attn_bwd_kernel<true, false>,
+                            (const void*)attn_bwd_kernel<false, true>, (const void*)attn_bwd_kernel<true, true>};
+    for (int i = 0; i < 4 && e == cudaSuccess; ++i)
+      e = cudaFuncSetAttribute(kerns[i], cudaFuncAttributeMaxDynamicSharedMemorySize, AttnBwdSmem::kBytes);
     if (e != cudaSuccess) return (int)e;
     attr = true;
   }
@@ -668,7 +696,16 @@ MFSDP_API int mfsdp_attention_bwd(const void* dout, const void* qkv, const void*
   a.lse2 = lse2; a.delta = delta;
   a.dqkv = (__nv_bfloat16*)dqkv; a.ld_dqkv = ld_dqkv; a.status = status;
   dim3 grid((S + 127) / 128, nH, B);
-  attn_bwd_kernel<false><<<grid, kAttnThreads, AttnBwdSmem::kBytes, st>>>(map_qkv, map_do, a);
-  attn_bwd_kernel<true><<<grid, kAttnThreads, AttnBwdSmem::kBytes, st>>>(map_qkv, map_do, a);
+  static const bool p_in_tmem = [] {
+    const char* e = getenv("MFSDP_ATTN_P_TMEM");
+    return e ? atoi(e) != 0 : true;
+  }();
+  if (p_in_tmem) {
+    attn_bwd_kernel<false, true><<<grid, kAttnThreads, AttnBwdSmem::kBytes, st>>>(map_qkv, map_do, a);
+    attn_bwd_kernel<true, true><<<grid, kAttnThreads, AttnBwdSmem::kBytes, st>>>(map_qkv, map_do, a);
+  } else {
+    attn_bwd_kernel<false, false><<<grid, kAttnThreads, AttnBwdSmem::kBytes, st>>>(map_qkv, map_do, a);
+    attn_bwd_kernel<true, false><<<grid, kAttnThreads, AttnBwdSmem::kBytes, st>>>(map_qkv, map_do, a);
+  }
   return (int)cudaGetLastError();
 }

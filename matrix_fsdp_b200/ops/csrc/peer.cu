@@ -14,6 +14,7 @@
 // kernels/native/matrix_nccl.cpp:111-335) and reduce_scatter_tensor + div_ / grouped ncclReduce
 // (collectives.py:927-990, matrix_nccl.cpp:337-395).
 #include "common.cuh"
+#include <cstdlib>
 #include <cstring>
 
 namespace mfsdp {
@@ -249,11 +250,22 @@ __global__ void rs_pull_adamw_kernel(PeerPtrs grads, int world, int rank, Reduce
   }
 }
 
+// Upper bound on the CTAs of one pull kernel (MFSDP_PEER_MAX_BLOCKS).  The pull kernels run beside the
+// GEMMs of the neighbouring block; fewer, longer-lived CTAs leave more issue slots to the tensor kernels.
+static long long peer_max_blocks() {
+  static long long v = [] {
+    const char* e = getenv("MFSDP_PEER_MAX_BLOCKS");
+    long long x = e ? atoll(e) : 0;
+    return x > 0 ? x : 148LL * 8;
+  }();
+  return v;
+}
+
 static inline dim3 seg_grid(long long max_len, int per_thread, int nseg) {
   long long bx = (max_len / per_thread + 255) / 256;
   if (bx < 1) bx = 1;
   int gy = nseg < 1024 ? nseg : 1024;
-  const long long cap = 148 * 8;
+  const long long cap = peer_max_blocks();
   if (bx * gy > cap) bx = (cap + gy - 1) / gy;
   return dim3((unsigned)bx, (unsigned)gy);
 }
