@@ -235,7 +235,7 @@ class _AttentionCore:
     def forward(qkv: torch.Tensor, s: BlockShape):
         from . import attention as A
 
-        if A.available():
+        if A.available() and s.head_dim == A.HEAD_DIM and A.supports(s.seq):
             out, lse = A.attention_fwd(qkv, s.batch, s.seq, s.n_heads, s.head_dim)
             return out, ("native", lse)
         h = s.n_heads * s.head_dim
