@@ -1,0 +1,136 @@
+"""Checkpoint contract details: legacy per-rank sidecars, optimizer component checks, HSDP payload keys with
+replica de-duplication, expert-owner hints in the metadata, and structural mismatches reported before loading."""
+import os
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from dist_utils import run_ranks
+from matrix_fsdp_b200 import configure_optimizer, fully_shard, load_matrix_dcp, save_matrix_dcp
+from matrix_fsdp_b200.api import reset_shared_owner_planners
+from matrix_fsdp_b200.checkpoint import read_global_metadata
+
+
+def _model(seed=0, width=10):
+    torch.manual_seed(seed)
+    return nn.Sequential(nn.Linear(6, width), nn.LayerNorm(width), nn.Linear(width, 4))
+
+
+def _step(model, opt, seed=1):
+    g = torch.Generator().manual_seed(seed)
+    model(torch.randn(3, 6, generator=g)).pow(2).mean().backward()
+    opt.step()
+    opt.zero_grad()
+
+
+def test_legacy_per_rank_sidecar_is_accepted_on_load():
+    reset_shared_owner_planners()
+    model = _model()
+    fully_shard(model)
+    opt = configure_optimizer(model, "adamw", lr=1e-2)
+    _step(model, opt)
+    with tempfile.TemporaryDirectory() as d:
+        save_matrix_dcp(model, d, optimizer=opt, no_dist=True)
+        payload = read_global_metadata(d)
+        os.remove(os.path.join(d, "matrix_metadata.pt"))
+        torch.save(payload["ranks"][0], os.path.join(d, "matrix_metadata_rank_0.pt"))     # the older layout
+        again = read_global_metadata(d)
+        assert again["metadata"]["ranks"] == (0,) and again["ranks"][0]["dcp_rank"] == 0
+        other = _model(seed=3)
+        fully_shard(other)
+        opt2 = configure_optimizer(other, "adamw", lr=1e-2)
+        load_matrix_dcp(other, d, optimizer=opt2, no_dist=True)
+        assert torch.equal(model._matrix_fsdp_param_group.flat_buffer.local_shard,
+                           other._matrix_fsdp_param_group.flat_buffer.local_shard)
+    with tempfile.TemporaryDirectory() as empty, pytest.raises(FileNotFoundError):
+        read_global_metadata(empty)
+
+
+def test_optimizer_component_and_structure_mismatches_raise():
+    reset_shared_owner_planners()
+    model = _model()
+    fully_shard(model, optimizer_policy="mixed_muon_adamw")
+    mixed = configure_optimizer(model, "mixed_muon_adamw", lr=1e-2, muon_lr=1e-2)
+    _step(model, mixed)
+    with tempfile.TemporaryDirectory() as d:
+        save_matrix_dcp(model, d, optimizer=mixed, no_dist=True)
+        meta = read_global_metadata(d)["ranks"][0]["optimizer"]
+        assert meta["kind"] == "mixed_muon_adamw" and set(meta["components"]) == {"muon", "adamw"}
+        # an optimizer with other components cannot take this state
+        reset_shared_owner_planners()
+        plain = _model(seed=2)
+        fully_shard(plain, optimizer_policy="mixed_muon_adamw")
+        adamw = configure_optimizer(plain, "adamw", lr=1e-2)
+        with pytest.raises(ValueError, match="component"):
+            load_matrix_dcp(plain, d, optimizer=adamw, no_dist=True)
+        # a model with a different parameter set is refused before any tensor is read
+        reset_shared_owner_planners()
+        wider = _model(width=12)
+        fully_shard(wider, optimizer_policy="mixed_muon_adamw")
+        with pytest.raises(ValueError):
+            load_matrix_dcp(wider, d, no_dist=True)
+    with tempfile.TemporaryDirectory() as d:
+        save_matrix_dcp(model, d, no_dist=True)                       # no optimizer saved
+        with pytest.raises(ValueError, match="no optimizer state"):
+            load_matrix_dcp(model, d, optimizer=mixed, no_dist=True)
+
+
+def test_expert_owner_hints_survive_in_metadata():
+    class Moe(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.router = nn.Linear(4, 2, bias=False)
+            self.experts = nn.ModuleList([nn.Sequential(nn.Linear(4, 8, bias=False), nn.Linear(8, 4, bias=False))
+                                          for _ in range(2)])
+
+        def forward(self, x):
+            w = torch.softmax(self.router(x), -1)
+            return sum(w[:, i:i + 1] * e(x) for i, e in enumerate(self.experts))
+
+    reset_shared_owner_planners()
+    torch.manual_seed(0)
+    m = Moe()
+    fully_shard(m, optimizer_policy="mixed_muon_adamw")
+    with tempfile.TemporaryDirectory() as d:
+        save_matrix_dcp(m, d, no_dist=True)
+        unit = read_global_metadata(d)["ranks"][0]["units"][0]
+        hint = unit["params"]["experts.1.0.weight"]["shard_hint"]
+        assert hint["runtime_kind"] == "expert_owner" and hint["expert_id"] == 1
+        assert unit["params"]["router.weight"]["shard_hint"]["parallel_role"] == "router"
+
+
+def _hsdp_worker(rank, world, directory):
+    from torch.distributed.device_mesh import init_device_mesh
+
+    from matrix_fsdp_b200 import DataParallelMeshDims
+
+    reset_shared_owner_planners()
+    mesh = init_device_mesh("cpu", (2, 2), mesh_dim_names=("dp_replicate", "dp_shard"))
+    model = _model()
+    fully_shard(model, mesh=mesh, dp_mesh_dims=DataParallelMeshDims(shard="dp_shard", replicate="dp_replicate"))
+    opt = configure_optimizer(model, "adamw", lr=1e-2)
+    _step(model, opt, seed=rank)
+    unit = model._matrix_fsdp_param_group
+    assert unit.rank == rank % 2 and unit.world_size == 2 and unit.replicate_world_size == 2
+    save_matrix_dcp(model, directory, optimizer=opt)
+    payload = read_global_metadata(directory)
+    assert payload["metadata"]["ranks"] == (0, 1, 2, 3)
+    mine = payload["ranks"][rank]
+    assert mine["dcp_rank"] == rank
+    u0 = mine["units"][0]
+    assert u0["dcp_payload_rank"] == f"shard_{rank % 2}" and u0["dcp_dedup_replicates"] is True
+    before = unit.flat_buffer.local_shard.clone()
+    _step(model, opt, seed=10 + rank)
+    load_matrix_dcp(model, directory, optimizer=opt)
+    assert torch.equal(unit.flat_buffer.local_shard, before)
+    dist.barrier()
+
+
+def test_hsdp_payload_keys_are_shared_by_replicas():
+    with tempfile.TemporaryDirectory() as d:
+        run_ranks(_hsdp_worker, 4, d)
+        files = os.listdir(d)
+        assert "matrix_metadata.pt" in files and not [f for f in files if f.startswith("matrix_metadata_rank_")]
