@@ -191,12 +191,16 @@ def _collect_wrap_policy_modules(module: nn.Module, wrap_policy: WrapPolicy, *, 
     """Post-order (children before parents) list of sub-modules selected by ``wrap_policy``."""
     ignored = {id(p) for p in ignored_params or ()}
     out: list[nn.Module] = []
+    claimed: set[int] = set()     # parameters that a selected descendant will already manage
 
     def visit(m: nn.Module) -> None:
         for child in m.children():
             visit(child)
-        if wrap_policy(m) and any(id(p) not in ignored for p in m.parameters()):
-            out.append(m)
+        if wrap_policy(m):
+            own = {id(p) for p in m.parameters()} - ignored - claimed
+            if own:
+                out.append(m)
+                claimed.update(own)
 
     visit(module)
     return out

@@ -51,6 +51,22 @@ def _adamw_reference_(p, m, v, g, *, lr, beta1, beta2, eps, weight_decay, step, 
         p_lp.copy_(p)
 
 
+# torch.optim keyword arguments that only select an implementation: accepted and irrelevant here
+_IMPLEMENTATION_OPTIONS = ("foreach", "fused", "capturable", "differentiable")
+
+
+def _check_torch_options(name: str, options: dict, **must_equal) -> None:
+    """Reject keyword arguments this optimizer would otherwise silently drop."""
+    for key, value in options.items():
+        if key in _IMPLEMENTATION_OPTIONS:
+            continue
+        if key in must_equal:
+            if value != must_equal[key]:
+                raise NotImplementedError(f"{name}: {key}={value!r} is not supported by the flat sharded optimizer.")
+            continue
+        raise TypeError(f"{name}: unexpected keyword argument {key!r}.")
+
+
 class _UnitState:
     """Flat optimizer state of one FSDP unit."""
 
@@ -141,7 +157,8 @@ class FlatShardedAdamW(_FlatShardedBase):
     _state_names = ("exp_avg", "exp_avg_sq")
 
     def __init__(self, params: Iterable, *, units=None, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
-                 weight_decay: float = 1e-2, fused_reduce_update: bool = False, **_ignored) -> None:
+                 weight_decay: float = 1e-2, fused_reduce_update: bool = False, **torch_options) -> None:
+        _check_torch_options("AdamW", torch_options, amsgrad=False, maximize=False)
         if lr < 0 or eps < 0 or not 0 <= betas[0] < 1 or not 0 <= betas[1] < 1 or weight_decay < 0:
             raise ValueError("invalid AdamW hyper-parameters")
         super().__init__(params, dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay), units)
@@ -234,7 +251,8 @@ class FlatShardedSGD(_FlatShardedBase):
     _state_names = ("momentum_buffer",)
 
     def __init__(self, params: Iterable, *, units=None, lr: float = 1e-3, momentum: float = 0.0,
-                 weight_decay: float = 0.0, **_ignored) -> None:
+                 weight_decay: float = 0.0, **torch_options) -> None:
+        _check_torch_options("SGD", torch_options, nesterov=False, dampening=0, maximize=False)
         super().__init__(params, dict(lr=lr, momentum=momentum, weight_decay=weight_decay), units)
 
     @torch.no_grad()
