@@ -578,7 +578,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_qkv, const __grid_consta
       mbar_wait(smem_u32(acc_done), 0, p.status, abort_flag);
       ok = !softmax_bar_or(*abort_flag != 0);
     }
-    if (ok && stat_idx < p.S) {
+    if (ok) {
+      // tcgen05.ld is warp-collective: every lane takes part, only the stores depend on the row being valid
+      const bool row_ok = stat_idx < p.S;
       tc_fence_after();
       __nv_bfloat16* grow = p.dqkv + (long long)(row_base + stat_idx) * p.ld_dqkv + h * kHd;
 #pragma unroll
@@ -590,6 +592,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_qkv, const __grid_consta
           uint32_t t4[32];
           tmem_ld_32x32b_x32((a == 0 ? tmem_acc0 : tmem_acc1) + lane_off + half * 64 + c * 32, t4);
           tmem_ld_wait();
+          if (!row_ok) continue;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 o;
