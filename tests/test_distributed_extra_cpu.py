@@ -1,0 +1,190 @@
+"""More multi-rank CPU (gloo) cases: a 3-D mesh whose tensor-parallel dim is left alone, mixed precision across
+ranks, activation checkpointing across ranks, and the owner-broadcast / padded variants of the library transport."""
+import copy
+import os
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from dist_utils import run_ranks
+
+
+def _model(seed=0):
+    torch.manual_seed(seed)
+    return nn.Sequential(nn.Sequential(nn.Linear(8, 12), nn.Tanh()), nn.Sequential(nn.Linear(12, 8), nn.Tanh()),
+                         nn.Linear(8, 3))
+
+
+def _allreduce_grads(model, group=None):
+    world = dist.get_world_size(group)
+    for p in model.parameters():
+        dist.all_reduce(p.grad, group=group)
+        p.grad.div_(world)
+
+
+def _full_params(model):
+    from matrix_fsdp_b200.parallel.unit_collection import collect_param_groups
+
+    units = collect_param_groups(model)
+    for u in units:
+        u.unshard("test")
+    out = {n: p.detach().clone().float() for n, p in model.named_parameters()}
+    for u in units:
+        u.reshard("test")
+    return out
+
+
+def _mesh3d_worker(rank, world):
+    """(dp_replicate=1, dp_shard=2, tp=2): shard over dp_shard only; ranks that differ in tp never talk."""
+    from torch.distributed.device_mesh import init_device_mesh
+
+    from matrix_fsdp_b200 import DataParallelMeshDims, configure_optimizer, fully_shard
+
+    mesh = init_device_mesh("cpu", (1, 2, 2), mesh_dim_names=("dp_replicate", "dp_shard", "tp"))
+    tp = rank % 2
+    model = _model(seed=tp)                      # different weights per tp coordinate, like TP-local slices
+    ref = copy.deepcopy(model)
+    dims = DataParallelMeshDims(shard="dp_shard", replicate="dp_replicate")
+    for blk in list(model.children())[:-1]:
+        fully_shard(blk, mesh=mesh, dp_mesh_dims=dims)
+    fully_shard(model, mesh=mesh, dp_mesh_dims=dims)
+    unit = model[0]._matrix_fsdp_param_group
+    assert unit.world_size == 2 and unit.rank == rank // 2 and unit.replicate_world_size == 1
+    opt = configure_optimizer(model, "adamw", lr=1e-2, weight_decay=0.0)
+    ropt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.0)
+    shard_group = mesh.get_group("dp_shard")
+    g = torch.Generator().manual_seed(10 + rank)
+    for _ in range(2):
+        x = torch.randn(4, 8, generator=g)
+        model(x).pow(2).mean().backward()
+        opt.step()
+        opt.zero_grad()
+        ref(x).pow(2).mean().backward()
+        _allreduce_grads(ref, shard_group)
+        ropt.step()
+        ropt.zero_grad()
+    full = _full_params(model)
+    for n, p in ref.named_parameters():
+        assert torch.allclose(full[n], p.detach(), atol=2e-5), n
+
+
+def test_three_d_mesh_leaves_the_tp_dim_alone():
+    run_ranks(_mesh3d_worker, 4)
+
+
+def _mixed_precision_worker(rank, world):
+    from torch.distributed.fsdp import MixedPrecisionPolicy
+
+    from matrix_fsdp_b200 import configure_optimizer, fully_shard
+    from matrix_fsdp_b200.parallel.unit_collection import collect_param_groups
+
+    model = _model()
+    mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+    root_mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32, output_dtype=torch.float32)
+    for blk in list(model.children())[:-1]:
+        fully_shard(blk, mp_policy=mp)
+    fully_shard(model, mp_policy=root_mp)                       # only the root casts the model output back
+    opt = configure_optimizer(model, "adamw", lr=1e-2)
+    x = torch.randn(4, 8, generator=torch.Generator().manual_seed(rank))
+    out = model(x)
+    assert out.dtype == torch.float32
+    out.pow(2).mean().backward()
+    for u in collect_param_groups(model):
+        fb = u.flat_buffer
+        assert fb.local_shard.dtype == torch.float32 and fb.param_dtype == torch.bfloat16
+        assert fb.local_grad_shard is None or fb.local_grad_shard.dtype == torch.float32
+    opt.step()
+    opt.zero_grad()
+    for st in opt.state.values():
+        assert st["exp_avg"].dtype == torch.float32
+    # both ranks hold shards of one consistent model
+    full = _full_params(model)
+    for n, t in full.items():
+        ref = t.clone()
+        dist.broadcast(ref, src=0)
+        assert torch.equal(ref, t), n
+
+
+def test_two_rank_mixed_precision_keeps_fp32_master():
+    run_ranks(_mixed_precision_worker, 2)
+
+
+def _checkpointing_worker(rank, world):
+    from torch.utils.checkpoint import checkpoint
+
+    from matrix_fsdp_b200 import configure_optimizer, fully_shard
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            torch.manual_seed(0)
+            self.blocks = nn.ModuleList([nn.Sequential(nn.Linear(8, 8), nn.Tanh()) for _ in range(3)])
+
+        def forward(self, x, ckpt):
+            for b in self.blocks:
+                x = checkpoint(b, x, use_reentrant=False) if ckpt else b(x)
+            return x
+
+    model, ref = Net(), Net()
+    for b in model.blocks:
+        fully_shard(b)
+    opt = configure_optimizer(model, "sgd", lr=0.1)
+    ropt = torch.optim.SGD(ref.parameters(), lr=0.1)
+    g = torch.Generator().manual_seed(3 + rank)
+    for _ in range(2):
+        x = torch.randn(4, 8, generator=g)
+        loss = model(x, True).pow(2).mean()
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        rl = ref(x, False).pow(2).mean()
+        rl.backward()
+        _allreduce_grads(ref)
+        ropt.step()
+        ropt.zero_grad()
+        assert torch.allclose(loss, rl, atol=1e-6)
+    events = [e.name for e in model.blocks[0]._matrix_fsdp_param_group.runtime_events]
+    assert "pre_forward_recompute_skip" in events or events.count("pre_forward") >= 2
+
+
+def test_two_rank_activation_checkpointing():
+    run_ranks(_checkpointing_worker, 2)
+
+
+def _library_variants_worker(rank, world, gather_impl, reduce_impl):
+    from matrix_fsdp_b200 import configure_optimizer, fully_shard
+    from matrix_fsdp_b200.api import reset_shared_owner_planners
+
+    os.environ["MFSDP_ALLGATHERV_IMPL"] = gather_impl
+    os.environ["MFSDP_REDUCE_SCATTERV_IMPL"] = reduce_impl
+    reset_shared_owner_planners()
+    model = _model()
+    ref = copy.deepcopy(model)
+    for blk in list(model.children())[:-1]:
+        fully_shard(blk, optimizer_policy="mixed_muon_adamw")          # whole-matrix owners: uneven shards
+    fully_shard(model, optimizer_policy="mixed_muon_adamw")
+    unit = model[0]._matrix_fsdp_param_group
+    assert unit.flat_buffer.transport.kind == "torch_dist"
+    assert unit.flat_buffer.transport.gather_impl == gather_impl
+    opt = configure_optimizer(model, "adamw", lr=1e-2, weight_decay=0.0)
+    ropt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.0)
+    g = torch.Generator().manual_seed(20 + rank)
+    for _ in range(2):
+        x = torch.randn(4, 8, generator=g)
+        model(x).pow(2).mean().backward()
+        opt.step()
+        opt.zero_grad()
+        ref(x).pow(2).mean().backward()
+        _allreduce_grads(ref)
+        ropt.step()
+        ropt.zero_grad()
+    full = _full_params(model)
+    for n, p in ref.named_parameters():
+        assert torch.allclose(full[n], p.detach(), atol=2e-5), (gather_impl, reduce_impl, n)
+
+
+def test_owner_layout_over_every_library_collective_variant():
+    for gather_impl, reduce_impl in (("owner_broadcast", "owner_reduce"), ("padded_all_gather", "padded_reduce_scatter"),
+                                     ("auto", "auto")):
+        run_ranks(_library_variants_worker, 2, gather_impl, reduce_impl)
