@@ -49,8 +49,9 @@ def available() -> bool:
 
 
 def supports(seq: int) -> bool:
-    """Sequence lengths the training path hands to these kernels (forward + backward)."""
-    return seq > 0 and seq % 128 == 0
+    """Sequence lengths the training path hands to these kernels (forward + backward): any positive length;
+    partial tiles are masked inside the kernels."""
+    return seq > 0
 
 
 def _check_qkv(qkv: torch.Tensor, batch: int, seq: int, n_heads: int, head_dim: int) -> None:
@@ -89,7 +90,7 @@ def attention_bwd(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, lse:
 
     _check_qkv(qkv, batch, seq, n_heads, head_dim)
     if not supports(seq):
-        raise ValueError(f"attention backward needs a sequence length that is a multiple of 128, got {seq}")
+        raise ValueError(f"attention backward needs a positive sequence length, got {seq}")
     scale = 1.0 / math.sqrt(head_dim) if softmax_scale is None else float(softmax_scale)
     dout = dout.contiguous()
     out = out if out.stride(0) == dout.stride(0) else out.contiguous()
