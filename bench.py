@@ -251,10 +251,10 @@ def main() -> None:
     if args.impl == "reference" and cfg.get("kind") == "moe" and world > 1:
         # The reference's fully_shard (mixed_muon_adamw owner layout, its own NCCL collectives on side streams)
         # combined with the all_to_all_single expert dispatcher of baseline/ref_moe.py stopped making progress
-        # on 2 GPUs: both ranks blocked inside the first backward (stack dump recorded in DESIGN.md).
+        # on 2 GPUs: both ranks blocked inside the first backward (MFSDP_BENCH_DUMP_STACKS_AFTER_S shows the stacks).
         if rank == 0:
             print(json.dumps({"impl": "reference", "unavailable": "reference fully_shard + all_to_all_single EP "
-                              "dispatcher hangs in the first backward at N>=2 on this box (see DESIGN.md)"}))
+                              "dispatcher hangs in the first backward at N>=2 on this box"}))
         return
     device = torch.device("cuda", local_rank) if cuda else torch.device("cpu")
     if cuda:
