@@ -31,3 +31,54 @@ def device_train_step(model: torch.nn.Module, optimizer, tokens: torch.Tensor, t
     optimizer.step()
     optimizer.zero_grad(set_to_none=True)
     return loss.detach()
+
+
+@torch.no_grad()
+def clip_grad_norm_(module_or_units, max_norm: float, norm_type: float = 2.0,
+                    error_if_nonfinite: bool = False) -> torch.Tensor:
+    """Clip the global gradient norm of a sharded model in place and return the norm before clipping.
+
+    Every rank only holds its shard of each unit's reduced gradient, so the norm is assembled from the local
+    shards with one all-reduce per shard group (replicas of an HSDP mesh hold identical shards and are not
+    counted twice).  Call it after ``backward()`` and before ``optimizer.step()``; it waits for the units'
+    pending reduce-scatters first.  ``torch.nn.utils.clip_grad_norm_`` on the module would see local shards
+    only, which is what the reference leaves its users with.
+    """
+    import math
+
+    import torch.distributed as dist
+
+    from ..parallel.unit_collection import collect_param_groups
+
+    units = collect_param_groups(module_or_units)
+    inf = math.isinf(norm_type)
+    per_group: dict[int, tuple[object, torch.Tensor]] = {}
+    shards = []
+    for u in units:
+        u.wait_post_backward_reduce()
+        g = u.flat_buffer.local_grad_shard
+        if g is None or g.numel() == 0:
+            continue
+        shards.append(g)
+        part = g.detach().float().abs().max() if inf else g.detach().float().norm(norm_type).pow(norm_type)
+        group = u.groups.shard_group if u.world_size > 1 else None
+        key = id(group)
+        if key in per_group:
+            prev = per_group[key][1]
+            per_group[key] = (group, torch.maximum(prev, part) if inf else prev + part)
+        else:
+            per_group[key] = (group, part)
+    if not shards:
+        return torch.zeros(())
+    total = None
+    for group, part in per_group.values():
+        if group is not None:
+            dist.all_reduce(part, op=dist.ReduceOp.MAX if inf else dist.ReduceOp.SUM, group=group)
+        total = part if total is None else (torch.maximum(total, part) if inf else total + part)
+    norm = total if inf else total.pow(1.0 / norm_type)
+    if error_if_nonfinite and not torch.isfinite(norm):
+        raise RuntimeError(f"The total norm of order {norm_type} for the gradients is non-finite.")
+    coef = (max_norm / (norm + 1e-6)).clamp(max=1.0)
+    for g in shards:
+        g.mul_(coef.to(g.dtype))
+    return norm

@@ -188,3 +188,36 @@ def test_owner_layout_over_every_library_collective_variant():
     for gather_impl, reduce_impl in (("owner_broadcast", "owner_reduce"), ("padded_all_gather", "padded_reduce_scatter"),
                                      ("auto", "auto")):
         run_ranks(_library_variants_worker, 2, gather_impl, reduce_impl)
+
+
+def _clip_worker(rank, world):
+    from matrix_fsdp_b200 import configure_optimizer, fully_shard
+    from matrix_fsdp_b200.utils import clip_grad_norm_
+
+    model = _model()
+    ref = copy.deepcopy(model)
+    for blk in list(model.children())[:-1]:
+        fully_shard(blk)
+    fully_shard(model)
+    opt = configure_optimizer(model, "sgd", lr=0.5)
+    ropt = torch.optim.SGD(ref.parameters(), lr=0.5)
+    g = torch.Generator().manual_seed(40 + rank)
+    for max_norm in (0.05, 1e6):                      # one step that clips, one that does not
+        x = torch.randn(4, 8, generator=g) * 3
+        model(x).pow(2).mean().backward()
+        total = clip_grad_norm_(model, max_norm)
+        opt.step()
+        opt.zero_grad()
+        ref(x).pow(2).mean().backward()
+        _allreduce_grads(ref)
+        rtotal = torch.nn.utils.clip_grad_norm_(ref.parameters(), max_norm)
+        ropt.step()
+        ropt.zero_grad()
+        assert torch.allclose(total, rtotal, rtol=1e-5), (total, rtotal)
+    full = _full_params(model)
+    for n, p in ref.named_parameters():
+        assert torch.allclose(full[n], p.detach(), atol=1e-5), n
+
+
+def test_two_rank_global_gradient_clipping():
+    run_ranks(_clip_worker, 2)
