@@ -466,7 +466,14 @@ def make_mixed_muon_adamw_optimizer(module_or_units, *, default_matrix_optimizer
 
 def _optimizer_params_from_module_or_units(module_or_units) -> tuple[nn.Parameter, ...]:
     if isinstance(module_or_units, nn.Module):
-        return tuple(module_or_units.parameters())
+        # parameters that a unit was told to ignore belong to the upper stack (tensor / expert parallel owners)
+        # and its optimizer; unmanaged parameters that nobody claimed are still stepped here
+        ignored: set[int] = set()
+        managed: set[int] = set()
+        for u in _normalize_param_groups(module_or_units):
+            ignored |= {id(p) for p in (u.ignored_params or ())}
+            managed |= {id(mp.param) for mp in u.registry}
+        return tuple(p for p in module_or_units.parameters() if id(p) in managed or id(p) not in ignored)
     seen, out = set(), []
     for u in _normalize_param_groups(module_or_units):
         for mp in u.registry:
