@@ -1,0 +1,122 @@
+"""Dispatch and fallbacks of the op layer without a GPU: PyTorch paths for CPU tensors, environment switch,
+library loading and signature registration, reference Newton-Schulz, rope tables."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from matrix_fsdp_b200.ops import functional as OF
+from matrix_fsdp_b200.ops import lib
+
+
+def test_library_loads_and_binds_every_registered_entry_point():
+    import matrix_fsdp_b200.ops.attention  # noqa: F401
+    import matrix_fsdp_b200.ops.moe_kernels  # noqa: F401
+    import matrix_fsdp_b200.parallel.peer  # noqa: F401
+
+    handle = lib.load()
+    if handle is None:
+        pytest.skip("kernel library not built in this checkout")
+    missing = [n for n in lib._SIGNATURES if not hasattr(handle, n)]
+    assert missing == []
+    assert lib.launch_count() >= 0
+
+
+def test_env_switch_disables_native_kernels(monkeypatch):
+    monkeypatch.setenv("MFSDP_DISABLE_NATIVE_KERNELS", "1")
+    assert lib.disabled_by_env()
+    from matrix_fsdp_b200.ops import attention
+
+    assert not attention.available()
+    monkeypatch.setenv("MFSDP_DISABLE_NATIVE_KERNELS", "0")
+    assert not lib.disabled_by_env()
+
+
+def test_cpu_tensors_take_the_pytorch_paths():
+    torch.manual_seed(0)
+    x = torch.randn(5, 16, requires_grad=True)
+    w = torch.randn(8, 16, requires_grad=True)
+    assert not OF.use_native(x)
+    y = OF.linear(x, w)
+    assert torch.allclose(y, F.linear(x, w))
+    g = torch.randn(16)
+    n = OF.rms_norm(x, g, 1e-5)
+    ref = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * g
+    assert torch.allclose(n, ref, atol=1e-6)
+    gu = torch.randn(5, 12)
+    assert torch.allclose(OF.swiglu(gu), F.silu(gu[:, :6]) * gu[:, 6:], atol=1e-6)
+    logits = torch.randn(7, 11, requires_grad=True)
+    target = torch.randint(0, 11, (7,))
+    loss = OF.fused_cross_entropy(logits, target)
+    assert torch.allclose(loss, F.cross_entropy(logits, target), atol=1e-6)
+    loss.backward()
+    assert logits.grad is not None
+    target[0] = -100
+    assert torch.allclose(OF.fused_cross_entropy(logits, target, ignore_index=-100),
+                          F.cross_entropy(logits, target, ignore_index=-100), atol=1e-6)
+
+
+def test_rope_reference_is_a_rotation_and_tables_are_cached():
+    cos, sin = OF.rope_tables(9, 8, 10000.0, "cpu")
+    assert cos.shape == (9, 4) and OF.rope_tables(9, 8, 10000.0, "cpu")[0] is cos
+    x = torch.randn(2, 9, 3, 8)
+    y = OF.apply_rope_reference(x, cos, sin)
+    assert torch.allclose(y.norm(dim=-1), x.norm(dim=-1), atol=1e-5)         # rotations keep lengths
+    assert torch.allclose(y[:, 0], x[:, 0], atol=1e-6)                        # position 0 is the identity
+    # relative property: <rope(q, m), rope(k, n)> depends on m - n only
+    q, k = torch.randn(1, 9, 1, 8), torch.randn(1, 9, 1, 8)
+    q[:, :] = q[:, :1]
+    k[:, :] = k[:, :1]
+    rq, rk = OF.apply_rope_reference(q, cos, sin), OF.apply_rope_reference(k, cos, sin)
+    d1 = (rq[0, 3, 0] * rk[0, 1, 0]).sum()
+    d2 = (rq[0, 7, 0] * rk[0, 5, 0]).sum()
+    assert torch.allclose(d1, d2, atol=1e-5)
+
+
+def test_causal_attention_reference_is_causal():
+    torch.manual_seed(0)
+    B, S, nH, hd = 1, 6, 2, 4
+    qkv = torch.randn(B * S, 3 * nH * hd)
+    out = OF.causal_attention_reference(qkv, B, S, nH, hd)
+    qkv2 = qkv.clone()
+    qkv2[4:] += 1.0                                   # changing later tokens must not move earlier outputs
+    out2 = OF.causal_attention_reference(qkv2, B, S, nH, hd)
+    assert torch.allclose(out[:4], out2[:4], atol=1e-6) and not torch.allclose(out[4:], out2[4:])
+
+
+def test_reference_newton_schulz_orthogonalises():
+    from matrix_fsdp_b200.optim.muon import adjust_lr, newton_schulz_reference
+
+    torch.manual_seed(0)
+    for shape in ((16, 32), (32, 16)):
+        g = torch.randn(*shape)
+        o = newton_schulz_reference(g, steps=5).float()
+        s = torch.linalg.svdvals(o)
+        assert s.max() < 1.6 and s.min() > 0.3                 # singular values pulled towards 1
+    assert adjust_lr(0.02, None, (8, 4)) == adjust_lr(0.02, "original", (8, 4))      # torch's default
+    assert adjust_lr(0.02, "original", (4, 8)) == 0.02
+    assert adjust_lr(0.02, "original", (8, 4)) == pytest.approx(0.02 * math.sqrt(2.0))
+    assert adjust_lr(0.02, "match_rms_adamw", (8, 4)) == pytest.approx(0.2 * 0.02 * math.sqrt(8))
+
+
+def test_muon_step_matches_torch_muon_on_cpu():
+    if not hasattr(torch.optim, "Muon"):
+        pytest.skip("torch.optim.Muon not available")
+    from matrix_fsdp_b200.optim.muon import MatrixMuon
+
+    torch.manual_seed(0)
+    w1 = torch.nn.Parameter(torch.randn(12, 20))
+    w2 = torch.nn.Parameter(w1.detach().clone())
+    ours = MatrixMuon([w1], lr=0.02, momentum=0.95, weight_decay=0.1, ns_steps=5)
+    theirs = torch.optim.Muon([w2], lr=0.02, momentum=0.95, weight_decay=0.1, ns_steps=5)
+    for s in range(3):
+        g = torch.randn(12, 20, generator=torch.Generator().manual_seed(s))
+        w1.grad, w2.grad = g.clone(), g.clone()
+        ours.step()
+        theirs.step()
+    assert torch.allclose(w1, w2, atol=2e-3), (w1 - w2).abs().max()
+    with pytest.raises(ValueError, match="2D"):
+        bad = MatrixMuon([torch.nn.Parameter(torch.randn(4))], lr=0.02)
+        bad.param_groups[0]["params"][0].grad = torch.randn(4)
+        bad.step()
