@@ -63,7 +63,8 @@ def _piece_shape(mp: ManagedParam, start: int, numel: int) -> tuple[int, ...]:
     return (numel,)
 
 
-_POISON = os.environ.get("MFSDP_DEBUG_POISON", "0") not in ("", "0")
+def _poison_enabled() -> bool:
+    return os.environ.get("MFSDP_DEBUG_POISON", "0") not in ("", "0")
 
 
 class MatrixFlatBuffer:
@@ -207,7 +208,7 @@ class MatrixFlatBuffer:
         st = self.full_buffer.untyped_storage()
         if st.size() != self._full_nbytes():
             st.resize_(self._full_nbytes())
-            if _POISON and self.full_buffer.is_floating_point():
+            if _poison_enabled() and self.full_buffer.is_floating_point():
                 # debug aid: a read of gathered parameters before they arrived shows up as NaN
                 # (ordered before the gather by the gather stream's wait on the current stream)
                 self.full_buffer.fill_(float("nan"))
