@@ -90,12 +90,91 @@ def set_model_state_dict(model: nn.Module, model_state_dict, *, options=None) ->
     load_matrix_state_dict(model, model_state_dict, strict=o.strict)
 
 
+def _full_optimizer_state(model: nn.Module, optimizer, cpu: bool) -> dict[str, Any]:
+    """``{component: {"state": {parameter name: {state name: full tensor or scalar}}, "param_groups": [...]}}``.
+
+    Every rank of a shard group holds disjoint pieces of each state tensor (the piece of its parameter shard),
+    so the full tensor is the sum of the pieces placed at their parameter offsets: one all-reduce per
+    (parameter, state) over the unit's shard group.  Collective: every rank must call it.
+    """
+    import torch.distributed as dist
+
+    units = collect_param_groups(model)
+    name_of = {id(p): n for n, p in model.named_parameters(remove_duplicate=False)}
+    out: dict[str, Any] = {}
+    for comp, opt in iter_optimizer_components(optimizer):
+        state_out: dict[str, dict[str, Any]] = {}
+        managed: set[int] = set()
+        for u in units:
+            group = u.groups.shard_group if u.world_size > 1 else None
+            local_names = {}
+            for mp in u.registry:
+                managed.add(id(mp.param))
+                st = opt.state.get(mp.param, {})
+                local_names[mp.fqn] = sorted(k for k, v in st.items() if isinstance(v, torch.Tensor) and v.dim() > 0) + \
+                    sorted("#" + k for k, v in st.items() if not (isinstance(v, torch.Tensor) and v.dim() > 0))
+            if group is not None:
+                gathered: list = [None] * u.world_size
+                dist.all_gather_object(gathered, local_names, group=group)
+            else:
+                gathered = [local_names]
+            for mp in u.registry:
+                names = sorted({n for g in gathered for n in g.get(mp.fqn, ())})
+                if not names:
+                    continue
+                st = opt.state.get(mp.param, {})
+                piece = u.flat_buffer.pieces.get(mp.fqn)
+                entry: dict[str, Any] = {}
+                for n in names:
+                    if n.startswith("#"):                                   # scalar state (step): same on every owner
+                        v = st.get(n[1:])
+                        val = torch.tensor(float(v) if v is not None else float("-inf"), dtype=torch.float64)
+                        if group is not None:
+                            val = val.to(u.flat_buffer.device)
+                            dist.all_reduce(val, op=dist.ReduceOp.MAX, group=group)
+                        entry[n[1:]] = float(val)
+                        continue
+                    local = st.get(n)
+                    dtype = local.dtype if local is not None else torch.float32
+                    if group is not None:
+                        code = torch.tensor([{torch.float32: 0, torch.bfloat16: 1, torch.float16: 2,
+                                              torch.float64: 3}.get(dtype, 0) if local is not None else -1],
+                                            device=u.flat_buffer.device)
+                        dist.all_reduce(code, op=dist.ReduceOp.MAX, group=group)
+                        dtype = (torch.float32, torch.bfloat16, torch.float16, torch.float64)[max(int(code), 0)]
+                    full = torch.zeros(mp.numel, dtype=torch.float32 if dtype != torch.float64 else dtype,
+                                       device=u.flat_buffer.device)
+                    if local is not None and piece is not None and local.numel() == piece.numel:
+                        full[piece.param_start:piece.param_start + piece.numel] = local.reshape(-1).to(full.dtype)
+                    if group is not None:
+                        dist.all_reduce(full, group=group)
+                    full = full.to(dtype).view(mp.shape)
+                    entry[n] = full.cpu() if cpu else full
+                key = name_of.get(id(mp.param), f"{u.name}.{mp.fqn}")
+                state_out[key] = entry
+        for g in opt.param_groups:                                           # parameters outside any unit
+            for p in g["params"]:
+                if id(p) in managed or p not in opt.state:
+                    continue
+                state_out[name_of.get(id(p), str(id(p)))] = {
+                    k: (v.detach().clone().cpu() if cpu else v.detach().clone()) if isinstance(v, torch.Tensor) else v
+                    for k, v in opt.state[p].items()}
+        groups = [{k: v for k, v in g.items() if k != "params"} for g in opt.param_groups]
+        out[comp] = {"state": state_out, "param_groups": groups}
+    return out
+
+
 def get_optimizer_state_dict(model: nn.Module, optimizers, *, options=None) -> dict[str, Any]:
+    """Local (sharded) optimizer state dicts per component; with ``options.full_state_dict`` the state tensors are
+    assembled to full size and keyed by parameter name instead (collective)."""
+    o = _opts(options)
     opts = optimizers if isinstance(optimizers, (list, tuple)) else [optimizers]
     out: dict[str, Any] = {}
     for i, opt in enumerate(opts):
-        comps = {name: o.state_dict() for name, o in iter_optimizer_components(opt)}
-        out[f"optimizer_{i}"] = comps
+        if o.full_state_dict:
+            out[f"optimizer_{i}"] = _full_optimizer_state(model, opt, o.cpu_offload)
+        else:
+            out[f"optimizer_{i}"] = {name: c.state_dict() for name, c in iter_optimizer_components(opt)}
     return out if len(opts) > 1 else out["optimizer_0"]
 
 

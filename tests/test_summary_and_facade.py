@@ -126,3 +126,22 @@ def test_unit_debug_accessors():
     assert unit.state.value == "unsharded" and model[0][0].weight.shape == (8, 6)
     unit.reshard()
     assert unit.state.value == "sharded"
+
+
+def test_full_optimizer_state_dict_is_keyed_by_parameter_name():
+    from matrix_fsdp_b200 import get_optimizer_state_dict
+    from matrix_fsdp_b200.checkpoint import MatrixStateDictOptions
+
+    model, opt = _trained()
+    full = get_optimizer_state_dict(model, opt, options=MatrixStateDictOptions(full_state_dict=True, cpu_offload=True))
+    comp = full["optimizer"]
+    names = dict(model.named_parameters()).keys()
+    assert set(comp["state"]) == set(names)
+    entry = comp["state"]["0.0.weight"]
+    assert entry["exp_avg"].shape == (8, 6) and entry["exp_avg_sq"].shape == (8, 6) and entry["step"] == 2.0
+    assert entry["exp_avg"].device.type == "cpu" and comp["param_groups"][0]["lr"] == 1e-2
+    mixed_model, mixed = _trained(policy="mixed_muon_adamw", optimizer="mixed_muon_adamw")
+    full2 = get_optimizer_state_dict(mixed_model, mixed, options=MatrixStateDictOptions(full_state_dict=True))
+    assert set(full2) == {"muon", "adamw"}
+    assert "momentum_buffer" in full2["muon"]["state"]["0.0.weight"]
+    assert "exp_avg" in full2["adamw"]["state"]["0.0.bias"]
