@@ -51,6 +51,9 @@ CONFIGS = {
     "5s": dict(model="moe-4L-h1024-e16x512-top2-v8192", kind="moe", vocab_size=8192, hidden=1024, n_layers=4,
                n_heads=8, head_dim=128, n_experts=16, expert_ffn=512, top_k=2, micro_batch=2, seq_len=1024,
                optimizer="mixed_muon_adamw", ac=False, lr=0.02, betas=(0.9, 0.95), weight_decay=0.1),
+    "4t": dict(model="llama-2L-h256-ffn688-v1024-hsdp", vocab_size=1024, hidden=256, n_layers=2, n_heads=2, head_dim=128,
+               ffn=688, micro_batch=2, seq_len=128, optimizer="mixed_muon_adamw", ac=True, lr=0.02, betas=(0.9, 0.95),
+               weight_decay=0.1, hsdp_replicate=2),
     "tiny": dict(model="llama-2L-h256-ffn688-v1024", vocab_size=1024, hidden=256, n_layers=2, n_heads=2,
                  head_dim=128, ffn=688, micro_batch=2, seq_len=128, optimizer="adamw", ac=False,
                  lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1),
@@ -223,6 +226,79 @@ def build_reference(cfg: dict, device, mesh, world: int):
     return model, opt
 
 
+# ------------------------------------------------------------------------------------ checkpoint reshard check
+def _state_checksums(model, opt) -> dict[str, int]:
+    """Layout-independent checksums: for every parameter and optimizer state tensor the sum of its elements' bit
+    patterns (as integers) over all ranks of the shard group.  Equal tensors give equal sums on any sharding."""
+    from matrix_fsdp_b200.checkpoint.state_dict import iter_optimizer_components
+    from matrix_fsdp_b200.parallel.unit_collection import collect_param_groups
+
+    def bits(t: torch.Tensor) -> torch.Tensor:
+        t = t.detach().contiguous().reshape(-1)
+        view = t.view(torch.int32) if t.element_size() == 4 else t.view(torch.int16)
+        return view.to(torch.int64).sum().reshape(1)
+
+    sums: dict[str, torch.Tensor] = {}
+    units = collect_param_groups(model)
+    for ui, u in enumerate(units):
+        fb = u.flat_buffer
+        for mp in u.registry:
+            piece = fb.pieces.get(mp.fqn)
+            zero = torch.zeros(1, dtype=torch.int64, device=fb.device)
+            sums[f"u{ui}.{mp.fqn}.param"] = bits(fb.local_shard[piece.local_start:piece.local_end]) if piece else zero
+            for comp, o in iter_optimizer_components(opt):
+                for name, v in sorted(o.state.get(mp.param, {}).items()):
+                    if isinstance(v, torch.Tensor) and v.dim() > 0 and piece is not None and v.numel() == piece.numel:
+                        sums[f"u{ui}.{mp.fqn}.{comp}.{name}"] = bits(v)
+    keys: list = [None] * (dist.get_world_size() if dist.is_initialized() else 1)
+    if dist.is_initialized():
+        dist.all_gather_object(keys, sorted(sums))
+    else:
+        keys = [sorted(sums)]
+    all_keys = sorted({k for ks in keys for k in ks})
+    dev = units[0].flat_buffer.device
+    vec = torch.cat([sums.get(k, torch.zeros(1, dtype=torch.int64, device=dev)).to(dev) for k in all_keys])
+    if dist.is_initialized():
+        dist.all_reduce(vec)                      # replicas count the same pieces: divide that factor out below
+    rep = max(units[0].replicate_world_size, 1)
+    return {k: int(v) // rep for k, v in zip(all_keys, vec.tolist())}
+
+
+def verify_reshard(cfg: dict, model, opt, device, world: int, rank: int) -> dict:
+    """save_matrix_dcp from the benchmarked (possibly HSDP) model, load_matrix_dcp(allow_reshard=True) into the same
+    model on a flat dp_shard = world mesh, and compare parameter / optimizer-state checksums."""
+    import shutil
+    import tempfile
+
+    from matrix_fsdp_b200 import load_matrix_dcp, save_matrix_dcp
+    from matrix_fsdp_b200.api import reset_shared_owner_planners
+
+    path = [tempfile.mkdtemp(prefix="mfsdp_reshard_") if rank == 0 else None]
+    if world > 1:
+        dist.broadcast_object_list(path, src=0)
+    t0 = time.perf_counter()
+    save_matrix_dcp(model, path[0], optimizer=opt)
+    before = _state_checksums(model, opt)
+    flat_cfg = {k: v for k, v in cfg.items() if k != "hsdp_replicate"}
+    mesh = None
+    if world > 1:
+        from torch.distributed.device_mesh import init_device_mesh
+
+        mesh = init_device_mesh(device.type, (world,), mesh_dim_names=("dp_shard",))
+    reset_shared_owner_planners()
+    model_b, opt_b = build_ours(flat_cfg, device, mesh, world)
+    load_matrix_dcp(model_b, path[0], optimizer=opt_b, allow_reshard=True)
+    after = _state_checksums(model_b, opt_b)
+    common = sorted(set(before) & set(after))
+    bad = [k for k in common if before[k] != after[k]]
+    if world > 1:
+        dist.barrier()
+    if rank == 0:
+        shutil.rmtree(path[0], ignore_errors=True)
+    return {"tensors_compared": len(common), "mismatched": bad[:5], "checksums_equal": not bad and bool(common),
+            "seconds": time.perf_counter() - t0, "target_parallelism": f"dp_shard{world}"}
+
+
 # ------------------------------------------------------------------------------------ main
 def main() -> None:
     ap = argparse.ArgumentParser()
@@ -232,6 +308,8 @@ def main() -> None:
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--config", default="2", choices=sorted(CONFIGS))
     ap.add_argument("--device", default=None)
+    ap.add_argument("--verify-reshard", action="store_true",
+                    help="after timing: save_matrix_dcp, load resharded onto a flat dp_shard mesh, compare checksums")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
     dump_after = float(os.environ.get("MFSDP_BENCH_DUMP_STACKS_AFTER_S", "0"))
@@ -402,6 +480,8 @@ def main() -> None:
                 "h2d_bytes_per_step": 2 * B * S * 8, "d2h_bytes_per_step": 4, "last_loss": e2e_loss},
         "gpu_launches": launches, "host_issue_ms_per_step": host_issue_ms,
     }
+    if args.verify_reshard and args.impl == "ours":
+        out["reshard"] = verify_reshard(cfg, model, opt, device, world, rank)
     if rank == 0:
         print(json.dumps(out))
     if world > 1:

@@ -50,3 +50,24 @@ def test_regression_package_check(capsys):
     assert regression.main(["package"]) == 0
     rec = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert rec["missing_entry_points"] == [] and rec["unresolved_public_names"] == []
+
+
+def test_bench_reshard_verification_on_four_cpu_ranks():
+    """bench.py --verify-reshard: HSDP 2 x 2 run, save, load resharded onto dp_shard = 4, equal checksums."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
+           "127.0.0.1", "--master-port", "29541", "bench.py", "--gpus", "4", "--config", "4t", "--device", "cpu",
+           "--steps", "1", "--warmup", "1", "--verify-reshard"]
+    env = dict(os.environ, GLOO_SOCKET_IFNAME="lo", OMP_NUM_THREADS="1")
+    p = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=600, env=env)
+    assert p.returncode == 0, p.stderr[-2000:]
+    line = next(ln for ln in reversed(p.stdout.splitlines()) if ln.startswith("{"))
+    rec = json.loads(line)
+    assert rec["config"]["parallelism"] == "dp_replicate2xdp_shard2" and rec["n_gpus"] == 4
+    assert rec["reshard"]["checksums_equal"] and rec["reshard"]["tensors_compared"] > 20
+    assert rec["reshard"]["target_parallelism"] == "dp_shard4"
