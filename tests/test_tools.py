@@ -71,3 +71,22 @@ def test_bench_reshard_verification_on_four_cpu_ranks():
     assert rec["config"]["parallelism"] == "dp_replicate2xdp_shard2" and rec["n_gpus"] == 4
     assert rec["reshard"]["checksums_equal"] and rec["reshard"]["tensors_compared"] > 20
     assert rec["reshard"]["target_parallelism"] == "dp_shard4"
+
+
+def test_compare_bench_against_fsdp2_and_eager(capsys):
+    import json
+
+    from matrix_fsdp_b200.tools import compare_bench
+
+    rc = compare_bench.main(["--world-size", "2", "--device", "cpu", "--modes", "matrix_default", "matrix_owner_muon",
+                             "fsdp2", "--hidden", "32", "--layers", "2", "--heads", "2", "--seq", "8", "--steps", "2",
+                             "--warmup", "1", "--correctness"])
+    assert rc == 0
+    rows = {r["mode"]: r for r in map(json.loads, capsys.readouterr().out.strip().splitlines())}
+    assert set(rows) == {"matrix_default", "matrix_owner_muon", "fsdp2"}
+    for mode, r in rows.items():
+        if "unavailable" in r:
+            assert mode == "fsdp2"                       # only the library mode may be missing in a torch build
+            continue
+        assert r["step_ms"] > 0 and set(r["phase_ms"]) == {"zero_grad", "forward", "backward", "step"}
+        assert r["max_loss_diff_vs_eager"] < 1e-5 and r["max_param_diff_vs_eager"] < 1e-4, (mode, r)
