@@ -23,7 +23,6 @@ Ranks are spawned with ``torch.multiprocessing`` and rendezvous through a ``file
 from __future__ import annotations
 
 import argparse
-import copy
 import json
 import os
 import tempfile
