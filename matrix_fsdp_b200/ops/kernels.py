@@ -3,6 +3,12 @@
 Each function validates shapes/dtypes, launches on the current CUDA stream and returns
 torch tensors.  They are the non-differentiable building blocks; autograd wiring lives
 in :mod:`matrix_fsdp_b200.ops.functional`.
+
+The reference has two device kernels of its own, both plain copies
+(``matrix_fsdp/kernels/native/matrix_copy_cuda.cu:8-36``, bound in ``matrix_copy.cpp:1-162`` and loaded by
+``matrix_fsdp/kernels/native.py:1-492``); every model op there goes through PyTorch / cuBLAS.  ``copy_segments``
+here is the counterpart of those copies; everything else replaces library calls of the reference's bench models
+(``test/fsdp/bench_fsdp2_compare.py:456-483``) and of ``torch.optim`` (AdamW, SGD, ``torch/optim/_muon.py:276-310``).
 """
 from __future__ import annotations
 

@@ -3,6 +3,10 @@
 Launchers take raw device pointers plus the CUDA stream handle, so the same symbols are
 callable from Python, from C and from a process that never imports torch.  On a machine
 with a GPU the library must be present: ops fail loudly instead of falling back.
+
+Counterpart of the reference's lazy extension loader (``matrix_fsdp/kernels/native.py:17-115``, pybind module
+``matrix_fsdp._matrix_fsdp_cuda``); ``MFSDP_DISABLE_NATIVE_KERNELS`` plays the role of
+``MATRIX_FSDP_DISABLE_NATIVE_KERNELS`` there.
 """
 from __future__ import annotations
 

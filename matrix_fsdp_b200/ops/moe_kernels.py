@@ -1,4 +1,9 @@
-"""Tensor-level wrappers of the MoE routing / expert-parallel kernels in ``csrc/moe.cu``."""
+"""Tensor-level wrappers of the MoE routing / expert-parallel kernels in ``csrc/moe.cu``.
+
+The reference ships no MoE kernels; the dispatcher these replace is the PyTorch fixture of its EP test
+(``test/fsdp/test_deepseek_v3_ep_train.py:472-563``: four ``all_to_all_single`` calls, argsort, index_select,
+scatter_add and a Python loop over local experts).
+"""
 from __future__ import annotations
 
 import ctypes as C

@@ -5,6 +5,9 @@
 Every number is CUDA-event timed after warm-up; between iterations the inputs rotate through enough
 distinct buffers to exceed L2.  Fractions are of the measured peaks in ``MEASURED_PEAKS.json``
 (fallback 6650 GB/s, 1590 TFLOP/s).  ``--small`` runs one tiny case, sized for profiler captures.
+
+The reference has no single-kernel benchmark; its closest tools are the copy-in and parameter-materialisation
+micro-benchmarks inside ``test/fsdp/bench_fsdp2_compare.py:2686-2770``.
 """
 from __future__ import annotations
 

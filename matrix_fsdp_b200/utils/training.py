@@ -1,7 +1,8 @@
 """Small user-facing training helpers.
 
 ``train_step`` is the whole per-step call a user makes: copy the step's token batch from pinned
-host memory, forward, backward, optimizer step, and read the loss back to the host.
+host memory, forward, backward, optimizer step, and read the loss back to the host.  The reference leaves the
+training loop to its users (its bench loop is ``test/fsdp/bench_fsdp2_compare.py:1658-1708``).
 """
 from __future__ import annotations
 
