@@ -51,6 +51,9 @@ CONFIGS = {
     "5s": dict(model="moe-4L-h1024-e16x512-top2-v8192", kind="moe", vocab_size=8192, hidden=1024, n_layers=4,
                n_heads=8, head_dim=128, n_experts=16, expert_ffn=512, top_k=2, micro_batch=2, seq_len=1024,
                optimizer="mixed_muon_adamw", ac=False, lr=0.02, betas=(0.9, 0.95), weight_decay=0.1),
+    "5t": dict(model="moe-2L-h256-e8x128-top2-v512", kind="moe", vocab_size=512, hidden=256, n_layers=2, n_heads=2,
+               head_dim=128, n_experts=8, expert_ffn=128, top_k=2, micro_batch=2, seq_len=64, optimizer="mixed_muon_adamw",
+               ac=False, lr=0.02, betas=(0.9, 0.95), weight_decay=0.1),
     "4t": dict(model="llama-2L-h256-ffn688-v1024-hsdp", vocab_size=1024, hidden=256, n_layers=2, n_heads=2, head_dim=128,
                ffn=688, micro_batch=2, seq_len=128, optimizer="mixed_muon_adamw", ac=True, lr=0.02, betas=(0.9, 0.95),
                weight_decay=0.1, hsdp_replicate=2),
@@ -197,7 +200,9 @@ def build_reference(cfg: dict, device, mesh, world: int):
         for layer in model.layers:
             R.fully_shard(layer, mesh=mesh, mp_policy=mp, optimizer_policy="mixed_muon_adamw",
                           ignored_params=set(layer.experts.parameters()))
-        R.fully_shard(model, mesh=mesh, mp_policy=mp, ignored_params=set(model.expert_parameters()))
+        # the reference's root call does not skip parameters that nested units already manage: name them
+        R.fully_shard(model, mesh=mesh, mp_policy=mp,
+                      ignored_params={p for layer in model.layers for p in layer.parameters()})
         dense = R.configure_optimizer(model, "mixed_muon_adamw", muon_lr=cfg["lr"], adamw_lr=3e-4,
                                       adamw_betas=cfg["betas"], weight_decay=cfg["weight_decay"], muon_momentum=0.95,
                                       muon_ns_steps=5, muon_adjust_lr_fn="original")
@@ -214,7 +219,10 @@ def build_reference(cfg: dict, device, mesh, world: int):
     policy = "mixed_muon_adamw" if cfg["optimizer"] == "mixed_muon_adamw" else None
     for layer in model.layers:
         R.fully_shard(layer, mesh=mesh, mp_policy=mp, optimizer_policy=policy)
-    R.fully_shard(model, mesh=mesh, mp_policy=mp)
+    # the reference's root call does not skip parameters that nested units already manage (it would register
+    # their local shard views a second time): pass them as ignored_params, which is its documented way
+    R.fully_shard(model, mesh=mesh, mp_policy=mp,
+                  ignored_params={p for layer in model.layers for p in layer.parameters()})
     if cfg["optimizer"] == "adamw":
         opt = R.configure_optimizer(model, "adamw", lr=cfg["lr"], betas=cfg["betas"], weight_decay=cfg["weight_decay"])
     else:
@@ -325,14 +333,6 @@ def main() -> None:
     if args.impl == "reference" and not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "matrix_fsdp")):
         if rank == 0:
             print(json.dumps({"impl": "reference", "unavailable": "reference package not installed under baseline/_ref"}))
-        return
-    if args.impl == "reference" and cfg.get("kind") == "moe" and world > 1:
-        # The reference's fully_shard (mixed_muon_adamw owner layout, its own NCCL collectives on side streams)
-        # combined with the all_to_all_single expert dispatcher of baseline/ref_moe.py stopped making progress
-        # on 2 GPUs: both ranks blocked inside the first backward (MFSDP_BENCH_DUMP_STACKS_AFTER_S shows the stacks).
-        if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": "reference fully_shard + all_to_all_single EP "
-                              "dispatcher hangs in the first backward at N>=2 on this box"}))
         return
     device = torch.device("cuda", local_rank) if cuda else torch.device("cpu")
     if cuda:
