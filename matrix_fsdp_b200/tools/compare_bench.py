@@ -13,8 +13,8 @@ Modes
   ``matrix_row``          row sharding (``shard_placement_fn=Shard(0)``), AdamW
   ``matrix_owner_muon``   ``optimizer_policy="mixed_muon_adamw"`` (whole-matrix owners) + mixed Muon / AdamW
   ``fsdp2``               ``torch.distributed.fsdp.fully_shard`` per block, AdamW
-  ``fsdp2_muon``          FSDP2 + ``torch.optim.Muon`` on full matrices gathered from DTensors (what a user of
-                          FSDP2 has to do for Muon) — reported only when this torch build can do it
+  ``fsdp2_muon``          FSDP2 + ``torch.optim.Muon`` on the DTensor shards (every Newton-Schulz product redistributes
+                          the sharded matrices) + AdamW for the rest: the baseline of the reference's Muon rows
 Per mode it reports the step time (host clock around synchronised steps, max over ranks), phase times
 (zero_grad / forward / backward / step), peak memory, and with ``--correctness`` the loss difference and the
 largest full-parameter difference against an eager model whose gradients the tool all-reduces itself.
@@ -95,8 +95,13 @@ def _setup_mode(mode: str, model: nn.Module, args):
     for blk in model:
         fsdp2_fully_shard(blk)
     if mode == "fsdp2_muon":
-        raise NotImplementedError("torch.optim.Muon does not accept DTensor shards; FSDP2 + Muon needs a full gather")
-    opt = torch.optim.AdamW(model.parameters(), lr=args.lr, weight_decay=0.0)
+        # torch.optim.Muon on DTensor shards: every Newton-Schulz matmul redistributes the sharded matrix
+        mats = [p for p in model.parameters() if p.dim() == 2]
+        rest = [p for p in model.parameters() if p.dim() != 2]
+        opt = _Both(torch.optim.Muon(mats, lr=args.muon_lr, momentum=0.95, nesterov=True, ns_steps=5, weight_decay=0.0),
+                    torch.optim.AdamW(rest, lr=args.lr, weight_decay=0.0))
+    else:
+        opt = torch.optim.AdamW(model.parameters(), lr=args.lr, weight_decay=0.0)
 
     def gather_full():
         out = {}
@@ -108,10 +113,25 @@ def _setup_mode(mode: str, model: nn.Module, args):
     return opt, gather_full
 
 
+class _Both:
+    """Two optimizers stepped together (Muon for the matrices, AdamW for the rest)."""
+
+    def __init__(self, *opts) -> None:
+        self.opts = opts
+
+    def step(self) -> None:
+        for o in self.opts:
+            o.step()
+
+    def zero_grad(self) -> None:
+        for o in self.opts:
+            o.zero_grad()
+
+
 def _eager_reference(args, device, world: int, rank: int, mode: str):
     """Eager model + the same optimizer family; gradients are averaged over ranks by hand."""
     ref = build_model(args.hidden, args.layers, args.heads, args.inter).to(device)
-    if mode == "matrix_owner_muon" and hasattr(torch.optim, "Muon"):
+    if mode in ("matrix_owner_muon", "fsdp2_muon") and hasattr(torch.optim, "Muon"):
         mats = [p for p in ref.parameters() if p.dim() == 2]
         rest = [p for p in ref.parameters() if p.dim() != 2]
         opts = [torch.optim.Muon(mats, lr=args.muon_lr, momentum=0.95, nesterov=True, ns_steps=5, weight_decay=0.0),
@@ -193,10 +213,11 @@ def _worker(rank: int, world: int, args, init_file: str, out_file: str) -> None:
         dist.init_process_group("nccl" if cuda else "gloo", init_method=f"file://{init_file}", rank=rank,
                                 world_size=world)
     rows = [_run_mode(m, args, device, world, rank) for m in args.modes]
-    base = next((r for r in rows if r["mode"] == "fsdp2" and "step_ms" in r), None)
     for r in rows:
-        if base and "step_ms" in r and r is not base:
-            r["speedup_vs_fsdp2"] = base["step_ms"] / r["step_ms"]
+        base_mode = "fsdp2_muon" if r["mode"] == "matrix_owner_muon" else "fsdp2"
+        base = next((b for b in rows if b["mode"] == base_mode and "step_ms" in b), None)
+        if base and "step_ms" in r and r is not base and not r["mode"].startswith("fsdp2"):
+            r[f"speedup_vs_{base_mode}"] = base["step_ms"] / r["step_ms"]
     if rank == 0:
         with open(out_file, "w") as f:
             json.dump(rows, f)
