@@ -380,14 +380,11 @@ def main() -> None:
         return loss
 
     def e2e_step(i: int) -> float:
+        # the user-facing call: pinned host batch -> device, forward, backward, optimizer step, loss back to the host
+        from matrix_fsdp_b200.utils import train_step
+
         hb = host[total_steps + i]
-        tokens = hb[:, :-1].to(device, non_blocking=True)
-        targets = hb[:, 1:].to(device, non_blocking=True)
-        loss = model(tokens, targets)
-        loss.backward()
-        opt.step()
-        opt.zero_grad(set_to_none=True)
-        return float(loss.item())
+        return train_step(model, opt, hb[:, :-1], hb[:, 1:], device)
 
     launches_before = 0
     counter = None
