@@ -380,11 +380,19 @@ def main() -> None:
         return loss
 
     def e2e_step(i: int) -> float:
-        # the user-facing call: pinned host batch -> device, forward, backward, optimizer step, loss back to the host
-        from matrix_fsdp_b200.utils import train_step
-
+        # pinned host batch -> device, forward, backward, optimizer step, loss back to the host
         hb = host[total_steps + i]
-        return train_step(model, opt, hb[:, :-1], hb[:, 1:], device)
+        if args.impl == "ours":
+            from matrix_fsdp_b200.utils import train_step        # the user-facing call of this package
+
+            return train_step(model, opt, hb[:, :-1], hb[:, 1:], device)
+        tokens = hb[:, :-1].to(device, non_blocking=True)        # same steps spelled out: nothing of this package
+        targets = hb[:, 1:].to(device, non_blocking=True)        # runs in the reference arm
+        loss = model(tokens, targets)
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return float(loss.item())
 
     launches_before = 0
     counter = None
