@@ -259,16 +259,29 @@ class _AttentionCore:
 
 # ---------------------------------------------------------------------------- the block node
 def _fused_weight(parts: list[torch.Tensor]) -> torch.Tensor | None:
-    """If ``parts`` are row-blocks laid out back to back in memory, view them as one matrix."""
+    """If ``parts`` are row-blocks laid out back to back in ONE storage, view them as one matrix.
+
+    Adjacent addresses are not enough: two separate allocations can sit next to each other, and a
+    view may not run past the storage it was made from.  So every part has to be a view of the
+    same untyped storage, at consecutive element offsets, and that storage has to cover the whole
+    stacked matrix.
+    """
     first = parts[0]
-    ptr = first.data_ptr()
+    if first.dim() != 2:
+        return None
+    store = first.untyped_storage()
+    base, esz = store.data_ptr(), first.element_size()
+    off = first.storage_offset()
     cols = first.shape[1]
     rows = 0
     for p in parts:
-        if p.data_ptr() != ptr or p.shape[1] != cols or not p.is_contiguous() or p.dtype != first.dtype:
+        if (p.dim() != 2 or p.shape[1] != cols or p.dtype != first.dtype or not p.is_contiguous()
+                or p.untyped_storage().data_ptr() != base or p.storage_offset() != off):
             return None
-        ptr += p.numel() * p.element_size()
+        off += p.numel()
         rows += p.shape[0]
+    if off * esz > store.nbytes():
+        return None
     return first.as_strided((rows, cols), (cols, 1))
 
 

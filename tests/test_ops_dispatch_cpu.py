@@ -120,3 +120,33 @@ def test_muon_step_matches_torch_muon_on_cpu():
         bad = MatrixMuon([torch.nn.Parameter(torch.randn(4))], lr=0.02)
         bad.param_groups[0]["params"][0].grad = torch.randn(4)
         bad.step()
+
+
+def test_fused_weight_needs_one_storage_not_adjacent_addresses():
+    """Row blocks are stacked into one matrix only when they are consecutive views of one storage."""
+    buf = torch.arange(6 * 4, dtype=torch.float32)
+    a, b = buf[:8].view(2, 4), buf[8:24].view(4, 4)
+    fused = OF._fused_weight([a, b])
+    assert fused is not None and fused.shape == (6, 4)
+    assert torch.equal(fused, buf.view(6, 4))
+    # a gap, a swapped order, or a different width break the stacking
+    assert OF._fused_weight([b, a]) is None
+    assert OF._fused_weight([buf[:8].view(2, 4), buf[12:24].view(3, 4)]) is None
+    assert OF._fused_weight([buf[:8].view(2, 4), buf[8:24].view(2, 8)]) is None
+    # two separate allocations never fuse, wherever the allocator put them
+    x, y = torch.zeros(2, 4), torch.zeros(4, 4)
+    assert OF._fused_weight([x, y]) is None
+
+    class FakeAdjacent(torch.Tensor):
+        """Second allocation that reports the address right behind the first one."""
+        @staticmethod
+        def __new__(cls, t, ptr):
+            r = torch.Tensor._make_subclass(cls, t)
+            r._ptr = ptr
+            return r
+
+        def data_ptr(self):
+            return self._ptr
+
+    fake = FakeAdjacent(y, x.data_ptr() + x.numel() * 4)
+    assert OF._fused_weight([x, fake]) is None
