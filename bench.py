@@ -307,6 +307,98 @@ def verify_reshard(cfg: dict, model, opt, device, world: int, rank: int) -> dict
             "seconds": time.perf_counter() - t0, "target_parallelism": f"dp_shard{world}"}
 
 
+# ------------------------------------------------------------------------------------ diagnostics
+def _transport_description(model) -> str:
+    from matrix_fsdp_b200.parallel.unit_collection import collect_param_groups
+
+    kinds = set()
+    for u in collect_param_groups(model):
+        t = u.flat_buffer.transport
+        kinds.add(t.describe() if hasattr(t, "describe") else t.kind)
+    return ",".join(sorted(kinds))
+
+
+def _moe_drop_report(model, device, world: int) -> dict:
+    """Rows the expert-parallel dispatch could not place (0 on a dropless run), summed over ranks."""
+    lost = torch.zeros(1, dtype=torch.int64, device=device)
+    routed = torch.zeros(1, dtype=torch.int64, device=device)
+    for layer in getattr(model, "layers", []):
+        ctx = getattr(layer, "_ep_ctx_last", None)
+        if ctx is not None and hasattr(ctx, "rows_lost_total"):
+            lost += int(ctx.rows_lost_total())
+            routed += int(ctx.rows_routed_total())
+    if world > 1:
+        dist.all_reduce(lost)
+        dist.all_reduce(routed)
+    return {"rows_lost": int(lost.item()), "rows_routed": int(routed.item())}
+
+
+def write_timeline(path: str, device_step, sync, rank: int, world: int, device, bench_line: dict) -> dict:
+    """Three extra steps with CUDA-event spans around every collective; per-row max over ranks."""
+    from matrix_fsdp_b200.parallel import device_timeline as TL
+
+    TL.enable(True)
+    device_step(0)                       # first step with recording on is not reported
+    sync()
+    TL.clear()
+    TL.mark_origin()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    n = 3
+    for i in range(n):
+        device_step(i + 1)
+    ev1.record()
+    spans = TL.resolve()
+    step_ms = ev0.elapsed_time(ev1) / n
+    TL.enable(False)
+    rows = [s.as_row() for s in spans if s.device_ms is not None]
+    gathered: list = [None] * world
+    if world > 1:
+        dist.all_gather_object(gathered, (step_ms, rows))
+    else:
+        gathered = [(step_ms, rows)]
+    totals = {"step_ms": max(g[0] for g in gathered)}
+    if rank != 0:
+        return totals
+    # same collectives in the same order on every rank: merge row by row
+    base = gathered[0][1]
+    lines = [f"# Step timeline: {bench_line['config']['model']}, {bench_line['config']['parallelism']}, "
+             f"transport {bench_line.get('transport')}", "",
+             f"Command: `python -m torch.distributed.run --nnodes=1 --nproc-per-node {world} bench.py --gpus {world} "
+             f"--steps {bench_line['steps']} --warmup {bench_line['warmup']} --timeline {path}` (for 1 GPU: plain "
+             "`python bench.py ...`).", "",
+             f"Spans are CUDA events on the communication streams, {n} steps after the timed region "
+             f"(device step {totals['step_ms']:.3f} ms with recording on; bench line: "
+             f"{bench_line['ms_per_step']:.3f} ms).  `exposed` is the time the compute stream stood still at the "
+             "wait for that collective; every figure is the max over ranks, per step-local row.", ""]
+    per_kind: dict[str, dict] = {}
+    table = ["| # | unit | collective | impl | MB | issued for | start ms | device ms (max) | device ms (min) | exposed ms (max) |",
+             "|---|---|---|---|---|---|---|---|---|---|"]
+    for i, r in enumerate(base):
+        peers = [g[1][i] for g in gathered if i < len(g[1])]
+        dmax = max(p["device_ms"] for p in peers)
+        dmin = min(p["device_ms"] for p in peers)
+        emax = max((p["exposed_ms"] or 0.0) for p in peers)
+        k = per_kind.setdefault(r["kind"], {"count": 0, "device_ms": 0.0, "exposed_ms": 0.0, "bytes": 0})
+        k["count"] += 1
+        k["device_ms"] += dmax
+        k["exposed_ms"] += emax
+        k["bytes"] += r["bytes"]
+        table.append(f"| {i} | {r['unit']} | {r['kind']} | {r['impl']} | {r['bytes'] / 2 ** 20:.1f} | {r['reason']} | "
+                     f"{(r['start_ms'] or 0.0):.3f} | {dmax:.3f} | {dmin:.3f} | {emax:.3f} |")
+    lines.append("| collective | count / step | device ms / step | exposed ms / step | MB / step |")
+    lines.append("|---|---|---|---|---|")
+    for kind, k in per_kind.items():
+        lines.append(f"| {kind} | {k['count'] / n:.1f} | {k['device_ms'] / n:.3f} | {k['exposed_ms'] / n:.3f} | "
+                     f"{k['bytes'] / n / 2 ** 20:.1f} |")
+        totals[kind] = {"device_ms_per_step": k["device_ms"] / n, "exposed_ms_per_step": k["exposed_ms"] / n}
+    lines += ["", "Rows (all recorded steps, in issue order on rank 0):", ""] + table
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    with open(path, "w") as f:
+        f.write("\n".join(lines) + "\n")
+    return totals
+
+
 # ------------------------------------------------------------------------------------ main
 def main() -> None:
     ap = argparse.ArgumentParser()
@@ -318,6 +410,9 @@ def main() -> None:
     ap.add_argument("--device", default=None)
     ap.add_argument("--verify-reshard", action="store_true",
                     help="after timing: save_matrix_dcp, load resharded onto a flat dp_shard mesh, compare checksums")
+    ap.add_argument("--timeline", default=None, metavar="FILE.md",
+                    help="after timing: run 3 more steps with CUDA-event spans around every collective and write "
+                         "the per-unit table (start, device time, exposed wait; max over ranks) to FILE.md")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
     dump_after = float(os.environ.get("MFSDP_BENCH_DUMP_STACKS_AFTER_S", "0"))
@@ -358,7 +453,8 @@ def main() -> None:
     B, S, V = cfg["micro_batch"], cfg["seq_len"], cfg["vocab_size"]
     total_steps = args.warmup + args.steps
     gen = torch.Generator().manual_seed(1234 + rank)
-    host = torch.randint(0, V, (2 * total_steps + 2, B, S + 1), generator=gen, dtype=torch.int64)
+    e2e_warm = min(3, args.steps)
+    host = torch.randint(0, V, (total_steps + e2e_warm + args.steps, B, S + 1), generator=gen, dtype=torch.int64)
     if cuda:
         host = host.pin_memory()
     dev_batches = host[: total_steps].to(device)
@@ -381,6 +477,7 @@ def main() -> None:
 
     def e2e_step(i: int) -> float:
         # pinned host batch -> device, forward, backward, optimizer step, loss back to the host
+        # (every call gets a batch no earlier step has seen)
         hb = host[total_steps + i]
         if args.impl == "ours":
             from matrix_fsdp_b200.utils import train_step        # the user-facing call of this package
@@ -447,12 +544,12 @@ def main() -> None:
         peak_mb += symmetric_mb
 
     # ---- end-to-end region (public train_step semantics: H2D each step, D2H loss read each step)
-    for i in range(min(3, args.steps)):
+    for i in range(e2e_warm):
         e2e_step(i)
     sync()
     t0 = time.perf_counter()
     for i in range(args.steps):
-        e2e_loss = e2e_step(i)
+        e2e_loss = e2e_step(e2e_warm + i)
     if cuda:
         torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3
@@ -482,9 +579,16 @@ def main() -> None:
                    "l2": "no explicit flush: each step streams >1 GB of weights/activations (L2 is 126 MB)"},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
-                "h2d_bytes_per_step": 2 * B * S * 8, "d2h_bytes_per_step": 4, "last_loss": e2e_loss},
+                "h2d_bytes_per_step": 2 * B * S * 8, "d2h_bytes_per_step": 4 + (4 if args.impl == "ours" and cuda else 0),
+                "last_loss": e2e_loss},
         "gpu_launches": launches, "host_issue_ms_per_step": host_issue_ms,
     }
+    if args.impl == "ours":
+        out["transport"] = _transport_description(model)
+        if cfg.get("kind") == "moe":
+            out["moe"] = _moe_drop_report(model, device, world)
+    if args.timeline and args.impl == "ours" and cuda:
+        out["timeline"] = write_timeline(args.timeline, device_step, sync, rank, world, device, out)
     if args.verify_reshard and args.impl == "ours":
         out["reshard"] = verify_reshard(cfg, model, opt, device, world, rank)
     if rank == 0:

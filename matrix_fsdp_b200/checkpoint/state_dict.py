@@ -181,6 +181,7 @@ def load_matrix_state_dict(model_or_units, state: Mapping[str, Any], *, strict: 
             u.flat_buffer.mark_master_updated(lp_written=False)
             if "grad_shard" in su:
                 u.flat_buffer._ensure_local_grad_shard().copy_(su["grad_shard"])
+                u.flat_buffer.local_grad_valid = True
                 u.flat_buffer.use_local_grad_shard()
 
 
@@ -397,6 +398,7 @@ def load_matrix_dcp(model_or_units, directory: str, optimizer=None, *, allow_res
         for u in units:
             u.flat_buffer.mark_master_updated(lp_written=False)
             if include_grads and u.flat_buffer.local_grad_shard is not None:
+                u.flat_buffer.local_grad_valid = True
                 u.flat_buffer.use_local_grad_shard()
         _restore_optimizer(staged, meta.get("optimizer"), optimizer)
     return meta

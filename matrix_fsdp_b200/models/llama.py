@@ -144,6 +144,19 @@ class LlamaBlock(nn.Module):
         return x + F.linear(hidden, self.w_down.weight)
 
 
+class LMHead(nn.Module):
+    """Final norm + vocabulary projection as one module, so they can be one FSDP unit of their own:
+    its all-gather is then prefetched behind the last block instead of riding with the embedding."""
+
+    def __init__(self, hidden: int, vocab_size: int, eps: float, std: float) -> None:
+        super().__init__()
+        self.final_norm = RMSNorm(hidden, eps)
+        self.lm_head = Matrix(hidden, vocab_size, std, is_lm_head=True)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.lm_head(self.final_norm(x))
+
+
 class LlamaModel(nn.Module):
     """Decoder-only LM.  ``forward(tokens, targets=None)`` returns logits or the mean CE loss."""
 
@@ -153,17 +166,23 @@ class LlamaModel(nn.Module):
         self.embed = nn.Embedding(cfg.vocab_size, cfg.hidden)
         nn.init.normal_(self.embed.weight, mean=0.0, std=cfg.init_std)
         self.layers = nn.ModuleList([LlamaBlock(cfg) for _ in range(cfg.n_layers)])
-        self.final_norm = RMSNorm(cfg.hidden, cfg.eps)
-        self.lm_head = Matrix(cfg.hidden, cfg.vocab_size, cfg.init_std, is_lm_head=True)
+        self.head = LMHead(cfg.hidden, cfg.vocab_size, cfg.eps, cfg.init_std)
         if cfg.tie_embeddings:
-            self.lm_head.weight = self.embed.weight
+            self.head.lm_head.weight = self.embed.weight
+
+    @property
+    def final_norm(self) -> RMSNorm:
+        return self.head.final_norm
+
+    @property
+    def lm_head(self) -> Matrix:
+        return self.head.lm_head
 
     def forward(self, tokens: torch.Tensor, targets: torch.Tensor | None = None) -> torch.Tensor:
         x = self.embed(tokens)
         for layer in self.layers:
             x = layer(x)
-        x = self.final_norm(x)
-        logits = self.lm_head(x)
+        logits = self.head(x)
         if targets is None:
             return logits
         n_valid = targets.numel() if self.cfg.loss_ignore_index is None else None
@@ -202,7 +221,9 @@ def _mark_fused_first_gemm(layer: LlamaBlock) -> None:
 
 def shard_llama(model: LlamaModel, *, mesh=None, dp_mesh_dims=None, mp_policy=None, optimizer_policy=None,
                 reshard_after_forward=None, shard_root: bool = True, **kw) -> LlamaModel:
-    """``fully_shard`` every block, then the root (embedding, final norm, LM head)."""
+    """``fully_shard`` every block, then the embedding and the head (final norm + LM head) as two units of
+    their own; with tied embeddings (one shared parameter) or an optimizer policy that plans the root as a
+    whole they stay one root unit."""
     from torch.distributed.fsdp import MixedPrecisionPolicy
 
     from ..api import fully_shard, matrix_fully_shard
@@ -213,20 +234,22 @@ def shard_llama(model: LlamaModel, *, mesh=None, dp_mesh_dims=None, mp_policy=No
                     reshard_after_forward=reshard_after_forward, **kw)
         _mark_fused_first_gemm(layer)
     if shard_root:
-        hints = None
-        if optimizer_policy is not None:
-            from ..planning.shard_hint import build_shard_hints
+        if model.cfg.tie_embeddings:
+            # one parameter serves as embedding and LM head: a single root unit that admits the alias
+            hints = None
+            if optimizer_policy is not None:
+                from ..planning.shard_hint import build_shard_hints
 
-            hints = {k: v for k, v in build_shard_hints(model).items() if not k.startswith("layers.")}
-        if model.cfg.tie_embeddings or hints is not None:
-            from ..core.mesh import DataParallelMeshDims  # noqa: F401
-
+                hints = {k: v for k, v in build_shard_hints(model).items() if not k.startswith("layers.")}
             matrix_fully_shard(model, mesh, dp_mesh_dims=dp_mesh_dims, mp_policy=mp, shard_hints=hints,
                                auto_planner_policy="muon_shard_aware" if optimizer_policy else None,
                                owner_assignment="role_greedy" if optimizer_policy else "rotate",
                                reshard_after_forward=True if reshard_after_forward is None else reshard_after_forward,
-                               allow_shared_params=model.cfg.tie_embeddings)
+                               allow_shared_params=True)
         else:
-            fully_shard(model, mesh=mesh, dp_mesh_dims=dp_mesh_dims, mp_policy=mp,
-                        reshard_after_forward=reshard_after_forward, **kw)
+            # two units: the head's gather is prefetched behind the last block and the embedding's behind
+            # the optimizer step; each reduce-scatter is half the bytes of a combined root
+            for part in (model.embed, model.head):
+                fully_shard(part, mesh=mesh, dp_mesh_dims=dp_mesh_dims, mp_policy=mp,
+                            optimizer_policy=optimizer_policy, reshard_after_forward=reshard_after_forward, **kw)
     return model

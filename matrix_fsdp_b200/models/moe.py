@@ -16,7 +16,7 @@ from torch import nn
 
 from ..ops import functional as OF
 from ..ops import moe_functional as MF
-from .llama import Matrix, RMSNorm
+from .llama import LMHead, Matrix, RMSNorm
 
 
 @dataclass
@@ -148,8 +148,15 @@ class MoEModel(nn.Module):
         self.embed = nn.Embedding(cfg.vocab_size, cfg.hidden)
         nn.init.normal_(self.embed.weight, mean=0.0, std=cfg.init_std)
         self.layers = nn.ModuleList([MoEBlock(cfg, i, ep_group, device=device, dtype=dtype) for i in range(cfg.n_layers)])
-        self.final_norm = RMSNorm(cfg.hidden, cfg.eps)
-        self.lm_head = Matrix(cfg.hidden, cfg.vocab_size, cfg.init_std, is_lm_head=True)
+        self.head = LMHead(cfg.hidden, cfg.vocab_size, cfg.eps, cfg.init_std)
+
+    @property
+    def final_norm(self) -> RMSNorm:
+        return self.head.final_norm
+
+    @property
+    def lm_head(self) -> Matrix:
+        return self.head.lm_head
 
     def expert_parameters(self) -> list[nn.Parameter]:
         return [p for layer in self.layers for p in layer.experts.parameters()]
@@ -158,8 +165,7 @@ class MoEModel(nn.Module):
         x = self.embed(tokens)
         for layer in self.layers:
             x = layer(x)
-        x = self.final_norm(x)
-        logits = self.lm_head(x)
+        logits = self.head(x)
         if targets is None:
             return logits
         n_valid = targets.numel() if self.cfg.loss_ignore_index is None else None
@@ -183,27 +189,19 @@ class MoEModel(nn.Module):
 
 def shard_moe(model: MoEModel, *, mesh=None, dp_mesh_dims=None, mp_policy=None, optimizer_policy=None,
               reshard_after_forward=None) -> MoEModel:
-    """``fully_shard`` the dense parameters of every block (experts ignored), then the root."""
+    """``fully_shard`` the dense parameters of every block (experts ignored), then embedding and head."""
     from torch.distributed.fsdp import MixedPrecisionPolicy
 
-    from ..api import fully_shard, matrix_fully_shard
+    from ..api import fully_shard
 
     mp = mp_policy or MixedPrecisionPolicy()
     for layer in model.layers:
         fully_shard(layer, mesh=mesh, dp_mesh_dims=dp_mesh_dims, mp_policy=mp, optimizer_policy=optimizer_policy,
                     reshard_after_forward=reshard_after_forward, ignored_params=set(layer.experts.parameters()))
-    ignored = set(model.expert_parameters())
-    if optimizer_policy is not None:
-        from ..planning.shard_hint import build_shard_hints
-
-        hints = {k: v for k, v in build_shard_hints(model).items() if not k.startswith("layers.")}
-        matrix_fully_shard(model, mesh, dp_mesh_dims=dp_mesh_dims, mp_policy=mp, shard_hints=hints,
-                           auto_planner_policy="muon_shard_aware", owner_assignment="role_greedy",
-                           reshard_after_forward=True if reshard_after_forward is None else reshard_after_forward,
-                           ignored_params=ignored)
-    else:
-        fully_shard(model, mesh=mesh, dp_mesh_dims=dp_mesh_dims, mp_policy=mp,
-                    reshard_after_forward=reshard_after_forward, ignored_params=ignored)
+    # embedding and head (final norm + LM head) are units of their own, like the dense model's
+    for part in (model.embed, model.head):
+        fully_shard(part, mesh=mesh, dp_mesh_dims=dp_mesh_dims, mp_policy=mp, optimizer_policy=optimizer_policy,
+                    reshard_after_forward=reshard_after_forward)
     return model
 
 

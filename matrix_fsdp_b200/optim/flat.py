@@ -150,7 +150,10 @@ class _FlatShardedBase(Optimizer):
         return us.step if us is not None else 0
 
     def _unit_grad(self, unit) -> torch.Tensor | None:
-        return unit.flat_buffer.local_grad_shard
+        """The unit's reduced gradient, or None when this step produced none for it (the buffer of an
+        earlier step may still exist; like ``param.grad is None`` such a unit is skipped)."""
+        fb = unit.flat_buffer
+        return fb.local_grad_shard if fb.local_grad_valid else None
 
 
 class FlatShardedAdamW(_FlatShardedBase):

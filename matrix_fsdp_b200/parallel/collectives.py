@@ -34,14 +34,21 @@ class MatrixCollectiveHandle:
         self._post = post
         self.info = info or {}
         self.done = False
+        self.span = None          # device-timeline record (device_timeline.CollectiveSpan) when enabled
 
     def wait(self) -> None:
         if self.done:
             return
+        if self.span is not None:
+            from . import device_timeline as _tl
+
+            _tl.begin_wait(self.span)
         for w in self._works:
             w.wait()
         if self._event is not None:
             torch.cuda.current_stream().wait_event(self._event)
+        if self.span is not None:
+            _tl.end_wait(self.span)
         if self._post is not None:
             self._post()
         self.done = True
@@ -72,14 +79,20 @@ def _rank(group) -> int:
 
 def _run(fn, *, stream, info) -> MatrixCollectiveHandle:
     """Run ``fn`` (which issues blocking collectives) on ``stream`` and return its handle."""
+    from . import device_timeline as _tl
+
     if stream is not None:
         stream.wait_stream(torch.cuda.current_stream())
+        span = _tl.open_span("", info.get("kind", ""), stream, impl=info.get("impl", ""), nbytes=info.get("bytes", 0))
         with torch.cuda.stream(stream):
             fn()
+            _tl.close_span(span, stream)
             ev = torch.cuda.Event()
             ev.record(stream)
         info["sync_mode"] = "stream_event"
-        return MatrixCollectiveHandle(event=ev, info=info)
+        h = MatrixCollectiveHandle(event=ev, info=info)
+        h.span = span
+        return h
     fn()
     info["sync_mode"] = "blocking"
     return MatrixCollectiveHandle(info=info)

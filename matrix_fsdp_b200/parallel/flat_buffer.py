@@ -71,7 +71,7 @@ class MatrixFlatBuffer:
     def __init__(self, registry: ManagedParamRegistry, layout: MatrixGroupLayout, *, rank: int, world_size: int,
                  transport, replicate_group=None, replicate_world_size: int = 1, param_dtype: torch.dtype | None = None,
                  reduce_dtype: torch.dtype | None = None, divide_grads_by_world: bool = True,
-                 unit_key: str = "") -> None:
+                 unit_key: str = "", exclusive_full_buffer: bool = False) -> None:
         self.registry = registry
         self.layout = layout
         self.rank, self.world_size = rank, world_size
@@ -130,10 +130,20 @@ class MatrixFlatBuffer:
                                    and segs[0].numel == self.total_numel)
 
         # ---- full buffer object (storage materialised lazily) and cached views
+        # ``full_persistent``: the transport handed out a persistent (symmetric, multicast-mapped) slot that
+        # this unit shares with units it is never unsharded together with; nothing is resized then.
+        self.full_persistent = False
         if self.full_aliases_shard:
             self.full_buffer = self._gather_source_tensor()
         else:
-            self.full_buffer = torch.empty(self.total_numel, dtype=self.param_dtype, device=self.device)
+            slot = None
+            alloc_full = getattr(transport, "alloc_full_buffer", None)
+            if alloc_full is not None:
+                slot = alloc_full(unit_key, self.total_numel, self.param_dtype, self.tables,
+                                  exclusive=exclusive_full_buffer)
+            self.full_persistent = slot is not None
+            self.full_buffer = slot if slot is not None else \
+                torch.empty(self.total_numel, dtype=self.param_dtype, device=self.device)
         # views are created while the storage exists; they stay valid across resize_(0) / resize_(n)
         self._full_views = {mp.fqn: self.full_buffer[mp.offset:mp.end].view(mp.shape) for mp in params}
         if not self.full_aliases_shard:
@@ -148,6 +158,10 @@ class MatrixFlatBuffer:
                                        self._bucket_dtype(), self.device)
         self.local_grad_shard: torch.Tensor | None = None
         self._local_grad_views: dict[str, torch.Tensor] = {}
+        # True from the moment a reduction into ``local_grad_shard`` was issued until ``zero_grad``:
+        # the buffer itself outlives the step, so optimizers must not read it without this flag
+        # (a unit that got no backward in a step has no gradient, like ``param.grad is None``).
+        self.local_grad_valid = False
         self.pending_gather: MatrixCollectiveHandle | None = None
         self.pending_reduce: MatrixCollectiveHandle | None = None
         self.grad_bucket_acquired = False
@@ -201,10 +215,16 @@ class MatrixFlatBuffer:
         return self.total_numel * self.full_buffer.element_size()
 
     def _shrink_full(self) -> None:
-        if not self.full_aliases_shard:
-            self.full_buffer.untyped_storage().resize_(0)
+        if self.full_aliases_shard:
+            return
+        if self.full_persistent:
+            self.transport.release_full_buffer(self.unit_key)   # peers may refill the slot from here on
+            return
+        self.full_buffer.untyped_storage().resize_(0)
 
     def _materialize_full(self) -> None:
+        if self.full_persistent:
+            return
         st = self.full_buffer.untyped_storage()
         if st.size() != self._full_nbytes():
             st.resize_(self._full_nbytes())
@@ -214,7 +234,16 @@ class MatrixFlatBuffer:
                 self.full_buffer.fill_(float("nan"))
 
     def full_storage_nbytes(self) -> int:
-        return 0 if self.full_aliases_shard else self.full_buffer.untyped_storage().size()
+        if self.full_aliases_shard:
+            return 0
+        if self.full_persistent:
+            return self._full_nbytes() if self.full_materialized else 0
+        return self.full_buffer.untyped_storage().size()
+
+    def full_slot_available(self) -> bool:
+        """False while another unit's parameters occupy the slot this unit's full buffer lives in."""
+        probe = getattr(self.transport, "full_slot_available", None)
+        return True if (probe is None or not self.full_persistent) else bool(probe(self.unit_key))
 
     # ------------------------------------------------------------------ all-gather
     def refresh_low_precision_shard(self) -> None:
@@ -379,6 +408,7 @@ class MatrixFlatBuffer:
             h = MatrixCollectiveHandle(info={"kind": "reduce_scatter", "impl": "alias", "backend": "local",
                                              "bytes": 0, "count": 0, "sync_mode": "local"})
             self.pending_reduce = h
+            self.local_grad_valid = True
             return h
         if self.fused_reduce_update is not None and self.replicate_world_size == 1 \
                 and not self.accumulate_into_local_grad and hasattr(self.transport, "reduce_update"):
@@ -417,6 +447,7 @@ class MatrixFlatBuffer:
 
         h._post = post
         self.pending_reduce = h
+        self.local_grad_valid = True
         return h
 
     def wait_reduce(self) -> MatrixCollectiveHandle | None:
@@ -445,6 +476,7 @@ class MatrixFlatBuffer:
             self.grad_bucket_acquired = False
 
     def clear_local_grad_shard(self) -> None:
+        self.local_grad_valid = False
         for mp in self.registry.params:
             mp.param.grad = None
         if self.local_grad_shard is not None and self.world_size == 1 and self.full_aliases_shard:

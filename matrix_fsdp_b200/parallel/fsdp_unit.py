@@ -227,7 +227,8 @@ class MatrixFSDPParamGroup:
             registry, result.layout, rank=self.rank, world_size=self.world_size, transport=transport,
             replicate_group=self.groups.replicate_group, replicate_world_size=self.replicate_world_size,
             param_dtype=getattr(mp, "param_dtype", None), reduce_dtype=getattr(mp, "reduce_dtype", None),
-            divide_grads_by_world=self.divide_grads_by_world, unit_key=self.name)
+            divide_grads_by_world=self.divide_grads_by_world, unit_key=self.name,
+            exclusive_full_buffer=not self.reshard_after_forward)
         self.flat_buffer.use_local_shards()
 
         ref = weakref.ref(self)
@@ -340,11 +341,14 @@ class MatrixFSDPParamGroup:
         defer = None
         if "backward" not in reason and getattr(self, "fused_first_gemm_range", None) is not None \
                 and not _in_backward() and torch.is_grad_enabled() \
-                and (not reason.endswith("prefetch") or os.environ.get("MFSDP_FUSED_AG_GEMM", "exposed") == "always"):
+                and (not reason.endswith("prefetch") or os.environ.get("MFSDP_FUSED_AG_GEMM", "exposed") == "always") \
+                and not self.flat_buffer.full_persistent:
             defer = self.fused_first_gemm_range
         with nvtx_range(f"mfsdp.all_gather:{self.name}"):
             h = self.flat_buffer.start_all_gather_full_params(stream=self.all_gather_stream, defer=defer)
         self.unshard_prefetched = reason.endswith("prefetch")
+        if getattr(h, "span", None) is not None:
+            h.span.unit, h.span.reason = self.name, reason
         self._record(f"start_unshard:{reason}", start=t0, handle=h, reason=reason, prefetched=self.unshard_prefetched)
 
     def wait_unshard(self, reason: str = "manual") -> None:
@@ -355,6 +359,8 @@ class MatrixFSDPParamGroup:
             self.start_unshard(reason)
         # rows left to the block's first GEMM stay pending only when the module said it will run that GEMM
         h = self.flat_buffer.wait_all_gather(keep_deferred=(reason == "pre_forward" and self._module_fuses_first_gemm))
+        if self.scheduler is not None and h is not None:
+            self.scheduler.note_unshard_wait(self, (time.perf_counter() - t0) * 1e3, getattr(h, "span", None))
         self.flat_buffer.use_full_param_buffer()
         self._transition(FSDPLifecycleState.UNSHARDED)
         self._record(f"wait_unshard:{reason}", start=t0, handle=h, reason=reason)
@@ -544,6 +550,8 @@ class MatrixFSDPParamGroup:
             with nvtx_range(f"mfsdp.reduce_scatter:{self.name}"):
                 h = self.flat_buffer.start_reduce_grad_bucket_to_local_shard(stream=self.reduce_scatter_stream)
         self.has_accumulated_grads = False
+        if getattr(h, "span", None) is not None:
+            h.span.unit, h.span.reason = self.name, "post_backward"
         self._record("start_reduce_scatter", start=t0, handle=h)
         if self.scheduler is not None:
             self.scheduler.after_backward_reduce_started(self)
@@ -567,6 +575,7 @@ class MatrixFSDPParamGroup:
         h = MatrixCollectiveHandle(info={"kind": "all_reduce", "impl": "per_param_allreduce", "backend": fb.transport.kind,
                                          "bytes": buf.numel() * buf.element_size(), "count": 1, "sync_mode": "blocking"})
         fb.pending_reduce = h
+        fb.local_grad_valid = True
         return h
 
     def wait_post_backward_reduce(self) -> None:

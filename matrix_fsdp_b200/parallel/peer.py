@@ -12,6 +12,16 @@ segments once.  :class:`PeerTransport` then implements the transport interface o
              applies the 1/world scale and writes the local gradient shard → publish "pulled" so
              owners may reuse their gradient buffers.
 
+With NVLS (``MFSDP_NVLS``, default on when the symmetric segments could be bound to an NVSwitch
+multicast object) the same two operations go through the switch instead: ``gather`` *pushes* only
+this rank's shard with ``multimem.st`` into a persistent, symmetric full-parameter slot (every
+rank's copy is written by the switch), ``reduce`` reads each owned element once with
+``multimem.ld_reduce`` (the switch sums the ranks' gradient buffers).  Slots are shared by units
+that are never unsharded together; a "free" flag published at reshard keeps a pusher from
+overwriting a slot a peer still reads.  The plain peer-load kernels stay as the fallback and are
+the only path when ``MFSDP_NVLS=0`` (failure tests: a rank must never exit while its memory is
+bound to a multicast object that others still use).
+
 Gradient buffers come from a small ring of symmetric slots per size class; a slot is handed to the
 next unit only after every peer has published "pulled" for its previous user.  All waits are
 bounded (``MFSDP_PEER_WAIT_TIMEOUT_S``) and report through the device status word.
@@ -31,6 +41,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import lib as _lib
+from . import device_timeline as _tl
 from .collectives import MatrixCollectiveHandle, SegmentTables
 from .transport import LocalTransport
 
@@ -44,16 +55,28 @@ _lib.register_signatures({
     "mfsdp_can_access_peer": [_i32, _i32],
     "mfsdp_peer_signal": [C.POINTER(_u64), _i32, _u64, _vp],
     "mfsdp_peer_wait": [_vp, _i32, _i32, _u64, _u64, _vp, _vp],
-    "mfsdp_ag_pull": [_vp, _vp, _vp, _vp, _i32, _i64, _i32, _vp],
+    "mfsdp_peer_signal_wait": [C.POINTER(_u64), _vp, _i32, _i32, _u64, _u64, _vp, _vp],
+    "mfsdp_validate_pull_table": [_vp, _vp, _vp, _i32, _i64, _i32, C.POINTER(_u64), C.POINTER(_u64), _i32, _vp, _vp],
+    "mfsdp_validate_reduce_table": [_vp, _vp, _vp, _i32, _i64, _i64, _vp, _vp],
+    "mfsdp_ag_pull": [_vp, _vp, _vp, _vp, _i32, _i64, _i32, _vp, _vp],
     "mfsdp_rs_pull_reduce": [C.POINTER(_u64), _i32, _i32, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32,
-                             C.c_float, _vp],
+                             C.c_float, _vp, _vp],
     "mfsdp_rs_pull_adamw": [C.POINTER(_u64), _i32, _i32, _vp, _vp, _vp, _i32, _i64, _i32, C.c_float, _vp, _vp, _vp,
-                            _vp, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, _i32, _vp],
+                            _vp, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, _i32, _vp, _vp],
+    "mfsdp_ag_push_mc": [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _vp, _vp],
+    "mfsdp_rs_mc_reduce": [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32, C.c_float, _vp, _vp],
+    "mfsdp_rs_mc_adamw": [_vp, _vp, _vp, _vp, _i32, _i64, _i32, C.c_float, _vp, _vp, _vp, _vp, C.c_float, C.c_float,
+                          C.c_float, C.c_float, C.c_float, _i32, _vp, _vp],
+    "mfsdp_ar_mc": [_vp, _i64, _i32, _i32, _i32, C.c_float, _vp, _vp],
 })
 
-KIND_SHARD, KIND_GRAD, KIND_PULLED = 0, 1, 2
+KIND_SHARD, KIND_GRAD, KIND_PULLED, KIND_FREE = 0, 1, 2, 3
+N_KINDS = 4
 MAX_UNITS = 2048
 SEGMENT_ENV = "MFSDP_PEER_SEGMENT_MB"
+NVLS_ENV = "MFSDP_NVLS"                    # auto (default) | 0 | 1
+FULL_SLOTS_ENV = "MFSDP_PEER_FULL_SLOTS"   # full-parameter slots per size class (NVLS all-gather)
+BOUNDS_ENV = "MFSDP_DEBUG_BOUNDS"          # 1: validate every pull / reduce table on the device
 TIMEOUT_ENV = "MFSDP_PEER_WAIT_TIMEOUT_S"
 RING_ENV = "MFSDP_PEER_GRAD_SLOTS"
 
@@ -63,12 +86,13 @@ def _stream_handle(stream) -> int:
 
 
 class SymBuffer:
-    """A symmetric allocation: the local tensor plus the address of the same bytes on every peer."""
+    """A symmetric allocation: the local tensor, the address of the same bytes on every peer, and (when
+    the segment is bound to an NVSwitch multicast object) the multicast address of those bytes."""
 
-    __slots__ = ("tensor", "peer_addr", "nbytes")
+    __slots__ = ("tensor", "peer_addr", "nbytes", "mc_addr")
 
-    def __init__(self, tensor: torch.Tensor, peer_addr: list[int], nbytes: int) -> None:
-        self.tensor, self.peer_addr, self.nbytes = tensor, peer_addr, nbytes
+    def __init__(self, tensor: torch.Tensor, peer_addr: list[int], nbytes: int, mc_addr: int = 0) -> None:
+        self.tensor, self.peer_addr, self.nbytes, self.mc_addr = tensor, peer_addr, nbytes, mc_addr
 
 
 class _RawDeviceMemory:
@@ -76,6 +100,11 @@ class _RawDeviceMemory:
 
     def __init__(self, ptr: int, nbytes: int) -> None:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def _nvls_requested() -> str:
+    v = os.environ.get(NVLS_ENV, "auto").strip().lower()
+    return {"": "auto", "true": "1", "on": "1", "false": "0", "off": "0"}.get(v, v)
 
 
 class PeerContext:
@@ -86,23 +115,60 @@ class PeerContext:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.lib = _lib.load(required=True)
-        self.segment_bytes = int(float(os.environ.get(SEGMENT_ENV, "512")) * 2 ** 20)
+        # small allocations share segments of this size; large ones get a segment of their own size
+        self.segment_bytes = int(float(os.environ.get(SEGMENT_ENV, "64")) * 2 ** 20)
         self._segments: list[dict] = []
         self._opened: dict[bytes, int] = {}
         self._by_ptr: dict[int, SymBuffer] = {}
         self.timeout_ns = int(float(os.environ.get(TIMEOUT_ENV, "120")) * 1e9)
-        flags = self.alloc(MAX_UNITS * 3 * self.world * 8, zero=True)
-        self.flags = flags
-        self.flags_u64 = flags.tensor.view(torch.int64)
+        self.debug_bounds = os.environ.get(BOUNDS_ENV, "0") not in ("", "0")
+        self.nvls = self._decide_nvls()
         from ..ops import kernels
 
         self.status = kernels.status_word(device)
+        flags = self.alloc(MAX_UNITS * N_KINDS * self.world * 8, zero=True)
+        self.flags = flags
+        self.flags_u64 = flags.tensor.view(torch.int64)
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
     # ------------------------------------------------------------------ symmetric allocation
-    def _new_segment(self, min_bytes: int) -> dict:
-        nbytes = max(self.segment_bytes, (min_bytes + 4095) // 4096 * 4096)
+    def _decide_nvls(self) -> bool:
+        """Collective: all ranks agree whether segments come from torch's symmetric-memory allocator
+        (``cuMemCreate`` + multicast binding, which gives every segment a multicast address)."""
+        want = _nvls_requested()
+        ok = False
+        if want != "0":
+            try:
+                import torch.distributed._symmetric_memory as symm_mem   # noqa: F401
+                from torch._C._autograd import DeviceType
+                from torch._C._distributed_c10d import _SymmetricMemory
+
+                ok = bool(_SymmetricMemory.has_multicast_support(DeviceType.CUDA, self.device.index or 0))
+            except Exception:  # noqa: BLE001  (an old torch, no fabric support, ...)
+                ok = False
+        votes: list = [None] * self.world
+        dist.all_gather_object(votes, ok, group=self.group)
+        ok = all(votes)
+        if want == "1" and not ok:
+            raise RuntimeError("MFSDP_NVLS=1 but NVSwitch multicast is not available on every rank")
+        return ok
+
+    def _new_segment(self, nbytes: int) -> dict:
+        nbytes = (nbytes + (2 << 20) - 1) // (2 << 20) * (2 << 20)
+        if self.nvls:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            t = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+            hdl = symm_mem.rendezvous(t, self.group)
+            bases = [int(a) for a in hdl.buffer_ptrs]
+            mc = int(hdl.multicast_ptr or 0)
+            if bases[self.rank] != t.data_ptr():
+                raise RuntimeError("symmetric-memory handle does not describe the local tensor")
+            PeerContext.symmetric_bytes += nbytes
+            seg = {"tensor": t, "bases": bases, "used": 0, "nbytes": nbytes, "mc": mc, "handle": hdl}
+            self._segments.append(seg)
+            return seg
         raw = C.c_void_p()
         rc = self.lib.mfsdp_dev_malloc(nbytes, C.byref(raw))
         if rc != 0:
@@ -132,7 +198,7 @@ class PeerContext:
                 base = int(out.value)
                 self._opened[h] = base
             bases.append(base + off)
-        seg = {"tensor": t, "bases": bases, "used": 0, "nbytes": nbytes}
+        seg = {"tensor": t, "bases": bases, "used": 0, "nbytes": nbytes, "mc": 0, "handle": None}
         self._segments.append(seg)
         return seg
 
@@ -140,19 +206,22 @@ class PeerContext:
         """Collective: every rank must call with the same ``nbytes`` in the same order."""
         nbytes = max(int(nbytes), 16)
         seg = None
-        for s in self._segments:
-            start = (s["used"] + align - 1) // align * align
-            if start + nbytes <= s["nbytes"]:
-                seg = s
-                break
-        if seg is None:
-            seg = self._new_segment(nbytes)
+        if nbytes * 4 >= self.segment_bytes:
+            seg = self._new_segment(nbytes)           # large buffers: a segment of exactly their size
+        else:
+            for s in self._segments:
+                start = (s["used"] + align - 1) // align * align
+                if start + nbytes <= s["nbytes"]:
+                    seg = s
+                    break
+            if seg is None:
+                seg = self._new_segment(self.segment_bytes)
         start = (seg["used"] + align - 1) // align * align
         seg["used"] = start + nbytes
         view = seg["tensor"][start:start + nbytes]
         if zero:
             view.zero_()
-        buf = SymBuffer(view, [b + start for b in seg["bases"]], nbytes)
+        buf = SymBuffer(view, [b + start for b in seg["bases"]], nbytes, seg["mc"] + start if seg["mc"] else 0)
         self._by_ptr[view.data_ptr()] = buf
         return buf
 
@@ -161,19 +230,29 @@ class PeerContext:
 
     # ------------------------------------------------------------------ flags
     def slot(self, unit_index: int, kind: int, src: int) -> int:
-        return (unit_index * 3 + kind) * self.world + src
+        return (unit_index * N_KINDS + kind) * self.world + src
+
+    def _slot_addrs(self, unit_index: int, kind: int):
+        idx = self.slot(unit_index, kind, self.rank)
+        return (_u64 * self.world)(*[self.flags.peer_addr[r] + idx * 8 for r in range(self.world)])
 
     def signal(self, unit_index: int, kind: int, value: int, stream) -> None:
         """Write ``value`` into my slot of every rank's flag page (including my own)."""
-        idx = self.slot(unit_index, kind, self.rank)
-        arr = (_u64 * self.world)(*[self.flags.peer_addr[r] + idx * 8 for r in range(self.world)])
-        _lib.check(self.lib.mfsdp_peer_signal(arr, self.world, value, _stream_handle(stream)), "peer_signal")
+        _lib.check(self.lib.mfsdp_peer_signal(self._slot_addrs(unit_index, kind), self.world, value,
+                                              _stream_handle(stream)), "peer_signal")
 
     def wait(self, unit_index: int, kind: int, value: int, stream) -> None:
         """Wait until every rank's slot in my page reached ``value``."""
         first = self.slot(unit_index, kind, 0)
         _lib.check(self.lib.mfsdp_peer_wait(self.flags.tensor.data_ptr(), first, self.world, value, self.timeout_ns,
                                             self.status.data_ptr(), _stream_handle(stream)), "peer_wait")
+
+    def signal_wait(self, unit_index: int, kind: int, value: int, stream) -> None:
+        """``signal`` then ``wait`` on the same slot row, as one launch."""
+        first = self.slot(unit_index, kind, 0)
+        _lib.check(self.lib.mfsdp_peer_signal_wait(self._slot_addrs(unit_index, kind), self.flags.tensor.data_ptr(),
+                                                   first, self.world, value, self.timeout_ns, self.status.data_ptr(),
+                                                   _stream_handle(stream)), "peer_signal_wait")
 
 
 class DeferredGather:
@@ -197,6 +276,7 @@ class DeferredGather:
         self.full_ptr = full.data_ptr()
         self.budget_ns = transport.ctx.timeout_ns
         self.lib = transport.ctx.lib
+        self.status_ptr = transport.ctx.status.data_ptr()
         block = self.bn * k
         nblocks = (n + self.bn - 1) // self.bn
         src, dst, nbytes, flag = [], [], [], []
@@ -240,7 +320,7 @@ class DeferredGather:
         t = self._plain
         run = stream if stream is not None else torch.cuda.current_stream()
         _lib.check(self.lib.mfsdp_ag_pull(self.full_ptr, t["src"].data_ptr(), t["dst"].data_ptr(), t["len"].data_ptr(),
-                                          t["n"], t["max"], 2, run.cuda_stream), "ag_pull")
+                                          t["n"], t["max"], 2, self.status_ptr, run.cuda_stream), "ag_pull")
 
 
 class _Slot:
@@ -248,6 +328,25 @@ class _Slot:
 
     def __init__(self, buf: SymBuffer) -> None:
         self.buf, self.held, self.last_unit, self.last_epoch, self.event = buf, False, None, 0, None
+
+
+class _FullSlot:
+    """A persistent symmetric full-parameter buffer shared by units that are never unsharded together."""
+
+    __slots__ = ("buf", "units", "holder", "last_unit", "last_epoch", "exclusive")
+
+    def __init__(self, buf: SymBuffer, exclusive: bool = False) -> None:
+        self.buf = buf
+        self.exclusive = exclusive
+        self.units: list[str] = []
+        self.holder: str | None = None      # unit whose parameters the slot holds right now
+        self.last_unit: str | None = None   # previous occupant and the gather epoch it was filled in
+        self.last_epoch = 0
+
+
+def _aligned16(tables: SegmentTables, es: int) -> bool:
+    return all((sg.global_start * es) % 16 == 0 and (sg.local_start * es) % 16 == 0 and (sg.numel * es) % 16 == 0
+               for segs in tables.rank_segments for sg in segs)
 
 
 class PeerTransport(LocalTransport):
@@ -269,6 +368,13 @@ class PeerTransport(LocalTransport):
         self.max_slots = int(os.environ.get(RING_ENV, "3"))
         self.launches = 0
         self._ar_state: dict[tuple, dict] = {}
+        # NVLS: persistent full-parameter slots (all-gather by multimem.st push)
+        self.nvls = ctx.nvls
+        self.nvls_gather = ctx.nvls and os.environ.get("MFSDP_NVLS_GATHER", "1") != "0"
+        self.nvls_reduce = ctx.nvls and os.environ.get("MFSDP_NVLS_REDUCE", "1") != "0"
+        self.full_slots_per_class = max(int(os.environ.get(FULL_SLOTS_ENV, "2")), 1)
+        self._full_rings: dict[int, list[_FullSlot]] = {}
+        self._full_slot_of_unit: dict[str, _FullSlot] = {}
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -309,6 +415,11 @@ class PeerTransport(LocalTransport):
             self._epochs[unit_key] = {"shard": 0, "grad": 0}
         return idx
 
+    def describe(self) -> str:
+        if not self.nvls:
+            return "peer"
+        return "peer+nvls(" + "+".join(n for n, on in (("gather", self.nvls_gather), ("reduce", self.nvls_reduce)) if on) + ")"
+
     # ------------------------------------------------------------------ allocation hooks
     def alloc_persistent(self, numel: int, dtype: torch.dtype, device: torch.device, tag: str = "",
                          symmetric_numel: int | None = None) -> torch.Tensor:
@@ -317,6 +428,49 @@ class PeerTransport(LocalTransport):
         t = buf.tensor.view(dtype)[:numel]
         self.ctx._by_ptr[t.data_ptr()] = buf
         return t
+
+    def alloc_full_buffer(self, unit_key: str, numel: int, dtype: torch.dtype, tables: SegmentTables,
+                          *, exclusive: bool = False) -> torch.Tensor | None:
+        """A persistent symmetric full-parameter buffer for the NVLS all-gather, or None when this unit
+        keeps the allocator-backed buffer (no multicast, or a layout whose pieces are not 16-byte aligned).
+
+        Collective: units are created in the same order on every rank, so the k-th unit of a size class
+        lands in slot ``k % slots`` everywhere.  ``exclusive`` units (never resharded between uses) get
+        a slot of their own."""
+        es = torch.empty((), dtype=dtype).element_size()
+        if not self.nvls_gather or es not in (2, 4) or numel * es < 16 or not _aligned16(tables, es):
+            return None
+        nbytes = (numel * es + 15) // 16 * 16
+        ring = self._full_rings.setdefault(nbytes, [])
+        shared = [s for s in ring if not s.exclusive]
+        k = sum(len(s.units) for s in shared)       # units of this class placed in shared slots so far
+        if exclusive or len(shared) < self.full_slots_per_class:
+            buf = self.ctx.alloc(nbytes)
+            if not buf.mc_addr:
+                return None
+            slot = _FullSlot(buf, exclusive)
+            ring.append(slot)
+        else:
+            slot = shared[k % len(shared)]
+        slot.units.append(unit_key)
+        self._full_slot_of_unit[unit_key] = slot
+        self._unit(unit_key)
+        return slot.buf.tensor.view(dtype)[:numel]
+
+    def full_slot_available(self, unit_key: str) -> bool:
+        slot = self._full_slot_of_unit.get(unit_key)
+        return slot is None or slot.holder in (None, unit_key)
+
+    def release_full_buffer(self, unit_key: str) -> None:
+        """The unit resharded: once the kernels already enqueued on the current stream are done, peers may
+        overwrite its slot (only published when another unit shares the slot)."""
+        slot = self._full_slot_of_unit.get(unit_key)
+        if slot is None or slot.holder != unit_key:
+            return
+        slot.holder = None
+        if len(slot.units) > 1:
+            self.ctx.signal(self._unit(unit_key), KIND_FREE, slot.last_epoch, None)
+            self.launches += 1
 
     def acquire_grad_buffer(self, unit_key, numel: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
         es = torch.empty((), dtype=dtype).element_size()
@@ -361,10 +515,21 @@ class PeerTransport(LocalTransport):
                     src.append(shard_buf.peer_addr[r] + s.local_start * es)
                     dst.append(s.global_start)
                     ln.append(s.numel)
-            # order so that the local rank's own segments come first (they need no NVLink traffic)
             t = {"src": torch.tensor(src, dtype=torch.int64, device=device),
                  "dst": torch.tensor(dst, dtype=torch.int64, device=device),
                  "len": torch.tensor(ln, dtype=torch.int64, device=device), "n": len(src), "max": max(ln, default=0)}
+            self._tables[key] = t
+        return t
+
+    def _push_tables(self, unit_key, tables: SegmentTables, es: int, device) -> dict:
+        key = ("push", unit_key)
+        t = self._tables.get(key)
+        if t is None:
+            segs = tables.my_segments
+            t = {"src": torch.tensor([s.local_start * es for s in segs], dtype=torch.int64, device=device),
+                 "dst": torch.tensor([s.global_start * es for s in segs], dtype=torch.int64, device=device),
+                 "len": torch.tensor([s.numel * es for s in segs], dtype=torch.int64, device=device), "n": len(segs),
+                 "max": max((s.numel * es for s in segs), default=0)}
             self._tables[key] = t
         return t
 
@@ -395,6 +560,15 @@ class PeerTransport(LocalTransport):
             self._tables[key] = hit
         return hit
 
+    def _validate_pull(self, t: dict, full: torch.Tensor, shard_buf: SymBuffer, run) -> None:
+        ctx = self.ctx
+        lo = (_u64 * ctx.world)(*shard_buf.peer_addr)
+        hi = (_u64 * ctx.world)(*[a + shard_buf.nbytes for a in shard_buf.peer_addr])
+        _lib.check(ctx.lib.mfsdp_validate_pull_table(t["src"].data_ptr(), t["dst"].data_ptr(), t["len"].data_ptr(),
+                                                     t["n"], full.numel(), full.element_size(), lo, hi, ctx.world,
+                                                     ctx.status.data_ptr(), run.cuda_stream), "validate_pull_table")
+        self.launches += 1
+
     def gather(self, shard, full, tables: SegmentTables, *, stream=None, unit_key=None,
                defer: tuple | None = None) -> MatrixCollectiveHandle:
         buf = self.ctx.lookup(shard)
@@ -405,36 +579,65 @@ class PeerTransport(LocalTransport):
         ep["shard"] += 1
         e = ep["shard"]
         es = full.element_size()
-        plan = None
-        if defer is not None and es == 2:
-            plan, t = self._deferred_tables(unit_key, buf, tables, full, defer)
-        else:
-            t = self._gather_tables(unit_key, buf, tables, es, full.device)
+        ctx = self.ctx
         cur = torch.cuda.current_stream()
         run = stream if stream is not None else cur
         if stream is not None:
             stream.wait_stream(cur)
-        self.ctx.signal(ui, KIND_SHARD, e, run)
-        self.ctx.wait(ui, KIND_SHARD, e, run)
-        _lib.check(self.ctx.lib.mfsdp_ag_pull(full.data_ptr(), t["src"].data_ptr(), t["dst"].data_ptr(),
-                                              t["len"].data_ptr(), t["n"], t["max"], es, run.cuda_stream), "ag_pull")
-        self.launches += 3
+        span = _tl.open_span(unit_key or "", "all_gather", run, nbytes=full.numel() * es)
+        fslot = self._full_slot_of_unit.get(unit_key)
+        plan = None
+        if fslot is not None and fslot.buf.tensor.data_ptr() == full.data_ptr():
+            # ---- NVLS: push my shard into every rank's copy of the slot through the switch
+            if fslot.holder not in (None, unit_key):
+                raise RuntimeError(
+                    f"full-parameter slot of {unit_key} still holds {fslot.holder}: more units are unsharded at once "
+                    f"than there are slots per size class; raise {FULL_SLOTS_ENV} or lower the prefetch depth")
+            if fslot.last_unit is not None and fslot.last_unit != unit_key and fslot.last_epoch > 0:
+                # every rank (this one included) has stopped reading the previous occupant
+                ctx.wait(self._unit(fslot.last_unit), KIND_FREE, fslot.last_epoch, run)
+                self.launches += 1
+            fslot.holder, fslot.last_unit, fslot.last_epoch = unit_key, unit_key, e
+            t = self._push_tables(unit_key, tables, es, full.device)
+            _lib.check(ctx.lib.mfsdp_ag_push_mc(shard.data_ptr(), fslot.buf.mc_addr, t["src"].data_ptr(),
+                                                t["dst"].data_ptr(), t["len"].data_ptr(), t["n"], t["max"],
+                                                ctx.status.data_ptr(), run.cuda_stream), "ag_push_mc")
+            # "my shard has landed everywhere" / "everybody's shard has landed here"
+            ctx.signal_wait(ui, KIND_SHARD, e, run)
+            self.launches += 2
+            impl = "ag_push_mc"
+        else:
+            if defer is not None and es == 2:
+                plan, t = self._deferred_tables(unit_key, buf, tables, full, defer)
+            else:
+                t = self._gather_tables(unit_key, buf, tables, es, full.device)
+            ctx.signal_wait(ui, KIND_SHARD, e, run)
+            if ctx.debug_bounds:
+                self._validate_pull(t, full, buf, run)
+            _lib.check(ctx.lib.mfsdp_ag_pull(full.data_ptr(), t["src"].data_ptr(), t["dst"].data_ptr(),
+                                             t["len"].data_ptr(), t["n"], t["max"], es, ctx.status.data_ptr(),
+                                             run.cuda_stream), "ag_pull")
+            self.launches += 2
+            impl = "ag_pull+gemm" if plan is not None else "ag_pull"
+        _tl.close_span(span, run, impl=impl)
         ev = None
         if stream is not None:
             ev = torch.cuda.Event()
             ev.record(stream)
         h = MatrixCollectiveHandle(event=ev, info={
-            "kind": "all_gather", "impl": "ag_pull+gemm" if plan is not None else "ag_pull", "backend": self.kind,
+            "kind": "all_gather", "impl": impl, "backend": self.kind,
             "bytes": full.numel() * es, "count": 1,
             "sync_mode": "stream_event" if stream is not None else "stream_order"})
         h.deferred = plan
+        h.span = span
         return h
 
     # ------------------------------------------------------------------ all-reduce (HSDP replicate group)
     def all_reduce(self, tensor, group, *, scale=None):
-        """Sum ``tensor`` over ``group`` with the same pull-and-sum kernel as the reduce-scatter: every
-        rank publishes its values in a symmetric staging buffer, waits for the others and reads all of
-        them (fixed rank order, fp32 sum), writing the result back into ``tensor``.
+        """Sum ``tensor`` over ``group`` with the same kernels as the reduce-scatter: every rank publishes
+        its values in a symmetric staging buffer, waits for the others and either reads all of them
+        (fixed rank order, fp32 sum) or, with NVLS, sums its slice through the switch and stores the
+        result to every copy (``multimem.ld_reduce`` + ``multimem.st``).
 
         Used for the dp_replicate step of HSDP after the dp_shard reduce-scatter (the reference runs
         ``dist.all_reduce`` + ``div_`` synchronously there, matrix_fsdp/runtime/flat_buffer.py:1472-1480).
@@ -450,29 +653,38 @@ class PeerTransport(LocalTransport):
         key = ("ar", tensor.numel(), tensor.dtype)   # one staging buffer per size: rounds are ordered by the flags
         st = self._ar_state.get(key)
         if st is None:
-            buf = ctx.alloc(tensor.numel() * tensor.element_size())
+            buf = ctx.alloc((tensor.numel() * tensor.element_size() + 15) // 16 * 16)
             dev = tensor.device
-            st = {"buf": buf, "view": buf.tensor.view(tensor.dtype), "epoch": 0, "unit": self._unit(key),
+            st = {"buf": buf, "view": buf.tensor.view(tensor.dtype)[:tensor.numel()], "epoch": 0,
+                  "unit": self._unit(key),
                   "g": torch.zeros(1, dtype=torch.int64, device=dev), "l": torch.zeros(1, dtype=torch.int64, device=dev),
                   "len": torch.tensor([tensor.numel()], dtype=torch.int64, device=dev)}
             self._ar_state[key] = st
         run = torch.cuda.current_stream()
         ui = st["unit"]
-        if st["epoch"] > 0:
+        is_bf16 = int(tensor.dtype == torch.bfloat16)
+        use_mc = bool(self.nvls_reduce and st["buf"].mc_addr and tensor.numel() % 8 == 0)
+        if st["epoch"] > 0 and not use_mc:
             ctx.wait(ui, KIND_PULLED, st["epoch"], run)          # everyone has read the previous round
         st["epoch"] += 1
         e = st["epoch"]
         st["view"].copy_(tensor.view(-1))
-        ctx.signal(ui, KIND_GRAD, e, run)
-        ctx.wait(ui, KIND_GRAD, e, run)
+        ctx.signal_wait(ui, KIND_GRAD, e, run)
+        if use_mc:
+            _lib.check(ctx.lib.mfsdp_ar_mc(st["buf"].mc_addr, tensor.numel(), is_bf16, ctx.rank, ctx.world,
+                                           float(1.0 if scale is None else scale), ctx.status.data_ptr(),
+                                           run.cuda_stream), "ar_mc")
+            ctx.signal_wait(ui, KIND_PULLED, e, run)             # every slice has been stored everywhere
+            tensor.view(-1).copy_(st["view"])
+            self.launches += 5
+            return
         ptrs = (_u64 * ctx.world)(*st["buf"].peer_addr)
-        is_bf16 = int(tensor.dtype == torch.bfloat16)
         _lib.check(ctx.lib.mfsdp_rs_pull_reduce(
             ptrs, ctx.world, ctx.rank, tensor.data_ptr(), st["g"].data_ptr(), st["l"].data_ptr(), st["len"].data_ptr(),
-            1, tensor.numel(), is_bf16, is_bf16, 0, float(1.0 if scale is None else scale), run.cuda_stream),
-            "rs_pull_reduce")
+            1, tensor.numel(), is_bf16, is_bf16, 0, float(1.0 if scale is None else scale), ctx.status.data_ptr(),
+            run.cuda_stream), "rs_pull_reduce")
         ctx.signal(ui, KIND_PULLED, e, run)
-        self.launches += 6
+        self.launches += 5
 
     # ------------------------------------------------------------------ reduce
     def _reduce_tables(self, unit_key, tables: SegmentTables, device) -> dict:
@@ -483,7 +695,8 @@ class PeerTransport(LocalTransport):
             t = {"g": torch.tensor([s.global_start for s in segs], dtype=torch.int64, device=device),
                  "l": torch.tensor([s.local_start for s in segs], dtype=torch.int64, device=device),
                  "len": torch.tensor([s.numel for s in segs], dtype=torch.int64, device=device), "n": len(segs),
-                 "max": max((s.numel for s in segs), default=0)}
+                 "max": max((s.numel for s in segs), default=0),
+                 "vec8": all(s.global_start % 8 == 0 and s.local_start % 8 == 0 and s.numel % 8 == 0 for s in segs)}
             self._tables[key] = t
         return t
 
@@ -514,36 +727,65 @@ class PeerTransport(LocalTransport):
         if stream is not None:
             stream.wait_stream(cur)
         ctx = self.ctx
-        ctx.signal(ui, KIND_GRAD, e, run)
-        ctx.wait(ui, KIND_GRAD, e, run)
-        ptrs = (_u64 * ctx.world)(*buf.peer_addr)
+        span = _tl.open_span(unit_key or "", "reduce_scatter", run,
+                             nbytes=full_grad.numel() * full_grad.element_size())
+        ctx.signal_wait(ui, KIND_GRAD, e, run)
+        in_bf16 = int(full_grad.dtype == torch.bfloat16)
+        sc = float(1.0 if scale is None else scale)
+        use_mc = bool(self.nvls_reduce and buf.mc_addr and t["vec8"]
+                      and (out_shard is None or out_shard.data_ptr() % 16 == 0))
+        if ctx.debug_bounds:
+            shard_numel = update["p"].numel() if update is not None else out_shard.numel()
+            _lib.check(ctx.lib.mfsdp_validate_reduce_table(t["g"].data_ptr(), t["l"].data_ptr(), t["len"].data_ptr(),
+                                                           t["n"], full_grad.numel(), shard_numel,
+                                                           ctx.status.data_ptr(), run.cuda_stream),
+                       "validate_reduce_table")
+            self.launches += 1
         if update is not None:
             u = update
-            _lib.check(ctx.lib.mfsdp_rs_pull_adamw(
-                ptrs, ctx.world, ctx.rank, t["g"].data_ptr(), t["l"].data_ptr(), t["len"].data_ptr(), t["n"], t["max"],
-                int(full_grad.dtype == torch.bfloat16), float(1.0 if scale is None else scale), u["p"].data_ptr(),
-                u["m"].data_ptr(), u["v"].data_ptr(), u["p_lp"].data_ptr() if u.get("p_lp") is not None else None,
-                float(u["lr"]), float(u["beta1"]), float(u["beta2"]), float(u["eps"]), float(u["weight_decay"]),
-                int(u["step"]), run.cuda_stream), "rs_pull_adamw")
+            tail = (u["p"].data_ptr(), u["m"].data_ptr(), u["v"].data_ptr(),
+                    u["p_lp"].data_ptr() if u.get("p_lp") is not None else None,
+                    float(u["lr"]), float(u["beta1"]), float(u["beta2"]), float(u["eps"]), float(u["weight_decay"]),
+                    int(u["step"]), ctx.status.data_ptr(), run.cuda_stream)
+            if use_mc:
+                _lib.check(ctx.lib.mfsdp_rs_mc_adamw(buf.mc_addr, t["g"].data_ptr(), t["l"].data_ptr(),
+                                                     t["len"].data_ptr(), t["n"], t["max"], in_bf16, sc, *tail),
+                           "rs_mc_adamw")
+            else:
+                ptrs = (_u64 * ctx.world)(*buf.peer_addr)
+                _lib.check(ctx.lib.mfsdp_rs_pull_adamw(ptrs, ctx.world, ctx.rank, t["g"].data_ptr(), t["l"].data_ptr(),
+                                                       t["len"].data_ptr(), t["n"], t["max"], in_bf16, sc, *tail),
+                           "rs_pull_adamw")
+            impl = "rs_mc_adamw" if use_mc else "rs_pull_adamw"
         else:
-            _lib.check(ctx.lib.mfsdp_rs_pull_reduce(
-                ptrs, ctx.world, ctx.rank, out_shard.data_ptr(), t["g"].data_ptr(), t["l"].data_ptr(),
-                t["len"].data_ptr(), t["n"], t["max"], int(full_grad.dtype == torch.bfloat16),
-                int(out_shard.dtype == torch.bfloat16), int(accumulate), float(1.0 if scale is None else scale),
-                run.cuda_stream), "rs_pull_reduce")
+            out_bf16 = int(out_shard.dtype == torch.bfloat16)
+            if use_mc:
+                _lib.check(ctx.lib.mfsdp_rs_mc_reduce(buf.mc_addr, out_shard.data_ptr(), t["g"].data_ptr(),
+                                                      t["l"].data_ptr(), t["len"].data_ptr(), t["n"], t["max"],
+                                                      in_bf16, out_bf16, int(accumulate), sc, ctx.status.data_ptr(),
+                                                      run.cuda_stream), "rs_mc_reduce")
+            else:
+                ptrs = (_u64 * ctx.world)(*buf.peer_addr)
+                _lib.check(ctx.lib.mfsdp_rs_pull_reduce(
+                    ptrs, ctx.world, ctx.rank, out_shard.data_ptr(), t["g"].data_ptr(), t["l"].data_ptr(),
+                    t["len"].data_ptr(), t["n"], t["max"], in_bf16, out_bf16, int(accumulate), sc,
+                    ctx.status.data_ptr(), run.cuda_stream), "rs_pull_reduce")
+            impl = "rs_mc_reduce" if use_mc else "rs_pull_reduce"
         ctx.signal(ui, KIND_PULLED, e, run)
-        self.launches += 4
+        self.launches += 3
+        _tl.close_span(span, run, impl=impl)
         ev = torch.cuda.Event()
         ev.record(run)
         if slot is not None:
             slot.event = ev
         if stream is None:
             ev = None
-        return MatrixCollectiveHandle(event=ev, info={
-            "kind": "reduce_scatter", "impl": "rs_pull_adamw" if update is not None else "rs_pull_reduce",
-            "backend": self.kind,
+        h = MatrixCollectiveHandle(event=ev, info={
+            "kind": "reduce_scatter", "impl": impl, "backend": self.kind,
             "bytes": full_grad.numel() * full_grad.element_size(), "count": 1,
             "sync_mode": "stream_event" if stream is not None else "stream_order"})
+        h.span = span
+        return h
 
     def check_health(self) -> None:
         """Raise if any bounded wait on this device ran out (reads the status word: a device sync)."""

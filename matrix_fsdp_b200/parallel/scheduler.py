@@ -67,6 +67,13 @@ class MatrixFSDPSchedulerConfig:
     trim_cuda_cache: bool = False
     cuda_cache_trim_threshold_mb: float = 1024.0
     validate_unit_order: bool = False
+    # after optimizer.step(): start the all-gather of the unit that ran first in the last forward, so the
+    # next step does not begin with an exposed gather (None: on for CUDA, off on CPU)
+    prefetch_first_unit_after_step: bool | None = None
+    # adaptive / profile_guided: exposed unshard wait (ms per unit) above which the prefetch depth grows,
+    # and how many iterations each candidate depth is measured for
+    adaptive_wait_threshold_ms: float = 0.05
+    profile_iterations: int = 3
 
     def __post_init__(self) -> None:
         if self.max_unsharded_prefetch_units < 0:
@@ -79,6 +86,8 @@ class MatrixFSDPSchedulerConfig:
 
 SCHEDULER_KWARGS = tuple(MatrixFSDPSchedulerConfig.__dataclass_fields__) + (
     "scheduler_config", "max_cached_full_param_buffers_per_key", "max_cached_workspaces_per_key")
+
+_POLICY_MAX_DEPTH = 2     # deepest prefetch the measuring policies try
 
 
 @dataclass
@@ -95,6 +104,9 @@ class SchedulerCounters:
     high_water_active_full_param_bytes: int = 0
     iterations: int = 0
     cache_trims: int = 0
+    next_step_prefetch_issued: int = 0
+    policy_adjustments: int = 0
+    mean_unshard_wait_us: int = 0
 
     def as_dict(self) -> dict[str, int]:
         return asdict(self)
@@ -144,6 +156,16 @@ class MatrixFSDPScheduler:
             del old
         if cfg.validate_unit_order:
             self.validate_unit_order()
+        # measuring prefetch policies: exposed waits of this iteration / of the one before (whose CUDA
+        # events have certainly completed by the time they are read, so reading them never blocks)
+        self._wait_samples: list[tuple] = []
+        self._prev_wait_samples: list[tuple] = []
+        self._profile: dict = {"depth": None, "iters": 0, "results": {}, "done": False}
+        if cfg.prefetch_policy != "static" and self.units[0].flat_buffer.device.type == "cuda":
+            from . import device_timeline
+
+            if not device_timeline.enabled():
+                device_timeline.enable(True, collect=False)
 
     # ------------------------------------------------------------------ limits
     def _fwd_budget(self) -> int:
@@ -170,6 +192,9 @@ class MatrixFSDPScheduler:
 
     def _caps_allow(self, unit) -> bool:
         c = self.config
+        slot_free = getattr(unit.flat_buffer, "full_slot_available", None)
+        if slot_free is not None and not slot_free():
+            return False      # its full-parameter slot still holds another unit (persistent symmetric slots)
         if c.max_active_full_param_buffers is not None and len(self._active) + 1 > c.max_active_full_param_buffers:
             return False
         extra = 0 if unit.flat_buffer.full_aliases_shard else unit.flat_buffer.total_numel
@@ -298,6 +323,71 @@ class MatrixFSDPScheduler:
         self._pre_forward_seen = []
         self.post_forward_order.clear()
         self.counters.iterations += 1
+        self._apply_prefetch_policy()
+
+    # ------------------------------------------------------------------ measuring prefetch policies
+    def note_unshard_wait(self, unit, host_ms: float, span) -> None:
+        """Called by a unit after it waited for its all-gather (``span``: device-timeline record or None)."""
+        if self.config.prefetch_policy != "static":
+            self._wait_samples.append((host_ms, span))
+
+    def _mean_exposed_wait_ms(self, samples) -> float | None:
+        vals = []
+        for host_ms, span in samples:
+            if span is None:
+                vals.append(host_ms)            # blocking transports (CPU): the host wait is the exposed time
+            elif span.wait_begin is not None and span.wait_end is not None and span.wait_end.query():
+                vals.append(max(span.wait_begin.elapsed_time(span.wait_end), 0.0))
+        return sum(vals) / len(vals) if vals else None
+
+    def _apply_prefetch_policy(self) -> None:
+        policy = self.config.prefetch_policy
+        if policy == "static":
+            return
+        measured = self._mean_exposed_wait_ms(self._prev_wait_samples)
+        self._prev_wait_samples, self._wait_samples = self._wait_samples, []
+        if measured is None:
+            return
+        self.counters.mean_unshard_wait_us = int(measured * 1e3)
+        if policy == "adaptive":
+            before = (self._fwd_budget(), self._bwd_budget())
+            self.adapt_prefetch(measured, threshold_ms=self.config.adaptive_wait_threshold_ms)
+            if (self._fwd_budget(), self._bwd_budget()) != before:
+                self.counters.policy_adjustments += 1
+            return
+        # profile_guided: measure each candidate depth for a few iterations, then keep the best
+        prof = self._profile
+        if prof["done"]:
+            return
+        if prof["depth"] is None:
+            prof["depth"], prof["iters"] = max(self._fwd_budget(), 1), 0
+            return
+        prof["results"].setdefault(prof["depth"], []).append(measured)
+        prof["iters"] += 1
+        if prof["iters"] < max(self.config.profile_iterations, 1):
+            return
+        if prof["depth"] < _POLICY_MAX_DEPTH and self._depth_fits(prof["depth"] + 1):
+            prof["depth"] += 1
+            prof["iters"] = 0
+            self.config.max_forward_prefetch_units = prof["depth"]
+            self.config.max_backward_prefetch_units = prof["depth"]
+            self.config.max_unsharded_prefetch_units = max(self.config.max_unsharded_prefetch_units, prof["depth"])
+            return
+        means = {d: sum(v) / len(v) for d, v in prof["results"].items()}
+        # the shallowest depth within 10 % (or 10 us) of the best: deeper prefetch costs memory
+        best = min(means.values())
+        pick = min(d for d, m in means.items() if m <= best * 1.1 + 0.01)
+        self.tune_prefetch(PrefetchProfileResult(pick, pick, sum(len(v) for v in prof["results"].values()), means[pick]))
+        prof["done"] = True
+        self.counters.policy_adjustments += 1
+
+    def _depth_fits(self, depth: int) -> bool:
+        """Persistent full-parameter slots bound how many units can be unsharded at once."""
+        for u in self.units:
+            per_class = getattr(u.flat_buffer.transport, "full_slots_per_class", None)
+            if getattr(u.flat_buffer, "full_persistent", False) and per_class is not None and depth + 1 > per_class:
+                return False
+        return True
 
     def record_post_optimizer_event(self) -> None:
         dev = self.units[0].flat_buffer.device
@@ -307,6 +397,25 @@ class MatrixFSDPScheduler:
             self._post_optimizer_event = ev
             self._waited_post_optimizer.clear()
         self.maybe_trim_cuda_cache()
+        self._prefetch_for_next_step()
+
+    def _prefetch_for_next_step(self) -> None:
+        """The parameters are final once the optimizer has run: gather the unit that opens the next
+        forward now, behind whatever the host does between two steps."""
+        want = self.config.prefetch_first_unit_after_step
+        dev = self.units[0].flat_buffer.device
+        if want is None:
+            want = dev.type == "cuda"
+        if not want or not self.forward_order or self._fwd_budget() <= 0:
+            return
+        first = self.forward_order[0]
+        if not first.forward_prefetch or first.state.value != "sharded" or first.flat_buffer.pending_gather is not None:
+            return
+        if not self._caps_allow(first):
+            return
+        first._record("forward_prefetch", reason="after_optimizer_step")
+        first.start_unshard("next_step_prefetch")
+        self.counters.next_step_prefetch_issued += 1
 
     def wait_for_post_optimizer_event_before_all_gather(self, unit) -> None:
         ev = self._post_optimizer_event
@@ -334,13 +443,16 @@ class MatrixFSDPScheduler:
         self.config.max_backward_prefetch_units = result.backward_prefetch_units
 
     def adapt_prefetch(self, mean_unshard_wait_ms: float, *, threshold_ms: float = 0.05) -> None:
-        """``prefetch_policy="adaptive"``: deepen prefetch while waits are visible, within the budget."""
+        """``prefetch_policy="adaptive"``: deepen prefetch while waits are visible, within the budget.
+        Called by the scheduler itself at the end of every iteration with the measured mean exposed wait."""
         if self.config.prefetch_policy != "adaptive":
             return
         cur = self._fwd_budget()
-        if mean_unshard_wait_ms > threshold_ms and cur < max(2, self.config.max_unsharded_prefetch_units):
+        if mean_unshard_wait_ms > threshold_ms and cur < max(_POLICY_MAX_DEPTH, self.config.max_unsharded_prefetch_units) \
+                and self._depth_fits(cur + 1):
             self.config.max_forward_prefetch_units = cur + 1
             self.config.max_backward_prefetch_units = self._bwd_budget() + 1
+            self.config.max_unsharded_prefetch_units = max(self.config.max_unsharded_prefetch_units, cur + 1)
 
     def validate_unit_order(self) -> None:
         """All ranks must have built the same units in the same order."""

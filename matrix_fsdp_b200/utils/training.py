@@ -22,7 +22,22 @@ def train_step(model: torch.nn.Module, optimizer, host_tokens: torch.Tensor, hos
     loss.backward()
     optimizer.step()
     optimizer.zero_grad(set_to_none=True)
-    return float(loss.item())
+    value = float(loss.item())
+    raise_on_device_error(tokens.device)
+    return value
+
+
+def raise_on_device_error(device=None) -> None:
+    """Read the device status word (4 bytes, after a point where the host already synchronised) and raise
+    if a bounded wait in one of the kernels gave up during the step: a peer that never published its
+    shard or gradients must stop the run instead of training on data that did not arrive."""
+    dev = torch.device(device) if device is not None else None
+    if dev is None or dev.type != "cuda":
+        return
+    from ..ops import kernels, lib
+
+    if lib.available() and not lib.disabled_by_env():
+        kernels.check_status(dev)
 
 
 def device_train_step(model: torch.nn.Module, optimizer, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
@@ -57,7 +72,7 @@ def clip_grad_norm_(module_or_units, max_norm: float, norm_type: float = 2.0,
     shards = []
     for u in units:
         u.wait_post_backward_reduce()
-        g = u.flat_buffer.local_grad_shard
+        g = u.flat_buffer.local_grad_shard if u.flat_buffer.local_grad_valid else None
         if g is None or g.numel() == 0:
             continue
         shards.append(g)

@@ -45,7 +45,7 @@ def _worker(rank, world):
     full = get_model_state_dict(model, options=MatrixStateDictOptions(full_state_dict=True))
     for k, v in ref.state_dict().items():
         assert torch.allclose(full[k], v, atol=2e-5, rtol=1e-4), k
-    assert full["lm_head.weight"].data_ptr() != 0 and torch.equal(full["lm_head.weight"], full["embed.weight"])
+    assert full["head.lm_head.weight"].data_ptr() != 0 and torch.equal(full["head.lm_head.weight"], full["embed.weight"])
 
 
 def test_config1_two_rank_gloo_matches_single_process():

@@ -3,6 +3,7 @@ ranks, activation checkpointing across ranks, and the owner-broadcast / padded v
 import copy
 import os
 
+import pytest
 import torch
 import torch.distributed as dist
 from torch import nn
@@ -221,3 +222,45 @@ def _clip_worker(rank, world):
 
 def test_two_rank_global_gradient_clipping():
     run_ranks(_clip_worker, 2)
+
+
+# ----------------------------------------------------------------------------- unused unit keeps its shard
+class _TwoBranch(nn.Module):
+    def __init__(self, d=8):
+        super().__init__()
+        self.a = nn.Linear(d, d)
+        self.b = nn.Linear(d, d)
+
+    def forward(self, x, use_b=True):
+        y = self.a(x)
+        return self.b(y) if use_b else y
+
+
+def _unused_unit_body(rank, world, opt_kind):
+    from matrix_fsdp_b200.api import fully_shard
+    from matrix_fsdp_b200.optim import configure_optimizer
+
+    torch.manual_seed(0)
+    model = _TwoBranch()
+    fully_shard(model.a)
+    fully_shard(model.b)
+    kw = dict(lr=0.01) if opt_kind == "adamw" else dict(lr=0.01, momentum=0.9)
+    opt = configure_optimizer(model, opt_kind, **kw)
+    x = torch.randn(4, 8, generator=torch.Generator().manual_seed(rank))
+    model(x).sum().backward()
+    opt.step()
+    opt.zero_grad()
+    fb = model.b._matrix_fsdp_param_group.flat_buffer
+    before = fb.local_shard.clone()
+    a_before = model.a._matrix_fsdp_param_group.flat_buffer.local_shard.clone()
+    # second step never runs b: it has no gradient, so its shard (and its moments) must not move
+    model(x, use_b=False).sum().backward()
+    opt.step()
+    opt.zero_grad()
+    assert torch.equal(fb.local_shard, before), "a unit without a gradient was updated with a stale one"
+    assert not torch.equal(model.a._matrix_fsdp_param_group.flat_buffer.local_shard, a_before)
+
+
+@pytest.mark.parametrize("opt_kind", ["adamw", "sgd"])
+def test_unit_without_backward_is_skipped_by_the_flat_optimizer(opt_kind):
+    run_ranks(_unused_unit_body, 2, opt_kind)

@@ -93,6 +93,90 @@ def _peer_collectives(rank, world):
     tr.check_health()
 
 
+def _nvls_collectives(rank, world):
+    """The multimem kernels (all-gather push, in-switch reduce-scatter, fused AdamW, slot hand-over)
+    against torch math; silently passes where the box has no NVSwitch multicast."""
+    import torch.distributed as dist
+
+    from matrix_fsdp_b200.core.layout import LayoutSegment as S
+    from matrix_fsdp_b200.parallel.collectives import SegmentTables
+    from matrix_fsdp_b200.parallel.peer import PeerTransport
+
+    os.environ["MFSDP_PEER_FULL_SLOTS"] = "1"          # both test units share one slot
+    dev = torch.device("cuda", rank)
+    tr = PeerTransport.create(dist.group.WORLD, dev)
+    assert tr is not None
+    if not tr.nvls:
+        return
+    total = 8 * 12_500 * world                         # every cut a multiple of 8 elements
+    cuts = [0] + [total * (i + 1) // (2 * world) // 8 * 8 + (64 if i % 2 else 0) for i in range(2 * world - 1)] + [total]
+    per_rank, local = [[] for _ in range(world)], [0] * world
+    for i in range(2 * world):
+        r = i % world
+        per_rank[r].append(S(cuts[i], cuts[i + 1], local[r]))
+        local[r] += cuts[i + 1] - cuts[i]
+    tables = SegmentTables.build(total, per_rank, rank)
+    side = torch.cuda.Stream()
+    units = {}
+    for key in ("nv0", "nv1"):
+        full = tr.alloc_full_buffer(key, total, torch.bfloat16, tables)
+        assert full is not None
+        shard = tr.alloc_persistent(tables.shard_sizes[rank], torch.bfloat16, dev, "shard", symmetric_numel=tables.max_shard)
+        units[key] = (full, shard)
+    assert units["nv0"][0].data_ptr() == units["nv1"][0].data_ptr()      # one shared slot
+    for it in range(3):
+        for ki, key in enumerate(("nv0", "nv1")):
+            full, shard = units[key]
+            torch.manual_seed(10 * it + ki)
+            ref_full = torch.randn(total, device=dev).bfloat16()
+            for sg in tables.my_segments:
+                shard[sg.local_start:sg.local_end].copy_(ref_full[sg.global_start:sg.global_end])
+            h = tr.gather(shard, full, tables, stream=side, unit_key=key)
+            assert h.info["impl"] == "ag_push_mc"
+            h.wait()
+            assert torch.equal(full, ref_full), (it, key)
+            tr.release_full_buffer(key)                # stream-ordered: the compare above has been enqueued
+    # in-switch reduce-scatter, plain and fused with AdamW
+    for it in range(2):
+        g = tr.acquire_grad_buffer("nv0", total, torch.bfloat16, dev)
+        torch.manual_seed(100 + it)
+        base = torch.randn(total, device=dev)
+        g.copy_((base * (rank + 1)).bfloat16())
+        out = torch.zeros(tables.shard_sizes[rank], device=dev)
+        h = tr.reduce(g, out, tables, scale=1.0 / world, stream=side, unit_key="nv0")
+        assert h.info["impl"] == "rs_mc_reduce"
+        h.wait()
+        tr.release_grad_buffer("nv0", g)
+        expect_full = sum((base * (r + 1)).bfloat16().float() for r in range(world)) / world
+        for sg in tables.my_segments:
+            got, want = out[sg.local_start:sg.local_end], expect_full[sg.global_start:sg.global_end]
+            # the switch returns the fp32 sum rounded to bf16
+            assert torch.allclose(got, want, atol=2e-2, rtol=1e-2), (got - want).abs().max()
+    n_loc = tables.shard_sizes[rank]
+    p = torch.randn(n_loc, device=dev)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    p_lp = torch.empty(n_loc, device=dev, dtype=torch.bfloat16)
+    p_ref = p.clone()
+    g = tr.acquire_grad_buffer("nv1", total, torch.bfloat16, dev)
+    torch.manual_seed(7)
+    base = torch.randn(total, device=dev)
+    g.copy_((base * (rank + 1)).bfloat16())
+    upd = dict(p=p, m=m, v=v, p_lp=p_lp, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=1)
+    h = tr.reduce_update(g, tables, upd, scale=1.0 / world, stream=side, unit_key="nv1")
+    assert h.info["impl"] == "rs_mc_adamw"
+    h.wait()
+    torch.cuda.synchronize()
+    gsum = (sum((base * (r + 1)).bfloat16().float() for r in range(world))).bfloat16().float() / world
+    gl = torch.cat([gsum[sg.global_start:sg.global_end] for sg in tables.my_segments])
+    opt_p = torch.nn.Parameter(p_ref.clone())
+    ref_opt = torch.optim.AdamW([opt_p], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    opt_p.grad = gl
+    ref_opt.step()
+    assert torch.allclose(p, opt_p.detach(), atol=2e-5, rtol=1e-5), (p - opt_p.detach()).abs().max()
+    assert torch.equal(p_lp, p.bfloat16())
+    tr.check_health()
+
+
 def _peer_all_reduce(rank, world):
     import torch.distributed as dist
 
@@ -167,6 +251,22 @@ def _train_both(rank, world, out_dir):
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_peer_collectives_match_torch():
     _run(_peer_collectives, min(_ngpu(), 4))
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_nvls_collectives_match_torch():
+    _run(_nvls_collectives, min(_ngpu(), 4))
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_sharded_training_without_nvls_matches():
+    """The plain peer-load kernels (the only path of the failure tests) train the same model."""
+    os.environ["MFSDP_NVLS"] = "0"
+    try:
+        with tempfile.TemporaryDirectory() as d:
+            _run(_train_both, 2, d)
+    finally:
+        os.environ.pop("MFSDP_NVLS", None)
 
 
 def _hsdp_train(rank, world, transport_kind):
@@ -244,8 +344,73 @@ def test_bounded_wait_reports_timeout_instead_of_hanging():
     assert rc == 0
     torch.cuda.synchronize()
     assert int(status.item()) == 2
+    # while the status word is set: later waits return at once and the data kernels touch nothing
+    import ctypes as C
+    import time
+
+    t0 = time.perf_counter()
+    L.mfsdp_peer_wait(flags.data_ptr(), 0, 4, 1, int(5e9), status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0
+    n = 4096
+    grad = torch.ones(n, device="cuda", dtype=torch.bfloat16)
+    p = torch.full((n,), 3.0, device="cuda")
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    p_lp = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    g0 = torch.zeros(1, dtype=torch.int64, device="cuda")
+    ln = torch.full((1,), n, dtype=torch.int64, device="cuda")
+    ptrs = (C.c_ulonglong * 1)(grad.data_ptr())
+
+    def fused_update():
+        rc = L.mfsdp_rs_pull_adamw(ptrs, 1, 0, g0.data_ptr(), g0.data_ptr(), ln.data_ptr(), 1, n, 1, 1.0,
+                                   p.data_ptr(), m.data_ptr(), v.data_ptr(), p_lp.data_ptr(), 0.1, 0.9, 0.95, 1e-8,
+                                   0.0, 1, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+
+    fused_update()
+    assert torch.equal(p, torch.full_like(p, 3.0)) and m.abs().sum().item() == 0.0, "update ran on data that never arrived"
     with pytest.raises(RuntimeError, match="peer flag wait timed out"):
         K.check_status()
     assert int(status.item()) == 0
+    fused_update()                                  # with a clean status word the same launch updates
+    assert not torch.equal(p, torch.full_like(p, 3.0))
     # the device still works
     assert torch.ones(4, device="cuda").sum().item() == 4.0
+
+
+def test_debug_bounds_check_flags_a_bad_pull_table():
+    """MFSDP_DEBUG_BOUNDS: a table entry that leaves the destination (or the peers' windows) sets status 4
+    and the pull kernel behind it copies nothing."""
+    import ctypes as C
+
+    from matrix_fsdp_b200.ops import kernels as K
+    from matrix_fsdp_b200.ops import lib
+    import matrix_fsdp_b200.parallel.peer  # noqa: F401
+
+    L = lib.load(required=True)
+    status = K.status_word()
+    status.zero_()
+    src = torch.arange(1024, device="cuda", dtype=torch.int32)
+    dst = torch.zeros(1024, device="cuda", dtype=torch.int32)
+    addr = torch.tensor([src.data_ptr()], dtype=torch.int64, device="cuda")
+    off = torch.tensor([512], dtype=torch.int64, device="cuda")
+    ln = torch.tensor([1024], dtype=torch.int64, device="cuda")      # 512 + 1024 > 1024: out of range
+    lo = (C.c_ulonglong * 1)(src.data_ptr())
+    hi = (C.c_ulonglong * 1)(src.data_ptr() + src.numel() * 4)
+    st = torch.cuda.current_stream().cuda_stream
+    assert L.mfsdp_validate_pull_table(addr.data_ptr(), off.data_ptr(), ln.data_ptr(), 1, 1024, 4, lo, hi, 1,
+                                       status.data_ptr(), st) == 0
+    assert L.mfsdp_ag_pull(dst.data_ptr(), addr.data_ptr(), off.data_ptr(), ln.data_ptr(), 1, 1024, 4,
+                           status.data_ptr(), st) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 4 and dst.abs().sum().item() == 0
+    with pytest.raises(RuntimeError, match="out of bounds"):
+        K.check_status()
+    # a good table passes and copies
+    off.zero_()
+    L.mfsdp_validate_pull_table(addr.data_ptr(), off.data_ptr(), ln.data_ptr(), 1, 1024, 4, lo, hi, 1,
+                                status.data_ptr(), st)
+    L.mfsdp_ag_pull(dst.data_ptr(), addr.data_ptr(), off.data_ptr(), ln.data_ptr(), 1, 1024, 4, status.data_ptr(), st)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and torch.equal(dst, src)
