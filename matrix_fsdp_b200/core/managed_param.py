@@ -116,93 +116,147 @@ class ManagedParamRegistry:
         ignored_params: set[nn.Parameter] | None = None,
         allow_shared: bool = False,
     ) -> "ManagedParamRegistry":
-        hints = dict(shard_hints or {})
-        ignored = {id(p) for p in ignored_params or ()}
-        names: dict[int, list[str]] = {}
-        for fqn, p in module.named_parameters(recurse=True, remove_duplicate=False):
-            if id(p) not in ignored:
-                names.setdefault(id(p), []).append(fqn)
-        shared = [v for v in names.values() if len(v) > 1]
-        if shared and not allow_shared:
-            listing = "; ".join(",".join(v) for v in shared)
+        """One walk over every (name, parameter) pair of the module, aliases included.  The first name a
+        tensor shows up under becomes its FQN and fixes its place in the flat space; later names of the
+        same tensor are aliases (rejected unless ``allow_shared``)."""
+        skip = {id(p) for p in ignored_params or ()}
+        slots: dict[int, _Slot] = {}
+        for name, tensor in module.named_parameters(recurse=True, remove_duplicate=False):
+            if id(tensor) in skip:
+                continue
+            slot = slots.get(id(tensor))
+            if slot is None:
+                slots[id(tensor)] = _Slot(name, tensor)
+            else:
+                slot.other_names.append(name)
+        tied = [slot for slot in slots.values() if slot.other_names]
+        if tied and not allow_shared:
+            listing = "; ".join(",".join([slot.name, *slot.other_names]) for slot in tied)
             raise NotImplementedError(
                 "MatrixFSDP does not support shared parameters yet. " f"Shared parameter aliases: {listing}."
             )
-        out: list[ManagedParam] = []
-        offset = 0
-        for fqn, p in module.named_parameters(recurse=True, remove_duplicate=True):
-            if id(p) in ignored:
-                continue
-            hint = hints.get(fqn, ParamShardHint())
-            validate_param_shard_hint(fqn, p.shape, p.numel(), hint)
-            aliases = tuple(n for n in names[id(p)] if n != fqn)
-            out.append(ManagedParam(fqn, p, p.shape, p.dtype, p.device, p.numel(), offset, offset + p.numel(), hint, aliases))
-            offset += p.numel()
-        known = {mp.fqn for mp in out} | {a for mp in out for a in mp.aliases}
-        unknown = set(hints) - known
-        if unknown:
-            raise ValueError(f"Shard hints refer to unknown parameters: {', '.join(sorted(unknown))}.")
-        return cls(tuple(out))
+        wanted = dict(shard_hints or {})
+        unclaimed = set(wanted)
+        managed: list[ManagedParam] = []
+        cursor = 0
+        for slot in slots.values():                      # dicts keep first-seen order = registration order
+            t = slot.tensor
+            hint = wanted.get(slot.name, _NO_HINT)
+            unclaimed.difference_update([slot.name, *slot.other_names])
+            validate_param_shard_hint(slot.name, t.shape, t.numel(), hint)
+            managed.append(ManagedParam(fqn=slot.name, param=t, shape=t.shape, dtype=t.dtype, device=t.device,
+                                        numel=t.numel(), offset=cursor, end=cursor + t.numel(), shard_hint=hint,
+                                        aliases=tuple(slot.other_names)))
+            cursor += t.numel()
+        if unclaimed:
+            raise ValueError(f"Shard hints refer to unknown parameters: {', '.join(sorted(unclaimed))}.")
+        return cls(tuple(managed))
+
+
+class _Slot:
+    """A distinct parameter tensor met during the module walk, with every name it goes by."""
+
+    __slots__ = ("name", "tensor", "other_names")
+
+    def __init__(self, name: str, tensor: nn.Parameter) -> None:
+        self.name, self.tensor, self.other_names = name, tensor, []
+
+
+_NO_HINT = ParamShardHint()
 
 
 def _fmt(values) -> str:
     return ", ".join(repr(v) for v in sorted(values, key=str))
 
 
+# ---------------------------------------------------------------------------- hint validation
+# The checks are data: each rule is (applies?, broken?, message) over one context object, evaluated in
+# table order; the first broken rule raises.  Rules that only make sense for one granularity carry that
+# condition in their ``applies`` part, so there is no branching in the driver.
+class _HintCheck:
+    __slots__ = ("fqn", "shape", "numel", "h", "g", "bs", "rows", "cols")
+
+    def __init__(self, fqn: str, shape, numel: int, hint: ParamShardHint) -> None:
+        self.fqn, self.shape, self.numel, self.h = fqn, tuple(shape), int(numel), hint
+        self.g, self.bs = hint.split_granularity, hint.block_shape
+        self.rows, self.cols = (self.shape + (None, None))[:2] if len(self.shape) == 2 else (None, None)
+
+
+def _member(attr: str, allowed) -> tuple:
+    return (lambda c: True,
+            lambda c: getattr(c.h, attr) not in allowed,
+            lambda c: f"Param {c.fqn} has unknown {attr}={getattr(c.h, attr)!r}; expected {_fmt(allowed)}.")
+
+
+def _non_negative(attr: str) -> tuple:
+    return (lambda c: getattr(c.h, attr) is not None,
+            lambda c: getattr(c.h, attr) < 0,
+            lambda c: f"Param {c.fqn} {attr} must be non-negative, got {getattr(c.h, attr)}.")
+
+
+_WHOLE = (None, "parameter", "matrix_owner")
+
+_HINT_RULES: tuple[tuple, ...] = (
+    _member("split_granularity", _GRANULARITIES),
+    _member("runtime_kind", _RUNTIME_KINDS),
+    _member("parallel_role", _PARALLEL_ROLES),
+    _non_negative("expert_id"),
+    _non_negative("owner_rank"),
+    (lambda c: bool(c.h.owner_replica_ranks),
+     lambda c: min(c.h.owner_replica_ranks) < 0,
+     lambda c: f"Param {c.fqn} owner_replica_ranks must be non-negative, got {c.h.owner_replica_ranks}."),
+    (lambda c: c.h.runtime_kind == ParamRuntimeKind.EXPERT_OWNER,
+     lambda c: not c.h.expert_group_id,
+     lambda c: f"Param {c.fqn} runtime_kind='expert_owner' requires expert_group_id metadata."),
+    # ---- block_shape on its own
+    (lambda c: c.bs is not None,
+     lambda c: len(c.bs) == 0,
+     lambda c: f"Param {c.fqn} block_shape cannot be empty."),
+    (lambda c: c.bs is not None,
+     lambda c: min(c.bs) <= 0,
+     lambda c: f"Param {c.fqn} block_shape dims must be positive, got {c.bs}."),
+    # ---- whole-parameter granularities take no block shape
+    (lambda c: c.g in _WHOLE,
+     lambda c: c.bs is not None,
+     lambda c: f"Param {c.fqn} split_granularity={c.g!r} does not accept block_shape."),
+    (lambda c: c.g == "matrix_owner",
+     lambda c: len(c.shape) != 2,
+     lambda c: f"Param {c.fqn} matrix_owner split_granularity expects a 2D tensor, got shape={c.shape}."),
+    # ---- flat blocks
+    (lambda c: c.g == "block",
+     lambda c: c.bs is None or len(c.bs) != 1,
+     lambda c: f"Param {c.fqn} block split_granularity expects a 1D block_shape."),
+    (lambda c: c.g == "block",
+     lambda c: c.numel % c.bs[0] != 0,
+     lambda c: f"Param {c.fqn} numel={c.numel} is not divisible by block_shape={c.bs}."),
+    # ---- row blocks of a matrix
+    (lambda c: c.g == "row_block",
+     lambda c: len(c.shape) != 2,
+     lambda c: f"Param {c.fqn} row_block split_granularity expects a 2D tensor, got shape={c.shape}."),
+    (lambda c: c.g == "row_block",
+     lambda c: c.bs is None or len(c.bs) not in (1, 2),
+     lambda c: f"Param {c.fqn} row_block split_granularity expects a 1D or 2D block_shape."),
+    (lambda c: c.g == "row_block" and len(c.bs) == 2,
+     lambda c: c.bs[1] != c.cols,
+     lambda c: f"Param {c.fqn} row_block block_shape second dim={c.bs[1]} must match cols={c.cols}."),
+    (lambda c: c.g == "row_block",
+     lambda c: c.rows % c.bs[0] != 0,
+     lambda c: f"Param {c.fqn} rows={c.rows} is not divisible by row block={c.bs[0]}."),
+)
+
+
 def validate_param_shard_hint(fqn: str, shape, numel: int, hint: ParamShardHint) -> None:
-    shape = tuple(shape)
-    if hint.split_granularity not in _GRANULARITIES:
-        raise ValueError(
-            f"Param {fqn} has unknown split_granularity={hint.split_granularity!r}; expected {_fmt(_GRANULARITIES)}.")
-    if hint.runtime_kind not in _RUNTIME_KINDS:
-        raise ValueError(f"Param {fqn} has unknown runtime_kind={hint.runtime_kind!r}; expected {_fmt(_RUNTIME_KINDS)}.")
-    if hint.parallel_role not in _PARALLEL_ROLES:
-        raise ValueError(
-            f"Param {fqn} has unknown parallel_role={hint.parallel_role!r}; expected {_fmt(_PARALLEL_ROLES)}.")
-    if hint.expert_id is not None and hint.expert_id < 0:
-        raise ValueError(f"Param {fqn} expert_id must be non-negative, got {hint.expert_id}.")
-    if hint.owner_rank is not None and hint.owner_rank < 0:
-        raise ValueError(f"Param {fqn} owner_rank must be non-negative, got {hint.owner_rank}.")
-    if any(r < 0 for r in hint.owner_replica_ranks):
-        raise ValueError(f"Param {fqn} owner_replica_ranks must be non-negative, got {hint.owner_replica_ranks}.")
-    if hint.runtime_kind == ParamRuntimeKind.EXPERT_OWNER and not hint.expert_group_id:
-        raise ValueError(f"Param {fqn} runtime_kind='expert_owner' requires expert_group_id metadata.")
-    bs = hint.block_shape
-    if bs is not None:
-        if len(bs) == 0:
-            raise ValueError(f"Param {fqn} block_shape cannot be empty.")
-        if any(d <= 0 for d in bs):
-            raise ValueError(f"Param {fqn} block_shape dims must be positive, got {bs}.")
-    g = hint.split_granularity
-    if g in (None, "parameter", "matrix_owner"):
-        if bs is not None:
-            raise ValueError(f"Param {fqn} split_granularity={g!r} does not accept block_shape.")
-        if g == "matrix_owner" and len(shape) != 2:
-            raise ValueError(f"Param {fqn} matrix_owner split_granularity expects a 2D tensor, got shape={shape}.")
-        return
-    if g == "block":
-        if bs is None or len(bs) != 1:
-            raise ValueError(f"Param {fqn} block split_granularity expects a 1D block_shape.")
-        if numel % bs[0] != 0:
-            raise ValueError(f"Param {fqn} numel={numel} is not divisible by block_shape={bs}.")
-        return
-    # row_block
-    if len(shape) != 2:
-        raise ValueError(f"Param {fqn} row_block split_granularity expects a 2D tensor, got shape={shape}.")
-    if bs is None or len(bs) not in (1, 2):
-        raise ValueError(f"Param {fqn} row_block split_granularity expects a 1D or 2D block_shape.")
-    rows, cols = shape
-    if len(bs) == 2 and bs[1] != cols:
-        raise ValueError(f"Param {fqn} row_block block_shape second dim={bs[1]} must match cols={cols}.")
-    if rows % bs[0] != 0:
-        raise ValueError(f"Param {fqn} rows={rows} is not divisible by row block={bs[0]}.")
+    """Raise ``ValueError`` for the first rule of the table that the hint breaks."""
+    ctx = _HintCheck(fqn, shape, numel, hint)
+    for applies, broken, message in _HINT_RULES:
+        if applies(ctx) and broken(ctx):
+            raise ValueError(message(ctx))
 
 
 def hint_block_units(mp: ManagedParam) -> int | None:
     """Smallest indivisible run of elements for a parameter, or ``None`` for whole-param."""
     h = mp.shard_hint
-    if h.split_granularity == "block" and h.block_shape:
-        return int(h.block_shape[0])
-    if h.split_granularity == "row_block" and h.block_shape:
-        return int(h.block_shape[0]) * int(mp.shape[1])
-    return None
+    if not h.block_shape:
+        return None
+    per_row = {"block": 1, "row_block": int(mp.shape[1]) if len(mp.shape) == 2 else 0}.get(h.split_granularity, 0)
+    return int(h.block_shape[0]) * per_row or None
