@@ -61,17 +61,33 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
   }
 }
 
+// Sum R values over the block at once (one round of barriers for R rows); `red` holds R * 32 floats.
+template <int R>
+__device__ __forceinline__ void block_sum_rows(float (&v)[R], float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int r = 0; r < R; ++r) v[r] = warp_sum(v[r]);
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) red[r * 32 + warp] = v[r];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < R; ++r) v[r] = warp_sum(lane < nwarps ? red[r * 32 + lane] : 0.f);
+  __syncthreads();
+}
+
 // dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres);  dw += sum_rows dy * xhat.
-// Persistent over rows so each CTA folds its dw partial into the fp32 accumulator once.
-template <int VPT>
-__global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
-                                   const __nv_bfloat16* __restrict__ x,
-                                   const __nv_bfloat16* __restrict__ w,
-                                   const float* __restrict__ rstd_in,
-                                   const __nv_bfloat16* __restrict__ dres,
-                                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_acc,
-                                   long long rows, int H) {
-  __shared__ float red[32];
+// Persistent over rows so each CTA folds its dw partial into the fp32 accumulator once.  A CTA works
+// on ROWS rows per trip: all their loads are issued before the first use and one pair of barriers
+// serves the ROWS row-dots, which is what the kernel's time goes to at hidden sizes of a few thousand.
+template <int VPT, int ROWS>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
+                   const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                   float* __restrict__ dw_acc, long long rows, int H) {
+  __shared__ float red[ROWS * 32];
   const int nvec = H >> 3;
   float dwp[VPT][8];
   float wf[VPT][8];
@@ -90,51 +106,77 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
       }
     }
   }
-  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
-    const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * H);
-    const float rstd = rstd_in[row];
-    float xh[VPT][8], g[VPT][8];
-    float dot = 0.f;
+  for (long long row0 = (long long)blockIdx.x * ROWS; row0 < rows; row0 += (long long)gridDim.x * ROWS) {
+    uint4 xv[ROWS][VPT], dv[ROWS][VPT];
+    float rstd[ROWS], dot[ROWS];
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int v = threadIdx.x + i * blockDim.x;
-      if (v < nvec) {
-        const uint4 xv = xr[v], dv = dyr[v];
-        const uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w};
-        const uint32_t du[4] = {dv.x, dv.y, dv.z, dv.w};
+    for (int r = 0; r < ROWS; ++r) {
+      const long long row = row0 + r;
+      const bool live = row < rows;
+      rstd[r] = live ? rstd_in[row] : 0.f;
+      dot[r] = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = threadIdx.x + i * blockDim.x;
+        if (live && v < nvec) {
+          xv[r][i] = reinterpret_cast<const uint4*>(x + row * H)[v];
+          dv[r][i] = reinterpret_cast<const uint4*>(dy + row * H)[v];
+        } else {
+          xv[r][i] = make_uint4(0, 0, 0, 0);
+          dv[r][i] = make_uint4(0, 0, 0, 0);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const uint32_t xu[4] = {xv[r][i].x, xv[r][i].y, xv[r][i].z, xv[r][i].w};
+        const uint32_t du[4] = {dv[r][i].x, dv[r][i].y, dv[r][i].z, dv[r][i].w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float2 xf = unpack_bf16x2(xu[e]);
           const float2 df = unpack_bf16x2(du[e]);
-          xh[i][2 * e] = xf.x * rstd; xh[i][2 * e + 1] = xf.y * rstd;
-          g[i][2 * e] = df.x * wf[i][2 * e]; g[i][2 * e + 1] = df.y * wf[i][2 * e + 1];
-          dwp[i][2 * e] += df.x * xh[i][2 * e];
-          dwp[i][2 * e + 1] += df.y * xh[i][2 * e + 1];
-          dot += g[i][2 * e] * xh[i][2 * e] + g[i][2 * e + 1] * xh[i][2 * e + 1];
+          const float xh0 = xf.x * rstd[r], xh1 = xf.y * rstd[r];
+          dwp[i][2 * e] += df.x * xh0;
+          dwp[i][2 * e + 1] += df.y * xh1;
+          dot[r] += df.x * wf[i][2 * e] * xh0 + df.y * wf[i][2 * e + 1] * xh1;
         }
       }
     }
-    dot = block_sum(dot, red) / (float)H;
+    block_sum_rows<ROWS>(dot, red);
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int v = threadIdx.x + i * blockDim.x;
-      if (v < nvec) {
-        float o[8];
+    for (int r = 0; r < ROWS; ++r) {
+      const long long row = row0 + r;
+      if (row >= rows) break;
+      const float mean_dot = dot[r] / (float)H;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = rstd * (g[i][e] - xh[i][e] * dot);
-        if (dres) {
-          const uint4 rv = reinterpret_cast<const uint4*>(dres + row * H)[v];
-          const uint32_t ru[4] = {rv.x, rv.y, rv.z, rv.w};
+      for (int i = 0; i < VPT; ++i) {
+        const int v = threadIdx.x + i * blockDim.x;
+        if (v < nvec) {
+          const uint32_t xu[4] = {xv[r][i].x, xv[r][i].y, xv[r][i].z, xv[r][i].w};
+          const uint32_t du[4] = {dv[r][i].x, dv[r][i].y, dv[r][i].z, dv[r][i].w};
+          float o[8];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float2 rf = unpack_bf16x2(ru[e]);
-            o[2 * e] += rf.x; o[2 * e + 1] += rf.y;
+            const float2 xf = unpack_bf16x2(xu[e]);
+            const float2 df = unpack_bf16x2(du[e]);
+            o[2 * e] = rstd[r] * (df.x * wf[i][2 * e] - xf.x * rstd[r] * mean_dot);
+            o[2 * e + 1] = rstd[r] * (df.y * wf[i][2 * e + 1] - xf.y * rstd[r] * mean_dot);
           }
+          if (dres) {
+            const uint4 rv = reinterpret_cast<const uint4*>(dres + row * H)[v];
+            const uint32_t ru[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 rf = unpack_bf16x2(ru[e]);
+              o[2 * e] += rf.x; o[2 * e + 1] += rf.y;
+            }
+          }
+          reinterpret_cast<uint4*>(dx + row * H)[v] =
+              make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]), pack_bf16x2(o[4], o[5]),
+                         pack_bf16x2(o[6], o[7]));
         }
-        reinterpret_cast<uint4*>(dx + row * H)[v] =
-            make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]), pack_bf16x2(o[4], o[5]),
-                       pack_bf16x2(o[6], o[7]));
       }
     }
   }
@@ -558,6 +600,15 @@ MFSDP_API int mfsdp_rmsnorm_fwd(const void* x, const void* w, void* y, float* rs
 // Rows of CTAs used by the backward kernel (= rows of the dw scratch matrix).
 MFSDP_API int mfsdp_rmsnorm_bwd_scratch_rows(long long rows) { return (int)(rows < 148 * 4 ? rows : 148 * 4); }
 
+// CTAs for `rows` rows taken `rows_per_trip` at a time with at most `cap` CTAs: every CTA makes the same
+// number of trips (up to rounding), so none idles while the others finish.
+static int rmsnorm_bwd_grid(long long rows, int rows_per_trip, int cap) {
+  const long long groups = (rows + rows_per_trip - 1) / rows_per_trip;
+  if (groups <= cap) return (int)(groups < 1 ? 1 : groups);
+  const long long trips = (groups + cap - 1) / cap;
+  return (int)((groups + trips - 1) / trips);
+}
+
 // dw_acc: fp32 scratch of mfsdp_rmsnorm_bwd_scratch_rows(rows) x H floats (fully overwritten, needs no
 // initialisation); dw (bf16) = (accumulate ? dw : 0) + column sums of the scratch.
 MFSDP_API int mfsdp_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
@@ -567,12 +618,12 @@ MFSDP_API int mfsdp_rmsnorm_bwd(const void* dy, const void* x, const void* w, co
   const int nvec = H / 8;
   const int threads = 256;
   const int vpt = (nvec + threads - 1) / threads;
-  const int grid = (int)(rows < 148 * 4 ? rows : 148 * 4);
+  const int grid = rmsnorm_bwd_grid(rows, vpt <= 1 ? 4 : (vpt <= 2 ? 2 : 1), mfsdp_rmsnorm_bwd_scratch_rows(rows));
   auto DY = (const __nv_bfloat16*)dy; auto X = (const __nv_bfloat16*)x; auto W = (const __nv_bfloat16*)w;
   auto DR = (const __nv_bfloat16*)dres; auto DX = (__nv_bfloat16*)dx;
-  if (vpt <= 1) rmsnorm_bwd_kernel<1><<<grid, threads, 0, st>>>(DY, X, W, rstd, DR, DX, dw_acc, rows, H);
-  else if (vpt <= 2) rmsnorm_bwd_kernel<2><<<grid, threads, 0, st>>>(DY, X, W, rstd, DR, DX, dw_acc, rows, H);
-  else if (vpt <= 4) rmsnorm_bwd_kernel<4><<<grid, threads, 0, st>>>(DY, X, W, rstd, DR, DX, dw_acc, rows, H);
+  if (vpt <= 1) rmsnorm_bwd_kernel<1, 4><<<grid, threads, 0, st>>>(DY, X, W, rstd, DR, DX, dw_acc, rows, H);
+  else if (vpt <= 2) rmsnorm_bwd_kernel<2, 2><<<grid, threads, 0, st>>>(DY, X, W, rstd, DR, DX, dw_acc, rows, H);
+  else if (vpt <= 4) rmsnorm_bwd_kernel<4, 1><<<grid, threads, 0, st>>>(DY, X, W, rstd, DR, DX, dw_acc, rows, H);
   else return -2;
   if (dw) colsum_f32_to_bf16_kernel<<<(H + 31) / 32, dim3(32, 8), 0, st>>>(dw_acc, (__nv_bfloat16*)dw, grid, H, accumulate_dw);
   return (int)cudaGetLastError();
@@ -739,12 +790,12 @@ MFSDP_API int mfsdp_rmsnorm_bwd_noalloc(const void* dy, const void* x, const voi
   const int nvec = H / 8;
   const int threads = 256;
   const int vpt = (nvec + threads - 1) / threads;
-  const int grid = (int)(rows < MFSDP_NOALLOC_SCRATCH_ROWS ? rows : MFSDP_NOALLOC_SCRATCH_ROWS);
+  const int grid = rmsnorm_bwd_grid(rows, vpt <= 1 ? 4 : (vpt <= 2 ? 2 : 1), MFSDP_NOALLOC_SCRATCH_ROWS);
   auto DY = (const __nv_bfloat16*)dy; auto X = (const __nv_bfloat16*)x; auto W = (const __nv_bfloat16*)w;
   auto DR = (const __nv_bfloat16*)dres; auto DX = (__nv_bfloat16*)dx;
-  if (vpt <= 1) rmsnorm_bwd_kernel<1><<<grid, threads, 0, st>>>(DY, X, W, rstd, DR, DX, scratch, rows, H);
-  else if (vpt <= 2) rmsnorm_bwd_kernel<2><<<grid, threads, 0, st>>>(DY, X, W, rstd, DR, DX, scratch, rows, H);
-  else if (vpt <= 4) rmsnorm_bwd_kernel<4><<<grid, threads, 0, st>>>(DY, X, W, rstd, DR, DX, scratch, rows, H);
+  if (vpt <= 1) rmsnorm_bwd_kernel<1, 4><<<grid, threads, 0, st>>>(DY, X, W, rstd, DR, DX, scratch, rows, H);
+  else if (vpt <= 2) rmsnorm_bwd_kernel<2, 2><<<grid, threads, 0, st>>>(DY, X, W, rstd, DR, DX, scratch, rows, H);
+  else if (vpt <= 4) rmsnorm_bwd_kernel<4, 1><<<grid, threads, 0, st>>>(DY, X, W, rstd, DR, DX, scratch, rows, H);
   else return -2;
   if (dw) colsum_f32_to_bf16_kernel<<<(H + 31) / 32, dim3(32, 8), 0, st>>>(scratch, (__nv_bfloat16*)dw, grid, H, accumulate_dw);
   return (int)cudaGetLastError();

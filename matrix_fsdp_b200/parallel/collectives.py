@@ -211,14 +211,85 @@ def broadcast_rank_segments_1d_into_async(shard: torch.Tensor, full: torch.Tenso
     return _run(body, stream=stream, info=info)
 
 
+def _is_nccl(group) -> bool:
+    try:
+        return dist.get_backend(group) == "nccl"
+    except Exception:  # noqa: BLE001
+        return False
+
+
+def all_gather_uneven_rank_segments_1d_into_async(shard: torch.Tensor, full: torch.Tensor, tables: SegmentTables, group,
+                                                  *, stream=None, workspace: torch.Tensor | None = None,
+                                                  ) -> MatrixCollectiveHandle:
+    """Uneven list all-gather: ``dist.all_gather`` with one output tensor per rank, each of that rank's
+    size.  With rank-contiguous chunks the outputs are views of the full buffer (nothing is staged or
+    padded); multi-segment shards land in per-rank staging tensors and are scattered afterwards.
+
+    The list form with unequal sizes exists for NCCL only and cannot carry an empty tensor, so other
+    backends take the padded gather and layouts with an empty rank take the owner broadcast
+    (``matrix_fsdp/runtime/collectives.py:330-410`` has the same two fall-backs)."""
+    if group is None:
+        scatter_local_segments(shard, full, tables.my_segments)
+        return MatrixCollectiveHandle(info={"kind": "all_gather", "impl": "local_copy", "bytes": 0, "count": 0,
+                                            "sync_mode": "local"})
+    if any(n == 0 for n in tables.shard_sizes):
+        return broadcast_rank_segments_1d_into_async(shard, full, tables, group, stream=stream)
+    if not _is_nccl(group):
+        return all_gather_matrix_1d_into_async(shard, full, tables, group, stream=stream, workspace=workspace)
+    info = {"kind": "all_gather", "impl": "uneven_all_gather", "bytes": full.numel() * full.element_size(), "count": 1}
+
+    def body():
+        direct = tables.rank_contiguous
+        outs = []
+        for r in range(tables.world_size):
+            n = tables.shard_sizes[r]
+            if direct:
+                seg = tables.rank_segments[r][0]
+                outs.append(full[seg.global_start:seg.global_end])
+            else:
+                outs.append(torch.empty(n, dtype=full.dtype, device=full.device))
+        dist.all_gather(outs, shard[: tables.shard_sizes[tables.rank]], group=group)
+        if not direct:
+            for r, buf in enumerate(outs):
+                scatter_local_segments(buf, full, tables.rank_segments[r])
+
+    return _run(body, stream=stream, info=info)
+
+
+def all_gather_by_all_reduce_1d_into_async(shard: torch.Tensor, full: torch.Tensor, tables: SegmentTables, group, *,
+                                           stream=None) -> MatrixCollectiveHandle:
+    """Diagnostic gather: zero the full buffer, drop the own segments in, sum over ranks.  Moves W times
+    the bytes of a real gather; useful to tell a layout problem from a collective problem
+    (``matrix_fsdp/kernels/custom_collectives.py:803-838``)."""
+    info = {"kind": "all_gather", "impl": "all_reduce_gather", "bytes": full.numel() * full.element_size(), "count": 1}
+    if group is None:
+        scatter_local_segments(shard, full, tables.my_segments)
+        return MatrixCollectiveHandle(info={**info, "impl": "local_copy", "sync_mode": "local"})
+
+    def body():
+        full.zero_()
+        scatter_local_segments(shard, full, tables.my_segments)
+        dist.all_reduce(full, group=group)
+
+    return _run(body, stream=stream, info=info)
+
+
 def all_gatherv_rank_segments_1d_into_async(shard: torch.Tensor, full: torch.Tensor, tables: SegmentTables, group, *,
                                             stream=None, impl: str = "auto",
                                             workspace: torch.Tensor | None = None) -> MatrixCollectiveHandle:
-    """Dispatch on layout shape: equal chunks, padded gather, or owner broadcast."""
-    if tables.equal_contiguous and impl in ("auto", "equal"):
+    """Dispatch on layout shape and ``impl``: equal chunks, padded gather, uneven list gather, owner
+    broadcast, or the all-reduce diagnostic."""
+    if impl in ("equal", "equal_all_gather") and not tables.equal_contiguous:
+        raise RuntimeError("param_gather_strategy='equal_all_gather' requires equal rank-ordered shards.")
+    if tables.equal_contiguous and impl in ("auto", "equal", "equal_all_gather"):
         return all_gather_equal_1d_into_async(shard, full, group, stream=stream)
     if impl in ("owner_broadcast", "broadcast"):
         return broadcast_rank_segments_1d_into_async(shard, full, tables, group, stream=stream)
+    if impl in ("uneven_all_gather", "uneven"):
+        return all_gather_uneven_rank_segments_1d_into_async(shard, full, tables, group, stream=stream,
+                                                             workspace=workspace)
+    if impl in ("all_reduce", "all_reduce_gather"):
+        return all_gather_by_all_reduce_1d_into_async(shard, full, tables, group, stream=stream)
     return all_gather_matrix_1d_into_async(shard, full, tables, group, stream=stream, workspace=workspace)
 
 
@@ -290,10 +361,108 @@ def reduce_owner_rank_chunks_1d_async(full_grad: torch.Tensor, out_shard: torch.
     return _run(body, stream=stream, info=info)
 
 
+def reduce_scatter_uneven_rank_chunks_1d_async(full_grad: torch.Tensor, out_shard: torch.Tensor, tables: SegmentTables,
+                                               group, *, scale: float | None = None, stream=None,
+                                               workspace: torch.Tensor | None = None) -> MatrixCollectiveHandle:
+    """Uneven list reduce-scatter: ``dist.reduce_scatter(out, [one view per rank])`` on the compact flat
+    gradient, no padding.  NCCL only and every rank needs at least one element; otherwise the padded
+    path runs (``matrix_fsdp/runtime/collectives.py:609-675``)."""
+    if group is None or not _is_nccl(group) or any(n == 0 for n in tables.shard_sizes) \
+            or out_shard.dtype != full_grad.dtype:
+        return reduce_scatter_padded_rank_chunks_1d_async(full_grad, out_shard, tables, group, scale=scale,
+                                                          stream=stream, workspace=workspace)
+    info = {"kind": "reduce_scatter", "impl": "uneven_reduce_scatter",
+            "bytes": full_grad.numel() * full_grad.element_size(), "count": 1}
+    n_local = tables.shard_sizes[tables.rank]
+
+    def body():
+        ins = []
+        for r in range(tables.world_size):
+            if tables.rank_contiguous:
+                seg = tables.rank_segments[r][0]
+                ins.append(full_grad[seg.global_start:seg.global_end])
+            else:
+                buf = torch.empty(tables.shard_sizes[r], dtype=full_grad.dtype, device=full_grad.device)
+                gather_local_segments(full_grad, buf, tables.rank_segments[r])
+                ins.append(buf)
+        dist.reduce_scatter(out_shard[:n_local], ins, group=group)
+        if scale is not None and scale != 1.0:
+            out_shard[:n_local].mul_(scale)
+
+    return _run(body, stream=stream, info=info)
+
+
+def param_segment_tables(tables: SegmentTables, start: int, end: int) -> tuple[SegmentTables, int]:
+    """Tables of the sub-range ``[start, end)`` of the flat space (one parameter), with offsets relative
+    to ``start`` and each rank's pieces packed from local offset 0; also returns where this rank's first
+    piece sits in its full local shard."""
+    per_rank, my_local = [], None
+    for r, segs in enumerate(tables.rank_segments):
+        out, cursor = [], 0
+        for sg in segs:
+            a, b = max(sg.global_start, start), min(sg.global_end, end)
+            if a >= b:
+                continue
+            if r == tables.rank and my_local is None:
+                my_local = sg.local_start + (a - sg.global_start)
+            out.append(LayoutSegment(a - start, b - start, cursor))
+            cursor += b - a
+        per_rank.append(out)
+    return SegmentTables.build(end - start, per_rank, tables.rank), (my_local if my_local is not None else 0)
+
+
+def reduce_scatter_per_param_async(full_grad: torch.Tensor, out_shard: torch.Tensor, tables: SegmentTables,
+                                  param_ranges: Sequence[tuple[int, int]], group, *, scale: float | None = None,
+                                  stream=None) -> MatrixCollectiveHandle:
+    """One reduce-scatter per parameter (``param_ranges``: [start, end) of each parameter in the flat
+    space), each over that parameter's own rank chunks.  A diagnostic strategy: it isolates one
+    parameter's gradient traffic and costs one collective per parameter
+    (``matrix_fsdp/runtime/flat_buffer.py:522-552``, ``runtime/collectives.py:993-1029``)."""
+    info = {"kind": "reduce_scatter", "impl": "per_param_reduce_scatter",
+            "bytes": full_grad.numel() * full_grad.element_size(), "count": len(param_ranges)}
+
+    def one(start: int, end: int) -> None:
+        sub, _ = param_segment_tables(tables, start, end)
+        n_mine = sub.shard_sizes[sub.rank]
+        piece = torch.empty(max(n_mine, 1), dtype=full_grad.dtype, device=full_grad.device)[:n_mine]
+        src = full_grad[start:end]
+        if group is None:
+            gather_local_segments(src, piece, sub.my_segments)
+        else:
+            W, mx = sub.world_size, max(sub.max_shard, 1)
+            packed = pack_rank_major_padded(src, sub) if sub.max_shard else src.new_zeros(W * mx)
+            recv = torch.empty(mx, dtype=full_grad.dtype, device=full_grad.device)
+            dist.reduce_scatter_tensor(recv, packed[: W * mx], group=group)
+            piece.copy_(recv[:n_mine])
+        # the parameter's pieces go back to where the unit-wide layout keeps them in the local shard
+        cursor = 0
+        for sg in tables.my_segments:
+            a, b = max(sg.global_start, start), min(sg.global_end, end)
+            if a >= b:
+                continue
+            dst = out_shard[sg.local_start + (a - sg.global_start): sg.local_start + (b - sg.global_start)]
+            dst.copy_(piece[cursor:cursor + (b - a)])
+            if scale is not None and scale != 1.0:
+                dst.mul_(scale)
+            cursor += b - a
+
+    def body():
+        for start, end in param_ranges:
+            one(int(start), int(end))
+
+    if group is None:
+        body()
+        return MatrixCollectiveHandle(info={**info, "sync_mode": "local"})
+    return _run(body, stream=stream, info=info)
+
+
 def reduce_scatterv_owner_rank_chunks_1d_async(full_grad, out_shard, tables, group, *, scale=None, stream=None,
                                                impl: str = "auto", workspace=None) -> MatrixCollectiveHandle:
     if impl in ("owner_reduce", "reduce", "native_reduce"):
         return reduce_owner_rank_chunks_1d_async(full_grad, out_shard, tables, group, scale=scale, stream=stream)
+    if impl in ("uneven_reduce_scatter", "uneven"):
+        return reduce_scatter_uneven_rank_chunks_1d_async(full_grad, out_shard, tables, group, scale=scale,
+                                                          stream=stream, workspace=workspace)
     return reduce_scatter_padded_rank_chunks_1d_async(full_grad, out_shard, tables, group, scale=scale,
                                                       stream=stream, workspace=workspace)
 

@@ -71,7 +71,8 @@ class MatrixFlatBuffer:
     def __init__(self, registry: ManagedParamRegistry, layout: MatrixGroupLayout, *, rank: int, world_size: int,
                  transport, replicate_group=None, replicate_world_size: int = 1, param_dtype: torch.dtype | None = None,
                  reduce_dtype: torch.dtype | None = None, divide_grads_by_world: bool = True,
-                 unit_key: str = "", exclusive_full_buffer: bool = False) -> None:
+                 unit_key: str = "", exclusive_full_buffer: bool = False, gather_impl: str | None = None,
+                 reduce_impl: str | None = None, shard_group=None) -> None:
         self.registry = registry
         self.layout = layout
         self.rank, self.world_size = rank, world_size
@@ -80,6 +81,12 @@ class MatrixFlatBuffer:
         self.replicate_world_size = replicate_world_size
         self.divide_grads_by_world = divide_grads_by_world
         self.unit_key = unit_key
+        # explicit collective variants (``param_gather_strategy`` / ``backward_reduce_strategy``): they are
+        # library collectives, run through a torch.distributed transport even when the unit's own
+        # transport is the peer-kernel one
+        self.gather_impl, self.reduce_impl = gather_impl, reduce_impl
+        self.shard_group = shard_group
+        self._library_transport = None
         params = registry.params
         if not params:
             raise ValueError("An FSDP unit needs at least one managed parameter.")
@@ -138,7 +145,7 @@ class MatrixFlatBuffer:
         else:
             slot = None
             alloc_full = getattr(transport, "alloc_full_buffer", None)
-            if alloc_full is not None:
+            if alloc_full is not None and gather_impl is None:
                 slot = alloc_full(unit_key, self.total_numel, self.param_dtype, self.tables,
                                   exclusive=exclusive_full_buffer)
             self.full_persistent = slot is not None
@@ -183,6 +190,16 @@ class MatrixFlatBuffer:
 
     def _gather_source_tensor(self) -> torch.Tensor:
         return self.local_shard_lp if self.mixed else self.local_shard
+
+    def library_transport(self):
+        """torch.distributed transport of this unit's shard group (the unit's own one when it already is)."""
+        if getattr(self.transport, "kind", "") in ("torch_dist", "local"):
+            return self.transport
+        if self._library_transport is None:
+            from .transport import TorchDistTransport
+
+            self._library_transport = TorchDistTransport(self.shard_group)
+        return self._library_transport
 
     def _rebuild_local_views(self) -> None:
         self._local_views = {}
@@ -274,13 +291,23 @@ class MatrixFlatBuffer:
                 h = self.transport.gather(self._gather_source_tensor(), self.full_buffer, self.tables, stream=stream,
                                           unit_key=self.unit_key, defer=defer)
                 self.deferred_gather = getattr(h, "deferred", None)
+            elif self.gather_impl is not None and self.world_size > 1:
+                if self.gather_impl == "equal_all_gather" and not self.tables.equal_contiguous:
+                    raise RuntimeError("param_gather_strategy='equal_all_gather' requires equal rank-ordered shards.")
+                if self.gather_impl == "owner_broadcast" and not self._whole_param_owners():
+                    raise RuntimeError("param_gather_strategy='owner_broadcast' requires whole-parameter owner shards.")
+                h = self.library_transport().gather(self._gather_source_tensor(), self.full_buffer, self.tables,
+                                                    stream=stream, unit_key=self.unit_key, impl=self.gather_impl)
             else:
                 h = self.transport.gather(self._gather_source_tensor(), self.full_buffer, self.tables, stream=stream,
                                           unit_key=self.unit_key)
-            h.info.setdefault("materialization", "storage_resize")
+            h.info.setdefault("materialization", "persistent_slot" if self.full_persistent else "storage_resize")
         self.full_materialized = True
         self.pending_gather = h
         return h
+
+    def _whole_param_owners(self) -> bool:
+        return all(len(self.layout.owner_ranks(mp.fqn)) == 1 for mp in self.registry.params)
 
     def wait_all_gather(self, *, keep_deferred: bool = False) -> MatrixCollectiveHandle | None:
         h, self.pending_gather = self.pending_gather, None
@@ -307,14 +334,15 @@ class MatrixFlatBuffer:
         self.deferred_gather = None
         return plan
 
-    def clear_full_params(self) -> None:
+    def clear_full_params(self, *, keep_storage: bool = False) -> None:
         """Drop the unsharded storage (params must already point at local views)."""
         if self.pending_gather is not None:
             self.wait_all_gather()
         if self.deferred_gather is not None:
             self.deferred_gather = None
             raise RuntimeError("rows of the all-gather were left to a fused GEMM that never ran")
-        self._shrink_full()
+        if not keep_storage:
+            self._shrink_full()
         self.full_materialized = self.full_aliases_shard
 
     # ------------------------------------------------------------------ gradients
@@ -393,8 +421,12 @@ class MatrixFlatBuffer:
             return 1.0
         return 1.0 / float(self.world_size * self.replicate_world_size)
 
-    def start_reduce_grad_bucket_to_local_shard(self, *, stream=None) -> MatrixCollectiveHandle:
-        """Reduce the bucket over the shard group (then the replicate group) into ``local_grad_shard``."""
+    def start_reduce_grad_bucket_to_local_shard(self, *, stream=None, strategy: str = "bucket_reduce_scatter",
+                                                ) -> MatrixCollectiveHandle:
+        """Reduce the bucket over the shard group (then the replicate group) into ``local_grad_shard``.
+
+        ``strategy``: ``bucket_reduce_scatter`` (the transport's own reduction), ``flat`` (one library
+        reduce-scatter over the flat gradient) or ``per_param`` (one library reduce-scatter per parameter)."""
         out = self._ensure_local_grad_shard()
         src = self.bucket.ensure()
         scale = self.grad_scale()
@@ -411,6 +443,7 @@ class MatrixFlatBuffer:
             self.local_grad_valid = True
             return h
         if self.fused_reduce_update is not None and self.replicate_world_size == 1 \
+                and strategy == "bucket_reduce_scatter" and self.reduce_impl is None \
                 and not self.accumulate_into_local_grad and hasattr(self.transport, "reduce_update"):
             update = self.fused_reduce_update()
             if update is not None:
@@ -419,7 +452,9 @@ class MatrixFlatBuffer:
                 self.fused_update_applied = True
                 self.pending_reduce = h
                 return h
-        needs_cast = out.dtype != src.dtype and not getattr(self.transport, "accumulates_fp32", False)
+        library = (strategy in ("flat", "per_param") or self.reduce_impl is not None) and self.world_size > 1
+        reducer = self.library_transport() if library else self.transport
+        needs_cast = out.dtype != src.dtype and not getattr(reducer, "accumulates_fp32", False)
         accumulate = self.accumulate_into_local_grad
         self.accumulate_into_local_grad = False
         if accumulate and out.dtype != self.shard_dtype:
@@ -430,7 +465,19 @@ class MatrixFlatBuffer:
             target = out
         shard_scale = scale if self.replicate_world_size == 1 else 1.0 / float(self.world_size) \
             if self.divide_grads_by_world else 1.0
-        h = self.transport.reduce(src, target, self.tables, scale=shard_scale, stream=stream, unit_key=self.unit_key)
+        if library and strategy == "per_param":
+            from .collectives import reduce_scatter_per_param_async
+
+            h = reduce_scatter_per_param_async(src, target, self.tables,
+                                               [(mp.offset, mp.end) for mp in self.registry.params],
+                                               self.shard_group, scale=shard_scale, stream=stream)
+            h.info["backend"] = reducer.kind
+        elif library:
+            h = reducer.reduce(src, target, self.tables, scale=shard_scale, stream=stream, unit_key=self.unit_key,
+                               impl=self.reduce_impl or "padded")
+        else:
+            h = self.transport.reduce(src, target, self.tables, scale=shard_scale, stream=stream,
+                                      unit_key=self.unit_key)
         replicate_group, rworld = self.replicate_group, self.replicate_world_size
         divide = self.divide_grads_by_world
         prev_post = h._post

@@ -53,6 +53,12 @@ class FSDPLifecycleState(str, Enum):
 
 FSDPRuntimeState = FSDPLifecycleState
 
+# ``param_gather_strategy``: "auto" leaves the choice to the unit's transport; every other value names a
+# library collective (matrix_fsdp/runtime/flat_buffer.py:304-382) and is run as such.
+_GATHER_STRATEGIES = {"auto": None, "equal_all_gather": "equal_all_gather", "matrix_all_gather": "padded",
+                      "owner_broadcast": "owner_broadcast", "uneven_all_gather": "uneven_all_gather",
+                      "all_reduce": "all_reduce"}
+
 _ALLOWED = {
     (FSDPLifecycleState.SHARDED, FSDPLifecycleState.UNSHARDED),
     (FSDPLifecycleState.UNSHARDED, FSDPLifecycleState.FORWARD_RESHARDED),
@@ -67,6 +73,15 @@ def _in_backward() -> bool:
         return torch._C._current_graph_task_id() != -1
     except Exception:  # pragma: no cover
         return False
+
+
+class _SavedFullView:
+    """What autograd keeps instead of a view of an unsharded buffer (``use_saved_tensor_hooks``)."""
+
+    __slots__ = ("unit", "offset", "size", "stride", "requires_grad")
+
+    def __init__(self, unit, offset: int, size: tuple, stride: tuple, requires_grad: bool) -> None:
+        self.unit, self.offset, self.size, self.stride, self.requires_grad = unit, offset, size, stride, requires_grad
 
 
 class MatrixFSDPNoSync:
@@ -119,6 +134,11 @@ class MatrixFSDPParamGroup:
                              f"expected one of {sorted(valid_reduce)}.")
         if runtime_layout_policy not in ("auto", "matrix_shard", "segment_runtime", "flat_reorder"):
             raise ValueError(f"Unknown runtime_layout_policy={runtime_layout_policy!r}.")
+        if param_gather_strategy not in _GATHER_STRATEGIES:
+            raise ValueError(f"param_gather_strategy must be one of {sorted(_GATHER_STRATEGIES)}, "
+                             f"got {param_gather_strategy!r}.")
+        if matrix_collective_backend not in ("torch", "owner_broadcast", "custom"):
+            raise ValueError("matrix_collective_backend must be 'torch', 'owner_broadcast', or 'custom'.")
         self.module = module
         self.mesh = mesh
         self.groups: ResolvedGroups = resolve_groups(mesh, dp_shard_mesh_dim, dp_replicate_mesh_dim,
@@ -169,6 +189,9 @@ class MatrixFSDPParamGroup:
         self._backward_callback_queued = False
         self._hook_handles: list = []
         self._initialized = False
+        self._saved_hooks_ctx = None
+        self._saved_view_count = 0
+        self._zero_copy_grads: dict[str, torch.Tensor] = {}
         self.planner_result: PlannerResult | None = None
         self.registry: ManagedParamRegistry | None = None
         self.flat_buffer: MatrixFlatBuffer | None = None
@@ -221,14 +244,21 @@ class MatrixFSDPParamGroup:
         if device.type == "cuda":
             self.all_gather_stream = torch.cuda.Stream(device=device, priority=-1)
             self.reduce_scatter_stream = torch.cuda.Stream(device=device, priority=-1)
-        transport = self._transport_override or make_transport(self.groups.shard_group, self.world_size, device)
+        # matrix_collective_backend: "torch" = library collectives only, "custom" = the peer kernels or an
+        # error, "owner_broadcast" (default) = whatever the node offers
+        prefer = {"torch": "torch_dist", "custom": "peer"}.get(self.matrix_collective_backend)
+        if prefer == "peer" and (device.type != "cuda" or self.world_size <= 1):
+            prefer = None
+        transport = self._transport_override or make_transport(self.groups.shard_group, self.world_size, device,
+                                                               prefer=prefer)
         mp = self.mp_policy
         self.flat_buffer = MatrixFlatBuffer(
             registry, result.layout, rank=self.rank, world_size=self.world_size, transport=transport,
             replicate_group=self.groups.replicate_group, replicate_world_size=self.replicate_world_size,
             param_dtype=getattr(mp, "param_dtype", None), reduce_dtype=getattr(mp, "reduce_dtype", None),
             divide_grads_by_world=self.divide_grads_by_world, unit_key=self.name,
-            exclusive_full_buffer=not self.reshard_after_forward)
+            exclusive_full_buffer=not self.reshard_after_forward or not self.shrink_full_param_storage_after_backward,
+            gather_impl=_GATHER_STRATEGIES[self.param_gather_strategy], shard_group=self.groups.shard_group)
         self.flat_buffer.use_local_shards()
 
         ref = weakref.ref(self)
@@ -371,14 +401,17 @@ class MatrixFSDPParamGroup:
         self.wait_unshard(reason)
         return self
 
-    def reshard(self, reason: str = "manual", *, to: FSDPLifecycleState = FSDPLifecycleState.SHARDED) -> None:
+    def reshard(self, reason: str = "manual", *, to: FSDPLifecycleState = FSDPLifecycleState.SHARDED,
+                keep_storage: bool = False) -> None:
+        """``keep_storage``: leave the unsharded storage allocated (its contents are stale from here on and
+        the next unshard gathers into it again); trades memory for allocator traffic."""
         if self.state != FSDPLifecycleState.UNSHARDED and self.flat_buffer.pending_gather is None:
             if to == FSDPLifecycleState.SHARDED and self.state == FSDPLifecycleState.FORWARD_RESHARDED:
                 self._transition(to)
             return
         t0 = time.perf_counter()
         self.flat_buffer.use_local_shards()
-        self.flat_buffer.clear_full_params()
+        self.flat_buffer.clear_full_params(keep_storage=keep_storage)
         if self.state == FSDPLifecycleState.UNSHARDED:
             self._transition(to)
         if self.scheduler is not None:
@@ -422,6 +455,8 @@ class MatrixFSDPParamGroup:
         self._module_fuses_first_gemm = False
         if self.scheduler is not None:
             self.scheduler.on_pre_forward(self)
+        if self.use_saved_tensor_hooks and grad_mode:
+            self._enter_saved_tensor_hooks()
         mp = self.mp_policy
         if mp is not None and getattr(mp, "cast_forward_inputs", False) and mp.param_dtype is not None:
             args = cast_floating_tensors(args, mp.param_dtype)
@@ -430,7 +465,58 @@ class MatrixFSDPParamGroup:
         del t0
         return None
 
+    # ------------------------------------------------------------------ saved-tensor hooks
+    def _enter_saved_tensor_hooks(self) -> None:
+        """While the module's forward runs, tensors that autograd saves and that are views of this unit's
+        unsharded buffer are saved as (offset, size, stride) and rebuilt from the buffer as it is at
+        backward time.  The graph then keeps no reference to the forward's storage, so the buffer may be
+        a different allocation in backward (and the saved views never pin a released one).
+        Parity: ``matrix_fsdp/runtime/fsdp_unit.py:1325-1382``."""
+        if self._saved_hooks_ctx is not None:
+            return
+        ref = weakref.ref(self)
+
+        def pack(t: torch.Tensor):
+            unit = ref()
+            if unit is None or not isinstance(t, torch.Tensor) or t.device != unit.flat_buffer.device:
+                return t
+            full = unit.flat_buffer.full_buffer
+            if not unit.flat_buffer.full_materialized or t.dtype != full.dtype or t.numel() == 0:
+                return t
+            try:
+                same = t.untyped_storage().data_ptr() == full.untyped_storage().data_ptr()
+            except RuntimeError:
+                return t
+            if not same:
+                return t
+            unit._saved_view_count += 1
+            return _SavedFullView(ref, t.storage_offset() - full.storage_offset(), tuple(t.shape), tuple(t.stride()),
+                                  t.requires_grad)
+
+        def unpack(obj):
+            if not isinstance(obj, _SavedFullView):
+                return obj
+            unit = obj.unit()
+            if unit is None:
+                raise RuntimeError("the FSDP unit that owned a saved parameter view no longer exists")
+            if unit.state != FSDPLifecycleState.UNSHARDED:
+                raise RuntimeError(f"{unit.name}: a saved parameter view was needed while the unit is "
+                                   f"{unit.state.value}; its backward has to run between pre-backward unshard and reshard.")
+            full = unit.flat_buffer.full_buffer
+            return full.as_strided(obj.size, obj.stride, full.storage_offset() + obj.offset)
+
+        self._saved_hooks_ctx = torch.autograd.graph.saved_tensors_hooks(pack, unpack)
+        self._saved_hooks_ctx.__enter__()
+        self._record("enter_saved_tensor_hooks")
+
+    def _exit_saved_tensor_hooks(self) -> None:
+        ctx, self._saved_hooks_ctx = self._saved_hooks_ctx, None
+        if ctx is not None:
+            ctx.__exit__(None, None, None)
+            self._record("exit_saved_tensor_hooks", extra={"saved_views": self._saved_view_count})
+
     def _post_forward(self, module, args, output):
+        self._exit_saved_tensor_hooks()
         if _in_backward() and self._pre_backward_done and self.state == FSDPLifecycleState.UNSHARDED:
             self._record("post_forward_recompute_skip", recompute=True)
             return output
@@ -467,11 +553,32 @@ class MatrixFSDPParamGroup:
         self.wait_unshard("pre_backward")
         if self._wants_direct_grad_writes():
             self.flat_buffer.prepare_grad_bucket()
+        elif self.use_zero_copy_grad_bucket:
+            self._attach_zero_copy_grads()
         if self.scheduler is not None:
             self.scheduler.on_pre_backward(self)
 
     def _wants_direct_grad_writes(self) -> bool:
         return bool(getattr(self.module, "_mfsdp_direct_grad", False))
+
+    def _attach_zero_copy_grads(self) -> None:
+        """``use_zero_copy_grad_bucket``: give every parameter a ``.grad`` that is a view of the unit's
+        gradient bucket before autograd runs, so gradient accumulation writes the reduce-scatter input
+        in place and no copy-in happens afterwards.  Needs the bucket in the parameters' dtype; the views
+        start at zero unless gradients of earlier micro-batches are being accumulated.
+        Parity: ``matrix_fsdp/runtime/flat_buffer.py:447-486,1208-1230``."""
+        fb = self.flat_buffer
+        if fb.bucket.dtype != fb.param_dtype:
+            return                                   # reduce dtype differs: gradients have to be converted anyway
+        buf = fb.prepare_grad_bucket()
+        if not self.has_accumulated_grads:
+            buf.zero_()
+        self._zero_copy_grads = {}
+        for mp in self.registry:
+            view = buf[mp.offset:mp.end].view(mp.shape)
+            mp.param.grad = view
+            self._zero_copy_grads[mp.fqn] = view
+        self._record("attach_zero_copy_grads")
 
     def grad_target(self, fqn: str) -> tuple[torch.Tensor, bool]:
         """Bucket view an op may write this parameter's gradient into, and whether to accumulate."""
@@ -521,11 +628,19 @@ class MatrixFSDPParamGroup:
             return
         t0 = time.perf_counter()
         fb = self.flat_buffer
+        if self._zero_copy_grads:
+            for mp in self.registry:
+                view = self._zero_copy_grads.get(mp.fqn)
+                g = mp.param.grad
+                if view is not None and g is not None and g.data_ptr() == view.data_ptr():
+                    self._direct_written.add(mp.fqn)     # autograd accumulated into the bucket in place
+            self._zero_copy_grads = {}
         any_grad = bool(self._direct_written) or any(mp.param.grad is not None for mp in self.registry)
         how = None
         if any_grad or self.has_accumulated_grads:
             how = fb.collect_param_grads(accumulate=self.has_accumulated_grads, written_direct=self._direct_written)
-        self.reshard("reshard_after_backward", to=FSDPLifecycleState.SHARDED)
+        self.reshard("reshard_after_backward", to=FSDPLifecycleState.SHARDED,
+                     keep_storage=not self.shrink_full_param_storage_after_backward)
         self._grads_seen.clear()
         self._direct_written = set()
         self._pre_backward_done = False
@@ -548,7 +663,8 @@ class MatrixFSDPParamGroup:
             h = self._reduce_by_allreduce()
         else:
             with nvtx_range(f"mfsdp.reduce_scatter:{self.name}"):
-                h = self.flat_buffer.start_reduce_grad_bucket_to_local_shard(stream=self.reduce_scatter_stream)
+                h = self.flat_buffer.start_reduce_grad_bucket_to_local_shard(
+                    stream=self.reduce_scatter_stream, strategy=self.backward_reduce_strategy)
         self.has_accumulated_grads = False
         if getattr(h, "span", None) is not None:
             h.span.unit, h.span.reason = self.name, "post_backward"

@@ -83,10 +83,11 @@ class TorchDistTransport(LocalTransport):
             return None
         return self.workspace_cache.lease(tables.world_size * tables.max_shard, like.dtype, like.device)
 
-    def gather(self, shard, full, tables, *, stream=None, unit_key=None):
-        lease = self._workspace(tables, full) if self.gather_impl not in ("owner_broadcast", "broadcast") else None
-        h = all_gatherv_rank_segments_1d_into_async(shard, full, tables, self.group, stream=stream,
-                                                    impl=self.gather_impl,
+    def gather(self, shard, full, tables, *, stream=None, unit_key=None, impl: str | None = None):
+        impl = impl or self.gather_impl
+        lease = self._workspace(tables, full) if impl not in ("owner_broadcast", "broadcast", "all_reduce",
+                                                              "all_reduce_gather") else None
+        h = all_gatherv_rank_segments_1d_into_async(shard, full, tables, self.group, stream=stream, impl=impl,
                                                     workspace=lease.tensor if lease else None)
         h.info["backend"] = self.kind
         if lease is not None:
@@ -96,10 +97,11 @@ class TorchDistTransport(LocalTransport):
             h._post = (lambda: (prev() if prev else None, lease.release()))
         return h
 
-    def reduce(self, full_grad, out_shard, tables, *, scale=None, stream=None, unit_key=None):
-        lease = self._workspace(tables, full_grad) if self.reduce_impl not in ("owner_reduce", "reduce") else None
+    def reduce(self, full_grad, out_shard, tables, *, scale=None, stream=None, unit_key=None, impl: str | None = None):
+        impl = impl or self.reduce_impl
+        lease = self._workspace(tables, full_grad) if impl not in ("owner_reduce", "reduce") else None
         h = reduce_scatterv_owner_rank_chunks_1d_async(full_grad, out_shard, tables, self.group, scale=scale,
-                                                       stream=stream, impl=self.reduce_impl,
+                                                       stream=stream, impl=impl,
                                                        workspace=lease.tensor if lease else None)
         h.info["backend"] = self.kind
         if lease is not None:
