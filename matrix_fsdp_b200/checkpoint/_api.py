@@ -172,20 +172,85 @@ def get_optimizer_state_dict(model: nn.Module, optimizers, *, options=None) -> d
     out: dict[str, Any] = {}
     for i, opt in enumerate(opts):
         if o.full_state_dict:
-            out[f"optimizer_{i}"] = _full_optimizer_state(model, opt, o.cpu_offload)
+            out[str(i)] = _full_optimizer_state(model, opt, o.cpu_offload)
         else:
-            out[f"optimizer_{i}"] = {name: c.state_dict() for name, c in iter_optimizer_components(opt)}
-    return out if len(opts) > 1 else out["optimizer_0"]
+            out[str(i)] = {name: c.state_dict() for name, c in iter_optimizer_components(opt)}
+    return out if len(opts) > 1 else out["0"]      # several optimizers: keyed "0", "1", … like the reference
+
+
+def _is_full_form(component_sd) -> bool:
+    """The gathered form keys ``state`` by parameter name; a local ``state_dict()`` keys it by integer."""
+    state = component_sd.get("state", {})
+    return bool(state) and all(isinstance(k, str) for k in state)
+
+
+def _load_full_optimizer_component(model: nn.Module, opt, component_sd) -> None:
+    """Scatter gathered (full-size) optimizer tensors back: every rank keeps the piece of each tensor that
+    matches the piece of the parameter it holds."""
+    units = collect_param_groups(model)
+    owner = {id(mp.param): (u, mp) for u in units for mp in u.registry}
+    by_name = dict(model.named_parameters(remove_duplicate=False))
+    with torch.no_grad():
+        for name, entry in component_sd["state"].items():
+            p = by_name.get(name)
+            if p is None:
+                raise KeyError(f"optimizer state names unknown parameter {name!r}")
+            hit = owner.get(id(p))
+            piece = hit[0].flat_buffer.pieces.get(hit[1].fqn) if hit is not None else None
+            if hit is not None and piece is None:
+                continue                                  # nothing of this parameter lives here
+            if not any(p is q for g in opt.param_groups for q in g["params"]):
+                continue                                  # another component's parameter
+            st = opt.state[p]
+            for k, v in entry.items():
+                if not torch.is_tensor(v) or v.dim() == 0:
+                    cur = st.get(k)
+                    if torch.is_tensor(cur) and cur.numel() == 1:
+                        cur.fill_(float(v))
+                    else:
+                        st[k] = torch.tensor(float(v)) if k == "step" else v
+                    continue
+                if hit is None:
+                    st[k] = v.detach().clone().to(p.device)
+                    continue
+                u, mp = hit
+                part = v.reshape(-1)[piece.param_start:piece.param_start + piece.numel].to(u.flat_buffer.device)
+                cur = st.get(k)
+                if torch.is_tensor(cur) and cur.numel() == part.numel():
+                    cur.copy_(part.view(cur.shape).to(cur.dtype))
+                else:
+                    st[k] = part.view(piece.shape).clone()
+        for g, sg in zip(opt.param_groups, component_sd.get("param_groups", [])):
+            for k, v in sg.items():
+                if k != "params":
+                    g[k] = v
+    unit_states = getattr(opt, "_unit_states", None)
+    if unit_states:                                       # flat optimizers keep one step counter per unit
+        for us in unit_states.values():
+            steps = [float(opt.state[mp.param]["step"]) for mp in us.unit.registry
+                     if mp.param in opt.state and "step" in opt.state[mp.param]]
+            if steps:
+                us.step = int(max(steps))
 
 
 def set_optimizer_state_dict(model: nn.Module, optimizers, optim_state_dict, *, options=None) -> None:
+    """Inverse of :func:`get_optimizer_state_dict` for both of its forms: the local one goes through
+    ``load_state_dict``, the gathered one (``options.full_state_dict`` or state keyed by parameter names)
+    is scattered onto the shards."""
+    o = _opts(options)
     opts = optimizers if isinstance(optimizers, (list, tuple)) else [optimizers]
     for i, opt in enumerate(opts):
-        sd = optim_state_dict[f"optimizer_{i}"] if len(opts) > 1 else optim_state_dict
-        for name, o in iter_optimizer_components(opt):
+        if len(opts) > 1:
+            sd = optim_state_dict[str(i)] if str(i) in optim_state_dict else optim_state_dict[f"optimizer_{i}"]
+        else:
+            sd = optim_state_dict
+        for name, comp in iter_optimizer_components(opt):
             if name not in sd:
                 raise ValueError(f"missing component {name!r} in optimizer state dict")
-            o.load_state_dict(sd[name])
+            if o.full_state_dict or _is_full_form(sd[name]):
+                _load_full_optimizer_component(model, comp, sd[name])
+            else:
+                comp.load_state_dict(sd[name])
 
 
 def get_state_dict(model: nn.Module, optimizers, *, options=None):
@@ -203,7 +268,13 @@ matrix_set_state_dict = set_state_dict
 
 def patch_model_state_dict(model: nn.Module, *, options=None) -> None:
     model.state_dict = functools.partial(get_model_state_dict, model, options=options)  # type: ignore[assignment]
-    model.load_state_dict = lambda sd, **kw: set_model_state_dict(model, sd, options=options)  # type: ignore[assignment]
+    base = _opts(options)
+
+    def load(sd, strict: bool = True, **kw):
+        set_model_state_dict(model, sd, options=MatrixStateDictOptions(base.full_state_dict, base.cpu_offload,
+                                                                       bool(strict) and base.strict))
+
+    model.load_state_dict = load  # type: ignore[assignment]
 
 
 def patch_optimizer_state_dict(model: nn.Module, *, optimizers, options=None) -> None:

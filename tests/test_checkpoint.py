@@ -105,7 +105,7 @@ def test_mixed_optimizer_components():
         om = meta["optimizer"]
         assert om["kind"] == "mixed_muon_adamw" and set(om["components"]) == {"muon", "adamw"}
         entry = next(iter(om["components"]["muon"]["state"].values()))
-        assert "momentum_buffer" in entry["tensors"] and "matrix_state" in entry["tensors"]["momentum_buffer"]
+        assert entry["entries"]["momentum_buffer"]["kind"] == "tensor" and "matrix_state" in entry["entries"]["momentum_buffer"]
         single = configure_optimizer(model, "adamw", lr=0.01)
         with pytest.raises(ValueError, match="unknown component"):
             load_matrix_dcp(model, d, optimizer=single, no_dist=True)

@@ -264,3 +264,65 @@ def _unused_unit_body(rank, world, opt_kind):
 @pytest.mark.parametrize("opt_kind", ["adamw", "sgd"])
 def test_unit_without_backward_is_skipped_by_the_flat_optimizer(opt_kind):
     run_ranks(_unused_unit_body, 2, opt_kind)
+
+
+# ----------------------------------------------------------------------------- full optimizer state round trip
+def _full_opt_roundtrip_body(rank, world, kind):
+    from matrix_fsdp_b200 import get_optimizer_state_dict, set_optimizer_state_dict
+    from matrix_fsdp_b200.api import fully_shard, reset_shared_owner_planners
+    from matrix_fsdp_b200.checkpoint import MatrixStateDictOptions
+    from matrix_fsdp_b200.optim import configure_optimizer
+
+    def build(seed):
+        reset_shared_owner_planners()
+        torch.manual_seed(seed)
+        m = nn.Sequential(nn.Linear(8, 12), nn.Tanh(), nn.Linear(12, 8, bias=False))
+        fully_shard(m, optimizer_policy="mixed_muon_adamw" if kind == "mixed_muon_adamw" else None)
+        return m, configure_optimizer(m, kind, lr=1e-2)
+
+    model, opt = build(0)
+    g = torch.Generator().manual_seed(9 + rank)
+    for _ in range(2):
+        model(torch.randn(4, 8, generator=g)).pow(2).mean().backward()
+        opt.step()
+        opt.zero_grad()
+    full_opts = MatrixStateDictOptions(full_state_dict=True)
+    full = get_optimizer_state_dict(model, opt, options=full_opts)
+    other, opt2 = build(0)
+    set_optimizer_state_dict(other, opt2, full, options=full_opts)          # used to raise KeyError('params')
+    again = get_optimizer_state_dict(other, opt2, options=full_opts)
+    assert set(again) == set(full)
+    for comp in full:
+        assert set(again[comp]["state"]) == set(full[comp]["state"]), comp
+        for name, entry in full[comp]["state"].items():
+            for k, v in entry.items():
+                w = again[comp]["state"][name][k]
+                assert (torch.equal(v, w) if torch.is_tensor(v) else float(v) == float(w)), (comp, name, k)
+    # the name-keyed form is recognised without the option, too
+    other3, opt3 = build(0)
+    set_optimizer_state_dict(other3, opt3, full)
+    # several optimizers are keyed "0", "1", ...
+    multi = get_optimizer_state_dict(model, [opt, opt], options=full_opts)
+    assert set(multi) == {"0", "1"}
+
+
+@pytest.mark.parametrize("kind", ["adamw", "mixed_muon_adamw"])
+def test_full_optimizer_state_dict_loads_back(kind):
+    run_ranks(_full_opt_roundtrip_body, 2, kind)
+
+
+def test_patched_load_state_dict_forwards_strict():
+    from matrix_fsdp_b200 import fully_shard, patch_model_state_dict
+    from matrix_fsdp_b200.api import reset_shared_owner_planners
+    from matrix_fsdp_b200.checkpoint import MatrixStateDictOptions
+
+    reset_shared_owner_planners()
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(4, 4), nn.Linear(4, 2))
+    fully_shard(model)
+    patch_model_state_dict(model, options=MatrixStateDictOptions(full_state_dict=True))
+    sd = model.state_dict()
+    partial = {k: v for k, v in sd.items() if not k.startswith("1.")}
+    with pytest.raises(KeyError):
+        model.load_state_dict(partial)
+    model.load_state_dict(partial, strict=False)
