@@ -348,6 +348,7 @@ def write_timeline(path: str, device_step, sync, rank: int, world: int, device, 
     for i in range(n):
         device_step(i + 1)
     ev1.record()
+    torch.cuda.synchronize()
     spans = TL.resolve()
     step_ms = ev0.elapsed_time(ev1) / n
     TL.enable(False)

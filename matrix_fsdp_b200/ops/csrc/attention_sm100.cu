@@ -23,7 +23,8 @@
 namespace mfsdp {
 
 int make_tmap_bf16_2d(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld,
-                      int box_rows, int box_cols);   // defined in gemm_sm100.cu
+                      int box_rows, int box_cols);   // defined in gemm_sm100.cu (cached)
+void ensure_context_on_this_thread();                // likewise
 
 constexpr int kHd = 128;            // head dim
 constexpr int kBq = 128;            // queries per CTA
@@ -647,7 +648,7 @@ using namespace mfsdp;
 MFSDP_API int mfsdp_attention_fwd(const void* qkv, void* out, float* lse, int B, int S, int nH, long long ld_qkv,
                                   long long ld_out, float softmax_scale, int* status, cudaStream_t st) {
   if (B <= 0 || S <= 0 || nH <= 0 || (ld_qkv % 8) || (ld_out % 8)) return -2;
-  cudaFree(nullptr);   // tensor-map encoding needs a current context on this thread
+  ensure_context_on_this_thread();
   CUtensorMap map;
   int rc = make_tmap_bf16_2d(&map, qkv, (long long)B * S, 3LL * nH * kHd, ld_qkv, 128, 64);
   if (rc) return rc;
@@ -672,7 +673,7 @@ MFSDP_API int mfsdp_attention_bwd(const void* dout, const void* qkv, const void*
                                   float* scratch, int B, int S, int nH, long long ld_qkv, long long ld_o,
                                   long long ld_dqkv, float softmax_scale, int* status, cudaStream_t st) {
   if (B <= 0 || S <= 0 || nH <= 0 || (ld_qkv % 8) || (ld_o % 8) || (ld_dqkv % 8) || !scratch) return -2;
-  cudaFree(nullptr);
+  ensure_context_on_this_thread();
   CUtensorMap map_qkv, map_do;
   int rc = make_tmap_bf16_2d(&map_qkv, qkv, (long long)B * S, 3LL * nH * kHd, ld_qkv, kBt, 64);
   if (rc) return rc;

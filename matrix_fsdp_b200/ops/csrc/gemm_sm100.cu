@@ -393,11 +393,60 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// rows x cols row-major bf16 tensor (row stride `ld` elements); box = box_rows x 64 cols.
+// Encoding a tensor map is a driver call; a training step asks for the same few hundred
+// (base, shape, stride, box) combinations over and over (persistent parameter, gradient and
+// activation buffers), so encoded maps are kept in a small per-process table.
+struct TmapKey {
+  const void* base;
+  long long rows, cols, ld;
+  int box_rows, box_cols;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows &&
+           box_cols == o.box_cols;
+  }
+};
+struct TmapSlot {
+  TmapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int kTmapSlots = 4096;   // direct-mapped; a collision simply re-encodes
+static TmapSlot g_tmap_cache[kTmapSlots];
+static std::mutex g_tmap_mutex;
+
+static inline size_t tmap_hash(const TmapKey& k) {
+  size_t h = reinterpret_cast<size_t>(k.base) >> 4;
+  h ^= (size_t)k.rows * 0x9E3779B97F4A7C15ull;
+  h ^= ((size_t)k.cols << 21) ^ ((size_t)k.ld << 7) ^ ((size_t)k.box_rows << 3) ^ (size_t)k.box_cols;
+  h ^= h >> 29;
+  return h % kTmapSlots;
+}
+
+// The driver needs a current context on the calling thread before it can encode a map; a thread that
+// has not made a runtime call yet (an autograd worker) has none until a runtime call binds it.
+void ensure_context_on_this_thread() {
+  thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
+// rows x cols row-major bf16 tensor (row stride `ld` elements); box = box_rows x box_cols.
 int make_tmap_bf16_2d(CUtensorMap* map, const void* base, long long rows, long long cols,
                       long long ld, int box_rows, int box_cols) {
+  const TmapKey key{base, rows, cols, ld, box_rows, box_cols};
+  TmapSlot& slot = g_tmap_cache[tmap_hash(key)];
+  {
+    std::lock_guard<std::mutex> lock(g_tmap_mutex);
+    if (slot.used && slot.key == key) {
+      *map = slot.map;
+      return 0;
+    }
+  }
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
+  ensure_context_on_this_thread();
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
   cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
@@ -405,7 +454,12 @@ int make_tmap_bf16_2d(CUtensorMap* map, const void* base, long long rows, long l
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : (int)r;
+  if (r != CUDA_SUCCESS) return (int)r;
+  std::lock_guard<std::mutex> lock(g_tmap_mutex);
+  slot.key = key;
+  slot.map = *map;
+  slot.used = true;
+  return 0;
 }
 
 template <int BN, bool A_MN, bool B_MN, bool GATHER = false>
@@ -445,9 +499,7 @@ MFSDP_API int mfsdp_gemm_bf16(const void* A, const void* B, void* D, const void*
                               int num_groups, long long k_total, int* status, int num_sms,
                               int force_bn, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K < 0) return -2;
-  // Tensor-map encoding is a driver call and needs a current context; a thread that has not yet
-  // made a runtime call (e.g. an autograd worker on device 0) has none until this binds it.
-  cudaFree(nullptr);
+  ensure_context_on_this_thread();
   if ((lda % 8) || (ldb % 8) || (ldd % 8)) return -2;
   if (((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)D & 15)) return -2;
   if (group_mode == 2 && (!a_mn_major || !b_mn_major || (M % BM) != 0)) return -2;
@@ -529,7 +581,7 @@ MFSDP_API int mfsdp_gemm_bf16_ag(const void* A, const void* B, void* D, const vo
                                  const int* ag_need, int bn, unsigned long long budget_ns, int* status,
                                  int num_sms, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || (bn != 128 && bn != 256) || njobs < 0) return -2;
-  cudaFree(nullptr);
+  ensure_context_on_this_thread();
   if ((lda % 8) || (K % 8) || (ldd % 8)) return -2;
   if (((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)D & 15)) return -2;
   GemmArgs args{};

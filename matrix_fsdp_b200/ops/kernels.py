@@ -136,8 +136,10 @@ def gemm_ag(a: torch.Tensor, b: torch.Tensor, plan, *, out: torch.Tensor | None 
 
 
 def grouped_gemm_m(a: torch.Tensor, b: torch.Tensor, tile_group: torch.Tensor, *,
-                   b_mn_major: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
-    """M-grouped GEMM: rows of ``a`` come in 128-row tiles, tile ``t`` uses ``b[tile_group[t]]``.
+                   b_mn_major: bool = False, out: torch.Tensor | None = None, cin: torch.Tensor | None = None,
+                   alpha: float = 1.0, beta: float = 0.0) -> torch.Tensor:
+    """M-grouped GEMM: rows of ``a`` come in 128-row tiles, tile ``t`` uses ``b[tile_group[t]]``;
+    ``out = alpha * a·b[g]ᵀ + beta * cin`` (``cin``: ``[Mtot, N]``).
 
     ``a``: ``[Mtot, K]``; ``b``: ``[G, N, K]`` (or ``[G, K, N]`` when ``b_mn_major``); tiles whose
     group id is negative are skipped (their output rows are left untouched).
@@ -157,9 +159,12 @@ def grouped_gemm_m(a: torch.Tensor, b: torch.Tensor, tile_group: torch.Tensor, *
     assert tile_group.numel() >= (Mtot + 127) // 128
     if out is None:
         out = torch.empty((Mtot, N), dtype=torch.bfloat16, device=a.device)
+    if cin is not None:
+        assert cin.shape == (Mtot, N) and cin.stride(1) == 1 and cin.dtype == torch.bfloat16
     rc = _L().mfsdp_gemm_bf16(
-        a.data_ptr(), b.data_ptr(), out.data_ptr(), None, Mtot, N, K, a.stride(0), ldb,
-        out.stride(0), 0, 0, int(b_mn_major), 1.0, 0.0, 1, tile_group.data_ptr(), None, G, 0,
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), cin.data_ptr() if cin is not None else None, Mtot, N, K,
+        a.stride(0), ldb, out.stride(0), cin.stride(0) if cin is not None else 0, 0, int(b_mn_major),
+        float(alpha), float(beta), 1, tile_group.data_ptr(), None, G, 0,
         status_word(a.device).data_ptr(), sm_count(a.device), 0, _stream())
     _lib.check(rc, "mfsdp_gemm_bf16[m-grouped]")
     return out

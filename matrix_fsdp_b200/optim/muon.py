@@ -25,6 +25,7 @@ from torch.optim import Optimizer
 DEFAULT_NS_COEFFICIENTS = (3.4445, -4.7750, 2.0315)
 DEFAULT_MUON_ADJUST_LR_FN = "match_rms_adamw"
 EPS = 1e-7
+MAX_BATCH_ELEMENTS = 1 << 28      # elements of one stacked Newton-Schulz operand (512 MB of bf16)
 
 
 def adjust_lr(lr: float, adjust_lr_fn: str | None, shape) -> float:
@@ -80,6 +81,62 @@ def newton_schulz_sm100(x: torch.Tensor, coefficients=DEFAULT_NS_COEFFICIENTS, s
     return x
 
 
+_TILE_GROUPS: dict[tuple, torch.Tensor] = {}
+
+
+def _tile_groups(groups: int, rows_per_group: int, device) -> torch.Tensor:
+    """int32 group id of every 128-row tile of ``groups`` stacked matrices of ``rows_per_group`` rows."""
+    key = (groups, rows_per_group, str(device))
+    t = _TILE_GROUPS.get(key)
+    if t is None:
+        t = torch.arange(groups, dtype=torch.int32, device=device).repeat_interleave(rows_per_group // 128)
+        _TILE_GROUPS[key] = t
+    return t
+
+
+def newton_schulz_sm100_batched(x: torch.Tensor, coefficients=DEFAULT_NS_COEFFICIENTS, steps: int = 5) -> torch.Tensor:
+    """Newton-Schulz on ``G`` normalised bf16 matrices of one shape, stacked as ``[G, rows, cols]``: every
+    product of an iteration is ONE grouped tcgen05 launch over all matrices (three launches per iteration
+    whatever G is), so the tiles of several matrices fill the 148 SMs' waves together — a single
+    4096 x 4096 product is 3.5 waves of 128 x 256 tiles, i.e. the last wave runs half empty.
+
+    Needs ``min(rows, cols)`` and, for tall matrices, ``rows`` to be multiples of 128 (tiles must not
+    straddle two matrices); callers fall back to :func:`newton_schulz_sm100` otherwise.
+    """
+    from ..ops import kernels as K
+
+    a, b, c = coefficients
+    G, rows, cols = x.shape
+    tall = rows > cols
+    n = cols if tall else rows
+    dev = x.device
+    gram = torch.empty((G * n, n), dtype=torch.bfloat16, device=dev)
+    poly = torch.empty_like(gram)
+    x2 = x.reshape(G * rows, cols)
+    nxt = torch.empty_like(x2)
+    tg_n = _tile_groups(G, n, dev)
+    if tall:
+        offsets = torch.arange(G + 1, dtype=torch.int32, device=dev) * rows
+        tg_rows = _tile_groups(G, rows, dev)
+    for _ in range(steps):
+        if tall:
+            K.grouped_gemm_k(x2, x2, offsets, G, out=gram.view(G, n, n))                                  # XᵀX
+            K.grouped_gemm_m(gram, gram.view(G, n, n), tg_n, out=poly, cin=gram, alpha=c, beta=b)        # bA + cAA
+            K.grouped_gemm_m(x2, poly.view(G, n, n), tg_rows, out=nxt, cin=x2, alpha=1.0, beta=a)        # aX + X B
+        else:
+            K.grouped_gemm_m(x2, x2.view(G, n, cols), tg_n, out=gram)                                     # XXᵀ
+            K.grouped_gemm_m(gram, gram.view(G, n, n), tg_n, out=poly, cin=gram, alpha=c, beta=b)
+            K.grouped_gemm_m(poly, x2.view(G, n, cols), tg_n, b_mn_major=True, out=nxt, cin=x2, alpha=1.0, beta=a)
+        x2, nxt = nxt, x2
+    return x2.view(G, rows, cols)
+
+
+def can_batch_newton_schulz(shape) -> bool:
+    rows, cols = int(shape[0]), int(shape[1])
+    n = min(rows, cols)
+    return n % 128 == 0 and (rows <= cols or rows % 128 == 0) and cols % 8 == 0
+
+
 def _use_kernels(t: torch.Tensor) -> bool:
     if t.device.type != "cuda":
         return False
@@ -116,13 +173,60 @@ class MatrixMuon(Optimizer):
             with torch.enable_grad():
                 loss = closure()
         for group in self.param_groups:
+            by_shape: dict[tuple, list] = {}
             for p in group["params"]:
                 if (p.grad is None and getattr(p, "_grad_override", None) is None) or p.numel() == 0:
                     continue
                 if p.ndim != 2:
                     raise ValueError("Muon only supports 2D parameters; route the rest to AdamW.")
-                self._step_one(p, group)
+                if self._kernel_path(p) and can_batch_newton_schulz(p.shape):
+                    by_shape.setdefault(tuple(p.shape), []).append(p)
+                else:
+                    self._step_one(p, group)
+            # matrices of one shape go through Newton-Schulz together (one grouped launch per product)
+            for shape, ps in by_shape.items():
+                per_chunk = max(1, MAX_BATCH_ELEMENTS // (shape[0] * shape[1]))
+                for i in range(0, len(ps), per_chunk):
+                    chunk = ps[i:i + per_chunk]
+                    if len(chunk) == 1:
+                        self._step_one(chunk[0], group)
+                    else:
+                        self._step_batched(chunk, group)
         return loss
+
+    def _grad_of(self, p):
+        g = getattr(p, "_grad_override", None)   # a gradient kept in another dtype (expert-parallel slices)
+        return p.grad if g is None else g
+
+    def _kernel_path(self, p) -> bool:
+        g = self._grad_of(p)
+        buf = self.state.get(p, {}).get("momentum_buffer")
+        return _use_kernels(p) and p.dtype == torch.float32 and (buf is None or buf.dtype == torch.float32) \
+            and g is not None and g.is_contiguous()
+
+    def _step_batched(self, ps: list, group: dict) -> None:
+        from ..ops import kernels as K
+
+        lr, wd, mu = float(group["lr"]), group["weight_decay"], group["momentum"]
+        rows, cols = ps[0].shape
+        dev = ps[0].device
+        u = torch.empty((len(ps), rows, cols), dtype=torch.bfloat16, device=dev)
+        ss = torch.zeros(len(ps), dtype=torch.float32, device=dev)
+        for i, p in enumerate(ps):
+            st = self.state[p]
+            if "momentum_buffer" not in st:
+                st["momentum_buffer"] = torch.zeros_like(p, dtype=torch.float32)
+            K.muon_momentum(st["momentum_buffer"].view(-1), self._grad_of(p).reshape(-1), u[i].view(-1), ss[i:i + 1],
+                            mu, float(self.grad_scale), group["nesterov"])
+            K.muon_normalize_(u[i].view(-1), ss[i:i + 1], group["eps"])
+        o = newton_schulz_sm100_batched(u, group["ns_coefficients"], group["ns_steps"])
+        alr = adjust_lr(lr, group["adjust_lr_fn"], (rows, cols))
+        for i, p in enumerate(ps):
+            lp = self._low_precision_of(p) if self._low_precision_of is not None else None
+            K.muon_apply_(p.data.view(-1), o[i].reshape(-1), rows, cols, False, lr, wd, alr,
+                          p_lp=lp.view(-1) if lp is not None and lp.dtype == torch.bfloat16 else None)
+            if lp is not None and lp.dtype != torch.bfloat16:
+                lp.copy_(p.data)
 
     def _step_one(self, p: torch.Tensor, group: dict) -> None:
         st = self.state[p]
@@ -132,9 +236,7 @@ class MatrixMuon(Optimizer):
         lr, wd, mu = float(group["lr"]), group["weight_decay"], group["momentum"]
         alr = adjust_lr(lr, group["adjust_lr_fn"], p.shape)
         lp = self._low_precision_of(p) if self._low_precision_of is not None else None
-        g = getattr(p, "_grad_override", None)   # a gradient kept in another dtype (expert-parallel slices)
-        if g is None:
-            g = p.grad
+        g = self._grad_of(p)
         if _use_kernels(p) and p.dtype == torch.float32 and buf.dtype == torch.float32 and g.is_contiguous():
             from ..ops import kernels as K
 

@@ -1,5 +1,11 @@
 """Pool of full-parameter (unsharded) buffers keyed by (device, dtype, numel).
 
+Used by units that run with ``use_saved_tensor_hooks=True``: their autograd graph holds no view
+of the unsharded buffer, so the buffer may be a different allocation at every unshard and is
+acquired here at unshard and released here at reshard (``MatrixFlatBuffer._materialize_full`` /
+``_shrink_full``).  Units without the hooks keep one tensor whose storage is resized instead,
+because views saved by autograd have to stay valid.
+
 A released buffer may still be read by kernels in flight, so release takes the CUDA event
 that marks the last use; the buffer returns to the free list only once that event has
 completed (checked lazily at the next acquire).  With the default

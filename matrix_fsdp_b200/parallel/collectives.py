@@ -111,19 +111,48 @@ class SegmentTables:
     equal_contiguous: bool = False
     rank_contiguous: bool = False
     signature: tuple = field(default=(), repr=False)
+    # Descriptor of how this layout is communicated (param_buffers.StaticParamBuffer for equal rank-ordered
+    # chunks, ElasticParamBuffer otherwise): the transports take their copy tables and workspace sizes from it.
+    param_buffer: object = field(default=None, repr=False, compare=False)
 
     @classmethod
     def build(cls, total_numel: int, rank_segments: Sequence[Sequence[LayoutSegment]], rank: int) -> "SegmentTables":
+        from .param_buffers import (ElasticParamBuffer, ElasticParamBufferLayout, StaticParamBuffer,
+                                    StaticParamBufferLayout)
+
         segs = tuple(tuple(s for s in rs if s.numel > 0) for rs in rank_segments)
         sizes = tuple(sum(s.numel for s in rs) for rs in segs)
         contiguous = rank_segments_are_rank_contiguous_chunks(segs)
         equal = contiguous and len(set(sizes)) == 1 and sizes[0] * len(sizes) == total_numel
         sig = (total_numel, tuple(tuple((s.global_start, s.global_end, s.local_start) for s in rs) for rs in segs))
-        return cls(int(total_numel), len(segs), int(rank), segs, sizes, max(sizes, default=0), equal, contiguous, sig)
+        if equal or len(segs) == 1:
+            desc = StaticParamBuffer(StaticParamBufferLayout(sizes, segs), int(total_numel))
+        else:
+            desc = ElasticParamBuffer(ElasticParamBufferLayout(sizes, segs), int(total_numel))
+        return cls(int(total_numel), len(segs), int(rank), segs, sizes, max(sizes, default=0), equal, contiguous, sig,
+                   desc)
 
     @property
     def my_segments(self) -> tuple[LayoutSegment, ...]:
         return self.rank_segments[self.rank]
+
+    def pull_rows(self) -> tuple[tuple[int, int, int, int], ...]:
+        """(owner rank, offset in the owner's shard, offset in the flat space, numel) of every run an
+        all-gather copies, adjacent runs merged: the elastic descriptor's communication plan, or one row
+        per rank for equal chunks."""
+        plan = getattr(self.param_buffer, "communication_plan", None)
+        if plan is not None:
+            return plan.peer_pull_table()
+        return tuple((r, s.local_start, s.global_start, s.numel) for r, rs in enumerate(self.rank_segments) for s in rs)
+
+    def staging_numel(self, transport_kind: str = "torch_dist") -> int:
+        """Elements of the rank-major staging buffer a library collective needs for this layout (0: none)."""
+        if self.param_buffer is None:
+            return 0 if self.equal_contiguous else self.world_size * self.max_shard
+        kw = {"can_direct_all_gather": self.equal_contiguous}
+        if hasattr(self.param_buffer, "communication_plan"):
+            kw["transport_kind"] = transport_kind
+        return self.param_buffer.workspace_plan(**kw).preferred_workspace_numel
 
 
 def validate_layout_signature(tables: SegmentTables, group) -> None:

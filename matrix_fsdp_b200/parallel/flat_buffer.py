@@ -140,6 +140,8 @@ class MatrixFlatBuffer:
         # ``full_persistent``: the transport handed out a persistent (symmetric, multicast-mapped) slot that
         # this unit shares with units it is never unsharded together with; nothing is resized then.
         self.full_persistent = False
+        self.full_pool = None
+        self._pooled: torch.Tensor | None = None
         if self.full_aliases_shard:
             self.full_buffer = self._gather_source_tensor()
         else:
@@ -231,16 +233,44 @@ class MatrixFlatBuffer:
     def _full_nbytes(self) -> int:
         return self.total_numel * self.full_buffer.element_size()
 
+    # ---- pooled mode: with saved-tensor hooks the autograd graph keeps no view of the unsharded buffer, so
+    # the buffer may be a different allocation every time; it then comes from a shared pool and goes back
+    # to it at reshard, reusable once the kernels that read it have finished (CUDA event).
+    def use_full_param_pool(self, pool) -> None:
+        if self.full_aliases_shard or self.full_persistent or self.full_materialized:
+            return
+        if self.full_pool is None:
+            self.full_buffer.untyped_storage().resize_(0)
+        self.full_pool = pool
+
     def _shrink_full(self) -> None:
         if self.full_aliases_shard:
             return
         if self.full_persistent:
             self.transport.release_full_buffer(self.unit_key)   # peers may refill the slot from here on
             return
+        if self.full_pool is not None:
+            if self._pooled is not None:
+                event = None
+                if self.device.type == "cuda":
+                    event = torch.cuda.Event()
+                    event.record(torch.cuda.current_stream(self.device))
+                self.full_pool.release(self._pooled, event)
+                self._pooled = None
+            return
         self.full_buffer.untyped_storage().resize_(0)
 
     def _materialize_full(self) -> None:
         if self.full_persistent:
+            return
+        if self.full_pool is not None:
+            if self._pooled is None:
+                self._pooled = self.full_pool.acquire(self.total_numel, self.param_dtype, self.device)
+                self.full_buffer = self._pooled
+                self._full_views = {mp.fqn: self.full_buffer[mp.offset:mp.end].view(mp.shape)
+                                    for mp in self.registry.params}
+                if _poison_enabled() and self.full_buffer.is_floating_point():
+                    self.full_buffer.fill_(float("nan"))
             return
         st = self.full_buffer.untyped_storage()
         if st.size() != self._full_nbytes():
@@ -255,6 +285,8 @@ class MatrixFlatBuffer:
             return 0
         if self.full_persistent:
             return self._full_nbytes() if self.full_materialized else 0
+        if self.full_pool is not None:
+            return self._full_nbytes() if self._pooled is not None else 0
         return self.full_buffer.untyped_storage().size()
 
     def full_slot_available(self) -> bool:

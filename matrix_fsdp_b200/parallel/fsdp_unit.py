@@ -260,6 +260,11 @@ class MatrixFSDPParamGroup:
             exclusive_full_buffer=not self.reshard_after_forward or not self.shrink_full_param_storage_after_backward,
             gather_impl=_GATHER_STRATEGIES[self.param_gather_strategy], shard_group=self.groups.shard_group)
         self.flat_buffer.use_local_shards()
+        if self.use_saved_tensor_hooks:
+            from .buffer_pool import global_full_param_buffer_pool
+
+            # saved views are re-created from the buffer of backward time, so the buffer can be pooled
+            self.flat_buffer.use_full_param_pool(global_full_param_buffer_pool())
 
         ref = weakref.ref(self)
         for mpm in registry:

@@ -261,8 +261,11 @@ class ElasticParamBuffer:
 
 
 def describe_unit_param_buffer(unit) -> StaticParamBuffer | ElasticParamBuffer:
-    """Descriptor matching a unit's layout: static for equal rank-ordered chunks, elastic otherwise."""
+    """The descriptor the unit's transports work from (built with its segment tables): static for equal
+    rank-ordered chunks, elastic otherwise."""
     fb = unit.flat_buffer
+    if getattr(fb.tables, "param_buffer", None) is not None:
+        return fb.tables.param_buffer
     if fb.tables.equal_contiguous or fb.world_size == 1:
         return StaticParamBuffer(StaticParamBufferLayout(fb.tables.shard_sizes, fb.tables.rank_segments), fb.total_numel)
     return ElasticParamBuffer(ElasticParamBufferLayout(fb.tables.shard_sizes, fb.tables.rank_segments), fb.total_numel)

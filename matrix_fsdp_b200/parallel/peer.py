@@ -510,11 +510,10 @@ class PeerTransport(LocalTransport):
         t = self._tables.get(key)
         if t is None:
             src, dst, ln = [], [], []
-            for r, segs in enumerate(tables.rank_segments):
-                for s in segs:
-                    src.append(shard_buf.peer_addr[r] + s.local_start * es)
-                    dst.append(s.global_start)
-                    ln.append(s.numel)
+            for r, local_off, global_off, numel in tables.pull_rows():    # merged runs of the layout's plan
+                src.append(shard_buf.peer_addr[r] + local_off * es)
+                dst.append(global_off)
+                ln.append(numel)
             t = {"src": torch.tensor(src, dtype=torch.int64, device=device),
                  "dst": torch.tensor(dst, dtype=torch.int64, device=device),
                  "len": torch.tensor(ln, dtype=torch.int64, device=device), "n": len(src), "max": max(ln, default=0)}

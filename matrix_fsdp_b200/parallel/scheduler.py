@@ -149,11 +149,13 @@ class MatrixFSDPScheduler:
         self.comm.all_gather_stream = first.all_gather_stream
         self.comm.reduce_scatter_stream = first.reduce_scatter_stream
         for u in self.units:
-            old = getattr(u, "scheduler", None)
             u.scheduler = self
             u.all_gather_stream = self.comm.all_gather_stream
             u.reduce_scatter_stream = self.comm.reduce_scatter_stream
-            del old
+            # units that take their unsharded buffer from a pool share this scheduler's one
+            fb = getattr(u, "flat_buffer", None)
+            if getattr(u, "use_saved_tensor_hooks", False) and hasattr(fb, "use_full_param_pool"):
+                fb.use_full_param_pool(self.comm.full_param_pool)
         if cfg.validate_unit_order:
             self.validate_unit_order()
         # measuring prefetch policies: exposed waits of this iteration / of the one before (whose CUDA

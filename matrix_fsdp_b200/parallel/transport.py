@@ -79,9 +79,10 @@ class TorchDistTransport(LocalTransport):
         self.workspace_cache = workspace_cache or CommWorkspaceCache(max_cached_per_key=1)
 
     def _workspace(self, tables: SegmentTables, like: torch.Tensor):
-        if tables.equal_contiguous:
+        numel = tables.staging_numel(self.kind)      # the layout's descriptor knows what staging it needs
+        if numel <= 0:
             return None
-        return self.workspace_cache.lease(tables.world_size * tables.max_shard, like.dtype, like.device)
+        return self.workspace_cache.lease(numel, like.dtype, like.device)
 
     def gather(self, shard, full, tables, *, stream=None, unit_key=None, impl: str | None = None):
         impl = impl or self.gather_impl

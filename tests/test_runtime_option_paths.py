@@ -219,3 +219,53 @@ def _policy_body(rank, world, policy):
 @pytest.mark.parametrize("policy", ["adaptive", "profile_guided"])
 def test_measuring_prefetch_policies_change_the_depth_from_measured_waits(policy):
     run_ranks(_policy_body, 2, policy)
+
+
+def _pooled_body(rank, world):
+    """With saved-tensor hooks the unsharded buffers come from the scheduler's pool and are reused."""
+    reset_shared_owner_planners()
+    torch.manual_seed(0)
+    blocks = [ViewSaver() for _ in range(3)]
+    model = nn.Sequential()
+    for i, b in enumerate(blocks):
+        model.add_module(str(i), nn.Sequential())
+    # three same-shaped units chained through a 6 -> 4 -> (pad) projection
+    class Chain(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.blocks = nn.ModuleList(blocks)
+            self.up = nn.Linear(4, 6)
+
+        def forward(self, x):
+            for b in self.blocks:
+                x = self.up(b(x))
+            return x
+
+    net, ref = Chain(), None
+    ref = copy.deepcopy(net)
+    for b in net.blocks:
+        matrix_fully_shard(b, use_saved_tensor_hooks=True)
+    fully_shard(net)
+    opt, ropt = configure_optimizer(net, "sgd", lr=0.05), torch.optim.SGD(ref.parameters(), lr=0.05)
+    g = torch.Generator().manual_seed(3 + rank)
+    for _ in range(3):
+        x = torch.randn(4, 6, generator=g)
+        net(x).pow(2).mean().backward()
+        ref(x).pow(2).mean().backward()
+        for p in ref.parameters():
+            dist.all_reduce(p.grad)
+            p.grad /= world
+        opt.step(), ropt.step()
+        opt.zero_grad(), ropt.zero_grad()
+    unit = net.blocks[0]._matrix_fsdp_param_group
+    pool = unit.scheduler.comm.full_param_pool
+    assert unit.flat_buffer.full_pool is pool
+    st = pool.stats
+    assert st.acquires >= 18 and st.reuses > 0 and st.allocations < st.acquires, st.as_dict()
+    assert unit.full_param_storage_nbytes() == 0
+    for (n, p), (_, q) in zip(_full(net).items(), ref.named_parameters()):
+        assert torch.allclose(p, q.detach(), atol=1e-6), n
+
+
+def test_saved_tensor_hooks_take_unsharded_buffers_from_the_pool():
+    run_ranks(_pooled_body, 2)
