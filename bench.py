@@ -319,18 +319,21 @@ def _transport_description(model) -> str:
 
 
 def _moe_drop_report(model, device, world: int) -> dict:
-    """Rows the expert-parallel dispatch could not place (0 on a dropless run), summed over ranks."""
+    """Rows the expert-parallel dispatch could not place (0 on a dropless run), summed over ranks and layers
+    for every step since the model was built."""
+    from matrix_fsdp_b200.parallel.expert_parallel import live_contexts
+
     lost = torch.zeros(1, dtype=torch.int64, device=device)
     routed = torch.zeros(1, dtype=torch.int64, device=device)
-    for layer in getattr(model, "layers", []):
-        ctx = getattr(layer, "_ep_ctx_last", None)
-        if ctx is not None and hasattr(ctx, "rows_lost_total"):
-            lost += int(ctx.rows_lost_total())
-            routed += int(ctx.rows_routed_total())
+    dropless = True
+    for ctx in live_contexts():
+        lost += ctx.rows_lost_total()
+        routed += ctx.rows_routed_total()
+        dropless = dropless and ctx.dropless
     if world > 1:
         dist.all_reduce(lost)
         dist.all_reduce(routed)
-    return {"rows_lost": int(lost.item()), "rows_routed": int(routed.item())}
+    return {"rows_lost": int(lost.item()), "rows_routed": int(routed.item()), "sized_for_worst_case": dropless}
 
 
 def write_timeline(path: str, device_step, sync, rank: int, world: int, device, bench_line: dict) -> dict:

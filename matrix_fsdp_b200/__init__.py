@@ -47,7 +47,7 @@ from .parallel.runtime_event import (CommBufferId, PlannerGroupId, RuntimeEvent,
 from .parallel.scheduler import (BackwardPrefetchTiming, MatrixFSDPScheduler, MatrixFSDPSchedulerConfig,
                                  PrefetchPolicy, PrefetchProfileResult)
 from .parallel.summary import (format_param_group_summary, format_runtime_events, summarize_param_groups,
-                               summarize_runtime_events)
+                               summarize_runtime_events, summarize_scheduler)
 from .parallel.unit_collection import collect_param_groups
 from .parallel.workspace_cache import CommWorkspaceCache, CommWorkspaceLease
 from .planning.auto_planner import (AutoPlannerReportRow, auto_group_plan, build_auto_planner_report,

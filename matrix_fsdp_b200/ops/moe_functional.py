@@ -96,6 +96,7 @@ class MoEFFNFunction(torch.autograd.Function):
         slot, counts = MK.assign_slots(idx, E)
         counts_all = ep.exchange_counts(counts)
         dest_base, group_offsets, group_rows, tile_group, stats = MK.plan(counts_all, ep.world, ep.rank, E, ep.cap_rows)
+        ep.note_plan(stats, T * top_k)
         route = MK.dispatch_push(x, idx, ep.recv_addrs, El, ep.cap_rows, slot=slot, dest_base=dest_base)
         MK.zero_pad(ep.recv, H, group_offsets, group_rows)
         ep.fence(1)

@@ -115,6 +115,22 @@ def end_wait(sp: CollectiveSpan | None) -> None:
     sp.wait_end.record(torch.cuda.current_stream())
 
 
+def try_resolve_span(sp: CollectiveSpan) -> bool:
+    """Fill ``device_ms`` / ``exposed_ms`` of one span without synchronising; False while its events are
+    still pending."""
+    if sp.device_ms is not None:
+        return True
+    if sp.start is None or sp.end is None or not sp.end.query():
+        return False
+    try:
+        sp.device_ms = sp.start.elapsed_time(sp.end)
+        if sp.wait_begin is not None and sp.wait_end is not None and sp.wait_end.query():
+            sp.exposed_ms = max(sp.wait_begin.elapsed_time(sp.wait_end), 0.0)
+    except RuntimeError:
+        return False
+    return True
+
+
 def resolve() -> list[CollectiveSpan]:
     """Synchronise and turn the recorded events into milliseconds relative to the origin."""
     if not _SPANS:

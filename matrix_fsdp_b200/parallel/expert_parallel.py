@@ -33,9 +33,16 @@ class ExpertParallelContext:
             raise ValueError(f"{n_experts} experts do not divide over {self.world} expert-parallel ranks")
         self.hidden, self.n_experts, self.top_k = hidden, n_experts, top_k
         self.experts_per_rank = n_experts // self.world
+        # Receive capacity.  ``capacity_factor`` <= 0 (or None) sizes for the worst case, every routed row of
+        # every rank landing here: nothing can ever be dropped.  A positive factor sizes for that multiple of
+        # the average load; rows beyond it are dropped on the owner, counted in ``lost_rows`` (never silently:
+        # ``rows_lost_total()`` is what benches and training loops report).
         rows = max_tokens * top_k
+        self.dropless = not capacity_factor or capacity_factor <= 0
         if self.world > 1:
-            rows = min(int(rows * capacity_factor), rows * self.world)
+            rows = rows * self.world if self.dropless else min(int(rows * capacity_factor), rows * self.world)
+        self.lost_rows = torch.zeros(1, dtype=torch.int64, device=device)
+        self.routed_rows = 0
         self.cap_rows = (rows + self.experts_per_rank * 128 + 127) // 128 * 128
         self.max_tokens = max_tokens
         self._epoch = {KIND_COUNTS: 0, KIND_PUSHED: 0, KIND_READY: 0}
@@ -88,8 +95,7 @@ class ExpertParallelContext:
             return
         self._epoch[kind] += 1
         stream = torch.cuda.current_stream(self.device)
-        self.peer.signal(self._flag_unit, kind, self._epoch[kind], stream)
-        self.peer.wait(self._flag_unit, kind, self._epoch[kind], stream)
+        self.peer.signal_wait(self._flag_unit, kind, self._epoch[kind], stream)
 
     def exchange_counts(self, counts: torch.Tensor) -> torch.Tensor:
         """All ranks learn every rank's per-expert counts; returns the local ``[W, E]`` table."""
@@ -98,6 +104,22 @@ class ExpertParallelContext:
         MK.push_counts(self.counts_addrs, self.world, self.rank, counts)
         self.fence(KIND_COUNTS)
         return self.counts_all
+
+    # ------------------------------------------------------------------ drop accounting
+    def note_plan(self, stats: torch.Tensor, routed: int) -> None:
+        """After every dispatch plan: ``stats[1]`` = rows this rank (as owner) could not place."""
+        self.lost_rows += stats[1:2].to(torch.int64)
+        self.routed_rows += int(routed)
+
+    def rows_lost_total(self) -> int:
+        return int(self.lost_rows.item())
+
+    def rows_routed_total(self) -> int:
+        return int(self.routed_rows)
+
+
+def live_contexts() -> list[ExpertParallelContext]:
+    return list(_CONTEXTS.values())
 
 
 def reset_contexts() -> None:

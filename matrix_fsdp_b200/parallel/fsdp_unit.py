@@ -324,6 +324,9 @@ class MatrixFSDPParamGroup:
             return
         dur = (time.perf_counter() - start) * 1e3 if start is not None else 0.0
         info = getattr(handle, "info", None) or {}
+        span = getattr(handle, "span", None)
+        if span is not None:
+            kw["extra"] = {**kw.get("extra", {}), "span": span}      # device-side times, resolved by the summaries
         snap = self.flat_buffer.memory_snapshot() if self.flat_buffer is not None else {}
         sched = self.scheduler
         self.runtime_events.append(RuntimeEvent(

@@ -145,3 +145,35 @@ def test_full_optimizer_state_dict_is_keyed_by_parameter_name():
     assert set(full2) == {"muon", "adamw"}
     assert "momentum_buffer" in full2["muon"]["state"]["0.0.weight"]
     assert "exp_avg" in full2["adamw"]["state"]["0.0.bias"]
+
+
+def test_event_summary_has_phase_collective_and_scheduler_tables():
+    import torch.nn as nn
+
+    from matrix_fsdp_b200 import (configure_optimizer, format_runtime_events, fully_shard, summarize_param_groups,
+                                  summarize_runtime_events, summarize_scheduler)
+    from matrix_fsdp_b200.api import reset_shared_owner_planners
+
+    reset_shared_owner_planners()
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Sequential(nn.Linear(6, 6), nn.Tanh()), nn.Sequential(nn.Linear(6, 3)))
+    for blk in model:
+        fully_shard(blk)
+    opt = configure_optimizer(model, "adamw", lr=1e-2)
+    for _ in range(2):
+        model(torch.randn(4, 6)).sum().backward()
+        opt.step()
+        opt.zero_grad()
+    s = summarize_runtime_events(model)
+    assert {"forward", "backward"} <= set(s["by_phase"])
+    assert s["by_phase"]["backward"]["collectives"] >= 2 and s["by_phase"]["forward"]["count"] > 0
+    coll = next(v for k, v in s["by_collective"].items() if k.startswith("reduce_scatter"))
+    assert {"issue_host_ms", "wait_host_ms", "device_ms", "exposed_ms", "prefetched", "max_bytes"} <= set(coll)
+    sched = summarize_scheduler(model)
+    assert sched["num_units"] == 2 and sched["forward_prefetch_depth"] == 1
+    assert sched["counters"]["iterations"] == 2 and "pool" in sched
+    text = format_runtime_events(model)
+    assert "by phase:" in text and "collectives:" in text
+    row = summarize_param_groups(model)[0]
+    assert row["full_buffer_mode"] in ("alias", "storage_resize") and "transport_detail" in row
+    assert len(row["communication"]) >= 20
