@@ -56,8 +56,10 @@ struct GemmArgs {
   const int* ag_bytes;                // [njobs] multiple of 16
   const int* ag_flag;                 // [njobs] B row-block (tile column) the job belongs to
   int ag_njobs;
-  unsigned* ag_flags;                 // [tiles_n] zero at launch
+  unsigned* ag_flags;                 // [2 * tiles_n] zero at launch: finished jobs per row-block, then claimed jobs
   const int* ag_need;                 // [tiles_n] jobs per row-block
+  const int* ag_first;                // [tiles_n] index of the first job of each row-block (jobs are sorted by block)
+  int ag_rotate;                      // tile columns are walked starting here (the local rank's rows come first)
   unsigned long long ag_budget_ns;
 };
 
@@ -93,7 +95,8 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, int tile) {
   const int first_m = gid * kGroupM;
   const int gsz = min(p.tiles_m - first_m, kGroupM);
   const int tm = first_m + (tile % per_group) % gsz;
-  const int tn = (tile % per_group) / gsz;
+  int tn = (tile % per_group) / gsz;
+  if (p.ag_rotate) tn = (tn + p.ag_rotate) % p.tiles_n;
   TileCoord c;
   c.skip = false;
   c.n0 = tn;  // scaled by the caller's BN
@@ -256,26 +259,46 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
       }
     }
   } else if (GATHER && warp >= 6) {
-    // ------------------------------------------------------------ gather warps (never wait on anything)
+    // ------------------------------------------------------------ gather warps
+    // Jobs are claimed, not assigned: a CTA first claims the jobs of the row-blocks its own tiles read (in
+    // the order it will read them), then whatever is left.  Every job is therefore executed by a CTA that
+    // is running, and a producer that waits for a row-block only ever waits for CTAs that are resident:
+    // the kernel makes progress with any number of co-resident CTAs, also when other streams hold SMs.
     const int gt = threadIdx.x - kGemmThreads;
-    for (int j = blockIdx.x; j < p.ag_njobs; j += gridDim.x) {
-      const uint4* src = reinterpret_cast<const uint4*>(p.ag_src[j]);
-      uint4* dst = reinterpret_cast<uint4*>(p.ag_dst[j]);
-      const int nvec = p.ag_bytes[j] >> 4;
-      int i = gt;
-      // 8 independent 16-byte peer loads in flight per thread to cover the NVLink latency
-      for (; i + 7 * kGatherThreads < nvec; i += 8 * kGatherThreads) {
-        uint4 v[8];
+    __shared__ int claimed_job;
+    unsigned* claims = p.ag_flags + p.tiles_n;
+    auto drain_block = [&](int b) {
+      const int need = p.ag_need[b];
+      while (true) {
+        if (gt == 0) claimed_job = (int)atomicAdd(claims + b, 1u);
+        asm volatile("bar.sync 3, 256;" ::: "memory");
+        const int k = claimed_job;
+        asm volatile("bar.sync 3, 256;" ::: "memory");
+        if (k >= need) break;
+        const int j = p.ag_first[b] + k;
+        const uint4* src = reinterpret_cast<const uint4*>(p.ag_src[j]);
+        uint4* dst = reinterpret_cast<uint4*>(p.ag_dst[j]);
+        const int nvec = p.ag_bytes[j] >> 4;
+        int i = gt;
+        // 8 independent 16-byte peer loads in flight per thread to cover the NVLink latency
+        for (; i + 7 * kGatherThreads < nvec; i += 8 * kGatherThreads) {
+          uint4 v[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = src[i + u * kGatherThreads];
+          for (int u = 0; u < 8; ++u) v[u] = src[i + u * kGatherThreads];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) dst[i + u * kGatherThreads] = v[u];
+          for (int u = 0; u < 8; ++u) dst[i + u * kGatherThreads] = v[u];
+        }
+        for (; i < nvec; i += kGatherThreads) dst[i] = src[i];
+        __threadfence();
+        asm volatile("bar.sync 3, 256;" ::: "memory");
+        if (gt == 0) red_release_gpu_add_u32(p.ag_flags + b, 1u);
       }
-      for (; i < nvec; i += kGatherThreads) dst[i] = src[i];
-      __threadfence();
-      asm volatile("bar.sync 3, 256;" ::: "memory");
-      if (gt == 0) red_release_gpu_add_u32(p.ag_flags + p.ag_flag[j], 1u);
+    };
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const TileCoord c = decode_tile(p, tile);
+      if (!c.skip) drain_block(c.n0);
     }
+    for (int b = 0; b < p.tiles_n; ++b) drain_block((b + p.ag_rotate) % p.tiles_n);
   } else {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;                // TMEM lane quarter this warp may read
@@ -572,14 +595,15 @@ MFSDP_API int mfsdp_gemm_bf16(const void* A, const void* B, void* D, const void*
 // where (parts of) B are not in local memory yet.  `njobs` copy jobs (device tables) bring them in
 // from peer memory with plain 16-byte loads while the tensor-core tiles whose B rows already
 // arrived run; ag_flag[j] names the bn-row block of B that job j belongs to and ag_need[b] is the
-// number of jobs of block b (0 for blocks that are already local).  `flags` (tiles_n words) must be
-// zero.  Returns the tile width used through *bn_out when called with njobs < 0 (planning call).
+// number of jobs of block b (0 for blocks that are already local), ag_first[b] the index of its first
+// job (jobs are sorted by block).  `flags` (2 * tiles_n words: finished and claimed jobs per block) must
+// be zero.  `rotate`: tile column the schedule starts at (the block holding the local rank's rows).  Returns the tile width used through *bn_out when called with njobs < 0 (planning call).
 MFSDP_API int mfsdp_gemm_bf16_ag(const void* A, const void* B, void* D, const void* Cin, int M, int N, int K,
                                  long long lda, long long ldd, long long ldcin, float alpha, float beta,
                                  const unsigned long long* ag_src, const unsigned long long* ag_dst,
                                  const int* ag_bytes, const int* ag_flag, int njobs, unsigned* flags,
-                                 const int* ag_need, int bn, unsigned long long budget_ns, int* status,
-                                 int num_sms, cudaStream_t stream) {
+                                 const int* ag_need, const int* ag_first, int rotate, int bn,
+                                 unsigned long long budget_ns, int* status, int num_sms, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || (bn != 128 && bn != 256) || njobs < 0) return -2;
   ensure_context_on_this_thread();
   if ((lda % 8) || (K % 8) || (ldd % 8)) return -2;
@@ -597,6 +621,8 @@ MFSDP_API int mfsdp_gemm_bf16_ag(const void* A, const void* B, void* D, const vo
   args.raster_group_m = 8;   // (walking a whole B row-block first measured slower: 0.193 vs 0.144 ms on 4 GPUs)
   args.ag_src = ag_src; args.ag_dst = ag_dst; args.ag_bytes = ag_bytes; args.ag_flag = ag_flag;
   args.ag_njobs = njobs; args.ag_flags = flags; args.ag_need = ag_need; args.ag_budget_ns = budget_ns;
+  args.ag_first = ag_first;
+  args.ag_rotate = (rotate > 0 && rotate < args.tiles_n) ? rotate : 0;
   CUtensorMap ta, tb, td;
   int rc = make_tmap_bf16_2d(&ta, A, M, K, lda, BM, 64);
   if (rc) return rc;

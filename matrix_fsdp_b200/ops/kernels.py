@@ -129,7 +129,8 @@ def gemm_ag(a: torch.Tensor, b: torch.Tensor, plan, *, out: torch.Tensor | None 
         a.data_ptr(), b.data_ptr(), out.data_ptr(), cin.data_ptr() if cin is not None else None, M, N, Kd,
         a.stride(0), out.stride(0), cin.stride(0) if cin is not None else 0, alpha, beta,
         plan.src.data_ptr(), plan.dst.data_ptr(), plan.nbytes.data_ptr(), plan.flag_idx.data_ptr(), plan.njobs,
-        plan.flags.data_ptr(), plan.need.data_ptr(), plan.bn, int(plan.budget_ns),
+        plan.flags.data_ptr(), plan.need.data_ptr(), plan.first.data_ptr(), int(plan.rotate), plan.bn,
+        int(plan.budget_ns),
         status_word(a.device).data_ptr(), sm_count(a.device), _stream())
     _lib.check(rc, "mfsdp_gemm_bf16_ag")
     return out

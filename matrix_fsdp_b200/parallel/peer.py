@@ -312,7 +312,17 @@ class DeferredGather:
         self.nbytes, self.flag_idx = i32([nbytes[i] for i in order]), i32([flag[i] for i in order])
         self.njobs = len(order)
         self.need = i32(need)
-        self.flags = torch.zeros(nblocks, dtype=torch.int32, device=dev)
+        first, acc = [], 0
+        for c in need:
+            first.append(acc)
+            acc += c
+        self.first = i32(first)                       # jobs are sorted by block: block b owns [first[b], first[b] + need[b])
+        # finished jobs per block, then claimed jobs per block (zeroed before every launch)
+        self.flags = torch.zeros(2 * nblocks, dtype=torch.int32, device=dev)
+        # the schedule starts at the block that holds this rank's own rows: they need no NVLink traffic
+        mine = [(max(sg.global_start, lo) - lo) // block for sg in tables.my_segments
+                if max(sg.global_start, lo) < min(sg.global_start + sg.numel, hi)]
+        self.rotate = min(mine) if mine else 0
         self._plain = {"src": i64(psrc), "dst": i64(pdst), "len": i64(plen), "n": len(psrc), "max": max(plen, default=0)}
 
     def complete(self, stream=None) -> None:

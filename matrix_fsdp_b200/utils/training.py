@@ -98,3 +98,39 @@ def clip_grad_norm_(module_or_units, max_norm: float, norm_type: float = 2.0,
     for g in shards:
         g.mul_(coef.to(g.dtype))
     return norm
+
+
+@torch.no_grad()
+def gather_full_grads(module_or_units) -> dict[str, torch.Tensor]:
+    """Full (unsharded) reduced gradients keyed by parameter name, assembled on every rank.
+
+    Call it after ``backward()`` and before ``optimizer.step()`` / ``zero_grad()``.  Every rank holds one
+    piece of each gradient (its part of the unit's reduced shard); the pieces are placed at their offsets in
+    a zero tensor of the parameter's size and summed over the unit's shard group.  Collective: every rank of
+    the group has to call it.  A debugging / verification aid (one all-reduce per parameter); the reference's
+    bench does the same comparison against FSDP2 (test/fsdp/bench_fsdp2_compare.py:1533-1597).
+    """
+    import torch.distributed as dist
+
+    from ..parallel.unit_collection import collect_param_groups
+
+    units = collect_param_groups(module_or_units)
+    names: dict[int, str] = {}
+    if isinstance(module_or_units, torch.nn.Module):
+        names = {id(p): n for n, p in module_or_units.named_parameters(remove_duplicate=False)}
+    out: dict[str, torch.Tensor] = {}
+    for ui, u in enumerate(units):
+        u.wait_post_backward_reduce()
+        fb = u.flat_buffer
+        shard = fb.local_grad_shard if fb.local_grad_valid else None
+        group = u.groups.shard_group if u.world_size > 1 else None
+        for mp in u.registry:
+            full = torch.zeros(mp.numel, dtype=torch.float32, device=fb.device)
+            piece = fb.pieces.get(mp.fqn)
+            if shard is not None and piece is not None:
+                full[piece.param_start:piece.param_start + piece.numel] = \
+                    shard[piece.local_start:piece.local_end].to(torch.float32)
+            if group is not None:
+                dist.all_reduce(full, group=group)
+            out[names.get(id(mp.param), f"unit{ui}.{mp.fqn}")] = full.view(mp.shape)
+    return out

@@ -269,14 +269,16 @@ def test_gemm_with_fused_gather_single_gpu():
         need[blk] += 1
         row = end
     dev = "cuda"
+    first = [sum(need[:i]) for i in range(nblocks)]                  # jobs above are generated in block order
     plan = SimpleNamespace(
-        b_ptr=b.data_ptr(), bn=bn, njobs=len(jobs), budget_ns=int(2e9),
+        b_ptr=b.data_ptr(), bn=bn, njobs=len(jobs), budget_ns=int(2e9), rotate=2,
+        first=torch.tensor(first, dtype=torch.int32, device=dev),
         src=torch.tensor([j[0] for j in jobs], dtype=torch.int64, device=dev),
         dst=torch.tensor([j[1] for j in jobs], dtype=torch.int64, device=dev),
         nbytes=torch.tensor([j[2] for j in jobs], dtype=torch.int32, device=dev),
         flag_idx=torch.tensor([j[3] for j in jobs], dtype=torch.int32, device=dev),
         need=torch.tensor(need, dtype=torch.int32, device=dev),
-        flags=torch.zeros(nblocks, dtype=torch.int32, device=dev))
+        flags=torch.zeros(2 * nblocks, dtype=torch.int32, device=dev))
     out = K.gemm_ag(a, b, plan)
     torch.cuda.synchronize()
     K.check_status()

@@ -4,7 +4,8 @@ Some users of the kernel library cannot allocate device memory at the point wher
 (no allocator of their own, or one that must not be entered there), so ``mfsdp_rmsnorm_bwd_noalloc``
 keeps its fp32 scratch inside the library.  The test drives it with ctypes exactly as a C caller
 would, twice in a row (every call reuses the same built-in scratch), and checks both results against
-the regular entry point, which takes its scratch from the caller.
+the regular entry point, which takes its scratch from the caller, and against the same math written
+in fp32 PyTorch.
 """
 import ctypes as C
 
@@ -47,6 +48,13 @@ def test_noalloc_rmsnorm_bwd_matches_regular_entry_point_twice():
         torch.cuda.synchronize()
         assert _rel(dx, ref_dx) < 1e-2
         assert _rel(dw, ref_dw) < 1e-2
+        # the op itself in fp32: dx = rstd (g - xhat mean(g xhat)) + dres with g = dy w, dw = sum_rows dy xhat
+        xhat = x.float() * rstd[:, None]
+        g = dy.float() * w.float()
+        fp32_dx = rstd[:, None] * (g - xhat * (g * xhat).mean(-1, keepdim=True)) + dres.float()
+        fp32_dw = (dy.float() * xhat).sum(0)
+        assert _rel(dx, fp32_dx) < 1e-2
+        assert _rel(dw, fp32_dw) < 1e-2
     # sizes beyond the built-in scratch are refused with the documented code
     assert fn(None, None, None, None, None, None, None, 0, 16, 8192 + 8, stream) == -2
     assert fn(None, None, None, None, None, None, None, 0, 16, 100, stream) == -2
