@@ -367,19 +367,27 @@ __device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const void* mc) {
                : "memory");
   return v;
 }
-// 8 summed elements at element offset `off` of the multicast gradient buffer
-__device__ __forceinline__ void mc_sum8(const __nv_bfloat16* mc, long long off, float (&acc)[8]) {
-  const uint4 u = multimem_ld_reduce_bf16x8(mc + off);
-  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+constexpr int kMcUnroll = 4;
+
+// Raw results of the in-switch reductions of one trip (converted to fp32 only when consumed, which keeps
+// the registers per thread low enough for four CTAs per SM).
+__device__ __forceinline__ Raw8bf mc_raw8(const __nv_bfloat16* mc, long long off) {
+  return {multimem_ld_reduce_bf16x8(mc + off)};
+}
+__device__ __forceinline__ Raw8f mc_raw8(const float* mc, long long off) {
+  return {multimem_ld_reduce_f32x4(mc + off), multimem_ld_reduce_f32x4(mc + off + 4)};
+}
+__device__ __forceinline__ void raw_to_f32(const Raw8bf& r, float (&acc)[8]) {
+  const uint32_t w[4] = {r.u.x, r.u.y, r.u.z, r.u.w};
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
     const float2 f = unpack_bf16x2(w[e]);
     acc[2 * e] = f.x; acc[2 * e + 1] = f.y;
   }
 }
-__device__ __forceinline__ void mc_sum8(const float* mc, long long off, float (&acc)[8]) {
-  const float4 a = multimem_ld_reduce_f32x4(mc + off), b = multimem_ld_reduce_f32x4(mc + off + 4);
-  acc[0] = a.x; acc[1] = a.y; acc[2] = a.z; acc[3] = a.w; acc[4] = b.x; acc[5] = b.y; acc[6] = b.z; acc[7] = b.w;
+__device__ __forceinline__ void raw_to_f32(const Raw8f& r, float (&acc)[8]) {
+  acc[0] = r.a.x; acc[1] = r.a.y; acc[2] = r.a.z; acc[3] = r.a.w;
+  acc[4] = r.b.x; acc[5] = r.b.y; acc[6] = r.b.z; acc[7] = r.b.w;
 }
 
 // All-gather as a push: copy this rank's segments (byte offsets, all multiples of 16) from its shard
@@ -415,54 +423,77 @@ __global__ void ag_push_mc_kernel(const char* __restrict__ shard, char* mc_full,
 // Reduce-scatter through the switch: out[local_off + i] = scale * (sum over ranks)[global_off + i].
 // Segment offsets and lengths are multiples of 8 elements (checked by the launcher's caller).
 template <typename TIn, typename TOut, bool ACCUM>
-__global__ void rs_mc_reduce_kernel(const TIn* mc_grad, TOut* __restrict__ out, ReduceTable tab, int nseg,
+__global__ void __launch_bounds__(256, 3) rs_mc_reduce_kernel(const TIn* mc_grad, TOut* __restrict__ out, ReduceTable tab, int nseg,
                                     float scale, const int* status) {
   if (status != nullptr && *status != 0) return;
   const long long stride = (long long)gridDim.x * blockDim.x;
   const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   for (int s = blockIdx.y; s < nseg; s += gridDim.y) {
     const long long g0 = tab.global_off[s], l0 = tab.local_off[s], nvec = tab.len[s] / 8;
-    for (long long i = tid; i < nvec; i += stride) {
-      float acc[8];
-      mc_sum8(mc_grad, g0 + i * 8, acc);
-      TOut* o = out + l0 + i * 8;
-      if (ACCUM) {
-        float prev[8];
-        load8(o, prev);
+    // kMcUnroll in-switch reductions in flight per thread: the round trip through the switch is several
+    // microseconds, so the loads of one trip are all issued before the first result is used
+    for (long long i0 = tid; i0 < nvec; i0 += kMcUnroll * stride) {
+      decltype(mc_raw8(mc_grad, 0)) raw[kMcUnroll];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = acc[e] * scale + prev[e];
-      } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] *= scale;
+      for (int u = 0; u < kMcUnroll; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < nvec) raw[u] = mc_raw8(mc_grad, g0 + i * 8);
       }
-      store8(o, acc);
+#pragma unroll
+      for (int u = 0; u < kMcUnroll; ++u) {
+        const long long i = i0 + u * stride;
+        if (i >= nvec) break;
+        float acc[8];
+        raw_to_f32(raw[u], acc);
+        TOut* o = out + l0 + i * 8;
+        if (ACCUM) {
+          float prev[8];
+          load8(o, prev);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = acc[e] * scale + prev[e];
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] *= scale;
+        }
+        store8(o, acc);
+      }
     }
   }
 }
 
 // The same reduction feeding the sharded AdamW update directly (the reduced gradient is never stored).
 template <typename TIn>
-__global__ void rs_mc_adamw_kernel(const TIn* mc_grad, ReduceTable tab, int nseg, float scale, AdamWArgs a,
+__global__ void __launch_bounds__(256, 2) rs_mc_adamw_kernel(const TIn* mc_grad, ReduceTable tab, int nseg, float scale, AdamWArgs a,
                                    const int* status) {
   if (status != nullptr && *status != 0) return;
   const long long stride = (long long)gridDim.x * blockDim.x;
   const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   for (int s = blockIdx.y; s < nseg; s += gridDim.y) {
     const long long g0 = tab.global_off[s], l0 = tab.local_off[s], nvec = tab.len[s] / 8;
-    for (long long i = tid; i < nvec; i += stride) {
-      float acc[8];
-      mc_sum8(mc_grad, g0 + i * 8, acc);
-      const long long j = l0 + i * 8;
-      float pp[8], mm[8], vv[8];
-      load8(a.p + j, pp);
-      load8(a.m + j, mm);
-      load8(a.v + j, vv);
+    for (long long i0 = tid; i0 < nvec; i0 += kMcUnroll * stride) {
+      decltype(mc_raw8(mc_grad, 0)) raw[kMcUnroll];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) adamw_one(pp[e], mm[e], vv[e], acc[e] * scale, a);
-      store8(a.p + j, pp);
-      store8(a.m + j, mm);
-      store8(a.v + j, vv);
-      if (a.p_lp) store8(a.p_lp + j, pp);
+      for (int u = 0; u < kMcUnroll; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < nvec) raw[u] = mc_raw8(mc_grad, g0 + i * 8);
+      }
+#pragma unroll
+      for (int u = 0; u < kMcUnroll; ++u) {
+        const long long i = i0 + u * stride;
+        if (i >= nvec) break;
+        const long long j = l0 + i * 8;
+        float acc[8], pp[8], mm[8], vv[8];
+        raw_to_f32(raw[u], acc);
+        load8(a.p + j, pp);
+        load8(a.m + j, mm);
+        load8(a.v + j, vv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) adamw_one(pp[e], mm[e], vv[e], acc[e] * scale, a);
+        store8(a.p + j, pp);
+        store8(a.m + j, mm);
+        store8(a.v + j, vv);
+        if (a.p_lp) store8(a.p_lp + j, pp);
+      }
     }
   }
 }
@@ -470,23 +501,32 @@ __global__ void rs_mc_adamw_kernel(const TIn* mc_grad, ReduceTable tab, int nseg
 // One-shot all-reduce in place on a multicast buffer: rank r sums the r-th slice through the switch
 // and stores the scaled result back through the multicast address, so every copy ends up equal.
 template <typename T>
-__global__ void ar_mc_kernel(T* mc_buf, long long nvec8, int rank, int world, float scale, const int* status) {
+__global__ void __launch_bounds__(256, 4) ar_mc_kernel(T* mc_buf, long long nvec8, int rank, int world, float scale, const int* status) {
   if (status != nullptr && *status != 0) return;
   const long long lo = nvec8 * rank / world, hi = nvec8 * (rank + 1) / world;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = lo + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < hi; i += stride) {
-    float acc[8];
-    mc_sum8(mc_buf, i * 8, acc);
+  for (long long i0 = lo + blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < hi; i0 += kMcUnroll * stride) {
+    decltype(mc_raw8(mc_buf, 0)) raw[kMcUnroll];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] *= scale;
-    if (sizeof(T) == 2) {
-      multimem_st16(mc_buf + i * 8, make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
-                                               pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7])));
-    } else {
-      multimem_st16(mc_buf + i * 8, make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]),
-                                               __float_as_uint(acc[2]), __float_as_uint(acc[3])));
-      multimem_st16(mc_buf + i * 8 + 4, make_uint4(__float_as_uint(acc[4]), __float_as_uint(acc[5]),
-                                                   __float_as_uint(acc[6]), __float_as_uint(acc[7])));
+    for (int u = 0; u < kMcUnroll; ++u)
+      if (i0 + u * stride < hi) raw[u] = mc_raw8(mc_buf, (i0 + u * stride) * 8);
+#pragma unroll
+    for (int u = 0; u < kMcUnroll; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= hi) break;
+      float acc[8];
+      raw_to_f32(raw[u], acc);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] *= scale;
+      if (sizeof(T) == 2) {
+        multimem_st16(mc_buf + i * 8, make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                                 pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7])));
+      } else {
+        multimem_st16(mc_buf + i * 8, make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]),
+                                                 __float_as_uint(acc[2]), __float_as_uint(acc[3])));
+        multimem_st16(mc_buf + i * 8 + 4, make_uint4(__float_as_uint(acc[4]), __float_as_uint(acc[5]),
+                                                     __float_as_uint(acc[6]), __float_as_uint(acc[7])));
+      }
     }
   }
   __threadfence_system();
@@ -683,13 +723,14 @@ MFSDP_API int mfsdp_rs_pull_adamw(const unsigned long long* grad_ptrs_host, int 
 }
 
 // ------------------------------------------------------------------ NVLS launchers
-// Grid of the multimem kernels: the switch does the fan-out / the sum, so a few CTAs per SM-pair keep
-// the links busy and the rest of the GPU stays with the GEMMs running beside them (MFSDP_NVLS_BLOCKS).
+// Grid of the multimem kernels (MFSDP_NVLS_BLOCKS).  The switch does the fan-out / the sum, but a round
+// trip through it takes several microseconds: what keeps the links busy is the number of 16-byte
+// requests in flight (CTAs x 256 threads x kMcUnroll), which 6 CTAs per SM provide.
 static long long nvls_blocks() {
   static long long v = [] {
     const char* e = getenv("MFSDP_NVLS_BLOCKS");
     long long x = e ? atoll(e) : 0;
-    return x > 0 ? x : 148LL * 2;
+    return x > 0 ? x : 148LL * 6;
   }();
   return v;
 }

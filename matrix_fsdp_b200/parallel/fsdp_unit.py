@@ -537,7 +537,12 @@ class MatrixFSDPParamGroup:
             ctx = ForwardBackwardContext(self._pre_backward_unshard)
             hooks = register_pre_backward_hooks(output, ctx)
             self.forward_count_since_backward += 1
-        if self.reshard_after_forward:
+        if self.reshard_after_forward and grad_mode and hooks and self.scheduler is not None \
+                and self.scheduler.keeps_unsharded_into_backward(self):
+            # the unit that closes the forward opens the backward: resharding it now would only make the
+            # backward start with the same gather again
+            self._record("keep_unsharded_into_backward")
+        elif self.reshard_after_forward:
             self.reshard("reshard_after_forward",
                          to=FSDPLifecycleState.FORWARD_RESHARDED if (grad_mode and hooks) else FSDPLifecycleState.SHARDED)
         elif not (grad_mode and hooks) and not self._keep_unsharded_in_eval():

@@ -478,9 +478,9 @@ class PeerTransport(LocalTransport):
         if slot is None or slot.holder != unit_key:
             return
         slot.holder = None
-        if len(slot.units) > 1:
-            self.ctx.signal(self._unit(unit_key), KIND_FREE, slot.last_epoch, None)
-            self.launches += 1
+        # always published: a unit built later (another model in this process) may come to share the slot
+        self.ctx.signal(self._unit(unit_key), KIND_FREE, slot.last_epoch, None)
+        self.launches += 1
 
     def acquire_grad_buffer(self, unit_key, numel: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
         es = torch.empty((), dtype=dtype).element_size()

@@ -70,6 +70,9 @@ class MatrixFSDPSchedulerConfig:
     # after optimizer.step(): start the all-gather of the unit that ran first in the last forward, so the
     # next step does not begin with an exposed gather (None: on for CUDA, off on CPU)
     prefetch_first_unit_after_step: bool | None = None
+    # the unit whose forward ran last in the previous iteration is not resharded after its forward (its
+    # backward follows at once); None: on for CUDA with more than one unit, off on CPU
+    keep_last_forward_unit_unsharded: bool | None = None
     # adaptive / profile_guided: exposed unshard wait (ms per unit) above which the prefetch depth grows,
     # and how many iterations each candidate depth is measured for
     adaptive_wait_threshold_ms: float = 0.05
@@ -249,6 +252,12 @@ class MatrixFSDPScheduler:
             nxt.start_unshard("forward_prefetch")
             self.counters.forward_prefetch_issued += 1
             issued += 1
+
+    def keeps_unsharded_into_backward(self, unit) -> bool:
+        want = self.config.keep_last_forward_unit_unsharded
+        if want is None:
+            want = unit.flat_buffer.device.type == "cuda"
+        return bool(want) and len(self.units) > 1 and bool(self.forward_order) and self.forward_order[-1] is unit
 
     def record_post_forward(self, unit) -> None:
         if torch.is_grad_enabled():
