@@ -367,7 +367,10 @@ __device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const void* mc) {
                : "memory");
   return v;
 }
-constexpr int kMcUnroll = 4;
+template <typename T>
+struct McUnroll {
+  static constexpr int value = sizeof(T) == 2 ? 8 : 4;   // 16-byte requests: one per 8 bf16, two per 8 fp32
+};
 
 // Raw results of the in-switch reductions of one trip (converted to fp32 only when consumed, which keeps
 // the registers per thread low enough for four CTAs per SM).
@@ -423,8 +426,9 @@ __global__ void ag_push_mc_kernel(const char* __restrict__ shard, char* mc_full,
 // Reduce-scatter through the switch: out[local_off + i] = scale * (sum over ranks)[global_off + i].
 // Segment offsets and lengths are multiples of 8 elements (checked by the launcher's caller).
 template <typename TIn, typename TOut, bool ACCUM>
-__global__ void __launch_bounds__(256, 3) rs_mc_reduce_kernel(const TIn* mc_grad, TOut* __restrict__ out, ReduceTable tab, int nseg,
+__global__ void __launch_bounds__(256, 2) rs_mc_reduce_kernel(const TIn* mc_grad, TOut* __restrict__ out, ReduceTable tab, int nseg,
                                     float scale, const int* status) {
+  constexpr int kMcUnroll = McUnroll<TIn>::value;
   if (status != nullptr && *status != 0) return;
   const long long stride = (long long)gridDim.x * blockDim.x;
   const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -465,6 +469,7 @@ __global__ void __launch_bounds__(256, 3) rs_mc_reduce_kernel(const TIn* mc_grad
 template <typename TIn>
 __global__ void __launch_bounds__(256, 2) rs_mc_adamw_kernel(const TIn* mc_grad, ReduceTable tab, int nseg, float scale, AdamWArgs a,
                                    const int* status) {
+  constexpr int kMcUnroll = McUnroll<TIn>::value;
   if (status != nullptr && *status != 0) return;
   const long long stride = (long long)gridDim.x * blockDim.x;
   const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -501,7 +506,8 @@ __global__ void __launch_bounds__(256, 2) rs_mc_adamw_kernel(const TIn* mc_grad,
 // One-shot all-reduce in place on a multicast buffer: rank r sums the r-th slice through the switch
 // and stores the scaled result back through the multicast address, so every copy ends up equal.
 template <typename T>
-__global__ void __launch_bounds__(256, 4) ar_mc_kernel(T* mc_buf, long long nvec8, int rank, int world, float scale, const int* status) {
+__global__ void __launch_bounds__(256, 2) ar_mc_kernel(T* mc_buf, long long nvec8, int rank, int world, float scale, const int* status) {
+  constexpr int kMcUnroll = McUnroll<T>::value;
   if (status != nullptr && *status != 0) return;
   const long long lo = nvec8 * rank / world, hi = nvec8 * (rank + 1) / world;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -538,7 +544,7 @@ static long long peer_max_blocks() {
   static long long v = [] {
     const char* e = getenv("MFSDP_PEER_MAX_BLOCKS");
     long long x = e ? atoll(e) : 0;
-    return x > 0 ? x : 148LL * 8;
+    return x > 0 ? x : 148LL * 2;
   }();
   return v;
 }
@@ -723,14 +729,17 @@ MFSDP_API int mfsdp_rs_pull_adamw(const unsigned long long* grad_ptrs_host, int 
 }
 
 // ------------------------------------------------------------------ NVLS launchers
-// Grid of the multimem kernels (MFSDP_NVLS_BLOCKS).  The switch does the fan-out / the sum, but a round
-// trip through it takes several microseconds: what keeps the links busy is the number of 16-byte
-// requests in flight (CTAs x 256 threads x kMcUnroll), which 6 CTAs per SM provide.
+// Grid of the multimem kernels (MFSDP_NVLS_BLOCKS, default one CTA per SM).  These kernels run beside the
+// GEMMs and attention kernels of the neighbouring block, which need one CTA on EVERY SM (persistent grids of
+// 148): a communication kernel that fills an SM's register file keeps that CTA from starting and the whole
+// GEMM waits for it.  So the footprint per SM is one CTA of 256 threads, and the bytes in flight that the
+// several-microsecond round trip through the switch needs come from kMcUnroll requests per thread instead
+// of from more CTAs.
 static long long nvls_blocks() {
   static long long v = [] {
     const char* e = getenv("MFSDP_NVLS_BLOCKS");
     long long x = e ? atoll(e) : 0;
-    return x > 0 ? x : 148LL * 6;
+    return x > 0 ? x : 148LL;
   }();
   return v;
 }

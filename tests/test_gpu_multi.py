@@ -269,6 +269,61 @@ def test_sharded_training_without_nvls_matches():
         os.environ.pop("MFSDP_NVLS", None)
 
 
+def _owner_muon_train(rank, world, transport_kind):
+    """Matrix-owner layout + mixed Muon / AdamW: every 2-D block matrix lives whole on one rank."""
+    from torch.distributed.fsdp import MixedPrecisionPolicy
+
+    from matrix_fsdp_b200.api import reset_shared_owner_planners
+    from matrix_fsdp_b200.checkpoint import MatrixStateDictOptions, get_model_state_dict
+    from matrix_fsdp_b200.models.llama import LlamaConfig, LlamaModel, shard_llama
+    from matrix_fsdp_b200.ops import kernels as K
+    from matrix_fsdp_b200.optim import configure_optimizer
+    from matrix_fsdp_b200.parallel.unit_collection import collect_param_groups
+
+    os.environ["MFSDP_TRANSPORT"] = transport_kind
+    reset_shared_owner_planners()
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=1024, hidden=256, n_layers=2, n_heads=2, head_dim=128, ffn=768)
+    model = LlamaModel(cfg).cuda()
+    shard_llama(model, mp_policy=MixedPrecisionPolicy(param_dtype=torch.bfloat16), optimizer_policy="mixed_muon_adamw")
+    units = collect_param_groups(model)
+    assert {u.flat_buffer.transport.kind for u in units} == {transport_kind}
+    block = model.layers[0]._matrix_fsdp_param_group
+    for fqn in ("wq.weight", "w_gate.weight", "w_down.weight"):
+        assert len(block.owner_ranks(fqn)) == 1, (fqn, block.owner_ranks(fqn))     # whole matrices
+    owners = {block.owner_ranks(f)[0] for f in block.registry.fqns if f.endswith(".weight") and "norm" not in f}
+    assert owners == set(range(world)), owners                                      # spread over the ranks
+    opt = configure_optimizer(model, "mixed_muon_adamw", muon_lr=0.02, adamw_lr=1e-3, muon_momentum=0.95,
+                              muon_ns_steps=5, muon_adjust_lr_fn="original", weight_decay=0.0)
+    g = torch.Generator().manual_seed(11 + rank)
+    losses = []
+    for _ in range(3):
+        tok = torch.randint(0, 1024, (2, 65), generator=g).cuda()
+        loss = model(tok[:, :-1], tok[:, 1:])
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        losses.append(loss.item())
+    K.check_status()
+    # momentum lives only with the owner of each matrix
+    for p, st in opt.muon.state.items():
+        assert p.numel() > 0 and st["momentum_buffer"].shape == p.shape
+    n_owned = sum(1 for u in units for mp in u.registry
+                  if mp.fqn in u.flat_buffer.pieces and mp.shard_hint.optimizer_type == "muon")
+    assert len(opt.muon.state) == n_owned, (len(opt.muon.state), n_owned)
+    full = get_model_state_dict(model, options=MatrixStateDictOptions(full_state_dict=True))
+    return losses, torch.cat([v.float().flatten().cpu() for _, v in sorted(full.items())])
+
+
+def _owner_muon_both(rank, world):
+    l_peer, p_peer = _owner_muon_train(rank, world, "peer")
+    l_lib, p_lib = _owner_muon_train(rank, world, "torch_dist")
+    for a, b in zip(l_peer, l_lib):
+        assert a == a and abs(a - b) < 2e-2 * abs(b), (l_peer, l_lib)
+    rel = ((p_peer - p_lib).norm() / p_lib.norm()).item()
+    assert rel < 5e-3, rel
+
+
 def _hsdp_train(rank, world, transport_kind):
     from torch.distributed.device_mesh import init_device_mesh
     from torch.distributed.fsdp import MixedPrecisionPolicy
@@ -316,6 +371,14 @@ def test_hsdp_2x2_peer_vs_nccl():
     """HSDP on a 2 x 2 mesh: reduce-scatter in the shard group and all-reduce in the replicate group,
     both through the peer kernels, against the library collectives."""
     _run(_hsdp_both, 4)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_matrix_owner_muon_peer_vs_library_collectives():
+    """The owner layout end to end on GPUs: reduce-to-owner, Newton-Schulz on the owner, gather from the
+    owner, through the peer kernels and through the library collectives (whose Muon step the CPU tests
+    compare with ``torch.optim.Muon``)."""
+    _run(_owner_muon_both, 2)
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
