@@ -3,12 +3,15 @@
     python -m matrix_fsdp_b200.tools.regression tests [--gpu] [--timeout 900]
     python -m matrix_fsdp_b200.tools.regression bench --configs 2 5s --gpus 1 2 --trials 2 [--impl ours reference]
     python -m matrix_fsdp_b200.tools.regression package
+    python -m matrix_fsdp_b200.tools.regression batch <name> [--dry-run] [--report-dir DIR]   (named GPU batches)
+    python -m matrix_fsdp_b200.tools.regression plan [--out-dir DIR]                          (no-GPU preflight + commands.sh)
+    python -m matrix_fsdp_b200.tools.regression summarize DIR [--json]                        (logs -> tables)
 
 ``tests`` runs every test file in its own interpreter (a crash or a hang in one file cannot take the
 others with it) and prints one line per file; ``bench`` runs ``bench.py`` once per (config, N, trial) in
 a fresh process, collects the JSON lines and prints a median table; ``package`` builds the kernel
 library for sm_100a, checks that every exported entry point the Python side binds is present, and
-imports the public API.  Child processes are ended by their own timeout only (never by name).
+imports the public API; ``batch`` / ``plan`` / ``summarize`` are described in ``gpu_runbook.py``.  Child processes are ended by their own timeout only (never by name).
 
 Parity: scripts/run_test.sh, scripts/run_isolated_gpu_benchmark.py, scripts/summarize_gpu_comm_report.py,
 scripts/check_package.sh and scripts/build_cuda_kernels.sh of the reference.
@@ -104,6 +107,58 @@ def cmd_package(args) -> int:
     return 1 if (missing or exported) else 0
 
 
+def _settings(args):
+    from .gpu_runbook import Settings
+
+    base = Settings()
+    kw = {}
+    for name, default in vars(base).items():
+        v = getattr(args, name, None)
+        if v is not None:
+            kw[name] = tuple(v) if isinstance(default, tuple) else v
+    return Settings(**kw)
+
+
+def _add_settings(p) -> None:
+    from .gpu_runbook import Settings
+
+    for name, default in vars(Settings()).items():
+        flag = "--" + name.replace("_", "-")
+        if isinstance(default, tuple):
+            p.add_argument(flag, type=int, nargs="+", default=None)
+        else:
+            p.add_argument(flag, type=int, default=None)
+
+
+def cmd_batch(args) -> int:
+    from . import gpu_runbook as rb
+
+    report_dir = args.report_dir or os.path.join(ROOT, "benchmark_results", f"{args.name}_{time.strftime('%Y%m%d_%H%M%S')}")
+    if args.dry_run:
+        print(rb.render_script(args.name, _settings(args), report_dir), end="")
+        return 0
+    return rb.run_batch(args.name, _settings(args), report_dir)
+
+
+def cmd_plan(args) -> int:
+    from . import gpu_runbook as rb
+
+    out_dir = args.out_dir or os.path.join(ROOT, "benchmark_results", f"gpu_preflight_{time.strftime('%Y%m%d_%H%M%S')}")
+    res = rb.prepare(out_dir, _settings(args), local_checks=not args.no_local_checks)
+    print(json.dumps(res))
+    return 1 if any(res["local_checks"].values()) else 0
+
+
+def cmd_summarize(args) -> int:
+    from pathlib import Path
+
+    from . import gpu_runbook as rb
+
+    summary = rb.summarize_report(Path(args.report_dir))
+    print(json.dumps(summary) if args.json else rb.format_summary(summary), end="" if not args.json else "\n")
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -120,8 +175,24 @@ def main(argv=None) -> int:
     b.add_argument("--timeout", type=float, default=900.0)
     b.add_argument("--out", default=None)
     sub.add_parser("package")
+    from .gpu_runbook import BATCHES
+
+    bt = sub.add_parser("batch", description="\n".join(f"{k:24s}{v[1]}" for k, v in BATCHES.items()),
+                        formatter_class=argparse.RawDescriptionHelpFormatter)
+    bt.add_argument("name", choices=sorted(BATCHES))
+    bt.add_argument("--dry-run", action="store_true", help="print the batch as a shell script")
+    bt.add_argument("--report-dir", default=None)
+    _add_settings(bt)
+    pl = sub.add_parser("plan")
+    pl.add_argument("--out-dir", default=None)
+    pl.add_argument("--no-local-checks", action="store_true")
+    _add_settings(pl)
+    sm = sub.add_parser("summarize")
+    sm.add_argument("report_dir")
+    sm.add_argument("--json", action="store_true")
     args = ap.parse_args(argv)
-    return {"tests": cmd_tests, "bench": cmd_bench, "package": cmd_package}[args.cmd](args)
+    return {"tests": cmd_tests, "bench": cmd_bench, "package": cmd_package, "batch": cmd_batch, "plan": cmd_plan,
+            "summarize": cmd_summarize}[args.cmd](args)
 
 
 if __name__ == "__main__":

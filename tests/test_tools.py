@@ -90,3 +90,104 @@ def test_compare_bench_against_fsdp2_and_eager(capsys):
             continue
         assert r["step_ms"] > 0 and set(r["phase_ms"]) == {"zero_grad", "forward", "backward", "step"}
         assert r["max_loss_diff_vs_eager"] < 1e-5 and r["max_param_diff_vs_eager"] < 1e-4, (mode, r)
+
+
+def test_nccl_feature_probe_with_fabricated_headers(tmp_path, monkeypatch):
+    """Header / version logic of the NCCL probe, on header files written by the test."""
+    import torch
+
+    from matrix_fsdp_b200.tools.device_api_probe import probe_nccl_features
+
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+    monkeypatch.setattr(device_api_probe, "_include_dirs", lambda extra: [__import__("pathlib").Path(p) for p in extra])
+    old, new = tmp_path / "old", tmp_path / "new"
+    old.mkdir(), new.mkdir()
+    (old / "nccl.h").write_text("typedef struct ncclDevComm ncclDevComm;\n")
+    (new / "nccl.h").write_text("typedef struct ncclDevComm ncclDevComm;\nncclResult_t ncclDevCommCreate();\n")
+    (new / "nccl_device").mkdir()
+    (new / "nccl_device" / "gin.h").write_text("struct ncclGin {};\n#define NCCL_GIN_SIGNAL_INC 1\n")
+
+    # a runtime older than the device API: the headers declare it, yet it is not ready, and the reason says why
+    monkeypatch.setattr(torch.cuda.nccl, "version", lambda: (2, 27, 5))
+    p = probe_nccl_features(extra_include_dirs=(str(old),), library="")
+    f = p["features"]["device_api"]
+    assert p["nccl_version"] == (2, 27, 5) and f["declared_in_headers"] and not f["runtime_new_enough"] and not f["ready"]
+    assert "older" in p["reason"]
+
+    # new runtime, headers without GIN: device API ready, GIN not
+    monkeypatch.setattr(torch.cuda.nccl, "version", lambda: 22809)     # packed integer form
+    p = probe_nccl_features(extra_include_dirs=(str(old),), library="")
+    assert p["nccl_version"] == (2, 28, 9)
+    assert p["features"]["device_api"]["ready"] and not p["features"]["gin"]["ready"] and "gin" in p["reason"]
+
+    # new runtime and GIN headers in the nccl_device/ subtree: everything visible
+    monkeypatch.setattr(torch.cuda.nccl, "version", lambda: "2.30.4")
+    p = probe_nccl_features(extra_include_dirs=(str(new),), library="")
+    assert all(v["ready"] for v in p["features"].values()) and "visible" in p["reason"]
+    assert any(h.endswith("gin.h") for h in p["headers"])
+
+    # no headers at all
+    p = probe_nccl_features(extra_include_dirs=(str(tmp_path / "nowhere"),), library="")
+    assert not p["features"]["device_api"]["ready"] and "No NCCL headers" in p["reason"]
+
+
+def test_runbook_batches_render_and_plan(tmp_path, capsys):
+    from matrix_fsdp_b200.tools import gpu_runbook as rb
+    from matrix_fsdp_b200.tools import regression
+
+    s = rb.Settings(world_size=8, layers=4)
+    for name in rb.BATCHES:
+        steps = rb.steps_of(name, s, str(tmp_path / "rep"))
+        assert steps and len({st.name for st in steps}) == len(steps), name
+        script = rb.render_script(name, s, str(tmp_path / "rep"))
+        assert script.count("timeout ") == len(steps) and "summarize" in script
+    assert regression.main(["batch", "trace-report", "--dry-run", "--world-size", "2", "--report-dir", str(tmp_path / "r")]) == 0
+    out = capsys.readouterr().out
+    assert "--nproc-per-node=2" in out and f"--timeline {tmp_path / 'r'}/step_timeline.md" in out
+    assert regression.main(["plan", "--out-dir", str(tmp_path / "pre"), "--no-local-checks", "--world-size", "4"]) == 0
+    res = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    text = open(res["commands"]).read()
+    assert res["steps"] == text.count(" || echo 'failed:") and "bench.py --impl reference --gpus 4" in text
+    assert "world_size=4" in (tmp_path / "pre" / "preflight_summary.txt").read_text()
+
+
+def test_runbook_summariser_builds_tables_from_logs(tmp_path, capsys):
+    from matrix_fsdp_b200.tools import gpu_runbook as rb
+    from matrix_fsdp_b200.tools import regression
+
+    rep = tmp_path / "rep"
+    rep.mkdir()
+    (rep / "compare_adamw.log").write_text("\n".join([
+        "NCCL version 2.28.9+cuda12.9",
+        json.dumps({"mode": "fsdp2", "step_ms": 20.0, "phase_ms": {"forward": 6.0, "backward": 12.0, "optimizer": 2.0},
+                    "peak_mb": 900.0}),
+        json.dumps({"mode": "matrix_default", "step_ms": 16.0, "phase_ms": {"forward": 5.0, "backward": 10.0, "optimizer": 1.0},
+                    "peak_mb": 800.0, "max_param_diff_vs_eager": 1e-3,
+                    "memory_trace": {"after_backward": {"allocated_mb": 1.0, "max_allocated_mb": 2.0, "reserved_mb": 3.0}}}),
+        json.dumps({"mode": "matrix_row", "unavailable": "ValueError: nope"})]))
+    (rep / "comm_bench_even.log").write_text("\n".join([
+        json.dumps({"transport": "peer", "op": "all_gather", "ms": 0.2, "recv_gb_per_s": 600.0,
+                    "frac_of_measured_nvlink_770": 0.78}),
+        json.dumps({"op": "rs+adamw", "unfused_ms": 0.5, "fused_ms": 0.3, "frac_of_roofline": 0.8})]))
+    (rep / "bench_reference_n2.log").write_text(json.dumps(
+        {"metric": "tokens_per_s", "value": 100.0, "unit": "tok/s", "impl": "reference", "n_gpus": 2, "ms_per_step": 10.0,
+         "config": {"model": "m"}}))
+    (rep / "bench_ours_n2.log").write_text(json.dumps(
+        {"metric": "tokens_per_s", "value": 150.0, "unit": "tok/s", "n_gpus": 2, "ms_per_step": 6.6, "config": {"model": "m"},
+         "e2e": {"value": 140.0}}))
+    (rep / "runtime_profile_prefetch.log").write_text(json.dumps(
+        {"mode": "prefetch", "step_ms": 3.0, "peak_mb": 10.0,
+         "events": {"by_collective": {"all_gather/ag_pull": {"count": 4, "device_ms": 0.4, "exposed_ms": 0.1}}}}))
+    (rep / "broken.log").write_text("Traceback (most recent call last):\n  boom\n")
+    s = rb.summarize_report(rep)
+    by_mode = {r["mode"]: r for r in s["phase"]}
+    assert abs(by_mode["matrix_default"]["vs_library"] - 1.25) < 1e-9 and by_mode["fsdp2"]["vs_library"] is None
+    assert s["arms"] == [{"config": "m", "n_gpus": 2, "reference": 100.0, "ours": 150.0, "ratio": 1.5}]
+    assert {c["op"] for c in s["comm"]} == {"all_gather", "rs+adamw"}
+    assert s["memory"][0]["phase"] == "after_backward" and s["timeline"][0]["collective"] == "all_gather/ag_pull"
+    assert {f["log"] for f in s["failures"]} == {"broken.log", "compare_adamw.log"}
+    assert regression.main(["summarize", str(rep)]) == 0
+    text = capsys.readouterr().out
+    for title in ("step time by mode", "both arms", "collectives", "device time of collectives", "memory", "failures"):
+        assert f"== {title} ==" in text
+    assert "1.250" in text and "1.500" in text
