@@ -315,13 +315,16 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dh,
 // ============================================================== cross-entropy
 // One CTA (1024 threads) per row keeps the whole row in registers (V <= 1024*8*VPT):
 // loss[row] = logsumexp - logit[target]; logits are overwritten with
-// (softmax - onehot) * grad_scale, i.e. the gradient of the mean loss.
+// (softmax - onehot) * grad_scale, i.e. the gradient of the mean loss.  When `grad_scale_dev` is
+// given the scale is read from device memory (1 / number of counted targets, computed on the device),
+// so a caller that masks targets needs no device-to-host read to launch this.
 template <int VPT>
 __global__ void __launch_bounds__(1024)
 cross_entropy_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ target,
                              float* __restrict__ loss, int V, long long ld, float grad_scale,
-                             long long ignore_index) {
+                             const float* __restrict__ grad_scale_dev, long long ignore_index) {
   __shared__ float red[32];
+  if (grad_scale_dev != nullptr) grad_scale = *grad_scale_dev;
   const long long row = blockIdx.x;
   __nv_bfloat16* lr = logits + row * ld;
   const int nvec = V >> 3;
@@ -653,19 +656,34 @@ MFSDP_API int mfsdp_swiglu_bwd(const void* dh, const void* gu, void* dgu, long l
   return (int)cudaGetLastError();
 }
 
-MFSDP_API int mfsdp_cross_entropy(void* logits, const long long* target, float* loss, long long rows,
-                                  int V, long long ld, float grad_scale, long long ignore_index,
-                                  cudaStream_t st) {
+static int launch_cross_entropy(void* logits, const long long* target, float* loss, long long rows, int V,
+                                long long ld, float grad_scale, const float* grad_scale_dev,
+                                long long ignore_index, cudaStream_t st) {
   if (V % 8 || ld % 8) return -2;
   const int nvec = V / 8;
   const int vpt = (nvec + 1023) / 1024;
   auto L = (__nv_bfloat16*)logits;
-  if (vpt <= 1) cross_entropy_fwd_bwd_kernel<1><<<(unsigned)rows, 1024, 0, st>>>(L, target, loss, V, ld, grad_scale, ignore_index);
-  else if (vpt <= 2) cross_entropy_fwd_bwd_kernel<2><<<(unsigned)rows, 1024, 0, st>>>(L, target, loss, V, ld, grad_scale, ignore_index);
-  else if (vpt <= 4) cross_entropy_fwd_bwd_kernel<4><<<(unsigned)rows, 1024, 0, st>>>(L, target, loss, V, ld, grad_scale, ignore_index);
-  else if (vpt <= 6) cross_entropy_fwd_bwd_kernel<6><<<(unsigned)rows, 1024, 0, st>>>(L, target, loss, V, ld, grad_scale, ignore_index);
+  const unsigned g = (unsigned)rows;
+  if (vpt <= 1) cross_entropy_fwd_bwd_kernel<1><<<g, 1024, 0, st>>>(L, target, loss, V, ld, grad_scale, grad_scale_dev, ignore_index);
+  else if (vpt <= 2) cross_entropy_fwd_bwd_kernel<2><<<g, 1024, 0, st>>>(L, target, loss, V, ld, grad_scale, grad_scale_dev, ignore_index);
+  else if (vpt <= 4) cross_entropy_fwd_bwd_kernel<4><<<g, 1024, 0, st>>>(L, target, loss, V, ld, grad_scale, grad_scale_dev, ignore_index);
+  else if (vpt <= 6) cross_entropy_fwd_bwd_kernel<6><<<g, 1024, 0, st>>>(L, target, loss, V, ld, grad_scale, grad_scale_dev, ignore_index);
   else return -2;
   return (int)cudaGetLastError();
+}
+
+MFSDP_API int mfsdp_cross_entropy(void* logits, const long long* target, float* loss, long long rows,
+                                  int V, long long ld, float grad_scale, long long ignore_index,
+                                  cudaStream_t st) {
+  return launch_cross_entropy(logits, target, loss, rows, V, ld, grad_scale, nullptr, ignore_index, st);
+}
+
+// Same, with the gradient scale read from device memory at `grad_scale_dev` (one float).
+MFSDP_API int mfsdp_cross_entropy_dev_scale(void* logits, const long long* target, float* loss, long long rows,
+                                            int V, long long ld, const float* grad_scale_dev,
+                                            long long ignore_index, cudaStream_t st) {
+  if (grad_scale_dev == nullptr) return -2;
+  return launch_cross_entropy(logits, target, loss, rows, V, ld, 0.f, grad_scale_dev, ignore_index, st);
 }
 
 MFSDP_API int mfsdp_adamw_flat(float* p, float* m, float* v, const void* g, int grad_is_bf16, void* p_lp,

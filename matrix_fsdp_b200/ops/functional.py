@@ -172,13 +172,15 @@ class _FusedCEFn(torch.autograd.Function):
         from . import kernels as K
 
         if n_valid is None:
-            # the kernel takes the scale as a host float: one small device->host read
-            n_valid = int((target != ignore_index).sum().item())
-        scale = 1.0 / float(max(int(n_valid), 1))
+            # the count of kept targets stays on the device; the kernel reads the scale from there
+            scale = (target != ignore_index).sum().clamp_(min=1).to(torch.float32).reciprocal_().view(1)
+        else:
+            scale = 1.0 / float(max(int(n_valid), 1))
         loss_rows = K.cross_entropy_(logits, target, scale, ignore_index)   # logits now hold dlogits
         ctx.save_for_backward(logits)
         ctx.unit_upstream_grad = unit_upstream_grad
-        return loss_rows.sum() * scale
+        total = loss_rows.sum()
+        return total * (scale[0] if isinstance(scale, torch.Tensor) else scale)
 
     @staticmethod
     def backward(ctx, dloss):
@@ -192,8 +194,8 @@ def fused_cross_entropy(logits: torch.Tensor, target: torch.Tensor, ignore_index
                         n_valid: int | None = None, unit_upstream_grad: bool = False) -> torch.Tensor:
     """Mean token cross-entropy; the logits buffer is consumed (overwritten with its gradient).
 
-    ``n_valid``: number of non-ignored targets when the caller knows it on the host (avoids a
-    device sync).  ``unit_upstream_grad``: promise that the returned loss is what ``backward()`` is
+    ``n_valid``: number of non-ignored targets when the caller knows it on the host; otherwise it is
+    counted on the device and the kernel reads the scale from device memory (no host sync either way).  ``unit_upstream_grad``: promise that the returned loss is what ``backward()`` is
     called on (upstream gradient 1), which skips one pass over the logits.
     """
     v = logits.shape[-1]

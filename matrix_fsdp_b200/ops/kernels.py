@@ -253,13 +253,20 @@ def swiglu_bwd(dh: torch.Tensor, gu: torch.Tensor, out: torch.Tensor | None = No
     return dgu
 
 
-def cross_entropy_(logits: torch.Tensor, target: torch.Tensor, grad_scale: float,
+def cross_entropy_(logits: torch.Tensor, target: torch.Tensor, grad_scale: float | torch.Tensor,
                    ignore_index: int = -100) -> torch.Tensor:
-    """Per-row loss (fp32); ``logits`` is overwritten with ``(softmax - onehot) * grad_scale``."""
+    """Per-row loss (fp32); ``logits`` is overwritten with ``(softmax - onehot) * grad_scale``.
+    ``grad_scale`` is a host float or a one-element fp32 device tensor (read by the kernel, no host sync)."""
     assert logits.dim() == 2 and logits.stride(1) == 1 and logits.dtype == torch.bfloat16
     assert target.dtype == torch.int64 and target.is_contiguous()
     rows, V = logits.shape
     loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    if isinstance(grad_scale, torch.Tensor):
+        assert grad_scale.dtype == torch.float32 and grad_scale.numel() == 1 and grad_scale.device == logits.device
+        _lib.check(_L().mfsdp_cross_entropy_dev_scale(logits.data_ptr(), target.data_ptr(), loss.data_ptr(), rows, V,
+                                                      logits.stride(0), grad_scale.data_ptr(), int(ignore_index),
+                                                      _stream()), "cross_entropy")
+        return loss
     _lib.check(_L().mfsdp_cross_entropy(logits.data_ptr(), target.data_ptr(), loss.data_ptr(), rows, V,
                                         logits.stride(0), float(grad_scale), int(ignore_index),
                                         _stream()), "cross_entropy")

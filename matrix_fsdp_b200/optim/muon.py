@@ -149,8 +149,36 @@ def _use_kernels(t: torch.Tensor) -> bool:
     return rows % 8 == 0 and cols % 8 == 0
 
 
+def ns_flops(shape, steps: int) -> int:
+    """Multiply-add count of ``steps`` Newton-Schulz iterations on a ``shape`` matrix (used to balance work)."""
+    m, n = min(shape), max(shape)
+    return steps * (2 * m * m * n * 2 + 2 * m * m * m)
+
+
+def assign_to_replicas(shapes: list, replicas: int, steps: int) -> list[int]:
+    """Replica index per matrix: largest first onto the least loaded replica (ties: lowest index).  Depends only on
+    the shapes and their order, so every replica computes the same table without talking."""
+    load = [0] * replicas
+    out = [0] * len(shapes)
+    for j in sorted(range(len(shapes)), key=lambda j: (-ns_flops(shapes[j], steps), j)):
+        r = min(range(replicas), key=lambda r: (load[r], r))
+        out[j] = r
+        load[r] += ns_flops(shapes[j], steps)
+    return out
+
+
 class MatrixMuon(Optimizer):
-    """Muon over 2-D parameters that this rank owns whole (matrix-owner layouts)."""
+    """Muon over 2-D parameters that this rank owns whole (matrix-owner layouts).
+
+    A step has three stages per matrix: *prepare* (momentum, Nesterov, Frobenius scaling -> the normalised
+    operand), *orthogonalise* (Newton-Schulz) and *apply* (decay, update, low-precision copy).  Under hybrid
+    sharding every replica owns the same matrices and holds the same reduced gradients, so
+    :meth:`share_newton_schulz_over` splits the orthogonalisation -- by far the most expensive stage -- across
+    the replicate group: each replica orthogonalises only its share (balanced by FLOPs), the results are
+    exchanged with one all-reduce of a buffer that is zero where a replica did no work (``x + 0`` is exact), and
+    every replica applies all of them.  The element-wise stages stay redundant so that the momentum buffers and
+    parameters of the replicas remain bit-identical.
+    """
 
     def __init__(self, params: Iterable, *, lr: float = 1e-3, weight_decay: float = 0.1, momentum: float = 0.95,
                  nesterov: bool = True, ns_coefficients=DEFAULT_NS_COEFFICIENTS, eps: float = EPS, ns_steps: int = 5,
@@ -165,6 +193,13 @@ class MatrixMuon(Optimizer):
         # optional callable param -> bf16 tensor to refresh after the update (all-gather source)
         self._low_precision_of = low_precision_of
         self.grad_scale = 1.0
+        self.ns_share_group = None
+        self.ns_matrices_done = 0        # matrices this rank orthogonalised in the last step (diagnostic)
+
+    def share_newton_schulz_over(self, group) -> None:
+        """Split Newton-Schulz over the ranks of ``group`` (the replicate group of a hybrid-sharded mesh); every
+        rank of it must own the same matrices with the same gradients.  ``None`` switches sharing off."""
+        self.ns_share_group = group
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -172,26 +207,33 @@ class MatrixMuon(Optimizer):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
+        self.ns_matrices_done = 0
         for group in self.param_groups:
-            by_shape: dict[tuple, list] = {}
+            todo = []
             for p in group["params"]:
                 if (p.grad is None and getattr(p, "_grad_override", None) is None) or p.numel() == 0:
                     continue
                 if p.ndim != 2:
                     raise ValueError("Muon only supports 2D parameters; route the rest to AdamW.")
+                todo.append(p)
+            if not todo:
+                continue
+            if self.ns_share_group is not None:
+                self._step_shared(todo, group)
+                continue
+            by_shape: dict[tuple, list] = {}
+            for p in todo:
                 if self._kernel_path(p) and can_batch_newton_schulz(p.shape):
                     by_shape.setdefault(tuple(p.shape), []).append(p)
                 else:
-                    self._step_one(p, group)
+                    self._apply(p, self._orthogonalize([self._prepare(p, group)], group)[0], group)
             # matrices of one shape go through Newton-Schulz together (one grouped launch per product)
             for shape, ps in by_shape.items():
                 per_chunk = max(1, MAX_BATCH_ELEMENTS // (shape[0] * shape[1]))
                 for i in range(0, len(ps), per_chunk):
                     chunk = ps[i:i + per_chunk]
-                    if len(chunk) == 1:
-                        self._step_one(chunk[0], group)
-                    else:
-                        self._step_batched(chunk, group)
+                    for p, o in zip(chunk, self._orthogonalize([self._prepare(p, group) for p in chunk], group)):
+                        self._apply(p, o, group)
         return loss
 
     def _grad_of(self, p):
@@ -204,59 +246,81 @@ class MatrixMuon(Optimizer):
         return _use_kernels(p) and p.dtype == torch.float32 and (buf is None or buf.dtype == torch.float32) \
             and g is not None and g.is_contiguous()
 
-    def _step_batched(self, ps: list, group: dict) -> None:
-        from ..ops import kernels as K
-
-        lr, wd, mu = float(group["lr"]), group["weight_decay"], group["momentum"]
-        rows, cols = ps[0].shape
-        dev = ps[0].device
-        u = torch.empty((len(ps), rows, cols), dtype=torch.bfloat16, device=dev)
-        ss = torch.zeros(len(ps), dtype=torch.float32, device=dev)
-        for i, p in enumerate(ps):
-            st = self.state[p]
-            if "momentum_buffer" not in st:
-                st["momentum_buffer"] = torch.zeros_like(p, dtype=torch.float32)
-            K.muon_momentum(st["momentum_buffer"].view(-1), self._grad_of(p).reshape(-1), u[i].view(-1), ss[i:i + 1],
-                            mu, float(self.grad_scale), group["nesterov"])
-            K.muon_normalize_(u[i].view(-1), ss[i:i + 1], group["eps"])
-        o = newton_schulz_sm100_batched(u, group["ns_coefficients"], group["ns_steps"])
-        alr = adjust_lr(lr, group["adjust_lr_fn"], (rows, cols))
-        for i, p in enumerate(ps):
-            lp = self._low_precision_of(p) if self._low_precision_of is not None else None
-            K.muon_apply_(p.data.view(-1), o[i].reshape(-1), rows, cols, False, lr, wd, alr,
-                          p_lp=lp.view(-1) if lp is not None and lp.dtype == torch.bfloat16 else None)
-            if lp is not None and lp.dtype != torch.bfloat16:
-                lp.copy_(p.data)
-
-    def _step_one(self, p: torch.Tensor, group: dict) -> None:
+    # ------------------------------------------------------------------ the three stages
+    def _prepare(self, p: torch.Tensor, group: dict) -> torch.Tensor:
+        """Momentum + Nesterov; returns the Newton-Schulz operand (kernel path: bf16, already divided by its
+        Frobenius norm; otherwise the raw update, normalised inside the reference iteration)."""
         st = self.state[p]
+        kernels = self._kernel_path(p)
         if "momentum_buffer" not in st:
             st["momentum_buffer"] = torch.zeros_like(p, dtype=torch.float32 if p.dtype == torch.float32 else p.dtype)
-        buf = st["momentum_buffer"]
-        lr, wd, mu = float(group["lr"]), group["weight_decay"], group["momentum"]
-        alr = adjust_lr(lr, group["adjust_lr_fn"], p.shape)
-        lp = self._low_precision_of(p) if self._low_precision_of is not None else None
-        g = self._grad_of(p)
-        if _use_kernels(p) and p.dtype == torch.float32 and buf.dtype == torch.float32 and g.is_contiguous():
+        buf, mu, g = st["momentum_buffer"], group["momentum"], self._grad_of(p)
+        if kernels:
             from ..ops import kernels as K
 
             u = torch.empty(p.shape, dtype=torch.bfloat16, device=p.device)
             ss = torch.zeros(1, dtype=torch.float32, device=p.device)
             K.muon_momentum(buf.view(-1), g.reshape(-1), u.view(-1), ss, mu, float(self.grad_scale), group["nesterov"])
             K.muon_normalize_(u.view(-1), ss, group["eps"])
-            o = newton_schulz_sm100(u, group["ns_coefficients"], group["ns_steps"])
+            return u
+        gf = g.to(buf.dtype)
+        if self.grad_scale != 1.0:
+            gf = gf * self.grad_scale
+        buf.lerp_(gf, 1 - mu)
+        return gf.lerp(buf, mu) if group["nesterov"] else buf
+
+    def _orthogonalize(self, us: list, group: dict) -> list:
+        """Newton-Schulz on each operand; same-shape bf16 CUDA operands go through the grouped kernels together."""
+        self.ns_matrices_done += len(us)
+        coef, steps = group["ns_coefficients"], group["ns_steps"]
+        native = [u.is_cuda and u.dtype == torch.bfloat16 and _use_kernels(u) for u in us]
+        if len(us) > 1 and all(native) and len({tuple(u.shape) for u in us}) == 1 and can_batch_newton_schulz(us[0].shape):
+            return list(newton_schulz_sm100_batched(torch.stack(us), coef, steps).unbind(0))
+        return [newton_schulz_sm100(u, coef, steps) if nat else newton_schulz_reference(u, coef, steps, group["eps"])
+                for u, nat in zip(us, native)]
+
+    def _apply(self, p: torch.Tensor, o: torch.Tensor, group: dict) -> None:
+        lr, wd = float(group["lr"]), group["weight_decay"]
+        alr = adjust_lr(lr, group["adjust_lr_fn"], p.shape)
+        lp = self._low_precision_of(p) if self._low_precision_of is not None else None
+        if self._kernel_path(p) and o.dtype == torch.bfloat16:
+            from ..ops import kernels as K
+
             K.muon_apply_(p.data.view(-1), o.reshape(-1), p.shape[0], p.shape[1], False, lr, wd, alr,
                           p_lp=lp.view(-1) if lp is not None and lp.dtype == torch.bfloat16 else None)
             if lp is not None and lp.dtype != torch.bfloat16:
                 lp.copy_(p.data)
             return
-        gf = g.to(buf.dtype)
-        if self.grad_scale != 1.0:
-            gf = gf * self.grad_scale
-        buf.lerp_(gf, 1 - mu)
-        update = gf.lerp(buf, mu) if group["nesterov"] else buf
-        o = newton_schulz_reference(update, group["ns_coefficients"], group["ns_steps"], group["eps"])
         p.data.mul_(1 - lr * wd)
         p.data.add_(o.to(p.dtype), alpha=-alr)
         if lp is not None:
             lp.copy_(p.data)
+
+    # ------------------------------------------------------------------ shared across replicas
+    def _step_shared(self, ps: list, group: dict) -> None:
+        import torch.distributed as dist
+
+        pg = self.ns_share_group
+        replicas, me = dist.get_world_size(pg), dist.get_rank(pg)
+        owner = assign_to_replicas([tuple(p.shape) for p in ps], replicas, group["ns_steps"])
+        us = [self._prepare(p, group) for p in ps]                     # every replica: keeps momentum in sync
+        offsets, total = [], 0
+        for p in ps:
+            offsets.append(total)
+            total += (p.numel() + 7) // 8 * 8
+        flat = torch.zeros(total, dtype=torch.bfloat16, device=ps[0].device)
+        mine_by_shape: dict[tuple, list[int]] = {}
+        for j, p in enumerate(ps):
+            if owner[j] == me:
+                mine_by_shape.setdefault(tuple(p.shape), []).append(j)
+        for shape, idx in mine_by_shape.items():
+            per_chunk = max(1, MAX_BATCH_ELEMENTS // (shape[0] * shape[1]))
+            for i in range(0, len(idx), per_chunk):
+                chunk = idx[i:i + per_chunk]
+                for j, o in zip(chunk, self._orthogonalize([us[j] for j in chunk], group)):
+                    flat[offsets[j]:offsets[j] + ps[j].numel()].copy_(o.reshape(-1))
+        del us
+        if replicas > 1:
+            dist.all_reduce(flat, group=pg)
+        for j, p in enumerate(ps):
+            self._apply(p, flat[offsets[j]:offsets[j] + p.numel()].view(p.shape), group)

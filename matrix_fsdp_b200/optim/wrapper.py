@@ -304,6 +304,16 @@ def classify_matrix_optimizer_params(module_or_units, *, default_matrix_optimize
                                            tuple(adamw_fqns))
 
 
+def _common_replicate_group(units):
+    """The replicate process group when every unit is hybrid-sharded over the same one, else ``None``.  Replicas
+    then own the same matrices with the same reduced gradients, which is what sharing Newton-Schulz needs."""
+    groups = {id(u.flat_buffer.replicate_group): u.flat_buffer.replicate_group for u in units
+              if u.flat_buffer.replicate_world_size > 1}
+    if len(groups) != 1 or any(u.flat_buffer.replicate_world_size <= 1 for u in units):
+        return None
+    return next(iter(groups.values()))
+
+
 class _LazyMuonOptimizer:
     """Placeholder used when this rank owns no Muon matrices (keeps the mixed API uniform)."""
 
@@ -334,7 +344,8 @@ class MixedMuonAdamWOptimizer:
                  adamw_foreach: bool | None = None, muon_weight_decay: float | None = None,
                  muon_momentum: float = 0.5, muon_ns_steps: int = 2, muon_nesterov: bool = True,
                  muon_ns_coefficients=None, muon_adjust_lr_fn: str | None = DEFAULT_MUON_ADJUST_LR_FN,
-                 lazy_muon_init: bool = True, **scheduler_kwargs) -> None:
+                 lazy_muon_init: bool = True, muon_share_ns_across_replicas: bool = True,
+                 **scheduler_kwargs) -> None:
         sched_kw, extra = _split_scheduler_kwargs(scheduler_kwargs)
         if extra:
             raise TypeError(f"Unknown mixed optimizer options: {', '.join(sorted(extra))}.")
@@ -357,6 +368,8 @@ class MixedMuonAdamWOptimizer:
                 lr=lr if adamw_lr is None else adamw_lr, betas=adamw_betas, eps=adamw_eps,
                 weight_decay=weight_decay if adamw_weight_decay is None else adamw_weight_decay)
         self.adamw._low_precision_of = lp_of
+        if muon_share_ns_across_replicas and isinstance(self.muon, MatrixMuon):
+            self.muon.share_newton_schulz_over(_common_replicate_group(units))
         for opt in (self.muon, self.adamw):
             if isinstance(opt, Optimizer):
                 opt._mfsdp_lifecycle_managed = True
@@ -516,8 +529,11 @@ def configure_optimizer(module_or_units, optimizer: str | MatrixOptimizerConfig 
             if len(owned) != len([p for p in params if p.numel() > 0]):
                 raise ValueError("Muon only supports 2D parameters; use 'mixed_muon_adamw' for models with "
                                  "norms, biases or embeddings.")
+            share = opt_kwargs.pop("share_ns_across_replicas", True)
             inner = MatrixMuon(owned or [torch.nn.Parameter(torch.zeros(0, 0))],
                                low_precision_of=_low_precision_lookup(units), **opt_kwargs)
+            if share and units:
+                inner.share_newton_schulz_over(_common_replicate_group(units))
         else:
             raise ValueError("optimizer must be one of 'adamw', 'sgd', 'muon', or 'mixed_muon_adamw', "
                              f"got {kind!r}.")

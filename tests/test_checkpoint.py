@@ -58,7 +58,8 @@ def test_single_process_roundtrip_and_format():
         _train(other, opt2, seed=9)
         assert torch.equal(u.flat_buffer.local_shard, u2.flat_buffer.local_shard)
         # tampering with structure is caught before tensors are read
-        payload["ranks"][0]["units"][0]["local_end"] = 3
+        for key in ("param_groups", "units"):          # the list is stored under both names
+            payload["ranks"][0][key][0]["local_end"] = 3
         torch.save(payload, os.path.join(d, "matrix_metadata.pt"))
         with pytest.raises(ValueError, match="local_end"):
             load_matrix_dcp(other, d, no_dist=True)

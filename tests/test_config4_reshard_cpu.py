@@ -95,3 +95,38 @@ def test_hsdp_2x2_checkpoint_reshards_onto_dp_shard_4():
     with tempfile.TemporaryDirectory() as d:
         run_ranks(_worker, 4, d, timeout=600.0)
         assert os.path.exists(os.path.join(d, "matrix_metadata.pt"))
+
+
+def _shared_ns_worker(rank, world):
+    """Splitting Newton-Schulz over the two replicas changes who computes, not what: parameters and momentum
+    are bitwise those of the run where every replica orthogonalises every matrix."""
+    from matrix_fsdp_b200.optim.muon import MatrixMuon
+
+    results = {}
+    for share in (True, False):
+        model, opt = _build("hsdp")
+        muon = opt.muon
+        if isinstance(muon, MatrixMuon):
+            assert muon.ns_share_group is not None                   # hybrid mesh: sharing is on by default
+            if not share:
+                muon.share_newton_schulz_over(None)
+        done = 0
+        for s in range(3):
+            _step(model, opt, s)
+            done += getattr(muon, "ns_matrices_done", 0)
+        params, optim = _full_state(model, opt)
+        results[share] = (params, _flatten(optim), done)
+    (pa, oa, done_shared), (pb, ob, done_all) = results[True], results[False]
+    for k in pa:
+        assert torch.equal(pa[k], pb[k]), k
+    for k in oa:
+        if oa[k].dim() > 0:
+            assert torch.equal(oa[k], ob[k]), k
+    counts = torch.tensor([done_shared, done_all])
+    dist.all_reduce(counts)
+    assert counts[1] == 2 * counts[0] and counts[0] > 0              # each matrix orthogonalised once, not twice
+    dist.barrier()
+
+
+def test_hsdp_replicas_share_newton_schulz():
+    run_ranks(_shared_ns_worker, 4)

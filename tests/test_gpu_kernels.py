@@ -173,6 +173,18 @@ def test_cross_entropy(K, V):
     loss = K.cross_entropy_(work, tgt, 1.0 / n_valid)
     assert torch.allclose(loss, ref, atol=2e-2, rtol=1e-2)
     assert _rel_err(work, lf.grad) < 2e-2
+    # the same with the scale read from device memory, and through the masked-target functional path
+    work2 = logits.clone()
+    scale_dev = torch.full((1,), 1.0 / n_valid, device="cuda")
+    loss2 = K.cross_entropy_(work2, tgt, scale_dev)
+    assert torch.equal(loss2, loss) and torch.equal(work2, work)
+    from matrix_fsdp_b200.ops import functional as OF
+
+    lg = logits.clone().requires_grad_(True)
+    out = OF.fused_cross_entropy(lg * 1.0, tgt, ignore_index=-100)
+    assert abs(float(out) - float(ref.sum() / n_valid)) < 2e-2
+    out.backward()
+    assert _rel_err(lg.grad, lf.grad) < 2e-2
 
 
 @pytest.mark.parametrize("gdtype", [torch.bfloat16, torch.float32])
