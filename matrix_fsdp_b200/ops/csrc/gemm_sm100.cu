@@ -47,6 +47,13 @@ struct GemmArgs {
   int tiles_m_per_group;     // mode 2
   int m_per_group;           // mode 2
   int raster_group_m;        // M-tiles per rasterisation group
+  int total_tiles;           // work items walked by the persistent CTAs
+  // Symmetric output (sym_rows > 0): every output matrix is sym_rows*128 square and equal to its own
+  // transpose (X Xᵀ, polynomials of it), so only tiles that reach the diagonal or lie above it are
+  // computed; the caller mirrors the rest.  Work items enumerate exactly those tiles, row by row.
+  int sym_rows;              // 128-row tile rows per symmetric matrix (0 = off)
+  int sym_q;                 // tile width / 128 (1 or 2)
+  int sym_tiles_per_matrix;
   // Fused all-gather (GATHER kernels only): B's rows are still on peer GPUs when the kernel starts.
   // Eight extra warps per CTA copy them into B's local buffer job by job (16-byte peer loads, local
   // stores) and count finished jobs per B tile row-block; the TMA producer waits (bounded) until
@@ -86,17 +93,37 @@ struct TileCoord {
   bool skip;
 };
 
+// Tiles of tile-row i of a symmetric matrix that lie entirely below the diagonal: floor(i / q); the
+// number of kept tiles in rows [0, i) is therefore i * tiles_n - S(i), S(i) = sum_{j<i} floor(j / q).
+__host__ __device__ __forceinline__ int sym_kept_before(int i, int tiles_n, int q) {
+  const int m = i / q;
+  return i * tiles_n - (q * (m * (m - 1) / 2) + (i - m * q) * m);
+}
+
 __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, int tile) {
-  // Grouped rasterisation: 8 M-tiles share each sweep over N so that the CTAs running
-  // at the same time reuse A and B tiles out of L2.
-  const int kGroupM = p.raster_group_m;
-  const int per_group = kGroupM * p.tiles_n;
-  const int gid = tile / per_group;
-  const int first_m = gid * kGroupM;
-  const int gsz = min(p.tiles_m - first_m, kGroupM);
-  const int tm = first_m + (tile % per_group) % gsz;
-  int tn = (tile % per_group) / gsz;
-  if (p.ag_rotate) tn = (tn + p.ag_rotate) % p.tiles_n;
+  int tm, tn;
+  if (p.sym_rows > 0) {
+    const int mat = tile / p.sym_tiles_per_matrix;
+    const int rem = tile - mat * p.sym_tiles_per_matrix;
+    int lo = 0, hi = p.sym_rows - 1;      // last row i with sym_kept_before(i) <= rem
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (sym_kept_before(mid, p.tiles_n, p.sym_q) <= rem) lo = mid; else hi = mid - 1;
+    }
+    tm = mat * p.sym_rows + lo;
+    tn = lo / p.sym_q + (rem - sym_kept_before(lo, p.tiles_n, p.sym_q));
+  } else {
+    // Grouped rasterisation: 8 M-tiles share each sweep over N so that the CTAs running
+    // at the same time reuse A and B tiles out of L2.
+    const int kGroupM = p.raster_group_m;
+    const int per_group = kGroupM * p.tiles_n;
+    const int gid = tile / per_group;
+    const int first_m = gid * kGroupM;
+    const int gsz = min(p.tiles_m - first_m, kGroupM);
+    tm = first_m + (tile % per_group) % gsz;
+    tn = (tile % per_group) / gsz;
+    if (p.ag_rotate) tn = (tn + p.ag_rotate) % p.tiles_n;
+  }
   TileCoord c;
   c.skip = false;
   c.n0 = tn;  // scaled by the caller's BN
@@ -169,7 +196,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int total_tiles = p.tiles_m * p.tiles_n;
+  const int total_tiles = p.total_tiles;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -515,13 +542,15 @@ using namespace mfsdp;
 // group_mode 2 (K-grouped): both operands are MN-major and stacked along the reduce
 //   dimension; group g reduces rows [group_offsets[g], group_offsets[g+1]) and writes
 //   D rows [g*M, (g+1)*M).  M must be a multiple of 128 and offsets multiples of 64.
-MFSDP_API int mfsdp_gemm_bf16(const void* A, const void* B, void* D, const void* Cin, int M, int N,
-                              int K, long long lda, long long ldb, long long ldd, long long ldcin,
-                              int a_mn_major, int b_mn_major, float alpha, float beta,
-                              int group_mode, const int* tile_group, const int* group_offsets,
-                              int num_groups, long long k_total, int* status, int num_sms,
-                              int force_bn, cudaStream_t stream) {
+static int gemm_bf16_impl(const void* A, const void* B, void* D, const void* Cin, int M, int N,
+                          int K, long long lda, long long ldb, long long ldd, long long ldcin,
+                          int a_mn_major, int b_mn_major, float alpha, float beta,
+                          int group_mode, const int* tile_group, const int* group_offsets,
+                          int num_groups, long long k_total, int* status, int num_sms,
+                          int force_bn, int symmetric, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K < 0) return -2;
+  // symmetric outputs: square matrices of N rows (stacked along M in the grouped modes), whole tiles
+  if (symmetric && ((N % BM) != 0 || (group_mode == 1 ? (M % N) != 0 : M != N))) return -2;
   ensure_context_on_this_thread();
   if ((lda % 8) || (ldb % 8) || (ldd % 8)) return -2;
   if (((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)D & 15)) return -2;
@@ -553,7 +582,8 @@ MFSDP_API int mfsdp_gemm_bf16(const void* A, const void* B, void* D, const void*
     bn = 128;
   } else {
     auto eff = [&](int b) {
-      const long long t = (long long)args.tiles_m * ((N + b - 1) / b);
+      long long t = (long long)args.tiles_m * ((N + b - 1) / b);
+      if (symmetric) t = (long long)(args.tiles_m / (N / BM)) * sym_kept_before(N / BM, (N + b - 1) / b, b / BM);
       const long long waves = (t + num_sms - 1) / num_sms;
       const double padded_n = (double)((N + b - 1) / b) * b;
       return ((double)t / (double)(waves * num_sms)) * ((double)N / padded_n) *
@@ -579,7 +609,14 @@ MFSDP_API int mfsdp_gemm_bf16(const void* A, const void* B, void* D, const void*
   rc = make_tmap_bf16_2d(&td, D, d_rows, N, ldd, BM, 64);
   if (rc) return rc;
 
-  const int total = args.tiles_m * args.tiles_n;
+  int total = args.tiles_m * args.tiles_n;
+  if (symmetric) {
+    args.sym_rows = N / BM;
+    args.sym_q = bn / BM;
+    args.sym_tiles_per_matrix = sym_kept_before(args.sym_rows, args.tiles_n, args.sym_q);
+    total = (args.tiles_m / args.sym_rows) * args.sym_tiles_per_matrix;
+  }
+  args.total_tiles = total;
   const int grid = total < num_sms ? total : num_sms;
 #define MFSDP_LAUNCH(BN_)                                                                   \
   (a_mn_major ? (b_mn_major ? launch_gemm<BN_, true, true>(ta, tb, td, args, grid, stream)  \
@@ -588,6 +625,56 @@ MFSDP_API int mfsdp_gemm_bf16(const void* A, const void* B, void* D, const void*
                             : launch_gemm<BN_, false, false>(ta, tb, td, args, grid, stream)))
   return bn == 256 ? MFSDP_LAUNCH(256) : MFSDP_LAUNCH(128);
 #undef MFSDP_LAUNCH
+}
+
+MFSDP_API int mfsdp_gemm_bf16(const void* A, const void* B, void* D, const void* Cin, int M, int N,
+                              int K, long long lda, long long ldb, long long ldd, long long ldcin,
+                              int a_mn_major, int b_mn_major, float alpha, float beta,
+                              int group_mode, const int* tile_group, const int* group_offsets,
+                              int num_groups, long long k_total, int* status, int num_sms,
+                              int force_bn, cudaStream_t stream) {
+  return gemm_bf16_impl(A, B, D, Cin, M, N, K, lda, ldb, ldd, ldcin, a_mn_major, b_mn_major, alpha, beta, group_mode,
+                        tile_group, group_offsets, num_groups, k_total, status, num_sms, force_bn, 0, stream);
+}
+
+// Same product for outputs known to be symmetric (every output matrix is N x N with N a multiple of 128:
+// M == N, or M a multiple of N in the M-grouped mode).  Only the tiles on or above the diagonal are
+// computed and written; entries below the diagonal that fall outside those tiles are left untouched, so
+// the caller follows with mfsdp_mirror_upper.
+MFSDP_API int mfsdp_gemm_bf16_sym(const void* A, const void* B, void* D, const void* Cin, int M, int N,
+                                  int K, long long lda, long long ldb, long long ldd, long long ldcin,
+                                  int a_mn_major, int b_mn_major, float alpha, float beta,
+                                  int group_mode, const int* tile_group, const int* group_offsets,
+                                  int num_groups, long long k_total, int* status, int num_sms,
+                                  int force_bn, cudaStream_t stream) {
+  return gemm_bf16_impl(A, B, D, Cin, M, N, K, lda, ldb, ldd, ldcin, a_mn_major, b_mn_major, alpha, beta, group_mode,
+                        tile_group, group_offsets, num_groups, k_total, status, num_sms, force_bn, 1, stream);
+}
+
+// D[i][j] = D[j][i] for i > j, for `mats` stacked n x n matrices (n a multiple of 64), 64 x 64 blocks.
+__global__ void __launch_bounds__(256) mirror_upper_kernel(__nv_bfloat16* __restrict__ d, int n, long long ldd) {
+  __shared__ unsigned short tile[64][66];
+  const int bj = blockIdx.x, bi = blockIdx.y;
+  if (bi <= bj) return;                           // diagonal blocks were computed whole
+  unsigned short* base = reinterpret_cast<unsigned short*>(d) + (long long)blockIdx.z * n * ldd;
+  const int cp = threadIdx.x & 31, r0 = threadIdx.x >> 5;
+  for (int r = r0; r < 64; r += 8) {              // source block (bj, bi): above the diagonal
+    const unsigned v = *reinterpret_cast<const unsigned*>(base + (long long)(bj * 64 + r) * ldd + bi * 64 + 2 * cp);
+    tile[r][2 * cp] = (unsigned short)(v & 0xffffu);
+    tile[r][2 * cp + 1] = (unsigned short)(v >> 16);
+  }
+  __syncthreads();
+  for (int r = r0; r < 64; r += 8) {              // destination block (bi, bj), row r = source column r
+    const unsigned v = (unsigned)tile[2 * cp][r] | ((unsigned)tile[2 * cp + 1][r] << 16);
+    *reinterpret_cast<unsigned*>(base + (long long)(bi * 64 + r) * ldd + bj * 64 + 2 * cp) = v;
+  }
+}
+
+MFSDP_API int mfsdp_mirror_upper(void* D, int n, long long ldd, int mats, cudaStream_t stream) {
+  if (n <= 0 || (n % 64) != 0 || (ldd % 2) != 0 || mats <= 0 || ((uintptr_t)D & 3)) return -2;
+  if (n == 64) return 0;
+  mirror_upper_kernel<<<dim3(n / 64, n / 64, mats), 256, 0, stream>>>((__nv_bfloat16*)D, n, ldd);
+  return (int)cudaGetLastError();
 }
 
 // All-gather fused into the GEMM that first consumes the gathered weight:
@@ -631,6 +718,7 @@ MFSDP_API int mfsdp_gemm_bf16_ag(const void* A, const void* B, void* D, const vo
   rc = make_tmap_bf16_2d(&td, D, M, N, ldd, BM, 64);
   if (rc) return rc;
   const int total = args.tiles_m * args.tiles_n;
+  args.total_tiles = total;
   const int grid = total < num_sms ? total : num_sms;
   return bn == 256 ? launch_gemm<256, false, false, true>(ta, tb, td, args, grid, stream)
                    : launch_gemm<128, false, false, true>(ta, tb, td, args, grid, stream);

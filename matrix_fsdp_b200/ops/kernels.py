@@ -79,11 +79,13 @@ def _scratch_f32(n: int, device, tag: str) -> torch.Tensor:
 # ------------------------------------------------------------------ GEMM
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_major: bool = False,
          out: torch.Tensor | None = None, cin: torch.Tensor | None = None, alpha: float = 1.0,
-         beta: float = 0.0, force_bn: int = 0) -> torch.Tensor:
+         beta: float = 0.0, force_bn: int = 0, symmetric: bool = False) -> torch.Tensor:
     """``out[M,N] = alpha * A·Bᵀ + beta * cin`` on the tcgen05 kernel (bf16, fp32 accumulate).
 
     ``a`` is ``[M,K]`` (or ``[K,M]`` when ``a_mn_major``); ``b`` is ``[N,K]`` (or ``[K,N]`` when
     ``b_mn_major``).  Row strides must be multiples of 8 elements, inner stride 1.
+    ``symmetric``: the caller knows the result equals its transpose (M == N, a multiple of 128); only the
+    tiles on or above the diagonal are computed and the rest is mirrored (about half the tensor-core work).
     """
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
@@ -101,13 +103,26 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     assert out.shape == (M, N) and out.stride(1) == 1 and out.dtype == torch.bfloat16
     if cin is not None:
         assert cin.shape == (M, N) and cin.stride(1) == 1 and cin.dtype == torch.bfloat16
-    rc = _L().mfsdp_gemm_bf16(
+    if symmetric:
+        assert M == N and N % 128 == 0, "symmetric outputs must be square with a multiple of 128 rows"
+    rc = (_L().mfsdp_gemm_bf16_sym if symmetric else _L().mfsdp_gemm_bf16)(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), cin.data_ptr() if cin is not None else None,
         M, N, K, a.stride(0), b.stride(0), out.stride(0), cin.stride(0) if cin is not None else 0,
         int(a_mn_major), int(b_mn_major), float(alpha), float(beta), 0, None, None, 0, 0,
         status_word(a.device).data_ptr(), sm_count(a.device), force_bn, _stream())
     _lib.check(rc, "mfsdp_gemm_bf16")
+    if symmetric:
+        mirror_upper_(out, 1)
     return out
+
+
+def mirror_upper_(d: torch.Tensor, mats: int = 1) -> torch.Tensor:
+    """``d``: ``mats`` square matrices stacked along dim 0 (``[mats * n, n]``); copies each matrix's upper
+    triangle onto its lower one in 64 x 64 blocks (diagonal blocks are left as they are)."""
+    n = d.shape[-1]
+    assert d.dtype == torch.bfloat16 and d.stride(-1) == 1 and d.numel() == mats * n * n and d.is_contiguous()
+    _lib.check(_L().mfsdp_mirror_upper(d.data_ptr(), n, n, mats, _stream()), "mfsdp_mirror_upper")
+    return d
 
 
 def gemm_ag(a: torch.Tensor, b: torch.Tensor, plan, *, out: torch.Tensor | None = None,
@@ -138,12 +153,14 @@ def gemm_ag(a: torch.Tensor, b: torch.Tensor, plan, *, out: torch.Tensor | None 
 
 def grouped_gemm_m(a: torch.Tensor, b: torch.Tensor, tile_group: torch.Tensor, *,
                    b_mn_major: bool = False, out: torch.Tensor | None = None, cin: torch.Tensor | None = None,
-                   alpha: float = 1.0, beta: float = 0.0) -> torch.Tensor:
+                   alpha: float = 1.0, beta: float = 0.0, symmetric: bool = False) -> torch.Tensor:
     """M-grouped GEMM: rows of ``a`` come in 128-row tiles, tile ``t`` uses ``b[tile_group[t]]``;
     ``out = alpha * a·b[g]ᵀ + beta * cin`` (``cin``: ``[Mtot, N]``).
 
     ``a``: ``[Mtot, K]``; ``b``: ``[G, N, K]`` (or ``[G, K, N]`` when ``b_mn_major``); tiles whose
-    group id is negative are skipped (their output rows are left untouched).
+    group id is negative are skipped (their output rows are left untouched).  ``symmetric``: ``a`` stacks
+    ``Mtot / N`` blocks of ``N`` rows whose outputs are symmetric ``N x N`` matrices (``N`` a multiple of 128);
+    tiles below the diagonal are mirrored instead of computed.
     """
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and b.dim() == 3
     assert b.is_contiguous() and a.stride(1) == 1 and tile_group.dtype == torch.int32
@@ -162,17 +179,21 @@ def grouped_gemm_m(a: torch.Tensor, b: torch.Tensor, tile_group: torch.Tensor, *
         out = torch.empty((Mtot, N), dtype=torch.bfloat16, device=a.device)
     if cin is not None:
         assert cin.shape == (Mtot, N) and cin.stride(1) == 1 and cin.dtype == torch.bfloat16
-    rc = _L().mfsdp_gemm_bf16(
+    if symmetric:
+        assert N % 128 == 0 and Mtot % N == 0 and out.is_contiguous()
+    rc = (_L().mfsdp_gemm_bf16_sym if symmetric else _L().mfsdp_gemm_bf16)(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), cin.data_ptr() if cin is not None else None, Mtot, N, K,
         a.stride(0), ldb, out.stride(0), cin.stride(0) if cin is not None else 0, 0, int(b_mn_major),
         float(alpha), float(beta), 1, tile_group.data_ptr(), None, G, 0,
         status_word(a.device).data_ptr(), sm_count(a.device), 0, _stream())
     _lib.check(rc, "mfsdp_gemm_bf16[m-grouped]")
+    if symmetric:
+        mirror_upper_(out, Mtot // N)
     return out
 
 
 def grouped_gemm_k(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Tensor, num_groups: int,
-                   out: torch.Tensor | None = None) -> torch.Tensor:
+                   out: torch.Tensor | None = None, symmetric: bool = False) -> torch.Tensor:
     """K-grouped GEMM (expert wgrad): ``out[g] = a[rows_g]ᵀ · b[rows_g]``.
 
     ``a``: ``[Ktot, M]``, ``b``: ``[Ktot, N]``; ``group_offsets`` int32 ``[G+1]`` with offsets that
@@ -184,11 +205,15 @@ def grouped_gemm_k(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Tensor
     assert b.shape[0] == Ktot and group_offsets.dtype == torch.int32
     if out is None:
         out = torch.empty((num_groups, M, N), dtype=torch.bfloat16, device=a.device)
-    rc = _L().mfsdp_gemm_bf16(
+    if symmetric:     # every out[g] equals its transpose (a is b): mirror instead of computing the lower tiles
+        assert M == N and N % 128 == 0 and out.is_contiguous()
+    rc = (_L().mfsdp_gemm_bf16_sym if symmetric else _L().mfsdp_gemm_bf16)(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), None, M, N, 0, a.stride(0), b.stride(0), N, 0,
         1, 1, 1.0, 0.0, 2, None, group_offsets.data_ptr(), num_groups, Ktot,
         status_word(a.device).data_ptr(), sm_count(a.device), 0, _stream())
     _lib.check(rc, "mfsdp_gemm_bf16[k-grouped]")
+    if symmetric:
+        mirror_upper_(out.view(num_groups * M, N), num_groups)
     return out
 
 

@@ -22,6 +22,9 @@ vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float
 _SIGNATURES: dict[str, list] = {
     "mfsdp_gemm_bf16": [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i32, i32, f32, f32,
                         i32, vp, vp, i32, i64, vp, i32, i32, vp],
+    "mfsdp_gemm_bf16_sym": [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i32, i32, f32, f32,
+                            i32, vp, vp, i32, i64, vp, i32, i32, vp],
+    "mfsdp_mirror_upper": [vp, i32, i64, i32, vp],
     "mfsdp_gemm_bf16_ag": [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, f32, f32, vp, vp, vp, vp, i32, vp, vp, vp, i32,
                            i32, C.c_ulonglong, vp, i32, vp],
     "mfsdp_rmsnorm_fwd": [vp, vp, vp, vp, i64, i32, f32, vp],

@@ -9,7 +9,10 @@ Update rule (identical to ``torch.optim.Muon``, ``torch/optim/_muon.py:276-310``
 
 On CUDA each Newton-Schulz product runs on the tcgen05 GEMM with the polynomial folded into
 the epilogue (``alpha * acc + beta * C``), so an iteration is three kernels with no separate
-axpy, and tall matrices are handled by switching operand majors instead of transposing.  The
+axpy, and tall matrices are handled by switching operand majors instead of transposing.  The Gram
+matrix and its polynomial are symmetric: their GEMMs compute only the tiles that reach the diagonal
+or lie above it and a small block-transpose kernel mirrors the rest (two of the three products of an
+iteration do about half the tensor-core work).  The
 element-wise stages (momentum/Nesterov + Frobenius norm, scaling, parameter update + bf16 emit)
 are single fused kernels.  The reference delegates all of this to ``torch.optim.Muon``
 (``matrix_fsdp/optim/wrapper.py:416-429``), i.e. 15 cuBLAS ``addmm`` calls per matrix.
@@ -17,6 +20,7 @@ are single fused kernels.  The reference delegates all of this to ``torch.optim.
 from __future__ import annotations
 
 import math
+import os
 from collections.abc import Iterable
 
 import torch
@@ -26,6 +30,8 @@ DEFAULT_NS_COEFFICIENTS = (3.4445, -4.7750, 2.0315)
 DEFAULT_MUON_ADJUST_LR_FN = "match_rms_adamw"
 EPS = 1e-7
 MAX_BATCH_ELEMENTS = 1 << 28      # elements of one stacked Newton-Schulz operand (512 MB of bf16)
+# X Xᵀ and b A + c A A are symmetric: compute the tiles on or above the diagonal, mirror the rest
+SYMMETRIC_PRODUCTS = os.environ.get("MFSDP_MUON_SYMMETRIC", "1") != "0"
 
 
 def adjust_lr(lr: float, adjust_lr_fn: str | None, shape) -> float:
@@ -68,14 +74,15 @@ def newton_schulz_sm100(x: torch.Tensor, coefficients=DEFAULT_NS_COEFFICIENTS, s
     gram = torch.empty((n, n), dtype=torch.bfloat16, device=x.device)
     poly = torch.empty_like(gram)
     nxt = torch.empty_like(x)
+    sym = n % 128 == 0 and SYMMETRIC_PRODUCTS     # Gram matrix and its polynomial equal their transposes
     for _ in range(steps):
         if tall:
-            K.gemm(x, x, a_mn_major=True, b_mn_major=True, out=gram)            # XᵀX
-            K.gemm(gram, gram, out=poly, cin=gram, alpha=c, beta=b)             # bA + cAA
+            K.gemm(x, x, a_mn_major=True, b_mn_major=True, out=gram, symmetric=sym)            # XᵀX
+            K.gemm(gram, gram, out=poly, cin=gram, alpha=c, beta=b, symmetric=sym)             # bA + cAA
             K.gemm(x, poly, out=nxt, cin=x, alpha=1.0, beta=a)                  # aX + X B
         else:
-            K.gemm(x, x, out=gram)                                              # XXᵀ
-            K.gemm(gram, gram, out=poly, cin=gram, alpha=c, beta=b)
+            K.gemm(x, x, out=gram, symmetric=sym)                                              # XXᵀ
+            K.gemm(gram, gram, out=poly, cin=gram, alpha=c, beta=b, symmetric=sym)
             K.gemm(poly, x, b_mn_major=True, out=nxt, cin=x, alpha=1.0, beta=a)  # aX + B X
         x, nxt = nxt, x
     return x
@@ -115,17 +122,18 @@ def newton_schulz_sm100_batched(x: torch.Tensor, coefficients=DEFAULT_NS_COEFFIC
     x2 = x.reshape(G * rows, cols)
     nxt = torch.empty_like(x2)
     tg_n = _tile_groups(G, n, dev)
+    sym = SYMMETRIC_PRODUCTS          # n is a multiple of 128 here
     if tall:
         offsets = torch.arange(G + 1, dtype=torch.int32, device=dev) * rows
         tg_rows = _tile_groups(G, rows, dev)
     for _ in range(steps):
         if tall:
-            K.grouped_gemm_k(x2, x2, offsets, G, out=gram.view(G, n, n))                                  # XᵀX
-            K.grouped_gemm_m(gram, gram.view(G, n, n), tg_n, out=poly, cin=gram, alpha=c, beta=b)        # bA + cAA
+            K.grouped_gemm_k(x2, x2, offsets, G, out=gram.view(G, n, n), symmetric=sym)                   # XᵀX
+            K.grouped_gemm_m(gram, gram.view(G, n, n), tg_n, out=poly, cin=gram, alpha=c, beta=b, symmetric=sym)  # bA + cAA
             K.grouped_gemm_m(x2, poly.view(G, n, n), tg_rows, out=nxt, cin=x2, alpha=1.0, beta=a)        # aX + X B
         else:
-            K.grouped_gemm_m(x2, x2.view(G, n, cols), tg_n, out=gram)                                     # XXᵀ
-            K.grouped_gemm_m(gram, gram.view(G, n, n), tg_n, out=poly, cin=gram, alpha=c, beta=b)
+            K.grouped_gemm_m(x2, x2.view(G, n, cols), tg_n, out=gram, symmetric=sym)                      # XXᵀ
+            K.grouped_gemm_m(gram, gram.view(G, n, n), tg_n, out=poly, cin=gram, alpha=c, beta=b, symmetric=sym)
             K.grouped_gemm_m(poly, x2.view(G, n, cols), tg_n, b_mn_major=True, out=nxt, cin=x2, alpha=1.0, beta=a)
         x2, nxt = nxt, x2
     return x2.view(G, rows, cols)
