@@ -191,3 +191,32 @@ def test_runbook_summariser_builds_tables_from_logs(tmp_path, capsys):
     for title in ("step time by mode", "both arms", "collectives", "device time of collectives", "memory", "failures"):
         assert f"== {title} ==" in text
     assert "1.250" in text and "1.500" in text
+
+
+def test_planner_report_units_models_and_json(capsys):
+    """Every model kind and unit granularity plans; the JSON form carries the per-unit candidate rows and the
+    per-rank totals, and the totals are the sums of the selected rows."""
+    for model in planner_report.MODELS:
+        assert planner_report.main(["--model", model, "--layers", "2", "--hidden", "128", "--heads", "2", "--experts", "4",
+                                    "--world-size", "4", "--selected-only"]) == 0
+        assert "== rank load ==" in capsys.readouterr().out
+    assert planner_report.main(["--model", "transformer", "--unit", "linear", "--policy", "balanced", "--layers", "1",
+                                "--hidden", "128", "--world-size", "2", "--format", "json"]) == 0
+    d = json.loads(capsys.readouterr().out)
+    assert len(d["units"]) == 5                      # qkv, proj, fc1, fc2 and the two norms as <root>
+    assert d["units"][-1]["unit"] == "<root>" and all(len(u["rows"]) > 1 for u in d["units"][:-1])
+    for key, field in (("rank_units", "rank_units"), ("rank_memory_bytes", "rank_memory_bytes"),
+                       ("rank_comm_bytes", "rank_comm_bytes")):
+        sums = [sum(u["rows"][0][field][r] for u in d["units"]) for r in range(2)]
+        assert list(d[key]) == sums
+    # a stateful owner planner sees the units in order: its running load is monotone and ends at the totals
+    assert planner_report.main(["--unit", "block", "--layers", "3", "--hidden", "128", "--world-size", "4",
+                                "--owner-assignment", "rotate", "--rotation-strategy", "round_robin", "--format", "json"]) == 0
+    d = json.loads(capsys.readouterr().out)
+    loads = [u["cumulative_rank_units"] for u in d["units"]]
+    assert list(loads[-1]) == list(d["rank_units"]) and all(a <= b for x, y in zip(loads, loads[1:]) for a, b in zip(x, y))
+    assert d["imbalance"]["units"] >= 1.0 and sum(d["rank_ns_flops"]) > 0
+    # the whole model as one unit under the model-wide assignment
+    assert planner_report.main(["--unit", "model", "--owner-assignment", "model_wide", "--layers", "2", "--hidden", "128",
+                                "--world-size", "4", "--selected-only"]) == 0
+    assert "<model>" in capsys.readouterr().out
