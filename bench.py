@@ -135,12 +135,20 @@ def build_ours_moe(cfg: dict, device, mesh, world: int):
               optimizer_policy="mixed_muon_adamw")
     opt = configure_moe_optimizer(model, "mixed_muon_adamw", muon_lr=cfg["lr"], adamw_lr=3e-4,
                                   adamw_betas=cfg["betas"], weight_decay=cfg["weight_decay"], muon_momentum=0.95,
-                                  muon_ns_steps=5, muon_adjust_lr_fn="original")
+                                  muon_ns_steps=5, muon_adjust_lr_fn="original", **_sched_overrides())
     from matrix_fsdp_b200.parallel.unit_collection import collect_param_groups
 
     for u in collect_param_groups(model):
         u.runtime_trace_enabled = False
     return model, opt
+
+
+_SCHED_OVERRIDES: dict = {}
+
+
+def _sched_overrides() -> dict:
+    """Scheduler options given as ``--sched KEY=VALUE`` (experiments; the headline run passes none)."""
+    return dict(_SCHED_OVERRIDES)
 
 
 def build_ours(cfg: dict, device, mesh, world: int):
@@ -166,11 +174,11 @@ def build_ours(cfg: dict, device, mesh, world: int):
         # the sharded AdamW update runs inside the gradient reduce-scatter kernel (peer transport, N > 1)
         fused = world > 1 and os.environ.get("MFSDP_FUSED_REDUCE_UPDATE", "1") != "0"
         opt = configure_optimizer(model, "adamw", lr=cfg["lr"], betas=cfg["betas"], weight_decay=cfg["weight_decay"],
-                                  fused_reduce_update=fused)
+                                  fused_reduce_update=fused, **_sched_overrides())
     else:
         opt = configure_optimizer(model, "mixed_muon_adamw", muon_lr=cfg["lr"], adamw_lr=3e-4,
                                   adamw_betas=cfg["betas"], weight_decay=cfg["weight_decay"], muon_momentum=0.95,
-                                  muon_ns_steps=5, muon_adjust_lr_fn="original")
+                                  muon_ns_steps=5, muon_adjust_lr_fn="original", **_sched_overrides())
     from matrix_fsdp_b200.parallel.unit_collection import collect_param_groups
 
     for u in collect_param_groups(model):
@@ -414,11 +422,17 @@ def main() -> None:
     ap.add_argument("--device", default=None)
     ap.add_argument("--verify-reshard", action="store_true",
                     help="after timing: save_matrix_dcp, load resharded onto a flat dp_shard mesh, compare checksums")
+    ap.add_argument("--sched", nargs="*", default=[], metavar="KEY=VALUE",
+                    help="scheduler options for the repo's arm, e.g. next_step_prefetch_units=1")
     ap.add_argument("--timeline", default=None, metavar="FILE.md",
                     help="after timing: run 3 more steps with CUDA-event spans around every collective and write "
                          "the per-unit table (start, device time, exposed wait; max over ranks) to FILE.md")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
+    for kv in args.sched:
+        k, _, v = kv.partition("=")
+        _SCHED_OVERRIDES[k] = {"true": True, "false": False, "none": None}.get(v.lower(), None) if v.lower() in (
+            "true", "false", "none") else (int(v) if v.lstrip("-").isdigit() else (float(v) if v.replace(".", "", 1).isdigit() else v))
     dump_after = float(os.environ.get("MFSDP_BENCH_DUMP_STACKS_AFTER_S", "0"))
     if dump_after > 0:           # diagnose a run that stops making progress: print every thread's stack
         import faulthandler

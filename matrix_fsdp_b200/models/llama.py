@@ -179,7 +179,7 @@ class LlamaModel(nn.Module):
         return self.head.lm_head
 
     def forward(self, tokens: torch.Tensor, targets: torch.Tensor | None = None) -> torch.Tensor:
-        x = self.embed(tokens)
+        x = OF.embedding(tokens, self.embed.weight, self.embed.weight)
         for layer in self.layers:
             x = layer(x)
         logits = self.head(x)

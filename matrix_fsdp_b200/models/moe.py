@@ -162,7 +162,7 @@ class MoEModel(nn.Module):
         return [p for layer in self.layers for p in layer.experts.parameters()]
 
     def forward(self, tokens: torch.Tensor, targets: torch.Tensor | None = None) -> torch.Tensor:
-        x = self.embed(tokens)
+        x = OF.embedding(tokens, self.embed.weight, self.embed.weight)
         for layer in self.layers:
             x = layer(x)
         logits = self.head(x)

@@ -580,6 +580,97 @@ static inline int grid_for(long long work, int threads, int max_blocks = 148 * 8
   return (int)b;
 }
 
+// ============================================================== embedding backward
+// dW[v, :] = sum over the positions t with ids[t] == v of dy[t, :], written (or accumulated) straight into
+// the gradient bucket.  A stable counting sort of the T token ids (count per id, exclusive scan over the
+// vocabulary, rank of each position among the earlier equal ids) gives every vocabulary row the list of its
+// positions in their original order, so the fp32 sum of a row is the same in every run; one CTA per
+// vocabulary row then sums its list and writes the row once, zeros where an id does not occur -- no separate
+// fill of the V x H gradient, no atomics on values, and five short launches instead of a 64-bit radix sort.
+__global__ void embed_count_kernel(const long long* __restrict__ ids, int T, int V, int* __restrict__ count) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  const long long v = ids[t];
+  if (v >= 0 && v < V) atomicAdd(&count[v], 1);
+}
+
+__global__ void __launch_bounds__(1024) embed_scan_kernel(const int* __restrict__ count, int* __restrict__ start, int V) {
+  __shared__ int part[1024];
+  const int per = (V + 1023) / 1024;
+  const int lo = min(threadIdx.x * per, V), hi = min(lo + per, V);
+  int s = 0;
+  for (int i = lo; i < hi; ++i) s += count[i];
+  part[threadIdx.x] = s;
+  __syncthreads();
+  for (int off = 1; off < 1024; off <<= 1) {      // inclusive scan of the 1024 partial sums
+    const int add = threadIdx.x >= off ? part[threadIdx.x - off] : 0;
+    __syncthreads();
+    part[threadIdx.x] += add;
+    __syncthreads();
+  }
+  int run = part[threadIdx.x] - s;
+  for (int i = lo; i < hi; ++i) {
+    start[i] = run;
+    run += count[i];
+  }
+}
+
+__global__ void __launch_bounds__(256) embed_place_kernel(const long long* __restrict__ ids, int T, int V,
+                                                          const int* __restrict__ start, int* __restrict__ order) {
+  __shared__ int tile[2048];
+  const int t = blockIdx.x * 256 + threadIdx.x;
+  const long long mine64 = t < T ? ids[t] : -1;
+  const bool valid = mine64 >= 0 && mine64 < V;
+  const int mine = valid ? (int)mine64 : -1;
+  const int limit = min((blockIdx.x + 1) * 256, T);   // positions before the end of this block
+  int rank = 0;
+  for (int base = 0; base < limit; base += 2048) {
+    const int n = min(2048, limit - base);
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += 256) {
+      const long long v = ids[base + i];
+      tile[i] = (v >= 0 && v < V) ? (int)v : -2;
+    }
+    __syncthreads();
+    if (valid) {
+      const int upto = min(n, t - base);             // only earlier positions count
+      for (int i = 0; i < upto; ++i) rank += (tile[i] == mine);
+    }
+  }
+  if (valid) order[start[mine] + rank] = t;
+}
+
+__global__ void __launch_bounds__(256) embed_sum_kernel(const __nv_bfloat16* __restrict__ dy, long long lddy,
+                                                        __nv_bfloat16* __restrict__ dw, long long lddw, int H,
+                                                        const int* __restrict__ count, const int* __restrict__ start,
+                                                        const int* __restrict__ order, int accumulate) {
+  const int v = blockIdx.x;
+  const int n = count[v];
+  if (n == 0 && accumulate) return;
+  const int first = start[v];
+  __nv_bfloat16* out = dw + (long long)v * lddw;
+  for (int c = threadIdx.x * 8; c < H; c += 256 * 8) {
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    if (accumulate) {
+      const uint4 u = *reinterpret_cast<const uint4*>(out + c);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { const float2 a = unpack_bf16x2(w[e]); acc[2 * e] = a.x; acc[2 * e + 1] = a.y; }
+    }
+    for (int j = 0; j < n; ++j) {
+      const int t = order[first + j];
+      const uint4 u = *reinterpret_cast<const uint4*>(dy + (long long)t * lddy + c);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { const float2 a = unpack_bf16x2(w[e]); acc[2 * e] += a.x; acc[2 * e + 1] += a.y; }
+    }
+    *reinterpret_cast<uint4*>(out + c) = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                                    pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+  }
+}
+
 }  // namespace mfsdp
 
 using namespace mfsdp;
@@ -645,6 +736,25 @@ MFSDP_API int mfsdp_swiglu_fwd(const void* gu, void* h, long long T, int F, cuda
   if (F % 8) return -2;
   swiglu_fwd_kernel<<<grid_for(T * (F / 8), 256, 148 * 16), 256, 0, st>>>((const __nv_bfloat16*)gu,
                                                                  (__nv_bfloat16*)h, T, F);
+  return (int)cudaGetLastError();
+}
+
+// dW[V, H] (row pitch lddw) from dy[T, H] (row pitch lddy) and ids[T]; `work` holds 2 * V + T ints.  Ids outside
+// [0, V) contribute nothing.  accumulate != 0 adds to what dW holds (rows whose id does not occur stay as they are).
+MFSDP_API int mfsdp_embedding_bwd(const void* dy, long long lddy, const long long* ids, void* dw, long long lddw,
+                                  int T, int V, int H, int accumulate, int* work, cudaStream_t st) {
+  if (T <= 0 || V <= 0 || H <= 0 || (H % 8) || (lddy % 8) || (lddw % 8)) return -2;
+  if (((uintptr_t)dy & 15) || ((uintptr_t)dw & 15)) return -2;
+  int* count = work;
+  int* start = work + V;
+  int* order = work + 2 * (long long)V;
+  cudaError_t e = cudaMemsetAsync(count, 0, sizeof(int) * (size_t)V, st);
+  if (e != cudaSuccess) return (int)e;
+  embed_count_kernel<<<(T + 255) / 256, 256, 0, st>>>(ids, T, V, count);
+  embed_scan_kernel<<<1, 1024, 0, st>>>(count, start, V);
+  embed_place_kernel<<<(T + 255) / 256, 256, 0, st>>>(ids, T, V, start, order);
+  embed_sum_kernel<<<V, 256, 0, st>>>((const __nv_bfloat16*)dy, lddy, (__nv_bfloat16*)dw, lddw, H, count, start, order,
+                                       accumulate);
   return (int)cudaGetLastError();
 }
 

@@ -278,6 +278,28 @@ def swiglu_bwd(dh: torch.Tensor, gu: torch.Tensor, out: torch.Tensor | None = No
     return dgu
 
 
+_EMBED_WORK: dict[tuple, torch.Tensor] = {}
+
+
+def embedding_bwd(dy: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch.Tensor:
+    """``out[v] (+)= sum of dy[t] over positions with ids[t] == v`` (bf16 rows, fp32 sums in position order).
+
+    ``dy``: ``[T, H]`` bf16, ``ids``: ``[T]`` int64, ``out``: ``[V, H]`` bf16 with unit inner stride.  Without
+    ``accumulate`` every row of ``out`` is written (zeros where an id does not occur)."""
+    assert dy.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and ids.dtype == torch.int64
+    assert dy.dim() == 2 and out.dim() == 2 and dy.stride(1) == 1 and out.stride(1) == 1 and ids.is_contiguous()
+    T, H = dy.shape
+    V = out.shape[0]
+    assert out.shape[1] == H and ids.numel() == T
+    key = (V, T, str(dy.device))
+    work = _EMBED_WORK.get(key)
+    if work is None:      # count | start | order; reused by every call of this size (calls are stream-ordered)
+        work = _EMBED_WORK[key] = torch.empty(2 * V + T, dtype=torch.int32, device=dy.device)
+    _lib.check(_L().mfsdp_embedding_bwd(dy.data_ptr(), dy.stride(0), ids.data_ptr(), out.data_ptr(), out.stride(0),
+                                        T, V, H, int(accumulate), work.data_ptr(), _stream()), "embedding_bwd")
+    return out
+
+
 def cross_entropy_(logits: torch.Tensor, target: torch.Tensor, grad_scale: float | torch.Tensor,
                    ignore_index: int = -100) -> torch.Tensor:
     """Per-row loss (fp32); ``logits`` is overwritten with ``(softmax - onehot) * grad_scale``.

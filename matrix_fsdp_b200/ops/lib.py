@@ -32,6 +32,7 @@ _SIGNATURES: dict[str, list] = {
     "mfsdp_rope": [vp, vp, vp, i64, i32, i32, i32, i32, i32, f32, vp],
     "mfsdp_swiglu_fwd": [vp, vp, i64, i32, vp],
     "mfsdp_swiglu_bwd": [vp, vp, vp, i64, i32, vp],
+    "mfsdp_embedding_bwd": [vp, i64, vp, vp, i64, i32, i32, i32, i32, vp, vp],
     "mfsdp_cross_entropy": [vp, vp, vp, i64, i32, i64, f32, i64, vp],
     "mfsdp_cross_entropy_dev_scale": [vp, vp, vp, i64, i32, i64, vp, i64, vp],
     "mfsdp_adamw_flat": [vp, vp, vp, vp, i32, vp, i64, f32, f32, f32, f32, f32, i64, f32, vp],

@@ -180,6 +180,7 @@ class MatrixFlatBuffer:
         # a callable returning the update arguments for this reduction, or None to reduce normally.
         self.fused_reduce_update = None
         self.fused_update_applied = False
+        self.update_done_event = None     # CUDA event after which this step's fused update of the unit is complete
         self.deferred_gather = None          # plan of the all-gather rows left to the first consumer GEMM
 
     # ------------------------------------------------------------------ helpers
@@ -307,9 +308,13 @@ class MatrixFlatBuffer:
                 self.local_shard_lp.copy_(self.local_shard)
             self.lp_stale = False
 
-    def start_all_gather_full_params(self, *, stream=None, defer: tuple | None = None) -> MatrixCollectiveHandle:
+    def start_all_gather_full_params(self, *, stream=None, defer: tuple | None = None,
+                                     ordered_by_caller: bool = False) -> MatrixCollectiveHandle:
         """``defer`` = (lo, hi, row_len): leave that range of the full buffer to the GEMM that reads it
-        first (transports that can; the plan is then in ``self.deferred_gather``)."""
+        first (transports that can; the plan is then in ``self.deferred_gather``).  ``ordered_by_caller``: the
+        caller made ``stream`` wait for the event after which this unit's shard is final, so the gather need
+        not wait for the rest of the current stream (only with a persistent full-parameter slot: a buffer from
+        the caching allocator is tied to the current stream)."""
         if self.pending_gather is not None:
             return self.pending_gather
         self.refresh_low_precision_shard()
@@ -330,6 +335,9 @@ class MatrixFlatBuffer:
                     raise RuntimeError("param_gather_strategy='owner_broadcast' requires whole-parameter owner shards.")
                 h = self.library_transport().gather(self._gather_source_tensor(), self.full_buffer, self.tables,
                                                     stream=stream, unit_key=self.unit_key, impl=self.gather_impl)
+            elif ordered_by_caller and self.full_persistent and stream is not None:
+                h = self.transport.gather(self._gather_source_tensor(), self.full_buffer, self.tables, stream=stream,
+                                          unit_key=self.unit_key, wait_current=False)
             else:
                 h = self.transport.gather(self._gather_source_tensor(), self.full_buffer, self.tables, stream=stream,
                                           unit_key=self.unit_key)
@@ -462,6 +470,7 @@ class MatrixFlatBuffer:
         out = self._ensure_local_grad_shard()
         src = self.bucket.ensure()
         scale = self.grad_scale()
+        self.update_done_event = None
         if self.world_size == 1 and self.replicate_world_size == 1 and self.full_aliases_shard \
                 and (src.dtype == out.dtype or self.fused_optimizer_consumes_bucket) and scale == 1.0 \
                 and not self.accumulate_into_local_grad:
@@ -482,6 +491,7 @@ class MatrixFlatBuffer:
                 h = self.transport.reduce_update(src, self.tables, update, scale=scale, stream=stream,
                                                  unit_key=self.unit_key)
                 self.fused_update_applied = True
+                self.update_done_event = getattr(h, "_event", None)
                 self.pending_reduce = h
                 return h
         library = (strategy in ("flat", "per_param") or self.reduce_impl is not None) and self.world_size > 1

@@ -367,11 +367,17 @@ class MatrixFSDPParamGroup:
                 raise RuntimeError(f"{self.name}: {self.state.value} but parameters still view the full buffer.")
 
     # ------------------------------------------------------------------ unshard / reshard
-    def start_unshard(self, reason: str = "manual") -> None:
+    def start_unshard(self, reason: str = "manual", after_event=None) -> None:
+        """``after_event``: the parameters of this unit are final once this CUDA event has happened (its
+        update ran inside its own reduce-scatter); the gather waits for it instead of the whole optimizer step."""
         if self.flat_buffer.pending_gather is not None or self.state == FSDPLifecycleState.UNSHARDED:
             return
         t0 = time.perf_counter()
-        if self.scheduler is not None:
+        if after_event is not None and self.all_gather_stream is not None:
+            self.all_gather_stream.wait_event(after_event)
+            if self.scheduler is not None:
+                self.scheduler.note_unshard_started(self)
+        elif self.scheduler is not None:
             self.scheduler.wait_for_post_optimizer_event_before_all_gather(self)
             self.scheduler.note_unshard_started(self)
         # Fuse the q|k|v rows into the block's first GEMM when the gather is on the critical path (issued by
@@ -383,7 +389,8 @@ class MatrixFSDPParamGroup:
                 and not self.flat_buffer.full_persistent:
             defer = self.fused_first_gemm_range
         with nvtx_range(f"mfsdp.all_gather:{self.name}"):
-            h = self.flat_buffer.start_all_gather_full_params(stream=self.all_gather_stream, defer=defer)
+            h = self.flat_buffer.start_all_gather_full_params(stream=self.all_gather_stream, defer=defer,
+                                                              ordered_by_caller=after_event is not None)
         self.unshard_prefetched = reason.endswith("prefetch")
         if getattr(h, "span", None) is not None:
             h.span.unit, h.span.reason = self.name, reason

@@ -579,7 +579,9 @@ class PeerTransport(LocalTransport):
         self.launches += 1
 
     def gather(self, shard, full, tables: SegmentTables, *, stream=None, unit_key=None,
-               defer: tuple | None = None) -> MatrixCollectiveHandle:
+               defer: tuple | None = None, wait_current: bool = True) -> MatrixCollectiveHandle:
+        """``wait_current=False``: the caller has already ordered ``stream`` behind everything the gather
+        depends on (the event of the unit's fused update); it is then not made to wait for the current stream."""
         buf = self.ctx.lookup(shard)
         if buf is None:
             raise RuntimeError("peer gather needs a shard that lives in symmetric memory")
@@ -591,7 +593,7 @@ class PeerTransport(LocalTransport):
         ctx = self.ctx
         cur = torch.cuda.current_stream()
         run = stream if stream is not None else cur
-        if stream is not None:
+        if stream is not None and wait_current:
             stream.wait_stream(cur)
         span = _tl.open_span(unit_key or "", "all_gather", run, nbytes=full.numel() * es)
         fslot = self._full_slot_of_unit.get(unit_key)

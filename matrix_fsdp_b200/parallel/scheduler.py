@@ -70,6 +70,11 @@ class MatrixFSDPSchedulerConfig:
     # after optimizer.step(): start the all-gather of the unit that ran first in the last forward, so the
     # next step does not begin with an exposed gather (None: on for CUDA, off on CPU)
     prefetch_first_unit_after_step: bool | None = None
+    # how many units of the next forward are gathered right after the step.  More than one only happens for
+    # units whose update was fused into their reduce-scatter: each of those gathers waits for its own unit's
+    # update alone, so the gather of the second unit runs beside the reduce-scatter of the first (opposite
+    # link directions) instead of after the whole optimizer step.
+    next_step_prefetch_units: int = 2
     # the unit whose forward ran last in the previous iteration is not resharded after its forward (its
     # backward follows at once); None: on for CUDA with more than one unit, off on CPU
     keep_last_forward_unit_unsharded: bool | None = None
@@ -419,10 +424,24 @@ class MatrixFSDPScheduler:
             want = dev.type == "cuda"
         if not want or not self.forward_order or self._fwd_budget() <= 0:
             return
-        first = self.forward_order[0]
-        if not first.forward_prefetch or first.state.value != "sharded" or first.flat_buffer.pending_gather is not None:
+
+        def ready(u) -> bool:
+            return u.forward_prefetch and u.state.value == "sharded" and u.flat_buffer.pending_gather is None \
+                and self._caps_allow(u)
+
+        head = self.forward_order[:max(int(self.config.next_step_prefetch_units), 1)]
+        own_events = [getattr(u.flat_buffer, "update_done_event", None) for u in head]
+        if len(head) > 1 and all(ev is not None for ev in own_events):
+            # in the order their updates finish (the reverse of the forward order): every gather starts as
+            # soon as its own unit is final
+            for u, ev in reversed(list(zip(head, own_events))):
+                if ready(u):
+                    u._record("forward_prefetch", reason="after_unit_update")
+                    u.start_unshard("next_step_prefetch", after_event=ev)
+                    self.counters.next_step_prefetch_issued += 1
             return
-        if not self._caps_allow(first):
+        first = head[0]
+        if not ready(first):
             return
         first._record("forward_prefetch", reason="after_optimizer_step")
         first.start_unshard("next_step_prefetch")

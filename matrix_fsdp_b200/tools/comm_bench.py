@@ -174,12 +174,29 @@ def main(argv=None) -> int:
         grad.normal_()
         out = torch.empty(n_local, dtype=torch.float32 if name == "peer" else torch.bfloat16, device=dev)
         key = f"bench_{name}"
-        ag = time_op(lambda: tr.gather(shard, full, tables, unit_key=key).wait(), args.iters)
-        rs = time_op(lambda: tr.reduce(grad, out, tables, scale=1.0 / world, unit_key=key).wait(), args.iters)
+        dst = full
+        if name == "peer":
+            # with NVSwitch multicast the gather pushes into a persistent symmetric full-parameter slot
+            slot = tr.alloc_full_buffer(key, args.numel, torch.bfloat16, tables, exclusive=True)
+            dst = slot if slot is not None else full
+        impls = {}
+
+        def run_ag():
+            h = tr.gather(shard, dst, tables, unit_key=key)
+            impls["all_gather"] = h.info.get("impl", "")
+            h.wait()
+
+        def run_rs():
+            h = tr.reduce(grad, out, tables, scale=1.0 / world, unit_key=key)
+            impls["reduce_scatter"] = h.info.get("impl", "")
+            h.wait()
+
+        ag = time_op(run_ag, args.iters)
+        rs = time_op(run_rs, args.iters)
         recv_bytes = (args.numel - n_local) * 2
         for op, ms in (("all_gather", ag), ("reduce_scatter", rs)):
             gbs = recv_bytes / (ms * 1e-3) / 1e9
-            results.append({"transport": name, "op": op, "ms": ms, "recv_gb_per_s": gbs,
+            results.append({"transport": name, "op": op, "impl": impls.get(op, ""), "ms": ms, "recv_gb_per_s": gbs,
                             "frac_of_measured_nvlink_770": gbs / NVLINK_PEER_GBS})
     if peer is not None and args.fused:
         results += fused_paths(peer, tables, args, world, dev)

@@ -302,3 +302,44 @@ def test_gemm_with_fused_gather_single_gpu():
     out2 = K.gemm_ag(a, b, plan)
     torch.cuda.synchronize()
     assert torch.equal(out2, out)
+
+
+@pytest.mark.parametrize("T,V,H", [(1000, 517, 256), (8192, 32000, 2048), (300, 40, 1024)])
+def test_embedding_backward_matches_fp32(K, T, V, H):
+    """Sum of the output-gradient rows of equal ids: against an fp32 index_add, with heavy duplicates, ids outside
+    the vocabulary, accumulation into an existing gradient, and run-to-run bitwise equality."""
+    torch.manual_seed(T + V)
+    dy = _rand(T, H)
+    ids = torch.randint(0, V, (T,), device="cuda")
+    ids[: T // 4] = ids[0]                      # one id that occurs T/4 times
+    ids[-1] = -1                                # an id that is not in the vocabulary contributes nothing
+    valid = ids >= 0
+    ref = torch.zeros(V, H, device="cuda").index_add_(0, ids[valid], dy[valid].float())
+    out = torch.full((V, H), float("nan"), device="cuda", dtype=torch.bfloat16)
+    K.embedding_bwd(dy, ids, out)
+    assert torch.isfinite(out.float()).all()
+    assert _rel_err(out, ref) < 5e-3
+    again = torch.empty_like(out)
+    K.embedding_bwd(dy, ids, again)
+    assert torch.equal(out, again)
+    prev = _rand(V, H)
+    acc = prev.clone()
+    K.embedding_bwd(dy, ids, acc, accumulate=True)
+    assert _rel_err(acc, ref + prev.float()) < 5e-3
+    untouched = torch.ones(V, dtype=torch.bool, device="cuda")
+    untouched[ids[valid]] = False
+    assert torch.equal(acc[untouched], prev[untouched])
+
+
+def test_embedding_function_gradient_matches_torch(K):
+    from matrix_fsdp_b200.ops import functional as OF
+
+    torch.manual_seed(3)
+    w = torch.nn.Parameter(_rand(1024, 512))
+    w_ref = torch.nn.Parameter(w.detach().clone())
+    ids = torch.randint(0, 1024, (4, 96), device="cuda")
+    up = _rand(4, 96, 512)
+    OF.embedding(ids, w, w).backward(up)
+    torch.nn.functional.embedding(ids, w_ref).backward(up)
+    assert w.grad is not None and w.grad.shape == w_ref.grad.shape
+    assert _rel_err(w.grad, w_ref.grad.float()) < 5e-3
