@@ -87,6 +87,13 @@ class Matrix(nn.Module):
         return OF.linear(x, self.weight, self.weight)
 
 
+class TokenEmbedding(nn.Embedding):
+    """``nn.Embedding`` (same parameter name and shape) whose backward writes the owning unit's gradient bucket."""
+
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        return OF.embedding(ids, self.weight, self.weight)
+
+
 class LlamaBlock(nn.Module):
     def __init__(self, cfg: LlamaConfig) -> None:
         super().__init__()
@@ -163,7 +170,7 @@ class LlamaModel(nn.Module):
     def __init__(self, cfg: LlamaConfig) -> None:
         super().__init__()
         self.cfg = cfg
-        self.embed = nn.Embedding(cfg.vocab_size, cfg.hidden)
+        self.embed = TokenEmbedding(cfg.vocab_size, cfg.hidden)
         nn.init.normal_(self.embed.weight, mean=0.0, std=cfg.init_std)
         self.layers = nn.ModuleList([LlamaBlock(cfg) for _ in range(cfg.n_layers)])
         self.head = LMHead(cfg.hidden, cfg.vocab_size, cfg.eps, cfg.init_std)
@@ -179,7 +186,7 @@ class LlamaModel(nn.Module):
         return self.head.lm_head
 
     def forward(self, tokens: torch.Tensor, targets: torch.Tensor | None = None) -> torch.Tensor:
-        x = OF.embedding(tokens, self.embed.weight, self.embed.weight)
+        x = self.embed(tokens)
         for layer in self.layers:
             x = layer(x)
         logits = self.head(x)

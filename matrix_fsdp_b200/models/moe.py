@@ -16,7 +16,7 @@ from torch import nn
 
 from ..ops import functional as OF
 from ..ops import moe_functional as MF
-from .llama import LMHead, Matrix, RMSNorm
+from .llama import LMHead, Matrix, RMSNorm, TokenEmbedding
 
 
 @dataclass
@@ -145,7 +145,7 @@ class MoEModel(nn.Module):
     def __init__(self, cfg: MoEConfig, ep_group=None, device=None, dtype=None) -> None:
         super().__init__()
         self.cfg = cfg
-        self.embed = nn.Embedding(cfg.vocab_size, cfg.hidden)
+        self.embed = TokenEmbedding(cfg.vocab_size, cfg.hidden)
         nn.init.normal_(self.embed.weight, mean=0.0, std=cfg.init_std)
         self.layers = nn.ModuleList([MoEBlock(cfg, i, ep_group, device=device, dtype=dtype) for i in range(cfg.n_layers)])
         self.head = LMHead(cfg.hidden, cfg.vocab_size, cfg.eps, cfg.init_std)
@@ -162,7 +162,7 @@ class MoEModel(nn.Module):
         return [p for layer in self.layers for p in layer.experts.parameters()]
 
     def forward(self, tokens: torch.Tensor, targets: torch.Tensor | None = None) -> torch.Tensor:
-        x = OF.embedding(tokens, self.embed.weight, self.embed.weight)
+        x = self.embed(tokens)
         for layer in self.layers:
             x = layer(x)
         logits = self.head(x)

@@ -41,6 +41,32 @@ def test_gemm_majors(K, a_mn, b_mn, shape):
     assert _rel_err(out2, ref) < 1e-2
 
 
+@pytest.mark.parametrize("a_mn", [False, True])
+@pytest.mark.parametrize("b_mn", [False, True])
+@pytest.mark.parametrize("shape", [(512, 512, 256), (384, 320, 200), (1024, 2304, 512), (4096, 2048, 2048), (136, 72, 64)])
+def test_gemm_cta_pair_kernel(K, a_mn, b_mn, shape):
+    """The two-CTA (cta_group::2) kernel: 256 x 256 tiles over a cluster of two, every operand-major form, ragged
+    edges (rows / columns / reduce length that do not fill a tile), and the scale / add epilogue."""
+    M, N, Kd = shape
+    torch.manual_seed(M + N)
+    a, b, c = _rand(M, Kd), _rand(N, Kd), _rand(M, N)
+    ref = a.float() @ b.float().t()
+    a_in = a.t().contiguous() if a_mn else a
+    b_in = b.t().contiguous() if b_mn else b
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    K.gemm(a_in, b_in, a_mn_major=a_mn, b_mn_major=b_mn, out=out, force_bn=2)
+    K.check_status()
+    assert torch.isfinite(out.float()).all()
+    assert _rel_err(out, ref) < 1e-2
+    out2 = K.gemm(a_in, b_in, a_mn_major=a_mn, b_mn_major=b_mn, cin=c, alpha=0.5, beta=2.0, force_bn=2)
+    K.check_status()
+    assert _rel_err(out2, 0.5 * ref + 2.0 * c.float()) < 1e-2
+    # repeated launches (barrier phases, tensor-memory alloc / free across launches) stay correct
+    for _ in range(3):
+        out3 = K.gemm(a_in, b_in, a_mn_major=a_mn, b_mn_major=b_mn, force_bn=2)
+    assert torch.equal(out3, out)
+
+
 def test_gemm_alpha_beta_cin(K):
     torch.manual_seed(1)
     a, b, c = _rand(512, 256), _rand(384, 256), _rand(512, 384)
