@@ -57,8 +57,8 @@ struct GemmArgs {
   // Symmetric output (sym_rows > 0): every output matrix is sym_rows*128 square and equal to its own
   // transpose (X Xᵀ, polynomials of it), so only tiles that reach the diagonal or lie above it are
   // computed; the caller mirrors the rest.  Work items enumerate exactly those tiles, row by row.
-  int sym_rows;              // 128-row tile rows per symmetric matrix (0 = off)
-  int sym_q;                 // tile width / 128 (1 or 2)
+  int sym_rows;              // tile rows (of tile_m rows) per symmetric matrix (0 = off)
+  int sym_q;                 // tile width / tile_m (1 or 2)
   int sym_tiles_per_matrix;
   // Fused all-gather (GATHER kernels only): B's rows are still on peer GPUs when the kernel starts.
   // Eight extra warps per CTA copy them into B's local buffer job by job (16-byte peer loads, local
@@ -90,6 +90,13 @@ struct GemmCfg {
 };
 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// Barrier of the four epilogue warps that also ORs a flag, so that all of them take the same way out.
+__device__ __forceinline__ bool epi_bar_any(int flag) {
+  uint32_t any;
+  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, 1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+               : "=r"(any) : "r"(flag) : "memory");
+  return any != 0;
+}
 
 struct TileCoord {
   int m0, n0;        // element offsets into the (per-group) output
@@ -141,14 +148,14 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, int tile) {
     c.m0 = tm * p.tile_m;
     c.out_row0 = c.m0;
   } else if (p.group_mode == 1) {
-    c.m0 = tm * BM;
+    c.m0 = tm * p.tile_m;
     c.out_row0 = c.m0;
-    const int g = p.tile_group[tm];
+    const int g = p.tile_group[c.m0 / BM];     // groups are named per 128-row tile
     if (g < 0) c.skip = true;
     c.b_row_off = (g < 0 ? 0 : g) * p.b_group_stride;
   } else {
     const int g = tm / p.tiles_m_per_group;
-    c.m0 = (tm % p.tiles_m_per_group) * BM;
+    c.m0 = (tm % p.tiles_m_per_group) * p.tile_m;
     c.out_row0 = g * p.m_per_group + c.m0;
     const int k_lo = p.group_offsets[g], k_hi = p.group_offsets[g + 1];
     c.a_row_k0 = k_lo;
@@ -368,11 +375,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
       const int n0 = c.n0 * BN;
       const uint32_t acc = lt & 1, aph = (lt >> 1) & 1;
       mbar_wait(smem_u32(&tfull_bar[acc]), aph, p.status, abort_flag);
-      epi_bar_sync();
-      if (*abort_flag) break;
+      if (epi_bar_any(*abort_flag)) break;     // a uniform decision: nobody is left behind at a later barrier
       tc_fence_after();
       const long long grow = (long long)c.out_row0 + pair_row + row_in_tile;
-      const bool row_ok = (p.group_mode == 2) ? (c.m0 + row_in_tile < p.m_per_group)
+      const bool row_ok = (p.group_mode == 2) ? (c.m0 + pair_row + row_in_tile < p.m_per_group)
                                               : (c.m0 + pair_row + row_in_tile < p.M);
 #pragma unroll 1
       for (int ch = 0; ch < BN / 64; ++ch) {
@@ -601,12 +607,13 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
   return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, td, args);
 }
 
-// MFSDP_GEMM_2SM = 0 (default): CTA pairs only on request, 1: whenever the problem is eligible, 2: when the
-// pair schedule fills its waves at least as well as the single-CTA one.
+// MFSDP_GEMM_2SM = 1 (default): CTA pairs whenever the problem is eligible (measured 3-14 % faster than the
+// single-CTA kernel on every dense shape of the models), 0: only on request, 2: only when the pair schedule
+// fills its waves at least as well as the single-CTA one.
 static int pair_mode() {
   static int v = [] {
     const char* e = getenv("MFSDP_GEMM_2SM");
-    return e ? atoi(e) : 0;
+    return e ? atoi(e) : 1;
   }();
   return v;
 }
@@ -684,25 +691,39 @@ static int gemm_bf16_impl(const void* A, const void* B, void* D, const void* Cin
     };
     bn = eff(256) >= eff(128) ? 256 : 128;
   }
-  // CTA pairs (256 x 256 tiles over two SMs): dense problems only.
+  // CTA pairs (256 x 256 tiles over two SMs).  force_bn == 2 asks for them whatever the environment says, and
+  // in the M-grouped mode it is also the caller's promise that every group has a multiple of 256 rows (a pair's
+  // two CTAs share one B operand, so a tile must not straddle two groups).
   bool pair = false;
-  // force_bn == 2 asks for the pair kernel whatever the environment says (tests, A/B timing).
-  if (force_bn == 2 && group_mode == 0 && !symmetric && K > 0) {
-    pair = true;
-  } else if (group_mode == 0 && !symmetric && force_bn == 0 && pair_mode() != 0 && M > BM && N > 128 && K > 0) {
-    const int np = pairs_resident(num_sms);
-    const long long t2 = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
-    const double fill2 = (double)t2 / (double)(((t2 + np - 1) / np) * np) * ((double)M / (double)(((M + 255) / 256) * 256)) *
-                         ((double)N / (double)(((N + 255) / 256) * 256));
-    const long long t1 = (long long)args.tiles_m * ((N + bn - 1) / bn);
-    const double fill1 = (double)t1 / (double)(((t1 + num_sms - 1) / num_sms) * num_sms) *
-                         ((double)N / (double)(((N + bn - 1) / bn) * bn)) * (bn == 256 ? 1.0 : 0.72);
-    pair = pair_mode() == 1 || fill2 * 1.05 >= fill1;
+  const bool pair_req = force_bn == 2;
+  const bool pair_auto = force_bn == 0 && pair_mode() != 0;
+  if (pair_req || pair_auto) {
+    const bool sym_ok = !symmetric || (N % 256) == 0;
+    if (group_mode == 0) {
+      if (pair_req || symmetric) {
+        pair = sym_ok && K > 0;
+      } else if (M > BM && N > 128 && K > 0) {
+        const int np = pairs_resident(num_sms);
+        const long long t2 = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+        const double fill2 = (double)t2 / (double)(((t2 + np - 1) / np) * np) *
+                             ((double)M / (double)(((M + 255) / 256) * 256)) * ((double)N / (double)(((N + 255) / 256) * 256));
+        const long long t1 = (long long)args.tiles_m * ((N + bn - 1) / bn);
+        const double fill1 = (double)t1 / (double)(((t1 + num_sms - 1) / num_sms) * num_sms) *
+                             ((double)N / (double)(((N + bn - 1) / bn) * bn)) * (bn == 256 ? 1.0 : 0.72);
+        pair = pair_mode() == 1 || fill2 * 1.05 >= fill1;
+      }
+    } else if (group_mode == 1) {
+      pair = pair_req && (M % 256) == 0 && sym_ok && K > 0;
+    } else {
+      pair = (M % 256) == 0 && sym_ok;          // K-grouped: whole 256-row tiles per group
+    }
   }
   if (pair) {
     bn = 256;
     args.tile_m = 2 * BM;
-    args.tiles_m = (M + 2 * BM - 1) / (2 * BM);
+    const int tiles_m_pair = (M + 2 * BM - 1) / (2 * BM);
+    args.tiles_m_per_group = tiles_m_pair;
+    args.tiles_m = (group_mode == 2) ? tiles_m_pair * num_groups : tiles_m_pair;
   }
   args.tiles_n = (N + bn - 1) / bn;
   args.b_group_stride = (group_mode == 1) ? (b_mn_major ? K : N) : 0;
@@ -724,8 +745,8 @@ static int gemm_bf16_impl(const void* A, const void* B, void* D, const void* Cin
 
   int total = args.tiles_m * args.tiles_n;
   if (symmetric) {
-    args.sym_rows = N / BM;
-    args.sym_q = bn / BM;
+    args.sym_rows = N / args.tile_m;
+    args.sym_q = bn / args.tile_m;
     args.sym_tiles_per_matrix = sym_kept_before(args.sym_rows, args.tiles_n, args.sym_q);
     total = (args.tiles_m / args.sym_rows) * args.sym_tiles_per_matrix;
   }

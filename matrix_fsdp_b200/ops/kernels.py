@@ -153,14 +153,16 @@ def gemm_ag(a: torch.Tensor, b: torch.Tensor, plan, *, out: torch.Tensor | None 
 
 def grouped_gemm_m(a: torch.Tensor, b: torch.Tensor, tile_group: torch.Tensor, *,
                    b_mn_major: bool = False, out: torch.Tensor | None = None, cin: torch.Tensor | None = None,
-                   alpha: float = 1.0, beta: float = 0.0, symmetric: bool = False) -> torch.Tensor:
+                   alpha: float = 1.0, beta: float = 0.0, symmetric: bool = False,
+                   groups_of_256_rows: bool = False) -> torch.Tensor:
     """M-grouped GEMM: rows of ``a`` come in 128-row tiles, tile ``t`` uses ``b[tile_group[t]]``;
     ``out = alpha * a·b[g]ᵀ + beta * cin`` (``cin``: ``[Mtot, N]``).
 
     ``a``: ``[Mtot, K]``; ``b``: ``[G, N, K]`` (or ``[G, K, N]`` when ``b_mn_major``); tiles whose
     group id is negative are skipped (their output rows are left untouched).  ``symmetric``: ``a`` stacks
     ``Mtot / N`` blocks of ``N`` rows whose outputs are symmetric ``N x N`` matrices (``N`` a multiple of 128);
-    tiles below the diagonal are mirrored instead of computed.
+    tiles below the diagonal are mirrored instead of computed.  ``groups_of_256_rows``: the caller's promise that
+    every group has a multiple of 256 rows, which lets the two-CTA kernel (256 x 256 tiles) run.
     """
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and b.dim() == 3
     assert b.is_contiguous() and a.stride(1) == 1 and tile_group.dtype == torch.int32
@@ -185,7 +187,7 @@ def grouped_gemm_m(a: torch.Tensor, b: torch.Tensor, tile_group: torch.Tensor, *
         a.data_ptr(), b.data_ptr(), out.data_ptr(), cin.data_ptr() if cin is not None else None, Mtot, N, K,
         a.stride(0), ldb, out.stride(0), cin.stride(0) if cin is not None else 0, 0, int(b_mn_major),
         float(alpha), float(beta), 1, tile_group.data_ptr(), None, G, 0,
-        status_word(a.device).data_ptr(), sm_count(a.device), 0, _stream())
+        status_word(a.device).data_ptr(), sm_count(a.device), 2 if groups_of_256_rows and Mtot % 256 == 0 else 0, _stream())
     _lib.check(rc, "mfsdp_gemm_bf16[m-grouped]")
     if symmetric:
         mirror_upper_(out, Mtot // N)

@@ -123,18 +123,23 @@ def newton_schulz_sm100_batched(x: torch.Tensor, coefficients=DEFAULT_NS_COEFFIC
     nxt = torch.empty_like(x2)
     tg_n = _tile_groups(G, n, dev)
     sym = SYMMETRIC_PRODUCTS          # n is a multiple of 128 here
+    p_n, p_rows = n % 256 == 0, rows % 256 == 0      # whole 256-row tiles per matrix: the two-CTA kernel may run
     if tall:
         offsets = torch.arange(G + 1, dtype=torch.int32, device=dev) * rows
         tg_rows = _tile_groups(G, rows, dev)
     for _ in range(steps):
         if tall:
             K.grouped_gemm_k(x2, x2, offsets, G, out=gram.view(G, n, n), symmetric=sym)                   # XᵀX
-            K.grouped_gemm_m(gram, gram.view(G, n, n), tg_n, out=poly, cin=gram, alpha=c, beta=b, symmetric=sym)  # bA + cAA
-            K.grouped_gemm_m(x2, poly.view(G, n, n), tg_rows, out=nxt, cin=x2, alpha=1.0, beta=a)        # aX + X B
+            K.grouped_gemm_m(gram, gram.view(G, n, n), tg_n, out=poly, cin=gram, alpha=c, beta=b, symmetric=sym,
+                             groups_of_256_rows=p_n)                                                      # bA + cAA
+            K.grouped_gemm_m(x2, poly.view(G, n, n), tg_rows, out=nxt, cin=x2, alpha=1.0, beta=a,
+                             groups_of_256_rows=p_rows)                                                   # aX + X B
         else:
-            K.grouped_gemm_m(x2, x2.view(G, n, cols), tg_n, out=gram, symmetric=sym)                      # XXᵀ
-            K.grouped_gemm_m(gram, gram.view(G, n, n), tg_n, out=poly, cin=gram, alpha=c, beta=b, symmetric=sym)
-            K.grouped_gemm_m(poly, x2.view(G, n, cols), tg_n, b_mn_major=True, out=nxt, cin=x2, alpha=1.0, beta=a)
+            K.grouped_gemm_m(x2, x2.view(G, n, cols), tg_n, out=gram, symmetric=sym, groups_of_256_rows=p_n)   # XXᵀ
+            K.grouped_gemm_m(gram, gram.view(G, n, n), tg_n, out=poly, cin=gram, alpha=c, beta=b, symmetric=sym,
+                             groups_of_256_rows=p_n)
+            K.grouped_gemm_m(poly, x2.view(G, n, cols), tg_n, b_mn_major=True, out=nxt, cin=x2, alpha=1.0, beta=a,
+                             groups_of_256_rows=p_n)
         x2, nxt = nxt, x2
     return x2.view(G, rows, cols)
 

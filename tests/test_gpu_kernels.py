@@ -369,3 +369,37 @@ def test_embedding_function_gradient_matches_torch(K):
     torch.nn.functional.embedding(ids, w_ref).backward(up)
     assert w.grad is not None and w.grad.shape == w_ref.grad.shape
     assert _rel_err(w.grad, w_ref.grad.float()) < 5e-3
+
+
+def test_grouped_gemms_on_cta_pairs(K):
+    """M-grouped GEMM with the caller's promise of 256-row groups, and K-grouped GEMM with 256-row outputs: both
+    run the two-CTA kernel and must match fp32."""
+    torch.manual_seed(11)
+    G, N, Kd = 3, 384, 320
+    rows = [256, 512, 256]
+    tile_group = torch.tensor(sum(([g] * (r // 128) for g, r in enumerate(rows)), []), dtype=torch.int32, device="cuda")
+    a, w, c = _rand(sum(rows), Kd), _rand(G, N, Kd), _rand(sum(rows), N)
+    out = torch.full((sum(rows), N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    K.grouped_gemm_m(a, w, tile_group, out=out, cin=c, alpha=1.0, beta=0.5, groups_of_256_rows=True)
+    K.check_status()
+    r0 = 0
+    for g, r in enumerate(rows):
+        ref = a[r0:r0 + r].float() @ w[g].float().t() + 0.5 * c[r0:r0 + r].float()
+        assert _rel_err(out[r0:r0 + r], ref) < 1e-2, g
+        r0 += r
+    # MN-major B (the aX + BX product of Newton-Schulz)
+    wt = w.transpose(1, 2).contiguous()
+    out2 = K.grouped_gemm_m(a, wt, tile_group, b_mn_major=True, groups_of_256_rows=True)
+    K.check_status()
+    r0 = 0
+    for g, r in enumerate(rows):
+        assert _rel_err(out2[r0:r0 + r], a[r0:r0 + r].float() @ w[g].float().t()) < 1e-2, g
+        r0 += r
+    # K-grouped, 512-row outputs
+    kk, M2, N2 = 192, 512, 320
+    a2, b2 = _rand(G * kk, M2), _rand(G * kk, N2)
+    offsets = torch.arange(G + 1, dtype=torch.int32, device="cuda") * kk
+    o3 = K.grouped_gemm_k(a2, b2, offsets, G)
+    K.check_status()
+    ref3 = torch.bmm(a2.view(G, kk, M2).float().transpose(1, 2), b2.view(G, kk, N2).float())
+    assert _rel_err(o3, ref3) < 1e-2
