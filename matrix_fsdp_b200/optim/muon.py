@@ -59,6 +59,13 @@ def newton_schulz_reference(u: torch.Tensor, coefficients=DEFAULT_NS_COEFFICIENT
     return x.T if tall else x
 
 
+def _symmetric_pays(n: int, matrices: int) -> bool:
+    """Skipping the tiles below the diagonal only shortens a product that has more than one wave of 256 x 256
+    tiles to begin with (74 CTA pairs); below that the extra mirror launch costs more than it saves (measured:
+    2048 x 2048 slower, 4096 x 4096 1.35x faster than the full products)."""
+    return SYMMETRIC_PRODUCTS and matrices * (n // 256) ** 2 >= 148
+
+
 def newton_schulz_sm100(x: torch.Tensor, coefficients=DEFAULT_NS_COEFFICIENTS, steps: int = 5) -> torch.Tensor:
     """Newton-Schulz on an already normalised bf16 ``[rows, cols]`` matrix with tcgen05 GEMMs.
 
@@ -74,7 +81,7 @@ def newton_schulz_sm100(x: torch.Tensor, coefficients=DEFAULT_NS_COEFFICIENTS, s
     gram = torch.empty((n, n), dtype=torch.bfloat16, device=x.device)
     poly = torch.empty_like(gram)
     nxt = torch.empty_like(x)
-    sym = n % 128 == 0 and SYMMETRIC_PRODUCTS     # Gram matrix and its polynomial equal their transposes
+    sym = n % 128 == 0 and _symmetric_pays(n, 1)  # Gram matrix and its polynomial equal their transposes
     for _ in range(steps):
         if tall:
             K.gemm(x, x, a_mn_major=True, b_mn_major=True, out=gram, symmetric=sym)            # XᵀX
@@ -122,7 +129,7 @@ def newton_schulz_sm100_batched(x: torch.Tensor, coefficients=DEFAULT_NS_COEFFIC
     x2 = x.reshape(G * rows, cols)
     nxt = torch.empty_like(x2)
     tg_n = _tile_groups(G, n, dev)
-    sym = SYMMETRIC_PRODUCTS          # n is a multiple of 128 here
+    sym = _symmetric_pays(n, G)       # n is a multiple of 128 here
     p_n, p_rows = n % 256 == 0, rows % 256 == 0      # whole 256-row tiles per matrix: the two-CTA kernel may run
     if tall:
         offsets = torch.arange(G + 1, dtype=torch.int32, device=dev) * rows

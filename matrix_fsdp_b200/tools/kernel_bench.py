@@ -59,15 +59,17 @@ def bench_gemm(small: bool, shape=None):
         t_nn = _time([lambda i=i: K.gemm(a[i], bt[i], b_mn_major=True, out=o[i]) for i in range(nbuf)])
         t_tn = _time([lambda i=i: K.gemm(at[i], bt[i], a_mn_major=True, b_mn_major=True, out=o[i]) for i in range(nbuf)])
         t_lib = _time([lambda i=i: torch.matmul(a[i], b[i].t(), out=o[i]) for i in range(nbuf)])
-        # the same three products on the two-CTA (cta_group::2, 256 x 256 tile) kernel
-        p_nt = _time([lambda i=i: K.gemm(a[i], b[i], out=o[i], force_bn=2) for i in range(nbuf)])
-        p_nn = _time([lambda i=i: K.gemm(a[i], bt[i], b_mn_major=True, out=o[i], force_bn=2) for i in range(nbuf)])
-        p_tn = _time([lambda i=i: K.gemm(at[i], bt[i], a_mn_major=True, b_mn_major=True, out=o[i], force_bn=2)
+        # the same three products on the single-CTA kernel (128 x 256 tiles); the default above is the two-CTA
+        # cta_group::2 kernel with 256 x 256 tiles
+        s_nt = _time([lambda i=i: K.gemm(a[i], b[i], out=o[i], force_bn=256) for i in range(nbuf)])
+        s_nn = _time([lambda i=i: K.gemm(a[i], bt[i], b_mn_major=True, out=o[i], force_bn=256) for i in range(nbuf)])
+        s_tn = _time([lambda i=i: K.gemm(at[i], bt[i], a_mn_major=True, b_mn_major=True, out=o[i], force_bn=256)
                       for i in range(nbuf)])
         rows.append({"shape": [M, N, Kd], "fwd_tflops": fl / t_nt, "dgrad_tflops": fl / t_nn, "wgrad_tflops": fl / t_tn,
-                     "pair_fwd_tflops": fl / p_nt, "pair_dgrad_tflops": fl / p_nn, "pair_wgrad_tflops": fl / p_tn,
-                     "cublas_tflops": fl / t_lib, "fwd_frac_of_%s_peak" % src: fl / t_nt / tf,
-                     "fwd_vs_cublas": t_lib / t_nt, "pair_fwd_vs_cublas": t_lib / p_nt})
+                     "single_cta_fwd_tflops": fl / s_nt, "single_cta_dgrad_tflops": fl / s_nn,
+                     "single_cta_wgrad_tflops": fl / s_tn, "cublas_tflops": fl / t_lib,
+                     "fwd_frac_of_%s_peak" % src: fl / t_nt / tf, "fwd_vs_cublas": t_lib / t_nt,
+                     "single_cta_fwd_vs_cublas": t_lib / s_nt})
         print(json.dumps(rows[-1]), flush=True)
     K.check_status()
     return rows
