@@ -139,6 +139,52 @@ def fused_paths(peer, tables: SegmentTables, args, world: int, dev) -> list[dict
     return res
 
 
+def moe_paths(args, world: int, dev) -> list[dict]:
+    """Expert-parallel dispatch (permute + all-to-all in one push kernel) and combine (all-to-all + unpermute +
+    weighted sum in one pull kernel) for ``--tokens`` tokens of width ``--hidden`` routed top-``--top-k`` over
+    ``--experts`` experts, against ``all_to_all_single`` moving the same rows there and back (which still needs the
+    permutation and the weighted sum around it).  Roofline = remote bytes / measured NVLink rate."""
+    from ..ops import moe_kernels as MK
+    from ..parallel.expert_parallel import KIND_PUSHED, KIND_READY, ExpertParallelContext
+
+    T, H, E, k = args.tokens, args.hidden, args.experts, args.top_k
+    ep = ExpertParallelContext.get(dist.group.WORLD, dev, H, E, k, T, capacity_factor=0.0)
+    El = ep.experts_per_rank
+    x = torch.randn(T, H, device=dev).bfloat16()
+    logits = torch.randn(T, E, device=dev).bfloat16()
+    _, idx, w = MK.router_topk(logits, k, torch.zeros(E, dtype=torch.float32, device=dev))
+    state = {}
+
+    def dispatch():
+        slot, counts = MK.assign_slots(idx, E)
+        counts_all = ep.exchange_counts(counts)
+        dest_base, group_offsets, group_rows, tile_group, stats = MK.plan(counts_all, ep.world, ep.rank, E, ep.cap_rows)
+        state["route"] = MK.dispatch_push(x, idx, ep.recv_addrs, El, ep.cap_rows, slot=slot, dest_base=dest_base)
+        ep.fence(KIND_PUSHED)
+
+    def combine():
+        ep.fence(KIND_READY)
+        MK.combine_pull(ep.recv_addrs, idx, state["route"], H, El, weight=w)      # pull the rows back, weighted sum
+
+    dispatch()
+    d_ms = time_op(dispatch, args.iters)
+    c_ms = time_op(combine, args.iters)
+    rows = T * k
+    remote = rows * H * 2 * (world - 1) / world
+    # library baseline: equal-split all-to-all of the same number of rows in both directions
+    per_peer = (rows + world - 1) // world
+    send = torch.randn(world * per_peer, H, device=dev).bfloat16()
+    recv = torch.empty_like(send)
+    a2a_ms = time_op(lambda: dist.all_to_all_single(recv, send), args.iters)
+    out = []
+    for op, ms in (("moe_dispatch_push", d_ms), ("moe_combine_pull", c_ms), ("nccl_all_to_all_single", a2a_ms)):
+        out.append({"op": op, "ms": ms, "rows": rows, "remote_mb": remote / 2 ** 20,
+                    "remote_gb_per_s": remote / (ms * 1e-3) / 1e9,
+                    "frac_of_measured_nvlink_770": remote / (ms * 1e-3) / 1e9 / NVLINK_PEER_GBS,
+                    "rows_lost": ep.rows_lost_total()})
+    return out
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--numel", type=int, default=50_593_792)   # one Llama-2048 block
@@ -149,6 +195,9 @@ def main(argv=None) -> int:
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--hidden", type=int, default=2048)
     ap.add_argument("--gemm-tflops", type=float, default=1400.0, help="sustained bf16 GEMM rate used as roofline")
+    ap.add_argument("--moe", action="store_true", help="also time the expert-parallel dispatch / combine kernels")
+    ap.add_argument("--experts", type=int, default=64)
+    ap.add_argument("--top-k", type=int, default=6)
     args = ap.parse_args(argv)
     rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(rank)
@@ -200,6 +249,8 @@ def main(argv=None) -> int:
                             "frac_of_measured_nvlink_770": gbs / NVLINK_PEER_GBS})
     if peer is not None and args.fused:
         results += fused_paths(peer, tables, args, world, dev)
+    if args.moe:
+        results += moe_paths(args, world, dev)
     if dist.get_rank() == 0:
         for r in results:
             print(json.dumps(r))
