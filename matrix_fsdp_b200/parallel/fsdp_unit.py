@@ -205,8 +205,21 @@ class MatrixFSDPParamGroup:
         if getattr(module, "_matrix_fsdp_param_group", None) is not None:
             raise ValueError("This module is already managed by an FSDP unit.")
         ignored = set(self.ignored_params or ())
-        # parameters already managed by nested units stay with them
-        nested = {id(p) for p in module.parameters() if getattr(p, "_matrix_fsdp_param_group_ref", None) is not None}
+        # parameters already managed by nested units stay with them; a parameter managed by a unit that is NOT
+        # inside this module is shared between two modules, and its other user would read it while the owning
+        # unit keeps it sharded
+        inner = {id(m) for m in module.modules()}
+        nested = set()
+        for fqn, p in module.named_parameters():
+            ref = getattr(p, "_matrix_fsdp_param_group_ref", None)
+            owner = ref() if ref is not None else None
+            if owner is None:
+                continue
+            if id(owner.module) not in inner and p not in ignored:
+                raise ValueError(f"Parameter {fqn!r} is shared with a module that another FSDP unit ({owner.name}) "
+                                 "already manages; shard both users in one unit (allow_shared_params=True on a common "
+                                 "parent) or pass it through ignored_params.")
+            nested.add(id(p))
         ignored |= {p for p in module.parameters() if id(p) in nested}
         hints = self.shard_hints
         if hints is None and self.auto_shard_hints:
