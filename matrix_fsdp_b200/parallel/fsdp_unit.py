@@ -340,6 +340,8 @@ class MatrixFSDPParamGroup:
         span = getattr(handle, "span", None)
         if span is not None:
             kw["extra"] = {**kw.get("extra", {}), "span": span}      # device-side times, resolved by the summaries
+        if info.get("host_phases_ms"):
+            kw["extra"] = {**kw.get("extra", {}), "host_phases_ms": dict(info["host_phases_ms"])}
         snap = self.flat_buffer.memory_snapshot() if self.flat_buffer is not None else {}
         sched = self.scheduler
         self.runtime_events.append(RuntimeEvent(

@@ -35,6 +35,7 @@ from __future__ import annotations
 
 import ctypes as C
 import os
+import time
 import socket
 
 import torch
@@ -585,6 +586,7 @@ class PeerTransport(LocalTransport):
         buf = self.ctx.lookup(shard)
         if buf is None:
             raise RuntimeError("peer gather needs a shard that lives in symmetric memory")
+        t_host = time.perf_counter()
         ui = self._unit(unit_key)
         ep = self._epochs[unit_key]
         ep["shard"] += 1
@@ -610,6 +612,7 @@ class PeerTransport(LocalTransport):
                 self.launches += 1
             fslot.holder, fslot.last_unit, fslot.last_epoch = unit_key, unit_key, e
             t = self._push_tables(unit_key, tables, es, full.device)
+            t_tables = time.perf_counter()
             _lib.check(ctx.lib.mfsdp_ag_push_mc(shard.data_ptr(), fslot.buf.mc_addr, t["src"].data_ptr(),
                                                 t["dst"].data_ptr(), t["len"].data_ptr(), t["n"], t["max"],
                                                 ctx.status.data_ptr(), run.cuda_stream), "ag_push_mc")
@@ -622,6 +625,7 @@ class PeerTransport(LocalTransport):
                 plan, t = self._deferred_tables(unit_key, buf, tables, full, defer)
             else:
                 t = self._gather_tables(unit_key, buf, tables, es, full.device)
+            t_tables = time.perf_counter()
             ctx.signal_wait(ui, KIND_SHARD, e, run)
             if ctx.debug_bounds:
                 self._validate_pull(t, full, buf, run)
@@ -635,10 +639,13 @@ class PeerTransport(LocalTransport):
         if stream is not None:
             ev = torch.cuda.Event()
             ev.record(stream)
+        t_end = time.perf_counter()
         h = MatrixCollectiveHandle(event=ev, info={
             "kind": "all_gather", "impl": impl, "backend": self.kind,
             "bytes": full.numel() * es, "count": 1,
-            "sync_mode": "stream_event" if stream is not None else "stream_order"})
+            "sync_mode": "stream_event" if stream is not None else "stream_order",
+            # host time inside the call: table lookup / slot handshake, then flag and kernel launches
+            "host_phases_ms": {"tables": (t_tables - t_host) * 1e3, "launch": (t_end - t_tables) * 1e3}})
         h.deferred = plan
         h.span = span
         return h
@@ -725,6 +732,7 @@ class PeerTransport(LocalTransport):
         if full_grad.dtype not in (torch.bfloat16, torch.float32) or \
                 (update is None and out_shard.dtype not in (torch.bfloat16, torch.float32)):
             raise TypeError("peer reduce supports bf16 / fp32 gradients")
+        t_host = time.perf_counter()
         ui = self._unit(unit_key)
         ep = self._epochs[unit_key]
         ep["grad"] += 1
@@ -733,6 +741,7 @@ class PeerTransport(LocalTransport):
         if slot is not None:
             slot.last_epoch = e
         t = self._reduce_tables(unit_key, tables, full_grad.device)
+        t_tables = time.perf_counter()
         cur = torch.cuda.current_stream()
         run = stream if stream is not None else cur
         if stream is not None:
@@ -791,10 +800,12 @@ class PeerTransport(LocalTransport):
             slot.event = ev
         if stream is None:
             ev = None
+        t_end = time.perf_counter()
         h = MatrixCollectiveHandle(event=ev, info={
             "kind": "reduce_scatter", "impl": impl, "backend": self.kind,
             "bytes": full_grad.numel() * full_grad.element_size(), "count": 1,
-            "sync_mode": "stream_event" if stream is not None else "stream_order"})
+            "sync_mode": "stream_event" if stream is not None else "stream_order",
+            "host_phases_ms": {"tables": (t_tables - t_host) * 1e3, "launch": (t_end - t_tables) * 1e3}})
         h.span = span
         return h
 

@@ -199,6 +199,8 @@ def summarize_runtime_events(module_or_units_or_events) -> dict[str, object]:
                 d["max_bytes"] = max(d["max_bytes"], e.collective_bytes)
                 d["collective_count"] += e.collective_count
                 d["issue_host_ms"] += e.duration_ms
+                for phase, ms in ((e.extra or {}).get("host_phases_ms") or {}).items():
+                    d[f"host_{phase}_ms"] = d.get(f"host_{phase}_ms", 0.0) + float(ms)     # inside the collective call
                 d["prefetched"] += int(e.prefetched)
                 d["workspace_reused"] += int(e.workspace_reused)
                 ph["collectives"] += 1
