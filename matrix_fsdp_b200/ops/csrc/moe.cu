@@ -5,7 +5,7 @@
 //   assign_slots     deterministic position of every (token, k) entry inside its expert's queue
 //   push_counts      every rank writes its per-expert counts into every peer's table
 //   plan             from the W x E table: where my rows for expert e start in the owner's buffer,
-//                    128-row aligned expert groups on the owner, tile->expert map for the grouped GEMM
+//                    256-row aligned expert groups on the owner, tile->expert map for the grouped GEMM
 //   dispatch_push    permute + all-to-all in one step: each entry's hidden row is stored straight
 //                    into the owner's receive buffer over mapped peer memory
 //   (grouped GEMMs on the owner: gemm_sm100.cu)
@@ -174,18 +174,22 @@ __global__ void moe_push_counts_kernel(EpPtrs tables, int W, int rank, const int
 
 // ------------------------------------------------------------------ plan
 // counts_all: [W, E] (row = source rank).  Expert e lives on rank e / El; on its owner the rows of
-// expert e form one group that starts on a 128-row boundary, ordered by source rank.
+// expert e form one group that starts on a 256-row boundary, ordered by source rank.
 //   dest_base[e]       row in the owner's buffer where this rank's rows for expert e start
 //   group_offsets[El+1] padded group starts of my experts (clamped to the capacity)
 //   group_rows[El]     real rows of each of my groups (clamped)
 //   tile_group[tiles]  expert of every 128-row tile of my buffer, -1 for unused tiles
 //   stats[0] = padded rows in use on this rank, stats[1] = rows lost to the capacity limit (this rank as owner)
+// Expert groups start on multiples of this many rows: whole 256-row tiles per group let the grouped GEMMs run on
+// CTA pairs (a pair's two CTAs share one B operand, so a 256-row tile must belong to one expert).
+constexpr int kGroupAlign = 256;
+
 __global__ void moe_plan_kernel(const int* __restrict__ counts_all, int W, int rank, int E, int cap_rows,
                                 int* __restrict__ dest_base, int* __restrict__ group_offsets,
                                 int* __restrict__ group_rows, int* __restrict__ tile_group, int* __restrict__ stats) {
   __shared__ int total[256], before[256], start[256];
   const int El = E / W;
-  const int cap = cap_rows / 128 * 128;
+  const int cap = cap_rows / kGroupAlign * kGroupAlign;
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int tot = 0, bef = 0;
     for (int s = 0; s < W; ++s) {
@@ -203,7 +207,7 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts_all, int W, int r
     for (int el = 0; el < El; ++el) {
       const int e = r * El + el;
       start[e] = acc;
-      acc += (total[e] + 127) / 128 * 128;
+      acc += (total[e] + kGroupAlign - 1) / kGroupAlign * kGroupAlign;
     }
     if (r == rank) {
       int lost = 0;
@@ -228,7 +232,7 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts_all, int W, int r
     int g = -1;
     for (int el = 0; el < El; ++el) {
       const int e = rank * El + el;
-      if (row >= start[e] && row < start[e] + (total[e] + 127) / 128 * 128) g = el;
+      if (row >= start[e] && row < start[e] + (total[e] + kGroupAlign - 1) / kGroupAlign * kGroupAlign) g = el;
     }
     tile_group[t] = g;
   }
@@ -240,7 +244,7 @@ __global__ void moe_zero_pad_kernel(__nv_bfloat16* __restrict__ buf, int H, cons
                                     const int* __restrict__ group_rows) {
   const int el = blockIdx.x;
   const int r0 = group_offsets[el] + group_rows[el];
-  const int r1 = min(group_offsets[el + 1], (r0 + 127) / 128 * 128);
+  const int r1 = min(group_offsets[el + 1], (r0 + kGroupAlign - 1) / kGroupAlign * kGroupAlign);
   const int vpr = H >> 3;
   const long long n = (long long)max(0, r1 - r0) * vpr;
   uint4* base = reinterpret_cast<uint4*>(buf + (long long)r0 * H);
@@ -265,7 +269,7 @@ __global__ void moe_dispatch_push_kernel(const __nv_bfloat16* __restrict__ x, lo
     row = route_in[i];
   } else {
     row = dest_base[e] + slot[i];
-    if (row >= cap_rows / 128 * 128) row = -1;
+    if (row >= cap_rows / 256 * 256) row = -1;
     if (lane == 0) route_out[i] = row;
   }
   if (row < 0) return;

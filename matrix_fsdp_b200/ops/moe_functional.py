@@ -100,9 +100,9 @@ class MoEFFNFunction(torch.autograd.Function):
         route = MK.dispatch_push(x, idx, ep.recv_addrs, El, ep.cap_rows, slot=slot, dest_base=dest_base)
         MK.zero_pad(ep.recv, H, group_offsets, group_rows)
         ep.fence(1)
-        gu = K.grouped_gemm_m(ep.recv, w_gu, tile_group)              # [cap, 2F]
+        gu = K.grouped_gemm_m(ep.recv, w_gu, tile_group, groups_of_256_rows=True)              # [cap, 2F]
         h = K.swiglu_fwd(gu)
-        K.grouped_gemm_m(h, w_down, tile_group, out=ep.out)
+        K.grouped_gemm_m(h, w_down, tile_group, out=ep.out, groups_of_256_rows=True)
         del h
         x_recv = ep.recv.clone() if ctx.needs_input_grad[3] or ctx.needs_input_grad[0] else None
         ep.fence(2)
@@ -130,12 +130,12 @@ class MoEFFNFunction(torch.autograd.Function):
         MK.dispatch_push(dy, idx, ep.recv_addrs, El, ep.cap_rows, route=route, scale=w)
         MK.zero_pad(ep.recv, H, group_offsets, group_rows)
         ep.fence(1)
-        dh = K.grouped_gemm_m(ep.recv, w_down, tile_group, b_mn_major=True)          # [cap, F]
+        dh = K.grouped_gemm_m(ep.recv, w_down, tile_group, b_mn_major=True, groups_of_256_rows=True)   # [cap, F]
         dgu, h = MK.swiglu_bwd_dot(dh, gu, ep.out_scalar, stats[0:1])
         del dh
         g_down = K.grouped_gemm_k(ep.recv, h, group_offsets, El)                     # [El, H, F]
         del h
-        K.grouped_gemm_m(dgu, w_gu, tile_group, b_mn_major=True, out=ep.out)         # [cap, H]
+        K.grouped_gemm_m(dgu, w_gu, tile_group, b_mn_major=True, out=ep.out, groups_of_256_rows=True)  # [cap, H]
         g_gu = K.grouped_gemm_k(dgu, x_recv, group_offsets, El)                      # [El, 2F, H]
         del dgu
         ep.fence(2)

@@ -6,7 +6,7 @@ The reference has no EP runtime (docs/introduction.md:238-271); its test fixture
 rank owns two row buffers in peer-mapped memory:
 
 * ``recv`` — rows that other ranks *push* into (tokens in forward, output gradients in backward),
-  grouped by local expert on 128-row boundaries so the grouped GEMM consumes them in place;
+  grouped by local expert on 256-row boundaries so the grouped GEMM consumes them in place;
 * ``out``  — rows this rank's experts produced, which the token owners *pull* and reduce.
 
 One context is shared by all MoE layers of a model: a rank can only start pushing layer ``l+1`` after
@@ -43,7 +43,8 @@ class ExpertParallelContext:
             rows = rows * self.world if self.dropless else min(int(rows * capacity_factor), rows * self.world)
         self.lost_rows = torch.zeros(1, dtype=torch.int64, device=device)
         self.routed_rows = 0
-        self.cap_rows = (rows + self.experts_per_rank * 128 + 127) // 128 * 128
+        # every expert group is padded to whole 256-row tiles (the grouped GEMMs run on CTA pairs)
+        self.cap_rows = (rows + self.experts_per_rank * 256 + 255) // 256 * 256
         self.max_tokens = max_tokens
         self._epoch = {KIND_COUNTS: 0, KIND_PUSHED: 0, KIND_READY: 0}
         nbytes = self.cap_rows * hidden * 2
