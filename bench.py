@@ -171,8 +171,9 @@ def build_ours(cfg: dict, device, mesh, world: int):
     policy = "mixed_muon_adamw" if cfg["optimizer"] == "mixed_muon_adamw" else None
     shard_llama(model, mesh=mesh, mp_policy=mp, optimizer_policy=policy)
     if cfg["optimizer"] == "adamw":
-        # the sharded AdamW update runs inside the gradient reduce-scatter kernel (peer transport, N > 1)
-        fused = world > 1 and os.environ.get("MFSDP_FUSED_REDUCE_UPDATE", "1") != "0"
+        # the sharded AdamW update runs inside the gradient reduce-scatter kernel (peer transport, N > 1) or, on one
+        # GPU, right after each unit's backward on a side stream (beside the next unit's backward GEMMs)
+        fused = os.environ.get("MFSDP_FUSED_REDUCE_UPDATE", "1") != "0"
         opt = configure_optimizer(model, "adamw", lr=cfg["lr"], betas=cfg["betas"], weight_decay=cfg["weight_decay"],
                                   fused_reduce_update=fused, **_sched_overrides())
     else:

@@ -472,6 +472,18 @@ class MatrixFlatBuffer:
         scale = self.grad_scale()
         self.update_done_event = None
         if self.world_size == 1 and self.replicate_world_size == 1 and self.full_aliases_shard \
+                and self.fused_reduce_update is not None and src.is_cuda and scale == 1.0 \
+                and strategy == "bucket_reduce_scatter" and not self.accumulate_into_local_grad \
+                and type(self.transport).__name__ == "LocalTransport":
+            # single rank with the update fused into the "reduce": the bucket is the gradient, AdamW runs now
+            update = self.fused_reduce_update()
+            if update is not None:
+                h = self.transport.local_update(src, update, stream=stream)
+                self.fused_update_applied = True
+                self.update_done_event = getattr(h, "_event", None)
+                self.pending_reduce = h
+                return h
+        if self.world_size == 1 and self.replicate_world_size == 1 and self.full_aliases_shard \
                 and (src.dtype == out.dtype or self.fused_optimizer_consumes_bucket) and scale == 1.0 \
                 and not self.accumulate_into_local_grad:
             # single rank, same dtype: the bucket *is* the local gradient

@@ -65,6 +65,30 @@ class LocalTransport:
     def all_reduce(self, tensor, group, *, scale=None):
         return all_reduce_full_grad(tensor, group, scale=scale)
 
+    def local_update(self, grad: torch.Tensor, update: dict, *, scale=None, stream=None) -> MatrixCollectiveHandle:
+        """One rank: the gradient bucket already is the reduced gradient, so the AdamW update of a unit can run
+        as soon as its backward has finished -- on ``stream``, beside the backward GEMMs of the next unit (a
+        bandwidth-bound kernel next to compute-bound ones) instead of after the whole backward pass.  ``update``
+        holds master / moments / bf16 shard and the hyper-parameters (``optim.flat.FlatShardedAdamW``)."""
+        from ..ops import kernels
+
+        cur = torch.cuda.current_stream(grad.device)
+        run = stream if stream is not None else cur
+        if stream is not None:
+            stream.wait_stream(cur)
+        with torch.cuda.stream(run):
+            kernels.adamw_flat_(update["p"], update["m"], update["v"], grad, lr=float(update["lr"]),
+                                beta1=update["beta1"], beta2=update["beta2"], eps=update["eps"],
+                                weight_decay=update["weight_decay"], step=int(update["step"]),
+                                grad_scale=float(1.0 if scale is None else scale), p_lp=update.get("p_lp"))
+        ev = None
+        if stream is not None:
+            ev = torch.cuda.Event()
+            ev.record(run)
+        return MatrixCollectiveHandle(event=ev, info={
+            "kind": "reduce_scatter", "impl": "local_adamw", "backend": self.kind, "bytes": 0, "count": 0,
+            "sync_mode": "stream_event" if stream is not None else "stream_order"})
+
 
 class TorchDistTransport(LocalTransport):
     kind = "torch_dist"

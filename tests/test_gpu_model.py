@@ -41,7 +41,8 @@ def test_decoder_block_matches_reference(recompute):
     K.check_status()
 
 
-def test_sharded_llama_step_world1_direct_grads_and_fused_adamw():
+@pytest.mark.parametrize("fused_update", [False, True])
+def test_sharded_llama_step_world1_direct_grads_and_fused_adamw(fused_update):
     from torch.distributed.fsdp import MixedPrecisionPolicy
 
     from matrix_fsdp_b200.models.llama import LlamaConfig, LlamaModel, shard_llama
@@ -53,7 +54,9 @@ def test_sharded_llama_step_world1_direct_grads_and_fused_adamw():
     model = LlamaModel(cfg).cuda()
     ref = copy.deepcopy(model)
     shard_llama(model, mp_policy=MixedPrecisionPolicy(param_dtype=torch.bfloat16))
-    opt = configure_optimizer(model, "adamw", lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
+    # fused_update: each unit's AdamW runs on a side stream right after that unit's backward
+    opt = configure_optimizer(model, "adamw", lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1,
+                              fused_reduce_update=fused_update)
     ropt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
     before = K.launch_count()
     losses, rlosses = [], []
@@ -78,3 +81,8 @@ def test_sharded_llama_step_world1_direct_grads_and_fused_adamw():
     # sharded fp32 masters track the eager model
     for (n, p), (_, pr) in zip(model.named_parameters(), ref.named_parameters()):
         assert _rel(p, pr) < 2e-2, n
+    if fused_update:
+        from matrix_fsdp_b200.parallel.unit_collection import collect_param_groups
+
+        impls = {e.collective_impl for u in collect_param_groups(model) for e in u.runtime_events if e.collective_impl}
+        assert "local_adamw" in impls, impls
