@@ -20,7 +20,7 @@ from ..planning.auto_planner import (available_auto_planner_policies, build_auto
                                      make_model_wide_muon_planner, make_muon_shard_aware_group_planner, muon_role_flops)
 from ..planning.planner_eval import call_group_planner
 from ..planning.shard_hint import build_shard_hints
-from .planner_report import build_model
+from .planner_report import ReportConfig, build_model
 
 STRATEGIES = ("rotate", "role_greedy", "cost_aware", "model_wide")
 
@@ -64,7 +64,9 @@ def main(argv=None) -> int:
     ap.add_argument("--repeat", type=int, default=3)
     ap.add_argument("--policies", action="store_true", help="also time the candidate evaluation of every named policy")
     args = ap.parse_args(argv)
-    _, blocks = build_model("llama", args.hidden, args.layers, args.ffn, args.vocab)
+    heads = max(1, args.hidden // 128)
+    _, blocks = build_model(ReportConfig(model="llama", hidden=args.hidden, layers=args.layers, heads=heads,
+                                         intermediate=args.ffn or 4 * args.hidden, vocab=args.vocab))
     regs = [ManagedParamRegistry.from_module(b, shard_hints=build_shard_hints(b)) for b in blocks]
     rows = []
     for world in args.world:
