@@ -343,7 +343,7 @@ def summarize_report(report_dir: Path) -> dict:
                 ph = r.get("phase_ms", {})
                 base = by_mode.get(_LIBRARY_ROW.get(r["mode"], "fsdp2"))
                 row = {"log": log.name, "mode": r["mode"], "step_ms": r["step_ms"], "fwd_ms": ph.get("forward"),
-                       "bwd_ms": ph.get("backward"), "opt_ms": ph.get("optimizer"), "peak_mb": r.get("peak_mb"),
+                       "bwd_ms": ph.get("backward"), "opt_ms": ph.get("step", ph.get("optimizer")), "peak_mb": r.get("peak_mb"),
                        "vs_library": (base["step_ms"] / r["step_ms"]) if base and base is not r and r["step_ms"] else None,
                        "max_param_diff": r.get("max_param_diff_vs_eager")}
                 phase.append(row)

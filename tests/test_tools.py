@@ -159,9 +159,9 @@ def test_runbook_summariser_builds_tables_from_logs(tmp_path, capsys):
     rep.mkdir()
     (rep / "compare_adamw.log").write_text("\n".join([
         "NCCL version 2.28.9+cuda12.9",
-        json.dumps({"mode": "fsdp2", "step_ms": 20.0, "phase_ms": {"forward": 6.0, "backward": 12.0, "optimizer": 2.0},
+        json.dumps({"mode": "fsdp2", "step_ms": 20.0, "phase_ms": {"forward": 6.0, "backward": 12.0, "step": 2.0},
                     "peak_mb": 900.0}),
-        json.dumps({"mode": "matrix_default", "step_ms": 16.0, "phase_ms": {"forward": 5.0, "backward": 10.0, "optimizer": 1.0},
+        json.dumps({"mode": "matrix_default", "step_ms": 16.0, "phase_ms": {"forward": 5.0, "backward": 10.0, "step": 1.0},
                     "peak_mb": 800.0, "max_param_diff_vs_eager": 1e-3,
                     "memory_trace": {"after_backward": {"allocated_mb": 1.0, "max_allocated_mb": 2.0, "reserved_mb": 3.0}}}),
         json.dumps({"mode": "matrix_row", "unavailable": "ValueError: nope"})]))
@@ -182,6 +182,7 @@ def test_runbook_summariser_builds_tables_from_logs(tmp_path, capsys):
     s = rb.summarize_report(rep)
     by_mode = {r["mode"]: r for r in s["phase"]}
     assert abs(by_mode["matrix_default"]["vs_library"] - 1.25) < 1e-9 and by_mode["fsdp2"]["vs_library"] is None
+    assert by_mode["matrix_default"]["opt_ms"] == 1.0 and by_mode["fsdp2"]["fwd_ms"] == 6.0
     assert s["arms"] == [{"config": "m", "n_gpus": 2, "reference": 100.0, "ours": 150.0, "ratio": 1.5}]
     assert {c["op"] for c in s["comm"]} == {"all_gather", "rs+adamw"}
     assert s["memory"][0]["phase"] == "after_backward" and s["timeline"][0]["collective"] == "all_gather/ag_pull"
