@@ -1,8 +1,9 @@
-"""Peer-memory transport: FSDP collectives as hand-written kernels over IPC-mapped peer buffers.
+"""Peer-memory transport: FSDP collectives as hand-written kernels over symmetric peer buffers.
 
 One :class:`PeerContext` per (process group, device) owns *symmetric* memory: every rank performs
-the same sequence of allocations, shares each segment through CUDA IPC, and maps all peers'
-segments once.  :class:`PeerTransport` then implements the transport interface on top of it:
+the same sequence of allocations and learns every peer's address of each segment once -- through
+``torch.distributed._symmetric_memory`` (which also yields the NVSwitch multicast address), or through
+``cudaMalloc`` + CUDA IPC handles where that is not available.  :class:`PeerTransport` then implements the transport interface on top of it:
 
 ``gather``   publish "my shard for this unit is ready (epoch e)" → wait for every peer's flag →
              ``ag_pull`` copies each peer's segments from its shard buffer straight into the local
