@@ -150,3 +150,35 @@ def test_fused_weight_needs_one_storage_not_adjacent_addresses():
 
     fake = FakeAdjacent(y, x.data_ptr() + x.numel() * 4)
     assert OF._fused_weight([x, fake]) is None
+
+
+def test_embedding_falls_back_to_torch_off_gpu_and_token_embedding_keeps_the_parameter_name():
+    import torch
+    from torch import nn
+
+    from matrix_fsdp_b200.models.llama import TokenEmbedding
+    from matrix_fsdp_b200.ops import functional as OF
+
+    torch.manual_seed(0)
+    emb = TokenEmbedding(50, 16)
+    assert isinstance(emb, nn.Embedding) and [n for n, _ in emb.named_parameters()] == ["weight"]
+    ids = torch.randint(0, 50, (3, 7))
+    out = emb(ids)
+    assert torch.equal(out, torch.nn.functional.embedding(ids, emb.weight))
+    out.sum().backward()
+    ref = torch.zeros(50, 16).index_add_(0, ids.reshape(-1), torch.ones(21, 16))
+    assert torch.allclose(emb.weight.grad, ref)
+    assert torch.equal(OF.embedding(ids, emb.weight.detach()), out.detach())
+
+
+def test_newton_schulz_shares_are_balanced_and_deterministic():
+    from matrix_fsdp_b200.optim.muon import assign_to_replicas, ns_flops
+
+    shapes = [(4096, 4096)] * 4 + [(11008, 4096)] * 3 + [(256, 256)]
+    owner = assign_to_replicas(shapes, 2, 5)
+    assert owner == assign_to_replicas(list(shapes), 2, 5) and set(owner) == {0, 1}
+    load = [sum(ns_flops(s, 5) for s, o in zip(shapes, owner) if o == r) for r in (0, 1)]
+    assert max(load) / min(load) < 1.35
+    assert assign_to_replicas(shapes, 1, 5) == [0] * len(shapes)
+    # more replicas than matrices: every matrix still has exactly one owner
+    assert sorted(assign_to_replicas([(8, 8), (16, 8)], 4, 5)) == [0, 1]
