@@ -221,3 +221,20 @@ def test_planner_report_units_models_and_json(capsys):
     assert planner_report.main(["--unit", "model", "--owner-assignment", "model_wide", "--layers", "2", "--hidden", "128",
                                 "--world-size", "4", "--selected-only"]) == 0
     assert "<model>" in capsys.readouterr().out
+
+
+def test_runtime_profile_models_units_and_output_file(tmp_path, capsys):
+    out = tmp_path / "profile.json"
+    assert runtime_profile.main(["--world-size", "2", "--model", "transformer", "--hidden", "32", "--heads", "4",
+                                 "--activation-checkpoint", "--dtype", "bfloat16", "--mode", "no_prefetch",
+                                 "--format", "json", "--output", str(out)]) == 0
+    assert capsys.readouterr().out.strip() == ""
+    d = json.loads(out.read_text())
+    assert d["model"] == "transformer" and d["dtype"] == "bfloat16" and d["activation_checkpoint"] and len(d["step_ms_each"]) == 2
+    assert d["scheduler"]["counters"]["forward_prefetch_issued"] == 0
+    # one unit per Linear plus one root unit per block for the norms; optimizer override; text form
+    assert runtime_profile.main(["--world-size", "1", "--model", "transformer_split_qkv", "--unit", "linear", "--layers", "2",
+                                 "--hidden", "32", "--heads", "4", "--optimizer", "sgd",
+                                 "--max-active-full-param-buffers", "3"]) == 0
+    text = capsys.readouterr().out
+    assert "optimizer=sgd" in text and text.count("param_group_") >= 2 * 7
