@@ -382,7 +382,12 @@ class PeerTransport(LocalTransport):
         self._ar_state: dict[tuple, dict] = {}
         # NVLS: persistent full-parameter slots (all-gather by multimem.st push)
         self.nvls = ctx.nvls
-        self.nvls_gather = ctx.nvls and os.environ.get("MFSDP_NVLS_GATHER", "1") != "0"
+        # The multicast push delivers every shard to ALL copies of the slot, the sender's own included, so a GPU
+        # ingests the whole buffer instead of (W-1)/W of it.  On 2 GPUs that doubles the inbound traffic and the
+        # pull gather wins by 0.75 ms per config-2 step (measured back to back); "auto" therefore pushes only
+        # from 4 ranks up.  MFSDP_NVLS_GATHER=1 / 0 forces either.
+        mode = os.environ.get("MFSDP_NVLS_GATHER", "auto")
+        self.nvls_gather = ctx.nvls and (mode == "1" or (mode not in ("0", "1") and ctx.world >= 4))
         self.nvls_reduce = ctx.nvls and os.environ.get("MFSDP_NVLS_REDUCE", "1") != "0"
         self.full_slots_per_class = max(int(os.environ.get(FULL_SLOTS_ENV, "2")), 1)
         self._full_rings: dict[int, list[_FullSlot]] = {}
