@@ -103,6 +103,7 @@ def _nvls_collectives(rank, world):
     from matrix_fsdp_b200.parallel.peer import PeerTransport
 
     os.environ["MFSDP_PEER_FULL_SLOTS"] = "1"          # both test units share one slot
+    os.environ["MFSDP_NVLS_GATHER"] = "1"              # the push gather is only the default from 4 ranks up
     dev = torch.device("cuda", rank)
     tr = PeerTransport.create(dist.group.WORLD, dev)
     assert tr is not None
