@@ -270,6 +270,18 @@ def test_sharded_training_without_nvls_matches():
         os.environ.pop("MFSDP_NVLS", None)
 
 
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_sharded_training_with_multicast_push_gather_matches():
+    """On 2 GPUs the push all-gather (persistent symmetric slots, slot hand-over flags) is not the default;
+    train with it on purpose so that path stays covered where only 2 GPUs are available."""
+    os.environ["MFSDP_NVLS_GATHER"] = "1"
+    try:
+        with tempfile.TemporaryDirectory() as d:
+            _run(_train_both, 2, d)
+    finally:
+        os.environ.pop("MFSDP_NVLS_GATHER", None)
+
+
 def _owner_muon_train(rank, world, transport_kind):
     """Matrix-owner layout + mixed Muon / AdamW: every 2-D block matrix lives whole on one rank."""
     from torch.distributed.fsdp import MixedPrecisionPolicy
