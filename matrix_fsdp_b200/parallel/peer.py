@@ -140,7 +140,11 @@ class PeerContext:
         (``cuMemCreate`` + multicast binding, which gives every segment a multicast address)."""
         want = _nvls_requested()
         ok = False
-        if want != "0":
+        # Sub-groups of the world (the shard and replicate groups of a hybrid mesh) keep CUDA-IPC segments: with
+        # symmetric-memory segments a 2 x 2 mesh stopped in the rendezvous of a gradient buffer allocated during the
+        # first backward (all four ranks inside ``rendezvous``, ended by the run's time limit; cause not found).
+        whole_world = dist.get_world_size(self.group) == dist.get_world_size()
+        if want != "0" and (whole_world or want == "1"):
             try:
                 import torch.distributed._symmetric_memory as symm_mem   # noqa: F401
                 from torch._C._autograd import DeviceType
