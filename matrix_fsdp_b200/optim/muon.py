@@ -30,6 +30,7 @@ DEFAULT_NS_COEFFICIENTS = (3.4445, -4.7750, 2.0315)
 DEFAULT_MUON_ADJUST_LR_FN = "match_rms_adamw"
 EPS = 1e-7
 MAX_BATCH_ELEMENTS = 1 << 28      # elements of one stacked Newton-Schulz operand (512 MB of bf16)
+SHARE_WINDOW_ELEMENTS = 1 << 29   # elements exchanged per all-reduce when replicas share Newton-Schulz (1 GB of bf16)
 # X Xᵀ and b A + c A A are symmetric: compute the tiles on or above the diagonal, mirror the rest
 SYMMETRIC_PRODUCTS = os.environ.get("MFSDP_MUON_SYMMETRIC", "1") != "0"
 
@@ -323,16 +324,34 @@ class MatrixMuon(Optimizer):
         pg = self.ns_share_group
         replicas, me = dist.get_world_size(pg), dist.get_rank(pg)
         owner = assign_to_replicas([tuple(p.shape) for p in ps], replicas, group["ns_steps"])
-        us = [self._prepare(p, group) for p in ps]                     # every replica: keeps momentum in sync
-        offsets, total = [], 0
-        for p in ps:
-            offsets.append(total)
-            total += (p.numel() + 7) // 8 * 8
-        flat = torch.zeros(total, dtype=torch.bfloat16, device=ps[0].device)
-        mine_by_shape: dict[tuple, list[int]] = {}
+        # Work through the matrices in windows of at most SHARE_WINDOW_ELEMENTS: the normalised operands and the
+        # exchange buffer of a window are temporaries (2 x 2 bytes per element), and a model's worth of them at
+        # once would cost as much memory as the bf16 parameters themselves.
+        window: list[int] = []
+        size = 0
         for j, p in enumerate(ps):
+            n = (p.numel() + 7) // 8 * 8
+            if window and size + n > SHARE_WINDOW_ELEMENTS:
+                self._share_window(ps, window, owner, me, replicas, pg, group)
+                window, size = [], 0
+            window.append(j)
+            size += n
+        if window:
+            self._share_window(ps, window, owner, me, replicas, pg, group)
+
+    def _share_window(self, ps: list, window: list[int], owner: list[int], me: int, replicas: int, pg, group: dict) -> None:
+        import torch.distributed as dist
+
+        us = {j: self._prepare(ps[j], group) for j in window}          # every replica: keeps momentum in sync
+        offsets, total = {}, 0
+        for j in window:
+            offsets[j] = total
+            total += (ps[j].numel() + 7) // 8 * 8
+        flat = torch.zeros(total, dtype=torch.bfloat16, device=ps[window[0]].device)
+        mine_by_shape: dict[tuple, list[int]] = {}
+        for j in window:
             if owner[j] == me:
-                mine_by_shape.setdefault(tuple(p.shape), []).append(j)
+                mine_by_shape.setdefault(tuple(ps[j].shape), []).append(j)
         for shape, idx in mine_by_shape.items():
             per_chunk = max(1, MAX_BATCH_ELEMENTS // (shape[0] * shape[1]))
             for i in range(0, len(idx), per_chunk):
@@ -342,5 +361,5 @@ class MatrixMuon(Optimizer):
         del us
         if replicas > 1:
             dist.all_reduce(flat, group=pg)
-        for j, p in enumerate(ps):
-            self._apply(p, flat[offsets[j]:offsets[j] + p.numel()].view(p.shape), group)
+        for j in window:
+            self._apply(ps[j], flat[offsets[j]:offsets[j] + ps[j].numel()].view(ps[j].shape), group)

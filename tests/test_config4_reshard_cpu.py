@@ -100,8 +100,10 @@ def test_hsdp_2x2_checkpoint_reshards_onto_dp_shard_4():
 def _shared_ns_worker(rank, world):
     """Splitting Newton-Schulz over the two replicas changes who computes, not what: parameters and momentum
     are bitwise those of the run where every replica orthogonalises every matrix."""
+    from matrix_fsdp_b200.optim import muon as muon_mod
     from matrix_fsdp_b200.optim.muon import MatrixMuon
 
+    muon_mod.SHARE_WINDOW_ELEMENTS = 2048        # several exchange windows per step (the matrices have 1536-3072 elements)
     results = {}
     for share in (True, False):
         model, opt = _build("hsdp")
