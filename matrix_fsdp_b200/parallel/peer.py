@@ -678,7 +678,7 @@ class PeerTransport(LocalTransport):
 
     def _all_reduce_own_group(self, tensor: torch.Tensor, scale) -> None:
         ctx = self.ctx
-        key = ("ar", tensor.numel(), tensor.dtype)   # one staging buffer per size: rounds are ordered by the flags
+        key = ("ar", tensor.numel(), tensor.dtype)   # one staging buffer per size: successive exchanges are ordered by the flags
         st = self._ar_state.get(key)
         if st is None:
             buf = ctx.alloc((tensor.numel() * tensor.element_size() + 15) // 16 * 16)
@@ -693,7 +693,7 @@ class PeerTransport(LocalTransport):
         is_bf16 = int(tensor.dtype == torch.bfloat16)
         use_mc = bool(self.nvls_reduce and st["buf"].mc_addr and tensor.numel() % 8 == 0)
         if st["epoch"] > 0 and not use_mc:
-            ctx.wait(ui, KIND_PULLED, st["epoch"], run)          # everyone has read the previous round
+            ctx.wait(ui, KIND_PULLED, st["epoch"], run)          # everyone has read the previous exchange
         st["epoch"] += 1
         e = st["epoch"]
         st["view"].copy_(tensor.view(-1))
