@@ -238,3 +238,21 @@ def test_runtime_profile_models_units_and_output_file(tmp_path, capsys):
                                  "--max-active-full-param-buffers", "3"]) == 0
     text = capsys.readouterr().out
     assert "optimizer=sgd" in text and text.count("param_group_") >= 2 * 7
+
+
+def test_runbook_runs_a_batch_and_writes_the_summary(tmp_path, monkeypatch, capsys):
+    """``run_batch`` executes every step in its own process, keeps one log per step and ends with the tables."""
+    import sys
+
+    from matrix_fsdp_b200.tools import gpu_runbook as rb
+
+    row = {"mode": "matrix_default", "step_ms": 2.0, "phase_ms": {"forward": 1.0, "backward": 0.8, "step": 0.2}, "peak_mb": 1.0}
+    ok = rb.Step("fake_compare", [sys.executable, "-c", f"import json; print(json.dumps({row!r}))"])
+    bad = rb.Step("fake_failure", [sys.executable, "-c", "raise SystemExit(3)"])
+    monkeypatch.setitem(rb.BATCHES, "fake", (lambda s: [ok, bad], "two fabricated steps"))
+    rc = rb.run_batch("fake", rb.Settings(), str(tmp_path / "rep"))
+    out = capsys.readouterr().out
+    assert rc == 1 and "fake_compare" in out and "rc=3" in out
+    assert (tmp_path / "rep" / "fake_compare.log").read_text().startswith("{")
+    summary = (tmp_path / "rep" / "summary.txt").read_text()
+    assert "== step time by mode ==" in summary and "matrix_default" in summary
