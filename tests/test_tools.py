@@ -256,3 +256,24 @@ def test_runbook_runs_a_batch_and_writes_the_summary(tmp_path, monkeypatch, caps
     assert (tmp_path / "rep" / "fake_compare.log").read_text().startswith("{")
     summary = (tmp_path / "rep" / "summary.txt").read_text()
     assert "== step time by mode ==" in summary and "matrix_default" in summary
+
+
+def test_compare_bench_modes_run_and_match_eager_on_two_cpu_ranks(capsys):
+    """A cross-section of the comparison bench's runtime modes on 2 Gloo ranks: every mode reports a step time,
+    none is unavailable, parameters after the steps equal the eager model's, and the full gradients gathered
+    by parameter name were checked."""
+    from matrix_fsdp_b200.tools import compare_bench
+
+    modes = ["matrix_default", "matrix_row", "matrix_owner_muon", "matrix_zero_copy_grads", "matrix_saved_tensor_hooks",
+             "matrix_per_param_reduce", "matrix_all_reduce_gather", "matrix_adaptive_prefetch", "matrix_fused_reduce_update",
+             "fsdp2"]
+    assert compare_bench.main(["--device", "cpu", "--world-size", "2", "--hidden", "32", "--heads", "2", "--layers", "2",
+                               "--seq", "8", "--steps", "1", "--warmup", "1", "--correctness", "--modes", *modes]) == 0
+    rows = [json.loads(ln) for ln in capsys.readouterr().out.splitlines() if ln.startswith("{")]
+    assert [r["mode"] for r in rows] == modes
+    for r in rows:
+        assert "unavailable" not in r and r["step_ms"] > 0, r
+        assert r["max_param_diff_vs_eager"] < 1e-4 and r["max_loss_diff_vs_eager"] < 1e-4, r
+    checked = [r for r in rows if "full_grad_check" in r]
+    assert len(checked) >= 5 and all(c["full_grad_check"]["max_abs_diff"] < 1e-4 and c["full_grad_check"]["params_compared"] > 0 for c in checked)
+    assert all(set(r["phase_ms"]) >= {"forward", "backward", "step"} for r in rows)
