@@ -91,6 +91,8 @@ class TokenEmbedding(nn.Embedding):
     """``nn.Embedding`` (same parameter name and shape) whose backward writes the owning unit's gradient bucket."""
 
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        if self.padding_idx is not None or self.max_norm is not None or self.scale_grad_by_freq or self.sparse:
+            return super().forward(ids)           # options the kernel path does not implement
         return OF.embedding(ids, self.weight, self.weight)
 
 
