@@ -613,6 +613,10 @@ def main() -> None:
     if rank == 0:
         print(json.dumps(out))
     if world > 1:
+        if args.impl == "ours" and cuda:
+            from matrix_fsdp_b200.parallel.peer import PeerTransport
+
+            PeerTransport.close_all()       # nobody exits while a peer may still touch its symmetric memory
         dist.destroy_process_group()
 
 

@@ -426,6 +426,18 @@ class PeerTransport(LocalTransport):
         cls._transports[key] = transport
         return transport
 
+    @classmethod
+    def close_all(cls) -> None:
+        """Collective, at the end of a program: every rank finishes its own GPU work, then waits for all others,
+        before any of them exits and its symmetric (possibly multicast-bound) memory goes away under a peer."""
+        for transport in list(cls._transports.values()):
+            ctx = transport.ctx
+            try:
+                torch.cuda.synchronize(ctx.device)
+                dist.barrier(group=ctx.group)
+            except Exception:  # noqa: BLE001  (the process group may already be gone)
+                pass
+
     def _unit(self, unit_key: str) -> int:
         idx = self._unit_index.get(unit_key)
         if idx is None:

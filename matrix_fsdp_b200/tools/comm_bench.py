@@ -257,6 +257,7 @@ def main(argv=None) -> int:
         if args.out:
             with open(args.out, "w") as f:
                 json.dump({"world": world, "numel": args.numel, "layout": args.layout, "results": results}, f, indent=1)
+    PeerTransport.close_all()
     dist.destroy_process_group()
     return 0
 
