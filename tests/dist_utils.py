@@ -1,6 +1,7 @@
 """Spawn helpers for multi-rank CPU tests (gloo over loopback, file:// rendezvous)."""
 import os
 import tempfile
+import time
 import traceback
 
 import torch
@@ -31,9 +32,20 @@ def run_ranks(fn, world: int, *args, timeout: float = 240.0):
         init_file = os.path.join(tmp, "rdzv")
         ctx = mp.spawn(_entry, args=(world, fn, init_file, args, tmp), nprocs=world, join=False)
         try:
+            # ``join`` returns each time one rank ends, so wait against a deadline; ranks still running after it
+            # are stuck (one left a collective the others are still in) and are ended here, by the handles this
+            # call started
+            deadline = time.monotonic() + 3 * timeout
             ok = ctx.join(timeout=timeout)
-            while not ok:
-                ok = ctx.join(timeout=timeout)
+            while not ok and time.monotonic() < deadline:
+                ok = ctx.join(timeout=max(1.0, deadline - time.monotonic()))
+            if not ok:
+                for proc in ctx.processes:
+                    if proc.is_alive():
+                        proc.terminate()
+                for proc in ctx.processes:
+                    proc.join(10)
+                raise TimeoutError(f"ranks still running after {3 * timeout:.0f} s")
         except Exception as exc:
             msgs = []
             for r in range(world):

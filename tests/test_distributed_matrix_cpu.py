@@ -1,0 +1,282 @@
+"""Two gloo ranks, one option per case: two training steps of the sharded model equal the eager model whose
+gradients are averaged over the ranks, and every unit ends sharded with no full-parameter storage.
+
+All cases of one world size run inside ONE spawn (the rendezvous and the imports are the expensive part); each
+case records its own outcome and is reported as its own test.  The reference keeps one test per option in
+test/fsdp/test_matrix_fsdp_distributed.py:2624-3121."""
+import copy
+import json
+import os
+import tempfile
+import traceback
+
+import pytest
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from dist_utils import run_ranks
+
+
+class Blk(nn.Module):
+    def __init__(self, d):
+        super().__init__()
+        self.a = nn.Linear(d, 2 * d)
+        self.n = nn.LayerNorm(2 * d)
+        self.b = nn.Linear(2 * d, d, bias=False)
+
+    def forward(self, x):
+        return x + self.b(torch.relu(self.n(self.a(x))))
+
+
+class CkptBlk(Blk):
+    def forward(self, x):
+        from torch.utils.checkpoint import checkpoint
+
+        return checkpoint(super().forward, x, use_reentrant=False)
+
+
+def _model(block=Blk, d=8, n=3):
+    torch.manual_seed(0)
+    m = nn.Sequential(*[block(d) for _ in range(n)])
+    m.add_module("head", nn.Linear(d, d))
+    return m
+
+
+def _bf16():
+    from torch.distributed.fsdp import MixedPrecisionPolicy
+
+    return MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+
+
+def _planner(name):
+    from matrix_fsdp_b200.planning import planner as P
+
+    return getattr(P, name)
+
+
+# name -> (wrap, shard kwargs factory, optimizer, options)
+#   wrap: "root" one unit | "units" one unit per block + root | "policy" wrap_policy over blocks + root
+CASES = {
+    "root_default": ("root", lambda: {}, "adamw", {}),
+    "units_default": ("units", lambda: {}, "adamw", {}),
+    "policy_default": ("policy", lambda: {}, "adamw", {}),
+    "root_keep_after_forward": ("root", lambda: dict(reshard_after_forward=False), "adamw", {}),
+    "units_keep_after_forward": ("units", lambda: dict(reshard_after_forward=False), "adamw", {}),
+    "policy_keep_after_forward": ("policy", lambda: dict(reshard_after_forward=False), "adamw", {}),
+    "root_finalize_at_end_of_backward": ("root", lambda: dict(finalize_after_backward=False), "adamw", {}),
+    "units_finalize_at_end_of_backward": ("units", lambda: dict(finalize_after_backward=False), "adamw", {}),
+    "policy_finalize_at_end_of_backward": ("policy", lambda: dict(finalize_after_backward=False), "adamw", {}),
+    "units_no_forward_prefetch": ("units", lambda: dict(forward_prefetch=False), "adamw", {}),
+    "units_no_backward_prefetch": ("units", lambda: dict(backward_prefetch=False), "adamw", {}),
+    "policy_no_prefetch_at_all": ("policy", lambda: dict(forward_prefetch=False, backward_prefetch=False), "sgd", {}),
+    "units_reduce_flat": ("units", lambda: dict(backward_reduce_strategy="flat"), "adamw", {}),
+    "units_reduce_per_param": ("units", lambda: dict(backward_reduce_strategy="per_param"), "adamw", {}),
+    "units_reduce_per_param_allreduce": ("units", lambda: dict(backward_reduce_strategy="per_param_allreduce"), "adamw", {}),
+    "units_grad_reduce_alias": ("units", lambda: dict(grad_reduce_strategy="bucket_reduce_scatter"), "sgd", {}),
+    "units_fsdp2_chunks": ("units", lambda: dict(group_planner=_planner("fsdp2_chunk_plan")), "adamw", {}),
+    "units_parameter_boundaries": ("units", lambda: dict(group_planner=_planner("parameter_boundary_plan")), "adamw", {}),
+    "units_ordered_groups": ("units", lambda: dict(group_planner=_planner("ordered_group_plan")), "adamw", {}),
+    "units_owner_tail": ("units", lambda: dict(group_planner=_planner("ordered_matrix_owner_tail_plan"),
+                                               auto_shard_hints=True), "adamw", {}),
+    "units_auto_balanced": ("units", lambda: dict(auto_planner_policy="balanced"), "adamw", {}),
+    "units_auto_zero_copy_friendly": ("units", lambda: dict(auto_planner_policy="zero_copy_friendly"), "adamw", {}),
+    "units_auto_min_comm": ("units", lambda: dict(auto_planner_policy="min_comm"), "sgd", {}),
+    "units_gather_equal": ("units", lambda: dict(param_gather_strategy="equal_all_gather"), "adamw", {}),
+    "units_gather_uneven": ("units", lambda: dict(param_gather_strategy="uneven_all_gather",
+                                                  group_planner=_planner("parameter_boundary_plan")), "adamw", {}),
+    "units_gather_padded": ("units", lambda: dict(param_gather_strategy="matrix_all_gather",
+                                                  group_planner=_planner("parameter_boundary_plan")), "adamw", {}),
+    "units_gather_owner_broadcast": ("units", lambda: dict(param_gather_strategy="owner_broadcast",
+                                                           group_planner=_planner("parameter_boundary_plan")), "adamw", {}),
+    "units_gather_all_reduce": ("units", lambda: dict(param_gather_strategy="all_reduce",
+                                                      group_planner=_planner("parameter_boundary_plan")), "adamw", {}),
+    "units_backend_torch": ("units", lambda: dict(matrix_collective_backend="torch",
+                                                  group_planner=_planner("parameter_boundary_plan")), "adamw", {}),
+    "units_layout_segment_runtime": ("units", lambda: dict(runtime_layout_policy="segment_runtime",
+                                                           group_planner=_planner("parameter_boundary_plan")), "adamw", {}),
+    "units_zero_copy_bucket": ("units", lambda: dict(use_zero_copy_grad_bucket=True), "adamw", {}),
+    "units_saved_tensor_hooks": ("units", lambda: dict(use_saved_tensor_hooks=True), "adamw", {}),
+    "units_keep_storage_after_backward": ("units", lambda: dict(shrink_full_param_storage_after_backward=False),
+                                          "adamw", {"storage_may_stay": True}),
+    "units_sum_not_mean": ("units", lambda: dict(divide_grads_by_world=False), "sgd", {"sum": True}),
+    "root_bf16": ("root", lambda: dict(mp_policy=_bf16()), "adamw", {"bf16": True}),
+    "units_bf16": ("units", lambda: dict(mp_policy=_bf16()), "adamw", {"bf16": True}),
+    "units_bf16_flat_reduce": ("units", lambda: dict(mp_policy=_bf16(), backward_reduce_strategy="flat"), "adamw",
+                               {"bf16": True}),
+    "root_no_sync": ("root", lambda: {}, "sgd", {"no_sync": True}),
+    "units_no_sync": ("units", lambda: {}, "sgd", {"no_sync": True}),
+    "units_no_sync_keep_after_forward": ("units", lambda: dict(reshard_after_forward=False), "sgd", {"no_sync": True}),
+    "units_no_sync_flat_reduce": ("units", lambda: dict(backward_reduce_strategy="flat"), "sgd", {"no_sync": True}),
+    "units_bf16_no_sync": ("units", lambda: dict(mp_policy=_bf16()), "sgd", {"no_sync": True, "bf16": True}),
+    "root_activation_checkpoint": ("root", lambda: {}, "adamw", {"ckpt": True}),
+    "units_activation_checkpoint": ("units", lambda: {}, "adamw", {"ckpt": True}),
+    "units_sched_two_ahead": ("units", lambda: {}, "adamw", {"opt_kw": dict(max_unsharded_prefetch_units=2)}),
+    "units_sched_post_reshard_prefetch": ("units", lambda: {}, "adamw",
+                                          {"opt_kw": dict(backward_prefetch_timing="post_reshard")}),
+    "units_sched_one_active_buffer": ("units", lambda: {}, "adamw", {"opt_kw": dict(max_active_full_param_buffers=1)}),
+    "units_sched_two_pending_reduces": ("units", lambda: {}, "adamw", {"opt_kw": dict(max_pending_backward_reduces=2)}),
+}
+
+
+# four ranks as a 2 x 2 mesh: shards inside a replica, replicas average the reduced shards
+HSDP_CASES = {
+    "hsdp_units_default": ("units", lambda: {}, "adamw", {}),
+    "hsdp_root_default": ("root", lambda: {}, "adamw", {}),
+    "hsdp_policy_default": ("policy", lambda: {}, "sgd", {}),
+    "hsdp_units_keep_after_forward": ("units", lambda: dict(reshard_after_forward=False), "adamw", {}),
+    "hsdp_units_reduce_flat": ("units", lambda: dict(backward_reduce_strategy="flat"), "adamw", {}),
+    "hsdp_units_reduce_per_param": ("units", lambda: dict(backward_reduce_strategy="per_param"), "adamw", {}),
+    "hsdp_units_parameter_boundaries": ("units", lambda: dict(group_planner=_planner("parameter_boundary_plan")),
+                                        "adamw", {}),
+    "hsdp_units_bf16": ("units", lambda: dict(mp_policy=_bf16()), "adamw", {"bf16": True}),
+    "hsdp_units_no_sync": ("units", lambda: {}, "sgd", {"no_sync": True}),
+    "hsdp_units_activation_checkpoint": ("units", lambda: {}, "adamw", {"ckpt": True}),
+    "hsdp_units_zero_copy_bucket": ("units", lambda: dict(use_zero_copy_grad_bucket=True), "adamw", {}),
+}
+
+
+def _shard(model, wrap, kw):
+    from matrix_fsdp_b200 import matrix_fully_shard
+    from matrix_fsdp_b200.policy.wrap import module_type_policy
+
+    if wrap == "units":
+        for blk in list(model.children())[:-1]:
+            matrix_fully_shard(blk, **kw)
+    elif wrap == "policy":
+        matrix_fully_shard(model, wrap_policy=module_type_policy(Blk), **kw)
+    matrix_fully_shard(model, **kw)          # the root unit: everything no block claimed (all of it for "root")
+
+
+_MESH = {}
+
+
+def _hsdp_mesh(world):
+    if world not in _MESH:                    # one mesh (one set of process groups) for all cases of the spawn
+        from torch.distributed.device_mesh import init_device_mesh
+
+        _MESH[world] = init_device_mesh("cpu", (2, world // 2), mesh_dim_names=("dp_replicate", "dp_shard"))
+    return _MESH[world]
+
+
+def _full_params(model):
+    from matrix_fsdp_b200.parallel.unit_collection import collect_param_groups
+
+    units = collect_param_groups(model)
+    for u in units:
+        u.unshard("test")
+    out = {n: p.detach().clone().float() for n, p in model.named_parameters()}
+    for u in units:
+        u.reshard("test")
+    return out
+
+
+def _run_case(rank, world, name):
+    from matrix_fsdp_b200 import configure_optimizer
+    from matrix_fsdp_b200.api import reset_shared_owner_planners
+    from matrix_fsdp_b200.parallel.unit_collection import collect_param_groups
+
+    wrap, make_kw, opt_kind, o = (HSDP_CASES if name.startswith("hsdp_") else CASES)[name]
+    reset_shared_owner_planners()
+    model = _model(CkptBlk if o.get("ckpt") else Blk)
+    ref = copy.deepcopy(model)
+    kw = make_kw()
+    if name.startswith("hsdp_"):
+        from matrix_fsdp_b200 import DataParallelMeshDims
+
+        kw.update(mesh=_hsdp_mesh(world), dp_mesh_dims=DataParallelMeshDims(shard="dp_shard", replicate="dp_replicate"))
+    _shard(model, wrap, kw)
+    hyper = dict(lr=1e-2, weight_decay=0.0) if opt_kind == "adamw" else dict(lr=0.05)
+    opt = configure_optimizer(model, opt_kind, **hyper, **o.get("opt_kw", {}))
+    ropt = (torch.optim.AdamW if opt_kind == "adamw" else torch.optim.SGD)(ref.parameters(), **hyper)
+    bf16 = bool(o.get("bf16"))
+    g = torch.Generator().manual_seed(100 + rank)
+
+    def loss_of(m, x):
+        y = m(x.bfloat16()) if (bf16 and m is model) else m(x)
+        return y.float().pow(2).mean()
+
+    for _ in range(2):
+        xs = [torch.randn(4, 8, generator=g) for _ in range(2 if o.get("no_sync") else 1)]
+        if o.get("no_sync"):
+            with model.no_sync():
+                loss_of(model, xs[0]).backward()
+            loss_of(model, xs[1]).backward()
+        else:
+            loss_of(model, xs[0]).backward()
+        opt.step()
+        opt.zero_grad()
+        for x in xs:
+            loss_of(ref, x).backward()
+        for p in ref.parameters():
+            dist.all_reduce(p.grad)
+            if not o.get("sum"):
+                p.grad /= world
+        ropt.step()
+        ropt.zero_grad()
+    full = _full_params(model)
+    tol = 3e-2 if bf16 else 3e-5
+    for n, p in ref.named_parameters():
+        assert torch.allclose(full[n], p.detach(), atol=tol, rtol=1e-3 if bf16 else 1e-4), \
+            (n, float((full[n] - p.detach()).abs().max()))
+    units = collect_param_groups(model)
+    assert len(units) == {"root": 1}.get(wrap, 4)
+    for u in units:
+        if name.startswith("hsdp_"):
+            assert u.world_size == world // 2 and u.replicate_world_size == 2
+        assert u.state.value == "sharded", (u.name, u.state)
+        assert u.flat_buffer.pending_reduce is None
+        if not o.get("storage_may_stay"):
+            assert u.full_param_storage_nbytes() == 0, u.name
+        # the optimizer state of a rank is the size of its own shard, never of the whole unit
+        assert u.flat_buffer.local_numel <= u.flat_buffer.total_numel
+    if world > 1:
+        assert sum(u.flat_buffer.local_numel for u in units) < sum(u.flat_buffer.total_numel for u in units)
+
+
+def _worker(rank, world, out_path, which):
+    results = {}
+    for name in (HSDP_CASES if which == "hsdp" else CASES):
+        try:
+            _run_case(rank, world, name)
+            mine = ""
+        except Exception:
+            mine = traceback.format_exc()
+        # a case fails if it failed on any rank (ranks stay in lock-step: every collective of a case either ran
+        # on both or raised before being issued)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, mine)
+        results[name] = "\n".join(f"--- rank {r} ---\n{t}" for r, t in enumerate(gathered) if t)
+    if rank == 0:
+        with open(out_path, "w") as f:
+            json.dump(results, f)
+
+
+@pytest.fixture(scope="module")
+def outcomes():
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "outcomes.json")
+        run_ranks(_worker, 2, path, "flat", timeout=600.0)
+        with open(path) as f:
+            return json.load(f)
+
+
+@pytest.fixture(scope="module")
+def hsdp_outcomes():
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "outcomes.json")
+        run_ranks(_worker, 4, path, "hsdp", timeout=600.0)
+        with open(path) as f:
+            return json.load(f)
+
+
+@pytest.mark.parametrize("case", sorted(CASES))
+def test_two_rank_step_matches_eager_model(outcomes, case):
+    assert case in outcomes, "the worker did not reach this case"
+    assert not outcomes[case], outcomes[case]
+
+
+@pytest.mark.parametrize("case", sorted(HSDP_CASES))
+def test_four_rank_hsdp_step_matches_eager_model(hsdp_outcomes, case):
+    assert case in hsdp_outcomes, "the worker did not reach this case"
+    assert not hsdp_outcomes[case], hsdp_outcomes[case]
