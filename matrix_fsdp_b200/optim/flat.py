@@ -141,6 +141,14 @@ class _FlatShardedBase(Optimizer):
                 if "step" in st:
                     us.step = int(float(st["step"]))
 
+    def _publish_step(self, us: _UnitState) -> None:
+        """Mirror the unit's step count into the per-parameter state (what a checkpoint saves and a load reads
+        back: a restored count of 0 would make the next step treat the moments as uninitialised)."""
+        for mp in us.unit.registry:
+            st = self.state.get(mp.param)
+            if st and "step" in st:
+                st["step"].fill_(us.step)
+
     def flat_state(self, unit) -> dict[str, torch.Tensor] | None:
         us = self._unit_states.get(id(unit))
         return us.buffers if us is not None else None
@@ -197,10 +205,7 @@ class FlatShardedAdamW(_FlatShardedBase):
                 # the reduce-scatter kernel already updated master, moments and the bf16 shard
                 fb.fused_update_applied = False
                 fb.mark_master_updated(lp_written=fb.local_shard_lp is not None)
-                for mp in unit.registry:
-                    st = self.state.get(mp.param)
-                    if st and "step" in st:
-                        st["step"].fill_(us.step)
+                self._publish_step(us)
                 continue
             g = self._unit_grad(unit)
             if g is None or fb.local_numel == 0:
@@ -218,10 +223,7 @@ class FlatShardedAdamW(_FlatShardedBase):
             else:
                 _adamw_reference_(fb.local_shard, us.buffers["exp_avg"], us.buffers["exp_avg_sq"], g, **kw)
             fb.mark_master_updated(lp_written=fb.local_shard_lp is not None)
-            for mp in unit.registry:
-                st = self.state.get(mp.param)
-                if st and "step" in st:
-                    st["step"].fill_(us.step)
+            self._publish_step(us)
         self._step_unmanaged()
         return loss
 
@@ -293,6 +295,7 @@ class FlatShardedSGD(_FlatShardedBase):
                 if fb.local_shard_lp is not None:
                     fb.local_shard_lp.copy_(fb.local_shard)
             fb.mark_master_updated(lp_written=fb.local_shard_lp is not None)
+            self._publish_step(us)
         for group in self.param_groups:
             for p in group["params"]:
                 if id(p) in self._managed_ids or p.grad is None or p.numel() == 0:
