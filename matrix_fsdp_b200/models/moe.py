@@ -207,7 +207,8 @@ def shard_moe(model: MoEModel, *, mesh=None, dp_mesh_dims=None, mp_policy=None, 
 
 def configure_moe_optimizer(model: MoEModel, optimizer: str = "mixed_muon_adamw", *, lr: float = 3e-4,
                             muon_lr: float = 0.02, weight_decay: float = 0.0, **kw):
-    """Dense parameters: ``configure_optimizer``; experts: Muon (or AdamW) on the owning rank."""
+    """Dense parameters: ``configure_optimizer``; experts: the same kind of optimizer (Muon, AdamW or SGD) on the
+    owning rank."""
     from ..optim.expert import CombinedOptimizer, ExpertParallelOptimizer
     from ..optim.wrapper import configure_optimizer
 
@@ -217,6 +218,10 @@ def configure_moe_optimizer(model: MoEModel, optimizer: str = "mixed_muon_adamw"
         experts = ExpertParallelOptimizer(model.expert_parameters(), "muon", lr=muon_lr, weight_decay=weight_decay,
                                           momentum=kw.get("muon_momentum", 0.95), ns_steps=kw.get("muon_ns_steps", 5),
                                           adjust_lr_fn=kw.get("muon_adjust_lr_fn"))
+    elif optimizer == "sgd":
+        dense = configure_optimizer(model, optimizer, lr=lr, weight_decay=weight_decay, **kw)
+        experts = ExpertParallelOptimizer(model.expert_parameters(), "sgd", lr=lr, weight_decay=weight_decay,
+                                          sgd_momentum=kw.get("momentum", 0.0))
     else:
         dense = configure_optimizer(model, optimizer, lr=lr, weight_decay=weight_decay, **kw)
         experts = ExpertParallelOptimizer(model.expert_parameters(), "adamw", lr=lr, weight_decay=weight_decay,

@@ -1,8 +1,8 @@
 """Optimizer for expert-parallel parameters (each rank owns its experts whole, no FSDP unit).
 
 Expert weights are bf16 ``[El, rows, cols]`` parameters; this optimizer keeps the fp32 master copy and
-the optimizer state, runs Muon (Newton-Schulz on the tcgen05 GEMM, one expert matrix at a time) or
-AdamW on the master, and writes the bf16 weights back in the same kernels.  The reference leaves
+the optimizer state, runs Muon (Newton-Schulz on the tcgen05 GEMM, one expert matrix at a time),
+AdamW or SGD on the master, and writes the bf16 weights back in the same kernels.  The reference leaves
 EP-owned parameters to the caller's own optimizer (``ignored_params``,
 test/fsdp/test_deepseek_v3_ep_train.py:600-640).
 """
@@ -17,15 +17,15 @@ from .muon import MatrixMuon
 class ExpertParallelOptimizer:
     def __init__(self, params, kind: str = "muon", *, lr: float = 0.02, weight_decay: float = 0.0,
                  momentum: float = 0.95, nesterov: bool = True, ns_steps: int = 5, adjust_lr_fn: str | None = None,
-                 betas=(0.9, 0.95), eps: float = 1e-8) -> None:
-        if kind not in ("muon", "adamw"):
+                 betas=(0.9, 0.95), eps: float = 1e-8, sgd_momentum: float = 0.0) -> None:
+        if kind not in ("muon", "adamw", "sgd"):
             raise ValueError(f"unknown expert optimizer {kind!r}")
         self.kind = kind
         self.params = [p for p in params]
         for p in self.params:
             if p.dim() != 3:
                 raise ValueError("expert parameters are [experts, rows, cols]")
-        self.defaults = dict(lr=lr, weight_decay=weight_decay, betas=tuple(betas), eps=eps)
+        self.defaults = dict(lr=lr, weight_decay=weight_decay, betas=tuple(betas), eps=eps, momentum=sgd_momentum)
         self.param_groups = [dict(params=self.params, **self.defaults)]
         self.masters = [p.detach().float().clone() for p in self.params]
         self.step_count = 0
@@ -45,6 +45,8 @@ class ExpertParallelOptimizer:
             self.muon = MatrixMuon(flat, lr=lr, weight_decay=weight_decay, momentum=momentum, nesterov=nesterov,
                                    ns_steps=ns_steps, adjust_lr_fn=adjust_lr_fn,
                                    low_precision_of=lambda s: self._lp[id(s)])
+        elif kind == "sgd":
+            self.momentum_buffer = [torch.zeros_like(m) for m in self.masters] if sgd_momentum else []
         else:
             self.exp_avg = [torch.zeros_like(m) for m in self.masters]
             self.exp_avg_sq = [torch.zeros_like(m) for m in self.masters]
@@ -65,6 +67,21 @@ class ExpertParallelOptimizer:
                     s._grad_override = None
             return
         g0 = self.param_groups[0]
+        if self.kind == "sgd":
+            # plain tensor ops on the fp32 masters (no Newton-Schulz, no moments worth a kernel of their own)
+            for i, (p, m) in enumerate(zip(self.params, self.masters)):
+                if p.grad is None:
+                    continue
+                g = p.grad.float() * float(self.grad_scale)
+                if g0["weight_decay"]:
+                    g = g.add(m, alpha=g0["weight_decay"])
+                if g0["momentum"]:
+                    buf = self.momentum_buffer[i]
+                    buf.copy_(g) if self.step_count == 1 else buf.mul_(g0["momentum"]).add_(g)
+                    g = buf
+                m.add_(g, alpha=-float(g0["lr"]))
+                p.data.copy_(m)
+            return
         from .flat import _adamw_reference_, _native
 
         for p, m, a, b in zip(self.params, self.masters, self.exp_avg, self.exp_avg_sq):
@@ -91,6 +108,8 @@ class ExpertParallelOptimizer:
         sd = {"kind": self.kind, "step": self.step_count, "masters": self.masters}
         if self.kind == "muon":
             sd["momentum"] = [[self.muon.state[s].get("momentum_buffer") for s in row] for row in self._slices]
+        elif self.kind == "sgd":
+            sd["momentum_buffer"] = self.momentum_buffer
         else:
             sd["exp_avg"], sd["exp_avg_sq"] = self.exp_avg, self.exp_avg_sq
         return sd
@@ -105,6 +124,9 @@ class ExpertParallelOptimizer:
                 for s, b in zip(row, bufs):
                     if b is not None:
                         self.muon.state[s]["momentum_buffer"] = b.clone()
+        elif self.kind == "sgd":
+            for dst, src in zip(self.momentum_buffer, sd.get("momentum_buffer", [])):
+                dst.copy_(src)
         else:
             for dst, src in zip(self.exp_avg, sd["exp_avg"]):
                 dst.copy_(src)

@@ -1,0 +1,176 @@
+"""Expert parallelism on gloo ranks, one (experts, top-k, optimizer) per case: three steps of the EP model (experts
+split over the ranks, dense parts sharded) equal the single-process model that keeps every expert local and sees
+the ranks' sequences as data-parallel micro-batches; plus checkpoint resume with experts split over the ranks,
+with AdamW, SGD and Muon on the experts.  All cases of a world size share one spawn.  The reference trains its
+EP model in test/fsdp/test_deepseek_v3_ep_train.py:472-563 (3 tests, GPU only)."""
+import json
+import os
+import tempfile
+import traceback
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from dist_utils import run_ranks
+
+# experts, top-k, optimizer
+TRAIN_CASES = ["E4-K1-adamw", "E4-K2-adamw", "E4-K3-adamw", "E8-K2-adamw", "E8-K4-adamw", "E4-K2-sgd", "E8-K3-sgd",
+               "E4-K2-sgdm", "E2-K1-adamw", "E2-K2-adamw"]
+RESUME_CASES = ["resume-E4-K2-adamw", "resume-E4-K2-sgd", "resume-E4-K2-mixed_muon_adamw", "resume-E8-K3-adamw"]
+TRAIN4_CASES = ["E4-K2-adamw", "E8-K2-adamw", "E8-K3-sgd"]
+RESUME4_CASES = ["resume-E8-K2-mixed_muon_adamw"]
+
+
+def _cfg(n_experts, top_k):
+    from matrix_fsdp_b200.models.moe import MoEConfig
+
+    return MoEConfig(vocab_size=96, hidden=32, n_layers=2, n_heads=2, head_dim=16, n_experts=n_experts, expert_ffn=24,
+                     top_k=top_k, max_seq_len=32)
+
+
+def _tokens(world):
+    return torch.randint(0, 96, (world, 13), generator=torch.Generator().manual_seed(0))
+
+
+def _parse(name):
+    e, k, opt = name.removeprefix("resume-").split("-")
+    return int(e[1:]), int(k[1:]), opt
+
+
+def _train_case(rank, world, name):
+    from matrix_fsdp_b200.api import reset_shared_owner_planners
+    from matrix_fsdp_b200.models.moe import MoEModel, configure_moe_optimizer, shard_moe
+    from matrix_fsdp_b200.parallel.expert_parallel import reset_contexts
+
+    n_experts, top_k, opt_kind = _parse(name)
+    reset_shared_owner_planners()
+    reset_contexts()
+    cfg = _cfg(n_experts, top_k)
+    torch.manual_seed(0)
+    model = MoEModel(cfg)
+    torch.manual_seed(0)
+    ref = MoEModel(cfg, ep_group=False)
+    el = n_experts // world
+    assert model.layers[0].experts.w_down.shape[0] == el
+    shard_moe(model)
+    momentum = 0.9 if opt_kind == "sgdm" else 0.0
+    hyper = dict(lr=1e-2, betas=(0.9, 0.95)) if opt_kind == "adamw" else dict(lr=0.05, momentum=momentum)
+    opt = configure_moe_optimizer(model, "adamw" if opt_kind == "adamw" else "sgd", **hyper)
+    ref_params = [p for n, p in ref.named_parameters() if ".experts." not in n] + ref.expert_parameters()
+    ropt = torch.optim.AdamW(ref_params, lr=1e-2, weight_decay=0.0, betas=(0.9, 0.95)) if opt_kind == "adamw" \
+        else torch.optim.SGD(ref_params, lr=0.05, momentum=momentum)
+    toks = _tokens(world)
+    for step in range(3):
+        mine = toks[rank:rank + 1]
+        loss = model(mine[:, :-1], mine[:, 1:])
+        loss.backward()
+        losses = []
+        for r in range(world):
+            l_r = ref(toks[r:r + 1, :-1], toks[r:r + 1, 1:])
+            (l_r / world).backward()
+            losses.append(l_r.detach())
+        assert torch.allclose(loss.detach(), losses[rank], atol=2e-5), (step, float(loss), float(losses[rank]))
+        for p in model.expert_parameters():                # EP sums all ranks' tokens; the DP mean needs 1 / world
+            p.grad.div_(world)
+        opt.step()
+        opt.zero_grad()
+        ropt.step()
+        ropt.zero_grad()
+    for a, b in zip(model.layers, ref.layers):
+        lo, hi = rank * el, (rank + 1) * el
+        assert torch.allclose(a.experts.w_down, b.experts.w_down[lo:hi], atol=3e-5)
+        assert torch.allclose(a.experts.w_gate_up, b.experts.w_gate_up[lo:hi], atol=3e-5)
+
+
+def _resume_case(rank, world, name, base_dir):
+    from matrix_fsdp_b200.api import reset_shared_owner_planners
+    from matrix_fsdp_b200.models.moe import (MoEModel, configure_moe_optimizer, load_moe_checkpoint, save_moe_checkpoint,
+                                             shard_moe)
+    from matrix_fsdp_b200.parallel.expert_parallel import reset_contexts
+
+    n_experts, top_k, opt_kind = _parse(name)
+    cfg = _cfg(n_experts, top_k)
+    toks = _tokens(world)[rank:rank + 1]
+    mixed = opt_kind == "mixed_muon_adamw"
+
+    def make(seed):
+        reset_shared_owner_planners()
+        torch.manual_seed(seed)
+        m = MoEModel(cfg)
+        shard_moe(m, optimizer_policy="mixed_muon_adamw" if mixed else None)
+        kw = dict(lr=1e-2, muon_lr=0.02) if mixed else (dict(lr=0.05, momentum=0.9) if opt_kind == "sgd" else dict(lr=1e-2))
+        return m, configure_moe_optimizer(m, opt_kind, **kw)
+
+    def step(m, o):
+        m(toks[:, :-1], toks[:, 1:]).backward()
+        o.step()
+        o.zero_grad()
+
+    reset_contexts()
+    model, opt = make(0)
+    for _ in range(2):
+        step(model, opt)
+    directory = os.path.join(base_dir, name)
+    if rank == 0:
+        os.makedirs(directory, exist_ok=True)
+    dist.barrier()
+    save_moe_checkpoint(model, directory, optimizer=opt)
+    step(model, opt)
+    expect = model(toks[:, :-1], toks[:, 1:]).detach()
+    twin, topt = make(3)                                      # other weights: everything has to come from the files
+    load_moe_checkpoint(twin, directory, optimizer=topt)
+    step(twin, topt)
+    got = twin(toks[:, :-1], toks[:, 1:]).detach()
+    assert torch.allclose(got, expect, atol=1e-5), (float(got), float(expect))
+    for a, b in zip(model.layers, twin.layers):
+        assert torch.allclose(a.experts.w_down, b.experts.w_down, atol=1e-6)
+
+
+def _worker(rank, world, out_path, names, base_dir):
+    results = {}
+    for name in names:
+        try:
+            if name.startswith("resume-"):
+                _resume_case(rank, world, name, base_dir)
+            else:
+                _train_case(rank, world, name)
+            mine = ""
+        except Exception:
+            mine = traceback.format_exc()
+        gathered = [None] * world
+        dist.all_gather_object(gathered, mine)
+        results[name] = "\n".join(f"--- rank {r} ---\n{t}" for r, t in enumerate(gathered) if t)
+    if rank == 0:
+        with open(out_path, "w") as f:
+            json.dump(results, f)
+
+
+def _spawn(world, names):
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "outcomes.json")
+        run_ranks(_worker, world, path, names, tmp, timeout=600.0)
+        with open(path) as f:
+            return json.load(f)
+
+
+@pytest.fixture(scope="module")
+def outcomes():
+    return _spawn(2, TRAIN_CASES + RESUME_CASES)
+
+
+@pytest.fixture(scope="module")
+def outcomes4():
+    return _spawn(4, TRAIN4_CASES + RESUME4_CASES)
+
+
+@pytest.mark.parametrize("case", TRAIN_CASES + RESUME_CASES)
+def test_two_rank_expert_parallel(outcomes, case):
+    assert case in outcomes, "the worker did not reach this case"
+    assert not outcomes[case], outcomes[case]
+
+
+@pytest.mark.parametrize("case", TRAIN4_CASES + RESUME4_CASES)
+def test_four_rank_expert_parallel(outcomes4, case):
+    assert case in outcomes4, "the worker did not reach this case"
+    assert not outcomes4[case], outcomes4[case]
