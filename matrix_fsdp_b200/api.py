@@ -32,7 +32,8 @@ from .parallel.fsdp_unit import MatrixFSDPNoSync, MatrixFSDPParamGroup
 from .parallel.scheduler import DEFAULT_MAX_UNSHARDED_PREFETCH_UNITS, MatrixFSDPScheduler
 from .parallel.unit_collection import collect_param_groups
 from .planning.auto_planner import (AutoPlannerPolicy, auto_group_plan, make_cost_aware_muon_shard_aware_group_planner,
-                                    make_muon_shard_aware_group_planner, make_scoped_muon_shard_aware_group_planner)
+                                    make_model_wide_muon_planner, make_muon_shard_aware_group_planner,
+                                    make_scoped_muon_shard_aware_group_planner)
 from .planning.planner import ShardPlan, hinted_ordered_group_plan
 from .planning.planner_eval import GroupPlanner
 from .planning.shard_hint import build_shard_hints
@@ -259,7 +260,7 @@ def matrix_fully_shard(module: nn.Module, mesh=None, *, dp_mesh_dims=None, dp_sh
     if auto_planner_policy is not None:
         if group_planner is not None or layout_planner is not None:
             raise ValueError("Pass either auto_planner_policy or an explicit group/layout planner, not both.")
-        if owner_assignment in ("scope_greedy", "cost_aware"):
+        if owner_assignment in ("scope_greedy", "cost_aware", "model_wide"):
             claimed: set[int] = set()
             scoped = []
             for m in selected:
@@ -269,8 +270,11 @@ def matrix_fully_shard(module: nn.Module, mesh=None, *, dp_mesh_dims=None, dp_sh
                     ignored_params=extra_ignored, allow_shared=allow_shared_params)
                 claimed |= {id(mp.param) for mp in reg}
                 scoped.append(reg.params)
-            maker = (make_cost_aware_muon_shard_aware_group_planner if owner_assignment == "cost_aware"
-                     else make_scoped_muon_shard_aware_group_planner)
+            # all three see every selected module's parameters before the first unit is planned; "model_wide"
+            # balances the owners by Newton-Schulz FLOPs over the whole model
+            maker = {"cost_aware": make_cost_aware_muon_shard_aware_group_planner,
+                     "scope_greedy": make_scoped_muon_shard_aware_group_planner,
+                     "model_wide": make_model_wide_muon_planner}[owner_assignment]
             group_planner = maker(tuple(scoped), policy=auto_planner_policy)
         else:
             group_planner = _resolve_auto_group_planner(auto_planner_policy, target_block_units=target_block_units,
