@@ -261,4 +261,14 @@ def shard_llama(model: LlamaModel, *, mesh=None, dp_mesh_dims=None, mp_policy=No
             for part in (model.embed, model.head):
                 fully_shard(part, mesh=mesh, dp_mesh_dims=dp_mesh_dims, mp_policy=mp,
                             optimizer_policy=optimizer_policy, reshard_after_forward=reshard_after_forward, **kw)
+    _attach_model_no_sync(model)
     return model
+
+
+def _attach_model_no_sync(model: nn.Module) -> None:
+    """``model.no_sync()`` over every unit below the model, also when the model itself is no unit (blocks,
+    embedding and head are units of their own, so no ``fully_shard`` call ever saw the root)."""
+    from ..api import _attach_no_sync
+    from ..parallel.unit_collection import collect_param_groups
+
+    _attach_no_sync(model, collect_param_groups(model))

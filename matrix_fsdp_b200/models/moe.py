@@ -202,6 +202,9 @@ def shard_moe(model: MoEModel, *, mesh=None, dp_mesh_dims=None, mp_policy=None, 
     for part in (model.embed, model.head):
         fully_shard(part, mesh=mesh, dp_mesh_dims=dp_mesh_dims, mp_policy=mp, optimizer_policy=optimizer_policy,
                     reshard_after_forward=reshard_after_forward)
+    from .llama import _attach_model_no_sync
+
+    _attach_model_no_sync(model)
     return model
 
 
