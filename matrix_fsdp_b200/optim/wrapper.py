@@ -173,10 +173,17 @@ class _suppress_auto_prepare:
 class MatrixFSDPOptimizer:
     """A torch optimizer plus the FSDP lifecycle around ``step()`` / ``zero_grad()``."""
 
-    def __init__(self, optimizer: Optimizer, units, scheduler: MatrixFSDPScheduler | None = None) -> None:
+    def __init__(self, optimizer: Optimizer, units, scheduler: MatrixFSDPScheduler | None = None,
+                 **scheduler_kwargs) -> None:
+        """``units``: a sharded module, one unit or a list of units (matrix_fsdp/optim/wrapper.py takes the module
+        too).  ``optimizer`` may be any element-wise torch optimizer built over ``model.parameters()``: while it
+        steps, every parameter is its local shard and ``.grad`` the matching piece of the reduced gradient."""
         self.optimizer = optimizer
-        self.fsdp_param_groups = list(units)
-        self.scheduler = scheduler if scheduler is not None else _ensure_scheduler(self.fsdp_param_groups)
+        self.fsdp_param_groups = _normalize_param_groups(units)
+        sched_kw, extra = _split_scheduler_kwargs(scheduler_kwargs)
+        if extra:
+            raise TypeError(f"Unknown optimizer wrapper options: {', '.join(sorted(extra))}.")
+        self.scheduler = scheduler if scheduler is not None else _ensure_scheduler(self.fsdp_param_groups, sched_kw)
         optimizer._mfsdp_lifecycle_managed = True
         self.state_manager = MatrixFSDPOptimizerStateManager(self.fsdp_param_groups, {"optimizer": optimizer})
 

@@ -116,6 +116,16 @@ CASES = {
                                           {"opt_kw": dict(backward_prefetch_timing="post_reshard")}),
     "units_sched_one_active_buffer": ("units", lambda: {}, "adamw", {"opt_kw": dict(max_active_full_param_buffers=1)}),
     "units_sched_two_pending_reduces": ("units", lambda: {}, "adamw", {"opt_kw": dict(max_pending_backward_reduces=2)}),
+    # any element-wise torch optimizer, built by the user over model.parameters() and wrapped
+    "wrapped_torch_adamw_amsgrad": ("units", lambda: {}, "torch:AdamW", {"torch_kw": dict(lr=1e-2, amsgrad=True)}),
+    "wrapped_torch_adam": ("units", lambda: {}, "torch:Adam", {"torch_kw": dict(lr=1e-2)}),
+    "wrapped_torch_sgd_nesterov": ("units", lambda: {}, "torch:SGD", {"torch_kw": dict(lr=0.05, momentum=0.9, nesterov=True)}),
+    "wrapped_torch_rmsprop": ("root", lambda: {}, "torch:RMSprop", {"torch_kw": dict(lr=1e-3)}),
+    "wrapped_torch_adagrad_owner_layout": ("units", lambda: dict(group_planner=_planner("parameter_boundary_plan")),
+                                           "torch:Adagrad", {"torch_kw": dict(lr=1e-2)}),
+    # the same without the wrapper: the optimizer hooks installed by the package run the lifecycle
+    "bare_torch_adamw": ("units", lambda: {}, "bare:AdamW", {"torch_kw": dict(lr=1e-2, weight_decay=0.0)}),
+    "bare_torch_sgd_bf16": ("units", lambda: dict(mp_policy=_bf16()), "bare:SGD", {"torch_kw": dict(lr=0.05), "bf16": True}),
 }
 
 
@@ -186,9 +196,21 @@ def _run_case(rank, world, name):
 
         kw.update(mesh=_hsdp_mesh(world), dp_mesh_dims=DataParallelMeshDims(shard="dp_shard", replicate="dp_replicate"))
     _shard(model, wrap, kw)
-    hyper = dict(lr=1e-2, weight_decay=0.0) if opt_kind == "adamw" else dict(lr=0.05)
-    opt = configure_optimizer(model, opt_kind, **hyper, **o.get("opt_kw", {}))
-    ropt = (torch.optim.AdamW if opt_kind == "adamw" else torch.optim.SGD)(ref.parameters(), **hyper)
+    if ":" in opt_kind:
+        from matrix_fsdp_b200.optim.wrapper import MatrixFSDPOptimizer, install_matrix_optimizer_auto_prepare
+
+        how, cls_name = opt_kind.split(":")
+        cls = getattr(torch.optim, cls_name)
+        opt = cls(model.parameters(), **o["torch_kw"])
+        if how == "torch":
+            opt = MatrixFSDPOptimizer(opt, model)
+        else:
+            install_matrix_optimizer_auto_prepare()
+        ropt = cls(ref.parameters(), **o["torch_kw"])
+    else:
+        hyper = dict(lr=1e-2, weight_decay=0.0) if opt_kind == "adamw" else dict(lr=0.05)
+        opt = configure_optimizer(model, opt_kind, **hyper, **o.get("opt_kw", {}))
+        ropt = (torch.optim.AdamW if opt_kind == "adamw" else torch.optim.SGD)(ref.parameters(), **hyper)
     bf16 = bool(o.get("bf16"))
     g = torch.Generator().manual_seed(100 + rank)
 
