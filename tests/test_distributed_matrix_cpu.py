@@ -9,6 +9,7 @@ import json
 import os
 import tempfile
 import traceback
+from collections import OrderedDict
 
 import pytest
 import torch
@@ -129,6 +130,77 @@ CASES = {
 }
 
 
+# how the units are called: name -> (forward function over the block stack, shard keywords)
+def _chain(m, x):
+    for blk in m.children():
+        x = blk(x)
+    return x
+
+
+def _twice(m, x):
+    return _chain(m, x) + _chain(m, x * 0.5)                    # every unit runs twice before one backward
+
+
+def _branches(m, x):
+    return m[0](x) + m[1](x) + m[2](x) + m.head(x)              # units side by side, not in a chain
+
+
+def _shared_block(m, x):
+    return m.head(m[1](m[0](m[1](x))))                          # one unit used at two depths, one unit never used
+
+
+def _partial_output(m, x):
+    y = _chain(m, x)
+    return y[:, :4]                                             # only a slice of the output reaches the loss
+
+
+def _checkpointed_chain(m, x):
+    from torch.utils.checkpoint import checkpoint
+
+    x = x.clone().requires_grad_(True)
+    for blk in list(m.children()):
+        x = checkpoint(blk, x, use_reentrant=False)
+    return x
+
+
+def _reentrant_checkpointed_chain(m, x):
+    from torch.utils.checkpoint import checkpoint
+
+    x = x.clone().requires_grad_(True)
+    for blk in list(m.children()):
+        x = checkpoint(blk, x, use_reentrant=True)
+    return x
+
+
+def _detached_prefix(m, x):
+    with torch.no_grad():
+        h = m[0](x)                                             # this unit gets no gradient in this step
+    return m.head(m[2](m[1](h)))
+
+
+TOPOLOGIES = {
+    "topo_twice_keep": (_twice, dict(reshard_after_forward=False)),
+    "topo_branches": (_branches, {}),
+    "topo_branches_no_prefetch": (_branches, dict(forward_prefetch=False, backward_prefetch=False)),
+    "topo_shared_block_keep": (_shared_block, dict(reshard_after_forward=False)),
+    "topo_partial_output": (_partial_output, {}),
+    "topo_checkpointed_chain": (_checkpointed_chain, {}),
+    "topo_reentrant_checkpointed_chain": (_reentrant_checkpointed_chain, {}),
+    "topo_detached_prefix": (_detached_prefix, {}),
+    "topo_detached_prefix_keep": (_detached_prefix, dict(reshard_after_forward=False)),
+}
+CASES.update({name: ("units", (lambda kw=kw: dict(kw)), "adamw", {"fn": fn}) for name, (fn, kw) in TOPOLOGIES.items()})
+
+
+class TopoNet(nn.Sequential):
+    """The block stack with a forward of its own choosing: the root has to stay the entry point (its hooks gather
+    the parameters the root unit owns, here the head), so the call pattern lives inside its forward."""
+    pattern = None
+
+    def forward(self, x):
+        return self.pattern(self, x) if self.pattern is not None else super().forward(x)
+
+
 # four ranks as a 2 x 2 mesh: shards inside a replica, replicas average the reduced shards
 HSDP_CASES = {
     "hsdp_units_default": ("units", lambda: {}, "adamw", {}),
@@ -189,6 +261,10 @@ def _run_case(rank, world, name):
     wrap, make_kw, opt_kind, o = (HSDP_CASES if name.startswith("hsdp_") else CASES)[name]
     reset_shared_owner_planners()
     model = _model(CkptBlk if o.get("ckpt") else Blk)
+    if o.get("fn"):
+        pattern = o["fn"]
+        model = TopoNet(OrderedDict(model._modules))
+        model.pattern = pattern
     ref = copy.deepcopy(model)
     kw = make_kw()
     if name.startswith("hsdp_"):
@@ -231,6 +307,8 @@ def _run_case(rank, world, name):
         for x in xs:
             loss_of(ref, x).backward()
         for p in ref.parameters():
+            if p.grad is None:                                  # a module the step did not use
+                continue
             dist.all_reduce(p.grad)
             if not o.get("sum"):
                 p.grad /= world
