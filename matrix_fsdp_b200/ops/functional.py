@@ -86,7 +86,7 @@ class GradSink:
         self.param = param
 
     def target(self):
-        ref = getattr(self.param, "_matrix_fsdp_param_group_ref", None)
+        ref = getattr(self.param, "_mfsdp_unit_ref", None)
         unit = ref() if ref is not None else None
         if unit is None or unit.state.value != "unsharded" or unit.flat_buffer.bucket.dtype != torch.bfloat16:
             return None
@@ -452,7 +452,7 @@ class DecoderBlockFunction(torch.autograd.Function):
 
 def _take_deferred_gather(bp: "BlockParams", wqkv: torch.Tensor | None):
     """Plan of the all-gather rows that the owning FSDP unit left to the QKV GEMM, if any."""
-    ref = getattr(bp.params[1], "_matrix_fsdp_param_group_ref", None)
+    ref = getattr(bp.params[1], "_mfsdp_unit_ref", None)
     unit = ref() if ref is not None else None
     if unit is None or unit.flat_buffer.deferred_gather is None:
         return None

@@ -98,9 +98,9 @@ def _units_of_optimizer(optimizer: Optimizer) -> list[MatrixFSDPParamGroup]:
     found: dict[int, MatrixFSDPParamGroup] = {}
     for g in optimizer.param_groups:
         for p in g["params"]:
-            ref = getattr(p, "_matrix_fsdp_param_group_ref", None)
+            ref = getattr(p, "_mfsdp_unit_ref", None)
             unit = ref() if ref is not None else None
-            if unit is not None:
+            if isinstance(unit, MatrixFSDPParamGroup):      # a unit of this package, not of one that shares the name
                 found[id(unit)] = unit
     return sorted(found.values(), key=lambda u: u.metadata.runtime_param_group_id)
 
@@ -244,7 +244,7 @@ class MatrixFSDPOptimizer:
             for p in g["params"]:
                 fqns.append(getattr(p, "_matrix_fsdp_fqn", "<unmanaged>"))
                 local += p.numel()
-                ref = getattr(p, "_matrix_fsdp_param_group_ref", None)
+                ref = getattr(p, "_mfsdp_unit_ref", None)
                 unit = ref() if ref else None
                 numel += unit.registry.param(p._matrix_fsdp_fqn).numel if unit is not None else p.numel()
             out.append(MatrixOptimizerParamGroupSummary(f"group_{i}", type(self.optimizer).__name__.lower(), tuple(fqns),

@@ -211,7 +211,7 @@ class MatrixFSDPParamGroup:
         inner = {id(m) for m in module.modules()}
         nested = set()
         for fqn, p in module.named_parameters():
-            ref = getattr(p, "_matrix_fsdp_param_group_ref", None)
+            ref = getattr(p, "_mfsdp_unit_ref", None)
             owner = ref() if ref is not None else None
             if owner is None:
                 continue
@@ -281,7 +281,9 @@ class MatrixFSDPParamGroup:
 
         ref = weakref.ref(self)
         for mpm in registry:
-            mpm.param._matrix_fsdp_param_group_ref = ref
+            # a name of this package's own: the reference package hooks every torch optimizer in the process and
+            # reads its own back-reference from the parameters, so the two must not share the attribute
+            mpm.param._mfsdp_unit_ref = ref
             mpm.param._matrix_fsdp_fqn = mpm.fqn
         module._matrix_fsdp_param_group = self
         self._register_hooks()

@@ -21,7 +21,7 @@ def collect_param_groups(module_or_units) -> list:
         elif isinstance(obj, nn.Module):
             for m in obj.modules():
                 u = getattr(m, "_matrix_fsdp_param_group", None)
-                if u is not None:
+                if isinstance(u, MatrixFSDPParamGroup):     # another package may use the same attribute name
                     found[id(u)] = u
         elif isinstance(obj, Iterable):
             for item in obj:

@@ -53,3 +53,40 @@ def run_ranks(fn, world: int, *args, timeout: float = 240.0):
                 if os.path.exists(p):
                     msgs.append(f"--- rank {r} ---\n" + open(p).read())
             raise AssertionError("\n".join(msgs) or str(exc)) from None
+
+
+def _cases_worker(rank, world, cases, out_path):
+    import json
+
+    results = {}
+    for name, fn, args in cases:
+        try:
+            fn(rank, world, *args)
+            mine = ""
+        except Exception:
+            mine = traceback.format_exc()
+        # a case fails if it failed on any rank; ranks stay in step because every case ends with this exchange
+        gathered = [None] * world
+        dist.all_gather_object(gathered, mine)
+        results[name] = "\n".join(f"--- rank {r} ---\n{t}" for r, t in enumerate(gathered) if t)
+    if rank == 0:
+        with open(out_path, "w") as f:
+            json.dump(results, f)
+
+
+def run_cases(world: int, cases, *, timeout: float = 600.0) -> dict:
+    """Run ``[(name, fn, args), ...]`` as ``fn(rank, world, *args)`` one after the other inside ONE spawn of
+    ``world`` gloo ranks (starting the ranks costs more than most cases) and return ``{name: "" or the ranks'
+    tracebacks}``.  Use it from a module-scoped fixture and give every case a test of its own."""
+    import json
+
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "outcomes.json")
+        run_ranks(_cases_worker, world, list(cases), path, timeout=timeout)
+        with open(path) as f:
+            return json.load(f)
+
+
+def check_case(outcomes: dict, name: str) -> None:
+    assert name in outcomes, "the ranks did not reach this case"
+    assert not outcomes[name], outcomes[name]

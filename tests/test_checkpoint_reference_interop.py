@@ -11,7 +11,6 @@ import pytest
 import torch
 from torch import nn
 
-from dist_utils import run_ranks
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REF = os.path.join(ROOT, "baseline", "_ref")
@@ -111,22 +110,67 @@ def _reader(rank, world, which, kind, d, reshard_from):
     opt.step()
 
 
+def _write_then_read(rank, world, writer, reader, kind, base):
+    d = os.path.join(base, f"{writer}-{reader}-{kind}-w{world}")
+    if rank == 0:
+        os.makedirs(d, exist_ok=True)
+    if world > 1:
+        torch.distributed.barrier()
+    _writer(rank, world, writer, kind, d)
+    if world > 1:
+        torch.distributed.barrier()
+    _reader(rank, world, reader, kind, d, None)
+
+
+def _write_for_reshard(rank, world, base):
+    d = os.path.join(base, "reshard-2-to-1")
+    if rank == 0:
+        os.makedirs(d, exist_ok=True)
+    torch.distributed.barrier()
+    _writer(rank, world, "ref", "adamw", d)
+
+
+def _read_resharded(rank, world, base):
+    _reader(rank, world, "ours", "adamw", os.path.join(base, "reshard-2-to-1"), 2)
+
+
+_PAIRS = [("ref", "ours"), ("ours", "ref")]
+
+
+@pytest.fixture(scope="module")
+def outcomes():
+    """Two spawns for the whole file: the two-rank cases first (one of them leaves the checkpoint that the
+    one-rank job re-shards), then the one-rank cases.  Both packages are loaded into the same ranks."""
+    from dist_utils import run_cases
+
+    with tempfile.TemporaryDirectory() as base:
+        two = [(f"adamw:{w}->{r}:2", _write_then_read, (w, r, "adamw", base)) for w, r in _PAIRS]
+        two.append(("reshard:write", _write_for_reshard, (base,)))
+        one = [(f"adamw:{w}->{r}:1", _write_then_read, (w, r, "adamw", base)) for w, r in _PAIRS]
+        one += [(f"mixed:{w}->{r}", _write_then_read, (w, r, "mixed_muon_adamw", base)) for w, r in _PAIRS]
+        one.append(("reshard:read", _read_resharded, (base,)))
+        out = run_cases(2, two)
+        out.update(run_cases(1, one))
+        return out
+
+
 @pytest.mark.parametrize("world", [1, 2])
-@pytest.mark.parametrize("writer,reader", [("ref", "ours"), ("ours", "ref")])
-def test_adamw_checkpoints_load_across_packages(writer, reader, world):
-    with tempfile.TemporaryDirectory() as d:
-        run_ranks(_writer, world, writer, "adamw", d)
-        run_ranks(_reader, world, reader, "adamw", d, None)
+@pytest.mark.parametrize("writer,reader", _PAIRS)
+def test_adamw_checkpoints_load_across_packages(outcomes, writer, reader, world):
+    from dist_utils import check_case
+
+    check_case(outcomes, f"adamw:{writer}->{reader}:{world}")
 
 
-@pytest.mark.parametrize("writer,reader", [("ref", "ours"), ("ours", "ref")])
-def test_mixed_muon_checkpoints_load_across_packages(writer, reader):
-    with tempfile.TemporaryDirectory() as d:
-        run_ranks(_writer, 1, writer, "mixed_muon_adamw", d)
-        run_ranks(_reader, 1, reader, "mixed_muon_adamw", d, None)
+@pytest.mark.parametrize("writer,reader", _PAIRS)
+def test_mixed_muon_checkpoints_load_across_packages(outcomes, writer, reader):
+    from dist_utils import check_case
+
+    check_case(outcomes, f"mixed:{writer}->{reader}")
 
 
-def test_reference_checkpoint_reshards_from_two_ranks_to_one():
-    with tempfile.TemporaryDirectory() as d:
-        run_ranks(_writer, 2, "ref", "adamw", d)
-        run_ranks(_reader, 1, "ours", "adamw", d, 2)
+def test_reference_checkpoint_reshards_from_two_ranks_to_one(outcomes):
+    from dist_utils import check_case
+
+    check_case(outcomes, "reshard:write")
+    check_case(outcomes, "reshard:read")

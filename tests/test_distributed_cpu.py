@@ -6,7 +6,7 @@ import torch
 import torch.distributed as dist
 from torch import nn
 
-from dist_utils import run_ranks
+from dist_utils import check_case, run_cases
 
 
 class Blk(nn.Module):
@@ -115,16 +115,23 @@ def _hsdp(rank, world):
     _train_compare(rank, world, "hsdp", {}, "adamw", dict(lr=1e-2, weight_decay=0.0))
 
 
-def test_two_rank_dense_even_split_adamw():
-    run_ranks(_world_dense, 2)
+@pytest.fixture(scope="module")
+def two_rank_outcomes():
+    """Every two-rank case of this file in one spawn (see ``dist_utils.run_cases``)."""
+    return run_cases(2, [("dense", _world_dense, ()), ("rows", _mesh_rows, ()), ("muon_owner", _muon_owner, ()),
+                         ("no_sync", _no_sync_and_accumulation, ())])
 
 
-def test_two_rank_row_sharding_sgd():
-    run_ranks(_mesh_rows, 2)
+def test_two_rank_dense_even_split_adamw(two_rank_outcomes):
+    check_case(two_rank_outcomes, "dense")
+
+
+def test_two_rank_row_sharding_sgd(two_rank_outcomes):
+    check_case(two_rank_outcomes, "rows")
 
 
 def test_four_rank_hsdp_2x2():
-    run_ranks(_hsdp, 4)
+    check_case(run_cases(4, [("hsdp", _hsdp, ())]), "hsdp")
 
 
 def _muon_owner(rank, world):
@@ -167,8 +174,8 @@ def _muon_owner(rank, world):
         assert torch.allclose(full[n], p.detach(), atol=2e-2, rtol=2e-2), n
 
 
-def test_two_rank_matrix_owner_mixed_muon():
-    run_ranks(_muon_owner, 2)
+def test_two_rank_matrix_owner_mixed_muon(two_rank_outcomes):
+    check_case(two_rank_outcomes, "muon_owner")
 
 
 def _no_sync_and_accumulation(rank, world):
@@ -201,5 +208,5 @@ def _no_sync_and_accumulation(rank, world):
         assert torch.allclose(full[n], p.detach(), atol=1e-5), n
 
 
-def test_two_rank_no_sync_and_grad_accumulation():
-    run_ranks(_no_sync_and_accumulation, 2)
+def test_two_rank_no_sync_and_grad_accumulation(two_rank_outcomes):
+    check_case(two_rank_outcomes, "no_sync")

@@ -8,7 +8,7 @@ import torch
 import torch.distributed as dist
 from torch import nn
 
-from dist_utils import run_ranks
+from dist_utils import check_case, run_cases
 
 
 def _model(seed=0):
@@ -70,8 +70,8 @@ def _mesh3d_worker(rank, world):
         assert torch.allclose(full[n], p.detach(), atol=2e-5), n
 
 
-def test_three_d_mesh_leaves_the_tp_dim_alone():
-    run_ranks(_mesh3d_worker, 4)
+def test_three_d_mesh_leaves_the_tp_dim_alone(four_rank_outcomes):
+    check_case(four_rank_outcomes, "mesh3d")
 
 
 def _mixed_precision_worker(rank, world):
@@ -107,8 +107,8 @@ def _mixed_precision_worker(rank, world):
         assert torch.equal(ref, t), n
 
 
-def test_two_rank_mixed_precision_keeps_fp32_master():
-    run_ranks(_mixed_precision_worker, 2)
+def test_two_rank_mixed_precision_keeps_fp32_master(two_rank_outcomes):
+    check_case(two_rank_outcomes, "mixed_precision")
 
 
 def _checkpointing_worker(rank, world):
@@ -149,8 +149,8 @@ def _checkpointing_worker(rank, world):
     assert "pre_forward_recompute_skip" in events or events.count("pre_forward") >= 2
 
 
-def test_two_rank_activation_checkpointing():
-    run_ranks(_checkpointing_worker, 2)
+def test_two_rank_activation_checkpointing(two_rank_outcomes):
+    check_case(two_rank_outcomes, "checkpointing")
 
 
 def _library_variants_worker(rank, world, gather_impl, reduce_impl):
@@ -185,10 +185,12 @@ def _library_variants_worker(rank, world, gather_impl, reduce_impl):
         assert torch.allclose(full[n], p.detach(), atol=2e-5), (gather_impl, reduce_impl, n)
 
 
-def test_owner_layout_over_every_library_collective_variant():
-    for gather_impl, reduce_impl in (("owner_broadcast", "owner_reduce"), ("padded_all_gather", "padded_reduce_scatter"),
-                                     ("auto", "auto")):
-        run_ranks(_library_variants_worker, 2, gather_impl, reduce_impl)
+_LIBRARY_VARIANTS = (("owner_broadcast", "owner_reduce"), ("padded_all_gather", "padded_reduce_scatter"), ("auto", "auto"))
+
+
+@pytest.mark.parametrize("gather_impl,reduce_impl", _LIBRARY_VARIANTS)
+def test_owner_layout_over_every_library_collective_variant(two_rank_outcomes, gather_impl, reduce_impl):
+    check_case(two_rank_outcomes, f"library:{gather_impl}:{reduce_impl}")
 
 
 def _clip_worker(rank, world):
@@ -220,8 +222,8 @@ def _clip_worker(rank, world):
         assert torch.allclose(full[n], p.detach(), atol=1e-5), n
 
 
-def test_two_rank_global_gradient_clipping():
-    run_ranks(_clip_worker, 2)
+def test_two_rank_global_gradient_clipping(two_rank_outcomes):
+    check_case(two_rank_outcomes, "clip")
 
 
 # ----------------------------------------------------------------------------- unused unit keeps its shard
@@ -262,8 +264,8 @@ def _unused_unit_body(rank, world, opt_kind):
 
 
 @pytest.mark.parametrize("opt_kind", ["adamw", "sgd"])
-def test_unit_without_backward_is_skipped_by_the_flat_optimizer(opt_kind):
-    run_ranks(_unused_unit_body, 2, opt_kind)
+def test_unit_without_backward_is_skipped_by_the_flat_optimizer(two_rank_outcomes, opt_kind):
+    check_case(two_rank_outcomes, f"unused_unit:{opt_kind}")
 
 
 # ----------------------------------------------------------------------------- full optimizer state round trip
@@ -307,8 +309,24 @@ def _full_opt_roundtrip_body(rank, world, kind):
 
 
 @pytest.mark.parametrize("kind", ["adamw", "mixed_muon_adamw"])
-def test_full_optimizer_state_dict_loads_back(kind):
-    run_ranks(_full_opt_roundtrip_body, 2, kind)
+def test_full_optimizer_state_dict_loads_back(two_rank_outcomes, kind):
+    check_case(two_rank_outcomes, f"full_opt:{kind}")
+
+
+@pytest.fixture(scope="module")
+def two_rank_outcomes():
+    """Every two-rank case of this file in one spawn (see ``dist_utils.run_cases``)."""
+    cases = [("mixed_precision", _mixed_precision_worker, ()), ("checkpointing", _checkpointing_worker, ()),
+             ("clip", _clip_worker, ())]
+    cases += [(f"library:{g}:{r}", _library_variants_worker, (g, r)) for g, r in _LIBRARY_VARIANTS]
+    cases += [(f"unused_unit:{k}", _unused_unit_body, (k,)) for k in ("adamw", "sgd")]
+    cases += [(f"full_opt:{k}", _full_opt_roundtrip_body, (k,)) for k in ("adamw", "mixed_muon_adamw")]
+    return run_cases(2, cases)
+
+
+@pytest.fixture(scope="module")
+def four_rank_outcomes():
+    return run_cases(4, [("mesh3d", _mesh3d_worker, ())])
 
 
 def test_patched_load_state_dict_forwards_strict():

@@ -19,6 +19,9 @@ def _hb_worker(rank, world, path, result_dir):
     store = dist.FileStore(path, world)
     health = RankHealth(store, rank, world, timeout_s=1.0)
     outcome = "finished"
+    deadline = time.time() + 60.0                      # start together: a rank that is still importing is not a failure
+    while time.time() < deadline and any(rec is None for rec in health.peers().values()):
+        time.sleep(0.05)
     try:
         for step in range(6):
             health.beat(step)
@@ -45,7 +48,9 @@ def test_heartbeat_detects_crashed_and_departed_ranks():
         mp.spawn(_hb_worker, args=(3, os.path.join(d, "store"), d), nprocs=3, join=True)
         out = {r: open(os.path.join(d, f"{r}.txt")).read() for r in range(3)}
     assert out[2] == "crashed"
-    assert out[0].startswith("detected:") and ("[2]" in out[0] or "[1]" in out[0])
+    assert out[0].startswith("detected:")
+    missing = out[0].split(":")[1]                      # "[2]", "[1]" or, on a loaded machine, "[1, 2]"
+    assert "1" in missing or "2" in missing, out
     assert out[1] == "left" or out[1].startswith("detected:")
 
 

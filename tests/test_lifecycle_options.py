@@ -103,7 +103,7 @@ def test_ignored_parameters_stay_ordinary_and_may_be_frozen():
     fully_shard(model, ignored_params={model[2].bias, model[2].weight})
     unit = model._matrix_fsdp_param_group
     assert [mp.fqn for mp in unit.registry] == ["0.weight", "0.bias"]
-    assert not hasattr(model[2].weight, "_matrix_fsdp_param_group_ref")
+    assert not hasattr(model[2].weight, "_mfsdp_unit_ref")
     opt = configure_optimizer(model, "sgd", lr=0.1)
     extra = torch.optim.SGD([model[2].weight], lr=0.1)      # the upper stack's own optimizer
     ropt = torch.optim.SGD([p for p in ref.parameters() if p.requires_grad], lr=0.1)

@@ -7,7 +7,7 @@ import torch
 import torch.distributed as dist
 from torch import nn
 
-from dist_utils import run_ranks
+from dist_utils import check_case, run_cases
 from matrix_fsdp_b200 import configure_optimizer, fully_shard, matrix_fully_shard
 from matrix_fsdp_b200.api import reset_shared_owner_planners
 from matrix_fsdp_b200.parallel.unit_collection import collect_param_groups
@@ -153,7 +153,7 @@ def _strategy_body(rank, world, kw, expect_impl_kind, expect_impl):
     assert expect_impl in impls, impls
 
 
-@pytest.mark.parametrize("kw,kind,impl", [
+_STRATEGIES = [
     (dict(backward_reduce_strategy="flat"), "reduce_scatter", "reduce_scatter_tensor"),
     (dict(backward_reduce_strategy="per_param"), "reduce_scatter", "per_param_reduce_scatter"),
     (dict(backward_reduce_strategy="per_param_allreduce"), "all_reduce", "per_param_allreduce"),
@@ -161,9 +161,26 @@ def _strategy_body(rank, world, kw, expect_impl_kind, expect_impl):
     (dict(param_gather_strategy="matrix_all_gather"), "all_gather", "padded_all_gather"),
     (dict(param_gather_strategy="all_reduce"), "all_gather", "all_reduce_gather"),
     (dict(param_gather_strategy="uneven_all_gather"), "all_gather", "padded_all_gather"),   # gloo: falls back
-])
-def test_strategy_selects_its_collective_and_keeps_the_result(kw, kind, impl):
-    run_ranks(_strategy_body, 2, kw, kind, impl)
+]
+
+
+def _strategy_name(kw):
+    return "strategy:" + ",".join(f"{k}={v}" for k, v in kw.items())
+
+
+@pytest.fixture(scope="module")
+def two_rank_outcomes():
+    """Every two-rank case of this file in one spawn (see ``dist_utils.run_cases``)."""
+    cases = [(_strategy_name(kw), _strategy_body, (kw, kind, impl)) for kw, kind, impl in _STRATEGIES]
+    cases.append(("owner_broadcast", _owner_broadcast_body, ()))
+    cases += [(f"policy:{p}", _policy_body, (p,)) for p in ("adaptive", "profile_guided")]
+    cases.append(("pooled", _pooled_body, ()))
+    return run_cases(2, cases)
+
+
+@pytest.mark.parametrize("kw,kind,impl", _STRATEGIES)
+def test_strategy_selects_its_collective_and_keeps_the_result(two_rank_outcomes, kw, kind, impl):
+    check_case(two_rank_outcomes, _strategy_name(kw))
 
 
 def _owner_broadcast_body(rank, world):
@@ -187,8 +204,8 @@ def _owner_broadcast_body(rank, world):
     assert "owner_broadcast" in impls, impls
 
 
-def test_owner_broadcast_strategy_needs_whole_parameter_owners():
-    run_ranks(_owner_broadcast_body, 2)
+def test_owner_broadcast_strategy_needs_whole_parameter_owners(two_rank_outcomes):
+    check_case(two_rank_outcomes, "owner_broadcast")
 
 
 def _policy_body(rank, world, policy):
@@ -217,8 +234,8 @@ def _policy_body(rank, world, policy):
 
 
 @pytest.mark.parametrize("policy", ["adaptive", "profile_guided"])
-def test_measuring_prefetch_policies_change_the_depth_from_measured_waits(policy):
-    run_ranks(_policy_body, 2, policy)
+def test_measuring_prefetch_policies_change_the_depth_from_measured_waits(two_rank_outcomes, policy):
+    check_case(two_rank_outcomes, f"policy:{policy}")
 
 
 def _pooled_body(rank, world):
@@ -267,5 +284,5 @@ def _pooled_body(rank, world):
         assert torch.allclose(p, q.detach(), atol=1e-6), n
 
 
-def test_saved_tensor_hooks_take_unsharded_buffers_from_the_pool():
-    run_ranks(_pooled_body, 2)
+def test_saved_tensor_hooks_take_unsharded_buffers_from_the_pool(two_rank_outcomes):
+    check_case(two_rank_outcomes, "pooled")
