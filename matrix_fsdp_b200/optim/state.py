@@ -73,11 +73,10 @@ class MatrixFSDPOptimizerStateManager:
                                                      piece.param_start)
 
     def iter_state_tensors(self):
-        for comp_opt in self.optimizers.values():
-            pass
+        by_name = {u.name: u for u in self.units}
         for p, info in self.iter_param_infos():
             state = self.optimizers[info.component].state.get(p, {})
-            unit = next(u for u in self.units if u.name == info.unit)
+            unit = by_name[info.unit]
             for name, value in state.items():
                 if not isinstance(value, torch.Tensor):
                     continue
