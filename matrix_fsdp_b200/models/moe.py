@@ -232,6 +232,20 @@ def configure_moe_optimizer(model: MoEModel, optimizer: str = "mixed_muon_adamw"
     return CombinedOptimizer(dense, experts)
 
 
+def clip_moe_grad_norm_(model: MoEModel, max_norm: float, norm_type: float = 2.0, *, expert_scale: float = 1.0,
+                        error_if_nonfinite: bool = False) -> torch.Tensor:
+    """Clip the global gradient norm of an MoE model: the sharded dense gradients plus the expert gradients, of
+    which every rank of the expert-parallel group holds its own experts'.  ``expert_scale`` is the factor the
+    expert optimizer applies to its gradients (``1 / world`` when they are to be means over the ranks' tokens; the
+    expert backward leaves sums).  Returns the norm before clipping; call it between ``backward()`` and ``step()``."""
+    from ..utils.training import clip_grad_norm_
+
+    group = model.layers[0]._group() if len(model.layers) else None
+    return clip_grad_norm_(model, max_norm, norm_type, error_if_nonfinite,
+                           extra_grads=[p.grad for p in model.expert_parameters()], extra_group=group,
+                           extra_scale=expert_scale)
+
+
 def save_moe_checkpoint(model: MoEModel, directory: str, optimizer=None) -> None:
     """Dense parameters (and their optimizer state) through ``save_matrix_dcp``; every EP rank adds one file
     with the experts it owns (weights, fp32 masters and optimizer state), keyed by global expert id."""

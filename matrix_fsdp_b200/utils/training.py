@@ -51,7 +51,8 @@ def device_train_step(model: torch.nn.Module, optimizer, tokens: torch.Tensor, t
 
 @torch.no_grad()
 def clip_grad_norm_(module_or_units, max_norm: float, norm_type: float = 2.0,
-                    error_if_nonfinite: bool = False) -> torch.Tensor:
+                    error_if_nonfinite: bool = False, *, extra_grads=(), extra_group=None,
+                    extra_scale: float = 1.0) -> torch.Tensor:
     """Clip the global gradient norm of a sharded model in place and return the norm before clipping.
 
     Every rank only holds its shard of each unit's reduced gradient, so the norm is assembled from the local
@@ -59,6 +60,11 @@ def clip_grad_norm_(module_or_units, max_norm: float, norm_type: float = 2.0,
     counted twice).  Call it after ``backward()`` and before ``optimizer.step()``; it waits for the units'
     pending reduce-scatters first.  ``torch.nn.utils.clip_grad_norm_`` on the module would see local shards
     only, which is what the reference leaves its users with.
+
+    ``extra_grads``: gradients of parameters no unit manages and that every rank of ``extra_group`` owns a
+    different part of (expert-parallel weights); their contribution is summed over ``extra_group``, counted
+    ``extra_scale`` times (the factor their optimizer applies to them, e.g. ``1 / world`` when they hold sums over
+    the ranks' tokens), and they are clipped in place with the same coefficient.
     """
     import math
 
@@ -68,7 +74,7 @@ def clip_grad_norm_(module_or_units, max_norm: float, norm_type: float = 2.0,
 
     units = collect_param_groups(module_or_units)
     inf = math.isinf(norm_type)
-    per_group: dict[int, tuple[object, torch.Tensor]] = {}
+    per_group: dict[object, tuple[object, torch.Tensor]] = {}
     shards = []
     for u in units:
         u.wait_post_backward_reduce()
@@ -84,7 +90,17 @@ def clip_grad_norm_(module_or_units, max_norm: float, norm_type: float = 2.0,
             per_group[key] = (group, torch.maximum(prev, part) if inf else prev + part)
         else:
             per_group[key] = (group, part)
-    if not shards:
+    extra_grads = list(extra_grads)
+    extra = [g for g in extra_grads if g is not None and g.numel()]
+    if extra_grads:                  # also a rank whose experts saw no token joins the group's sum
+        parts = [g.detach().float().abs().max() if inf else g.detach().float().norm(norm_type).pow(norm_type)
+                 for g in extra]
+        ref = shards[0] if shards else (extra[0] if extra else None)
+        part = (torch.stack(parts).max() if inf else torch.stack(parts).sum()) if parts else \
+            torch.zeros((), device=ref.device if ref is not None else None)
+        part = part * (abs(extra_scale) if inf else abs(extra_scale) ** norm_type)
+        per_group[("extra", id(extra_group))] = (extra_group, part)
+    if not per_group:
         return torch.zeros(())
     total = None
     for group, part in per_group.values():
@@ -95,8 +111,8 @@ def clip_grad_norm_(module_or_units, max_norm: float, norm_type: float = 2.0,
     if error_if_nonfinite and not torch.isfinite(norm):
         raise RuntimeError(f"The total norm of order {norm_type} for the gradients is non-finite.")
     coef = (max_norm / (norm + 1e-6)).clamp(max=1.0)
-    for g in shards:
-        g.mul_(coef.to(g.dtype))
+    for g in (*shards, *extra):
+        g.mul_(coef.to(device=g.device, dtype=g.dtype))
     return norm
 
 

@@ -17,6 +17,7 @@ from dist_utils import run_ranks
 # experts, top-k, optimizer
 TRAIN_CASES = ["E4-K1-adamw", "E4-K2-adamw", "E4-K3-adamw", "E8-K2-adamw", "E8-K4-adamw", "E4-K2-sgd", "E8-K3-sgd",
                "E4-K2-sgdm", "E2-K1-adamw", "E2-K2-adamw"]
+CLIP_CASES = ["clip-2", "clip-1", "clip-inf"]
 RESUME_CASES = ["resume-E4-K2-adamw", "resume-E4-K2-sgd", "resume-E4-K2-mixed_muon_adamw", "resume-E8-K3-adamw"]
 TRAIN4_CASES = ["E4-K2-adamw", "E8-K2-adamw", "E8-K3-sgd"]
 RESUME4_CASES = ["resume-E8-K2-mixed_muon_adamw"]
@@ -83,6 +84,56 @@ def _train_case(rank, world, name):
         assert torch.allclose(a.experts.w_gate_up, b.experts.w_gate_up[lo:hi], atol=3e-5)
 
 
+def _clip_case(rank, world, name):
+    """Global-norm clipping over dense shards plus expert gradients equals clipping the all-local model."""
+    import math
+
+    from matrix_fsdp_b200.api import reset_shared_owner_planners
+    from matrix_fsdp_b200.models.moe import MoEModel, clip_moe_grad_norm_, configure_moe_optimizer, shard_moe
+    from matrix_fsdp_b200.parallel.expert_parallel import reset_contexts
+
+    norm_type = math.inf if name.endswith("inf") else float(name.rsplit("-", 1)[1])
+    reset_shared_owner_planners()
+    reset_contexts()
+    cfg = _cfg(4, 2)
+    torch.manual_seed(0)
+    model = MoEModel(cfg)
+    torch.manual_seed(0)
+    ref = MoEModel(cfg, ep_group=False)
+    shard_moe(model)
+    opt = configure_moe_optimizer(model, "sgd", lr=0.05)
+    ref_params = [p for n, p in ref.named_parameters() if ".experts." not in n] + ref.expert_parameters()
+    ropt = torch.optim.SGD(ref_params, lr=0.05)
+    toks = _tokens(world)
+    el = cfg.n_experts // world
+    for max_norm_factor in (0.3, 10.0):                       # one step that clips, one that does not
+        mine = toks[rank:rank + 1]
+        model(mine[:, :-1], mine[:, 1:]).backward()
+        for r in range(world):
+            (ref(toks[r:r + 1, :-1], toks[r:r + 1, 1:]) / world).backward()
+        rtotal = torch.nn.utils.get_total_norm([p.grad for p in ref_params], norm_type)
+        max_norm = float(rtotal) * max_norm_factor
+        total = clip_moe_grad_norm_(model, max_norm, norm_type, expert_scale=1.0 / world)
+        assert torch.allclose(total, rtotal, rtol=1e-4), (float(total), float(rtotal))
+        torch.nn.utils.clip_grad_norm_(ref_params, max_norm, norm_type)
+        for p in model.expert_parameters():                   # what expert_scale stood for
+            p.grad.div_(world)
+        opt.step()
+        opt.zero_grad()
+        ropt.step()
+        ropt.zero_grad()
+    for a, b in zip(model.layers, ref.layers):
+        lo, hi = rank * el, (rank + 1) * el
+        assert torch.allclose(a.experts.w_down, b.experts.w_down[lo:hi], atol=3e-5)
+        assert torch.allclose(a.experts.w_gate_up, b.experts.w_gate_up[lo:hi], atol=3e-5)
+    from matrix_fsdp_b200.checkpoint import MatrixStateDictOptions, get_model_state_dict
+
+    full = get_model_state_dict(model, options=MatrixStateDictOptions(full_state_dict=True))
+    for n, p in ref.named_parameters():
+        if ".experts." not in n:
+            assert torch.allclose(full[n], p.detach(), atol=3e-5), n
+
+
 def _resume_case(rank, world, name, base_dir):
     from matrix_fsdp_b200.api import reset_shared_owner_planners
     from matrix_fsdp_b200.models.moe import (MoEModel, configure_moe_optimizer, load_moe_checkpoint, save_moe_checkpoint,
@@ -133,6 +184,8 @@ def _worker(rank, world, out_path, names, base_dir):
         try:
             if name.startswith("resume-"):
                 _resume_case(rank, world, name, base_dir)
+            elif name.startswith("clip-"):
+                _clip_case(rank, world, name)
             else:
                 _train_case(rank, world, name)
             mine = ""
@@ -156,7 +209,7 @@ def _spawn(world, names):
 
 @pytest.fixture(scope="module")
 def outcomes():
-    return _spawn(2, TRAIN_CASES + RESUME_CASES)
+    return _spawn(2, TRAIN_CASES + RESUME_CASES + CLIP_CASES)
 
 
 @pytest.fixture(scope="module")
@@ -164,7 +217,7 @@ def outcomes4():
     return _spawn(4, TRAIN4_CASES + RESUME4_CASES)
 
 
-@pytest.mark.parametrize("case", TRAIN_CASES + RESUME_CASES)
+@pytest.mark.parametrize("case", TRAIN_CASES + RESUME_CASES + CLIP_CASES)
 def test_two_rank_expert_parallel(outcomes, case):
     assert case in outcomes, "the worker did not reach this case"
     assert not outcomes[case], outcomes[case]
