@@ -270,7 +270,10 @@ def save_moe_checkpoint(model: MoEModel, directory: str, optimizer=None) -> None
 
 
 def load_moe_checkpoint(model: MoEModel, directory: str, optimizer=None, allow_reshard: bool = False) -> None:
-    """Inverse of :func:`save_moe_checkpoint` for the same expert-parallel size."""
+    """Inverse of :func:`save_moe_checkpoint`.  With ``allow_reshard`` the expert-parallel size may differ from the
+    one that wrote the files: experts are addressed by their global id, every rank reads the files that hold the
+    experts it owns now and cuts their rows (weights, masters and optimizer state) out of them."""
+    import glob
     import os
 
     from ..checkpoint import load_matrix_dcp
@@ -278,18 +281,72 @@ def load_moe_checkpoint(model: MoEModel, directory: str, optimizer=None, allow_r
     dense_opt = getattr(optimizer, "dense", optimizer)
     load_matrix_dcp(model, directory, optimizer=dense_opt, allow_reshard=allow_reshard)
     rank = dist.get_rank() if dist.is_initialized() else 0
-    payload = torch.load(os.path.join(directory, f"experts_rank{rank}.pt"), map_location="cpu", weights_only=False)
-    for li, layer in enumerate(model.layers):
-        rec = payload["experts"][li]
-        ex = layer.experts
-        if rec["first_expert"] != ex.first_expert or rec["w_down"].shape != ex.w_down.shape:
-            raise ValueError("expert checkpoint was written with a different expert-parallel layout")
-        with torch.no_grad():
-            ex.w_gate_up.copy_(rec["w_gate_up"])
-            ex.w_down.copy_(rec["w_down"])
     expert_opt = getattr(optimizer, "experts", None)
-    if expert_opt is not None and payload.get("optimizer") is not None:
-        expert_opt.load_state_dict(payload["optimizer"])
+    mine = os.path.join(directory, f"experts_rank{rank}.pt")
+    payload = torch.load(mine, map_location="cpu", weights_only=False) if os.path.exists(mine) else None
+    same = payload is not None and all(
+        payload["experts"][li]["first_expert"] == layer.experts.first_expert
+        and payload["experts"][li]["w_down"].shape == layer.experts.w_down.shape
+        for li, layer in enumerate(model.layers))
+    if same:
+        for li, layer in enumerate(model.layers):
+            rec, ex = payload["experts"][li], layer.experts
+            with torch.no_grad():
+                ex.w_gate_up.copy_(rec["w_gate_up"])
+                ex.w_down.copy_(rec["w_down"])
+        if expert_opt is not None and payload.get("optimizer") is not None:
+            expert_opt.load_state_dict(payload["optimizer"])
+        return
+    if not allow_reshard:
+        raise ValueError("expert checkpoint was written with a different expert-parallel layout")
+    files = sorted(glob.glob(os.path.join(directory, "experts_rank*.pt")))
+    sources = [torch.load(f, map_location="cpu", weights_only=False) for f in files]
+    for li, layer in enumerate(model.layers):
+        ex = layer.experts
+        with torch.no_grad():
+            for name in ("w_gate_up", "w_down"):
+                rows = _expert_rows([(src["experts"][li]["first_expert"], src["experts"][li][name]) for src in sources],
+                                    ex.first_expert, ex.n_local)
+                getattr(ex, name).copy_(rows)
+    if expert_opt is not None and all(src.get("optimizer") is not None for src in sources):
+        # optimizer entries are per expert parameter, in ``model.expert_parameters()`` order: two per layer
+        firsts = [[src["experts"][li]["first_expert"] for li in range(len(model.layers)) for _ in range(2)]
+                  for src in sources]
+        my = [(layer.experts.first_expert, layer.experts.n_local) for layer in model.layers for _ in range(2)]
+        expert_opt.load_state_dict(_reshard_expert_optimizer_state([s["optimizer"] for s in sources], firsts, my))
+
+
+def _expert_rows(sources, first: int, count: int):
+    """Rows ``[first, first + count)`` by global expert id out of ``[(first id, tensor or list), ...]``."""
+    picked = []
+    for e in range(first, first + count):
+        for src_first, rows in sources:
+            if src_first <= e < src_first + len(rows):
+                picked.append(rows[e - src_first])
+                break
+        else:
+            raise ValueError(f"no checkpoint file holds expert {e}")
+    return picked if not isinstance(picked[0], torch.Tensor) else torch.stack(picked)
+
+
+def _reshard_expert_optimizer_state(states: list, firsts: list, mine: list) -> dict:
+    """One expert-optimizer state dict for the experts this rank owns, cut from the writers' state dicts."""
+    kinds = {s["kind"] for s in states}
+    if len(kinds) != 1:
+        raise ValueError(f"expert optimizer kinds differ between files: {sorted(kinds)}")
+    out = {"kind": states[0]["kind"], "step": max(int(s["step"]) for s in states)}
+    per_param = {"masters": True, "exp_avg": True, "exp_avg_sq": True, "momentum_buffer": True, "momentum": True}
+    for key in states[0]:
+        if key not in per_param:
+            continue
+        if any(len(s[key]) == 0 for s in states):            # SGD without momentum keeps an empty list
+            out[key] = []
+            continue
+        out[key] = []
+        for i, (first, count) in enumerate(mine):
+            rows = _expert_rows([(firsts[k][i], s[key][i]) for k, s in enumerate(states)], first, count)
+            out[key].append(rows)
+    return out
 
 
 def _to_cpu(obj):

@@ -178,6 +178,85 @@ def _resume_case(rank, world, name, base_dir):
         assert torch.allclose(a.experts.w_down, b.experts.w_down, atol=1e-6)
 
 
+def _reshard_model(opt_kind, seed):
+    from matrix_fsdp_b200.api import reset_shared_owner_planners
+    from matrix_fsdp_b200.models.moe import MoEModel, configure_moe_optimizer, shard_moe
+    from matrix_fsdp_b200.parallel.expert_parallel import reset_contexts
+
+    reset_shared_owner_planners()
+    reset_contexts()
+    mixed = opt_kind == "mixed_muon_adamw"
+    torch.manual_seed(seed)
+    m = MoEModel(_cfg(8, 2))
+    shard_moe(m, optimizer_policy="mixed_muon_adamw" if mixed else None)
+    kw = {"adamw": dict(lr=1e-2), "sgd": dict(lr=0.05, momentum=0.9), "mixed_muon_adamw": dict(lr=1e-2, muon_lr=0.02)}
+    return m, configure_moe_optimizer(m, opt_kind, **kw[opt_kind])
+
+
+def _expert_state_rows(model, opt):
+    """{name: [n_local, ...] tensor} of everything the expert optimizer and the experts hold, per expert row."""
+    ex_opt = opt.experts
+    out = {}
+    for i, p in enumerate(model.expert_parameters()):
+        out[f"w{i}"] = p.detach().clone()
+        out[f"master{i}"] = ex_opt.masters[i].clone()
+        if ex_opt.kind == "adamw":
+            out[f"exp_avg{i}"], out[f"exp_avg_sq{i}"] = ex_opt.exp_avg[i].clone(), ex_opt.exp_avg_sq[i].clone()
+        elif ex_opt.kind == "sgd":
+            out[f"momentum{i}"] = ex_opt.momentum_buffer[i].clone()
+        else:
+            out[f"momentum{i}"] = torch.stack([ex_opt.muon.state[s]["momentum_buffer"] for s in ex_opt._slices[i]])
+    return out
+
+
+def _reshard_write_case(rank, world, name, base_dir):
+    """Two ranks train, save, and leave every expert's state gathered by global id for the readers to check."""
+    from matrix_fsdp_b200.models.moe import save_moe_checkpoint
+
+    opt_kind = name.split("-", 1)[1]
+    model, opt = _reshard_model(opt_kind, 0)
+    toks = _tokens(world)[rank:rank + 1]
+    for _ in range(2):
+        model(toks[:, :-1], toks[:, 1:]).backward()
+        opt.step()
+        opt.zero_grad()
+    directory = os.path.join(base_dir, f"reshard-{opt_kind}")
+    if rank == 0:
+        os.makedirs(directory, exist_ok=True)
+    dist.barrier()
+    save_moe_checkpoint(model, directory, optimizer=opt)
+    rows = _expert_state_rows(model, opt)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, rows)
+    if rank == 0:
+        torch.save({k: torch.cat([g[k] for g in gathered]) for k in rows}, os.path.join(directory, "all_experts.pt"))
+    dist.barrier()
+
+
+def _reshard_read_case(rank, world, name, base_dir):
+    """Another expert-parallel size reads the files: every rank finds its experts' rows, and trains on."""
+    from matrix_fsdp_b200.models.moe import load_moe_checkpoint
+
+    opt_kind = name.split("-", 1)[1]
+    directory = os.path.join(base_dir, f"reshard-{opt_kind}")
+    model, opt = _reshard_model(opt_kind, 5)
+    with pytest.raises(ValueError):
+        load_moe_checkpoint(model, directory, optimizer=opt)              # another layout: has to be asked for
+    model, opt = _reshard_model(opt_kind, 5)
+    load_moe_checkpoint(model, directory, optimizer=opt, allow_reshard=True)
+    want = torch.load(os.path.join(directory, "all_experts.pt"))
+    el = 8 // world
+    for k, v in _expert_state_rows(model, opt).items():
+        assert torch.equal(v, want[k][rank * el:(rank + 1) * el]), k
+    toks = _tokens(world)[rank:rank + 1]
+    before = model.layers[0].experts.w_down.detach().clone()
+    loss = model(toks[:, :-1], toks[:, 1:])
+    loss.backward()
+    opt.step()
+    opt.zero_grad()
+    assert torch.isfinite(loss) and not torch.equal(model.layers[0].experts.w_down, before)
+
+
 def _worker(rank, world, out_path, names, base_dir):
     results = {}
     for name in names:
@@ -186,6 +265,10 @@ def _worker(rank, world, out_path, names, base_dir):
                 _resume_case(rank, world, name, base_dir)
             elif name.startswith("clip-"):
                 _clip_case(rank, world, name)
+            elif name.startswith("reshardwrite-"):
+                _reshard_write_case(rank, world, name, base_dir)
+            elif name.startswith("reshardread-"):
+                _reshard_read_case(rank, world, name, base_dir)
             else:
                 _train_case(rank, world, name)
             mine = ""
@@ -199,22 +282,32 @@ def _worker(rank, world, out_path, names, base_dir):
             json.dump(results, f)
 
 
-def _spawn(world, names):
+def _spawn(world, names, base_dir):
+    path = os.path.join(base_dir, f"outcomes-{world}.json")
+    run_ranks(_worker, world, path, names, base_dir, timeout=600.0)
+    with open(path) as f:
+        return json.load(f)
+
+
+RESHARD_KINDS = ("adamw", "sgd", "mixed_muon_adamw")
+RESHARD_WRITE = [f"reshardwrite-{k}" for k in RESHARD_KINDS]
+RESHARD_READ = [f"reshardread-{k}" for k in RESHARD_KINDS]
+
+
+@pytest.fixture(scope="module")
+def shared_dir():
     with tempfile.TemporaryDirectory() as tmp:
-        path = os.path.join(tmp, "outcomes.json")
-        run_ranks(_worker, world, path, names, tmp, timeout=600.0)
-        with open(path) as f:
-            return json.load(f)
+        yield tmp
 
 
 @pytest.fixture(scope="module")
-def outcomes():
-    return _spawn(2, TRAIN_CASES + RESUME_CASES + CLIP_CASES)
+def outcomes(shared_dir):
+    return _spawn(2, TRAIN_CASES + RESUME_CASES + CLIP_CASES + RESHARD_WRITE, shared_dir)
 
 
 @pytest.fixture(scope="module")
-def outcomes4():
-    return _spawn(4, TRAIN4_CASES + RESUME4_CASES)
+def outcomes4(shared_dir, outcomes):                  # after the two-rank job: it reads what that one wrote
+    return _spawn(4, TRAIN4_CASES + RESUME4_CASES + RESHARD_READ, shared_dir)
 
 
 @pytest.mark.parametrize("case", TRAIN_CASES + RESUME_CASES + CLIP_CASES)
@@ -227,3 +320,9 @@ def test_two_rank_expert_parallel(outcomes, case):
 def test_four_rank_expert_parallel(outcomes4, case):
     assert case in outcomes4, "the worker did not reach this case"
     assert not outcomes4[case], outcomes4[case]
+
+
+@pytest.mark.parametrize("kind", RESHARD_KINDS)
+def test_expert_checkpoint_moves_from_two_ranks_to_four(outcomes, outcomes4, kind):
+    assert not outcomes[f"reshardwrite-{kind}"], outcomes[f"reshardwrite-{kind}"]
+    assert not outcomes4[f"reshardread-{kind}"], outcomes4[f"reshardread-{kind}"]
