@@ -300,6 +300,12 @@ class MatrixFSDPParamGroup:
         if self.planner is not None:
             plan = self.planner(registry.total_numel, world)
             return planner_result_from_output(getattr(self.planner, "__name__", "planner"), plan, params, world)
+        if any(mp.shard_hint is not None and mp.shard_hint.split_granularity is not None for mp in params):
+            # hints without a planner: an even split would cut what the hints forbid to cut (and be refused by the
+            # validator), so take the rank-contiguous plan that cuts only where every hint allows
+            from ..planning.planner import hinted_ordered_group_plan
+
+            return call_group_planner(hinted_ordered_group_plan, params, world)
         # on CUDA every shard boundary sits on a 16-byte boundary of the bf16 wire format so the peer
         # kernels (and TMA) can address any rank's shard with full-width vector accesses
         align = 8 if registry[0].device.type == "cuda" and registry.total_numel >= 64 * world else 1

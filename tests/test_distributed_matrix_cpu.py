@@ -80,6 +80,19 @@ CASES = {
     "units_ordered_groups": ("units", lambda: dict(group_planner=_planner("ordered_group_plan")), "adamw", {}),
     "units_owner_tail": ("units", lambda: dict(group_planner=_planner("ordered_matrix_owner_tail_plan"),
                                                auto_shard_hints=True), "adamw", {}),
+    "units_plain_planner": ("units", lambda: dict(planner=_planner("contiguous_even_plan")), "adamw", {}),
+    "units_layout_planner": ("units", lambda: dict(layout_planner=_planner("parameter_boundary_plan")), "adamw", {}),
+    "units_auto_hints_only": ("units", lambda: dict(auto_shard_hints=True), "adamw", {}),
+    "units_auto_max_balance": ("units", lambda: dict(auto_planner_policy="max_balance"), "adamw", {}),
+    "units_auto_debug": ("units", lambda: dict(auto_planner_policy="debug"), "sgd", {}),
+    "units_auto_block_units": ("units", lambda: dict(auto_planner_policy="balanced", target_block_units=16), "adamw", {}),
+    "units_auto_muon_zero_copy": ("units", lambda: dict(auto_planner_policy="muon_zero_copy", auto_shard_hints=True),
+                                  "adamw", {}),
+    "units_auto_muon_shard_aware_round_robin": ("units", lambda: dict(auto_planner_policy="muon_shard_aware",
+                                                                      auto_shard_hints=True,
+                                                                      rotation_strategy="round_robin"), "sgd", {}),
+    "units_auto_muon_full_matrix": ("units", lambda: dict(auto_planner_policy="muon_full_matrix", auto_shard_hints=True),
+                                    "sgd", {}),
     "units_auto_balanced": ("units", lambda: dict(auto_planner_policy="balanced"), "adamw", {}),
     "units_auto_zero_copy_friendly": ("units", lambda: dict(auto_planner_policy="zero_copy_friendly"), "adamw", {}),
     "units_auto_min_comm": ("units", lambda: dict(auto_planner_policy="min_comm"), "sgd", {}),
@@ -96,6 +109,11 @@ CASES = {
                                                   group_planner=_planner("parameter_boundary_plan")), "adamw", {}),
     "units_layout_segment_runtime": ("units", lambda: dict(runtime_layout_policy="segment_runtime",
                                                            group_planner=_planner("parameter_boundary_plan")), "adamw", {}),
+    "units_layout_flat_reorder": ("units", lambda: dict(runtime_layout_policy="flat_reorder",
+                                                        group_planner=_planner("parameter_boundary_plan")), "adamw", {}),
+    "units_layout_matrix_shard": ("units", lambda: dict(runtime_layout_policy="matrix_shard"), "adamw", {}),
+    "root_layout_flat_reorder_sgd": ("root", lambda: dict(runtime_layout_policy="flat_reorder",
+                                                           group_planner=_planner("parameter_boundary_plan")), "sgd", {}),
     "units_zero_copy_bucket": ("units", lambda: dict(use_zero_copy_grad_bucket=True), "adamw", {}),
     "units_saved_tensor_hooks": ("units", lambda: dict(use_saved_tensor_hooks=True), "adamw", {}),
     "units_keep_storage_after_backward": ("units", lambda: dict(shrink_full_param_storage_after_backward=False),
