@@ -50,6 +50,12 @@ def _bf16():
     return MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
 
 
+def _rows(param):
+    from torch.distributed.tensor.placement_types import Shard
+
+    return Shard(0)
+
+
 def _planner(name):
     from matrix_fsdp_b200.planning import planner as P
 
@@ -114,6 +120,8 @@ CASES = {
     "units_layout_matrix_shard": ("units", lambda: dict(runtime_layout_policy="matrix_shard"), "adamw", {}),
     "root_layout_flat_reorder_sgd": ("root", lambda: dict(runtime_layout_policy="flat_reorder",
                                                            group_planner=_planner("parameter_boundary_plan")), "sgd", {}),
+    "units_rows": ("units", lambda: dict(shard_placement_fn=_rows), "adamw", {}),
+    "root_rows": ("root", lambda: dict(shard_placement_fn=_rows), "sgd", {}),
     "units_zero_copy_bucket": ("units", lambda: dict(use_zero_copy_grad_bucket=True), "adamw", {}),
     "units_saved_tensor_hooks": ("units", lambda: dict(use_saved_tensor_hooks=True), "adamw", {}),
     "units_keep_storage_after_backward": ("units", lambda: dict(shrink_full_param_storage_after_backward=False),
@@ -237,8 +245,13 @@ HSDP_CASES = {
 
 
 def _shard(model, wrap, kw):
-    from matrix_fsdp_b200 import matrix_fully_shard
+    from matrix_fsdp_b200 import fully_shard, matrix_fully_shard
     from matrix_fsdp_b200.policy.wrap import module_type_policy
+
+    if "shard_placement_fn" in kw:                              # an option of the FSDP2-shaped entry point only
+        for m in ([] if wrap == "root" else list(model.children())[:-1]) + [model]:
+            fully_shard(m, **kw)
+        return
 
     if wrap == "units":
         for blk in list(model.children())[:-1]:
@@ -352,9 +365,19 @@ def _run_case(rank, world, name):
         assert sum(u.flat_buffer.local_numel for u in units) < sum(u.flat_buffer.total_numel for u in units)
 
 
+# an odd world size: shard sizes with a remainder, rows that do not divide, three owners
+THREE_RANK_CASES = ["root_default", "units_default", "policy_default", "units_keep_after_forward", "units_reduce_flat",
+                    "units_reduce_per_param", "units_reduce_per_param_allreduce", "units_parameter_boundaries",
+                    "units_ordered_groups", "units_owner_tail", "units_auto_balanced", "units_auto_min_comm",
+                    "units_gather_padded", "units_gather_owner_broadcast", "units_gather_all_reduce", "units_rows",
+                    "root_rows", "units_zero_copy_bucket", "units_saved_tensor_hooks", "units_bf16", "units_no_sync",
+                    "units_activation_checkpoint", "units_layout_flat_reorder", "topo_branches", "topo_twice_keep",
+                    "wrapped_torch_adam", "bare_torch_adamw"]
+
+
 def _worker(rank, world, out_path, which):
     results = {}
-    for name in (HSDP_CASES if which == "hsdp" else CASES):
+    for name in {"hsdp": HSDP_CASES, "three": THREE_RANK_CASES}.get(which, CASES):
         try:
             _run_case(rank, world, name)
             mine = ""
@@ -380,6 +403,15 @@ def outcomes():
 
 
 @pytest.fixture(scope="module")
+def three_rank_outcomes():
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "outcomes.json")
+        run_ranks(_worker, 3, path, "three", timeout=600.0)
+        with open(path) as f:
+            return json.load(f)
+
+
+@pytest.fixture(scope="module")
 def hsdp_outcomes():
     with tempfile.TemporaryDirectory() as tmp:
         path = os.path.join(tmp, "outcomes.json")
@@ -398,3 +430,9 @@ def test_two_rank_step_matches_eager_model(outcomes, case):
 def test_four_rank_hsdp_step_matches_eager_model(hsdp_outcomes, case):
     assert case in hsdp_outcomes, "the worker did not reach this case"
     assert not hsdp_outcomes[case], hsdp_outcomes[case]
+
+
+@pytest.mark.parametrize("case", THREE_RANK_CASES)
+def test_three_rank_step_matches_eager_model(three_rank_outcomes, case):
+    assert case in three_rank_outcomes, "the worker did not reach this case"
+    assert not three_rank_outcomes[case], three_rank_outcomes[case]
