@@ -1,4 +1,4 @@
-"""matrix_dcp checkpoints cross world sizes: written by 1 process, 2 gloo ranks (flat) and 4 gloo ranks (HSDP 2 x 2),
+"""matrix_dcp checkpoints cross world sizes: written by 1 process, 2 and 3 flat gloo ranks and 4 gloo ranks (HSDP 2 x 2),
 each read back, re-sharded, by every OTHER arrangement.  Parameters have to arrive bitwise, and one more training
 step (optimizer state included) has to land where the writer's own next step landed.  Every rank of every
 arrangement trains on the same batch, so the averaged gradient does not depend on the arrangement.
@@ -18,7 +18,7 @@ from torch import nn
 
 from dist_utils import run_ranks
 
-ARRANGEMENTS = ("w1", "w2", "w4hsdp")
+ARRANGEMENTS = ("w1", "w2", "w3", "w4hsdp")
 OPTIMIZERS = ("adamw", "sgd", "mixed_muon_adamw")
 CASES = [f"{src}->{dst}:{opt}" for src in ARRANGEMENTS for dst in ARRANGEMENTS if src != dst for opt in OPTIMIZERS]
 
@@ -140,7 +140,8 @@ def _visit(arrangement, base_dir, sources, save):
     if arrangement == "w1":
         return _stage("w1", base_dir, sources, save=save)
     out_path = os.path.join(base_dir, f"outcomes-{arrangement}-{int(save)}.json")
-    run_ranks(_worker, {"w2": 2, "w4hsdp": 4}[arrangement], arrangement, base_dir, sources, save, out_path, timeout=600.0)
+    run_ranks(_worker, {"w2": 2, "w3": 3, "w4hsdp": 4}[arrangement], arrangement, base_dir, sources, save, out_path,
+              timeout=600.0)
     with open(out_path) as f:
         return json.load(f)
 
@@ -151,9 +152,11 @@ def outcomes():
     with tempfile.TemporaryDirectory() as tmp:
         results.update(_visit("w1", tmp, (), True))
         results.update(_visit("w2", tmp, ("w1",), True))
-        results.update(_visit("w4hsdp", tmp, ("w1", "w2"), True))
-        results.update(_visit("w2", tmp, ("w4hsdp",), False))
-        results.update(_visit("w1", tmp, ("w2", "w4hsdp"), False))
+        results.update(_visit("w3", tmp, ("w1", "w2"), True))
+        results.update(_visit("w4hsdp", tmp, ("w1", "w2", "w3"), True))
+        results.update(_visit("w3", tmp, ("w4hsdp",), False))
+        results.update(_visit("w2", tmp, ("w3", "w4hsdp"), False))
+        results.update(_visit("w1", tmp, ("w2", "w3", "w4hsdp"), False))
     return results
 
 
