@@ -21,7 +21,7 @@ from dist_utils import run_ranks
 
 OPTIMIZERS = ("adamw", "sgd", "mixed_muon_adamw")
 WRAPS = ("root", "units")
-ROUTES = ("dcp", "dcp_reshard", "in_memory", "facade_sharded", "facade_full")
+ROUTES = ("dcp", "dcp_reshard", "dcp_full_state", "in_memory", "facade_sharded", "facade_full")
 CASES = [f"{o}-{w}-{r}" for o, w, r in itertools.product(OPTIMIZERS, WRAPS, ROUTES)]
 
 
@@ -81,13 +81,22 @@ def _run_case(rank, world, name, base_dir):
     reshard = route == "dcp_reshard"
     # the muon layout is already uneven (owners); re-shard it into the even split of plain AdamW-style sharding
     dst, dst_opt = _build(5, opt_kind, wrap, other_layout=reshard)
-    if route in ("dcp", "dcp_reshard"):
+    if route in ("dcp", "dcp_reshard", "dcp_full_state"):
         directory = os.path.join(base_dir, name)
         if rank == 0:
             os.makedirs(directory, exist_ok=True)
         dist.barrier()
-        save_matrix_dcp(src, directory, optimizer=src_opt)
+        save_matrix_dcp(src, directory, optimizer=src_opt, full_state=(route == "dcp_full_state"))
         dist.barrier()
+        if route == "dcp_full_state":
+            # the same files also hold every parameter whole, readable without the model or a process group
+            from matrix_fsdp_b200 import load_matrix_dcp_full_state
+
+            whole = load_matrix_dcp_full_state(directory)["params"]
+            want = _full(src)
+            assert set(whole) == set(want), (sorted(whole), sorted(want))
+            for k, v in want.items():
+                assert torch.equal(whole[k], v), k
         if reshard and opt_kind != "mixed_muon_adamw":
             with pytest.raises(ValueError):                  # a different layout is refused unless asked for
                 load_matrix_dcp(dst, directory, optimizer=dst_opt)
