@@ -209,3 +209,37 @@ def test_mesh_helpers_describe_the_shard_and_replicate_dims(two_rank_outcomes):
 
 def test_a_shard_can_be_viewed_as_a_dtensor_with_a_matrix_shard_placement(two_rank_outcomes):
     check_case(two_rank_outcomes, "dtensor")
+
+
+# ------------------------------------------------------------------------------------------ training helpers
+def _tiny_llama():
+    from matrix_fsdp_b200.models.llama import LlamaConfig, LlamaModel, shard_llama
+
+    reset_shared_owner_planners()
+    torch.manual_seed(0)
+    model = LlamaModel(LlamaConfig(vocab_size=32, hidden=16, n_layers=1, n_heads=2, head_dim=8, ffn=24, max_seq_len=8))
+    shard_llama(model)
+    return model, P.configure_optimizer(model, "adamw", lr=1e-2)
+
+
+def test_train_step_is_forward_backward_step_and_a_loss_read_back():
+    from matrix_fsdp_b200.utils.training import device_train_step, pin, train_step
+
+    tok = torch.randint(0, 32, (2, 7), generator=torch.Generator().manual_seed(1))
+    x, y = tok[:, :-1], tok[:, 1:]
+    a, aopt = _tiny_llama()
+    b, bopt = _tiny_llama()
+    c, copt = _tiny_llama()
+    assert pin(x) is x or pin(x).is_pinned()                               # nothing to pin without a CUDA device
+    loss_a = train_step(a, aopt, x, y, "cpu")
+    loss_b = device_train_step(b, bopt, x, y)
+    loss_c = c(x, y)
+    loss_c.backward()
+    copt.step()
+    copt.zero_grad()
+    assert isinstance(loss_a, float) and loss_a == pytest.approx(float(loss_b)) == pytest.approx(float(loss_c.detach()))
+    sa = [u.flat_buffer.local_shard for u in P.collect_param_groups(a)]
+    for other in (b, c):
+        for s, t in zip(sa, [u.flat_buffer.local_shard for u in P.collect_param_groups(other)]):
+            assert torch.equal(s, t)
+    assert train_step(a, aopt, x, y, "cpu") < loss_a                       # the step went downhill on the same batch
