@@ -277,3 +277,20 @@ def test_compare_bench_modes_run_and_match_eager_on_two_cpu_ranks(capsys):
     checked = [r for r in rows if "full_grad_check" in r]
     assert len(checked) >= 5 and all(c["full_grad_check"]["max_abs_diff"] < 1e-4 and c["full_grad_check"]["params_compared"] > 0 for c in checked)
     assert all(set(r["phase_ms"]) >= {"forward", "backward", "step"} for r in rows)
+
+
+def test_selfcheck_runs_its_checks_on_two_ranks(capsys):
+    import json
+
+    from matrix_fsdp_b200.tools import selfcheck
+
+    assert selfcheck.main(["--ranks", "2", "--steps", "2", "--json"]) == 0
+    result = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert result["ok"] and result["ranks"] == 2 and len(result["reports"]) == 2
+    names = [c["name"] for c in result["reports"][0]["checks"]]
+    assert "re-sharded checkpoint restores the parameters bit for bit" in names and all(
+        c["ok"] for rep in result["reports"] for c in rep["checks"])
+    text = selfcheck.format_result(result)
+    assert "RESULT: all checks held" in text and "param_group_0" in text
+    broken = dict(result, ok=False, reports=[dict(result["reports"][0], error="Traceback: boom"), result["reports"][1]])
+    assert "FAILED" in selfcheck.format_result(broken) and "boom" in selfcheck.format_result(broken)
