@@ -186,6 +186,7 @@ class MatrixFSDPParamGroup:
         self._grads_seen: set[str] = set()
         self._direct_written: set[str] = set()
         self._pre_backward_done = False
+        self._backward_contexts: list = []          # weak references to the hook contexts of live graphs
         self._backward_callback_queued = False
         self._hook_handles: list = []
         self._initialized = False
@@ -567,6 +568,11 @@ class MatrixFSDPParamGroup:
             ctx = ForwardBackwardContext(self._pre_backward_unshard)
             hooks = register_pre_backward_hooks(output, ctx)
             self.forward_count_since_backward += 1
+            if hooks:
+                # remembered (weakly: the hooks on the outputs own it) so that it can fire again in a later
+                # backward pass over the same graph, see ``finalize_backward``
+                self._backward_contexts = [r for r in self._backward_contexts if r() is not None]
+                self._backward_contexts.append(weakref.ref(ctx))
         if self.reshard_after_forward and grad_mode and hooks and self.scheduler is not None \
                 and self.scheduler.keeps_unsharded_into_backward(self):
             # the unit that closes the forward opens the backward: resharding it now would only make the
@@ -589,6 +595,16 @@ class MatrixFSDPParamGroup:
     def _pre_backward_unshard(self) -> None:
         if self._pre_backward_done and self.state == FSDPLifecycleState.UNSHARDED:
             return
+        if self.state == FSDPLifecycleState.SHARDED and self.finalized_after_backward:
+            # another backward pass over a graph that was kept: this unit already reduced the gradients of the
+            # earlier pass.  Finish that reduction, take its result off the parameters (their shapes are about to
+            # change) and let this pass's reduction add to it, exactly as a new forward would.
+            if self.flat_buffer.pending_reduce is not None:
+                if self.scheduler is not None:
+                    self.scheduler.drop_pending_reduce(self)
+                self.wait_post_backward_reduce()
+            self.flat_buffer.stash_local_grads_for_accumulation()
+            self.finalized_after_backward = False
         self._record("pre_backward_unshard")
         self._pre_backward_done = True
         self._queue_backward_callback()
@@ -689,6 +705,12 @@ class MatrixFSDPParamGroup:
         self._pre_backward_done = False
         self.forward_count_since_backward = 0
         self.finalized_after_backward = True
+        # a graph that is kept (``retain_graph=True``, two losses over one forward) can be walked again: its
+        # output hooks have to gather the parameters again, and the gradients of that pass add to this one's
+        for r in self._backward_contexts:
+            ctx = r()
+            if ctx is not None:
+                ctx.reset()
         self._record("finalize_backward", start=t0, reason=reason, extra={"copy_in": how})
         if not (any_grad or self.has_accumulated_grads):
             return

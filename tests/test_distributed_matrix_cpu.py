@@ -143,6 +143,17 @@ CASES = {
                                           {"opt_kw": dict(backward_prefetch_timing="post_reshard")}),
     "units_sched_one_active_buffer": ("units", lambda: {}, "adamw", {"opt_kw": dict(max_active_full_param_buffers=1)}),
     "units_sched_two_pending_reduces": ("units", lambda: {}, "adamw", {"opt_kw": dict(max_pending_backward_reduces=2)}),
+    # two backward passes over one kept graph (two losses on one forward)
+    "root_two_losses": ("root", lambda: {}, "adamw", {"two_losses": True}),
+    "units_two_losses": ("units", lambda: {}, "adamw", {"two_losses": True}),
+    "policy_two_losses_keep_after_forward": ("policy", lambda: dict(reshard_after_forward=False), "sgd", {"two_losses": True}),
+    "units_two_losses_zero_copy_bucket": ("units", lambda: dict(use_zero_copy_grad_bucket=True), "adamw", {"two_losses": True}),
+    "units_two_losses_flat_reduce": ("units", lambda: dict(backward_reduce_strategy="flat"), "sgd", {"two_losses": True}),
+    "units_two_losses_owner_layout": ("units", lambda: dict(group_planner=_planner("parameter_boundary_plan")), "adamw",
+                                      {"two_losses": True}),
+    "units_two_losses_bf16": ("units", lambda: dict(mp_policy=_bf16()), "adamw", {"two_losses": True, "bf16": True}),
+    "units_two_losses_no_sync": ("units", lambda: {}, "sgd", {"two_losses": True, "no_sync": True}),
+    "units_two_losses_activation_checkpoint": ("units", lambda: {}, "adamw", {"two_losses": True, "ckpt": True}),
     # any element-wise torch optimizer, built by the user over model.parameters() and wrapped
     "wrapped_torch_adamw_amsgrad": ("units", lambda: {}, "torch:AdamW", {"torch_kw": dict(lr=1e-2, amsgrad=True)}),
     "wrapped_torch_adam": ("units", lambda: {}, "torch:Adam", {"torch_kw": dict(lr=1e-2)}),
@@ -241,6 +252,7 @@ HSDP_CASES = {
     "hsdp_units_no_sync": ("units", lambda: {}, "sgd", {"no_sync": True}),
     "hsdp_units_activation_checkpoint": ("units", lambda: {}, "adamw", {"ckpt": True}),
     "hsdp_units_zero_copy_bucket": ("units", lambda: dict(use_zero_copy_grad_bucket=True), "adamw", {}),
+    "hsdp_units_two_losses": ("units", lambda: {}, "adamw", {"two_losses": True}),
 }
 
 
@@ -325,18 +337,27 @@ def _run_case(rank, world, name):
         y = m(x.bfloat16()) if (bf16 and m is model) else m(x)
         return y.float().pow(2).mean()
 
+    def backward_of(m, x):
+        if not o.get("two_losses"):
+            loss_of(m, x).backward()
+            return
+        # two losses over one forward: the graph is kept and walked twice, the gradients add up
+        y = (m(x.bfloat16()) if (bf16 and m is model) else m(x)).float()
+        y.pow(2).mean().backward(retain_graph=True)
+        y.abs().mean().backward()
+
     for _ in range(2):
         xs = [torch.randn(4, 8, generator=g) for _ in range(2 if o.get("no_sync") else 1)]
         if o.get("no_sync"):
             with model.no_sync():
-                loss_of(model, xs[0]).backward()
-            loss_of(model, xs[1]).backward()
+                backward_of(model, xs[0])
+            backward_of(model, xs[1])
         else:
-            loss_of(model, xs[0]).backward()
+            backward_of(model, xs[0])
         opt.step()
         opt.zero_grad()
         for x in xs:
-            loss_of(ref, x).backward()
+            backward_of(ref, x)
         for p in ref.parameters():
             if p.grad is None:                                  # a module the step did not use
                 continue
@@ -372,7 +393,7 @@ THREE_RANK_CASES = ["root_default", "units_default", "policy_default", "units_ke
                     "units_gather_padded", "units_gather_owner_broadcast", "units_gather_all_reduce", "units_rows",
                     "root_rows", "units_zero_copy_bucket", "units_saved_tensor_hooks", "units_bf16", "units_no_sync",
                     "units_activation_checkpoint", "units_layout_flat_reorder", "topo_branches", "topo_twice_keep",
-                    "wrapped_torch_adam", "bare_torch_adamw"]
+                    "wrapped_torch_adam", "bare_torch_adamw", "units_two_losses", "root_two_losses"]
 
 
 def _worker(rank, world, out_path, which):

@@ -350,3 +350,23 @@ def test_second_forward_after_the_step_starts_a_fresh_cycle():
     names = [e.name for e in u.runtime_events]
     assert names.count("pre_forward") == 1 and names.count("finalize_backward") == 1
     _same_params(model, ref)
+
+
+@pytest.mark.parametrize("reshard", [True, False])
+def test_two_losses_over_one_forward_add_their_gradients(reshard):
+    """``loss_a.backward(retain_graph=True); loss_b.backward()``: the kept graph is walked twice, every unit gathers
+    its parameters again for the second pass and the two reductions add up."""
+    model, ref = _pair(reshard_after_forward=reshard)
+    opt, ropt = configure_optimizer(model, "sgd", lr=0.05), torch.optim.SGD(ref.parameters(), lr=0.05)
+    for seed in range(2):
+        x = torch.randn(4, 8, generator=torch.Generator().manual_seed(seed))
+        for m in (model, ref):
+            y = m(x)
+            y.pow(2).mean().backward(retain_graph=True)
+            y.abs().mean().backward()
+        opt.step(), ropt.step()
+        opt.zero_grad(), ropt.zero_grad()
+    _same_params(model, ref)
+    unit = model[0]._matrix_fsdp_param_group
+    names = [e.name for e in unit.runtime_events]
+    assert names.count("pre_backward_unshard") == 4 and names.count("start_reduce_scatter") == 4   # 2 steps x 2 passes
