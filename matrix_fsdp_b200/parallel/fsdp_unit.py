@@ -796,6 +796,12 @@ class MatrixFSDPParamGroup:
         self.discard_unused_prefetch()
         self.flush_deferred_reduce()
         self.wait_post_backward_reduce()
+        fb = self.flat_buffer
+        if fb.local_grad_valid and not fb.params_use_full and fb.pending_reduce is None:
+            # reduced gradients that were taken off the parameters for a pass that then produced nothing (a forward
+            # without a backward, an output that reaches no parameter) go back on: optimizers that read
+            # ``param.grad`` must see what the flat ones read from the shard
+            fb.use_local_grad_shard()
         self.used_in_forward = False
 
     def no_sync(self) -> MatrixFSDPNoSync:

@@ -370,3 +370,56 @@ def test_two_losses_over_one_forward_add_their_gradients(reshard):
     unit = model[0]._matrix_fsdp_param_group
     names = [e.name for e in unit.runtime_events]
     assert names.count("pre_backward_unshard") == 4 and names.count("start_reduce_scatter") == 4   # 2 steps x 2 passes
+
+
+class _PassThrough(nn.Module):
+    """Two outputs; the second one reaches no parameter of the unit."""
+
+    def __init__(self):
+        super().__init__()
+        self.lin = nn.Linear(8, 8)
+
+    def forward(self, x):
+        return self.lin(x), x * 2.0
+
+
+@pytest.mark.parametrize("wrapped_torch", [False, True])
+def test_an_output_that_reaches_no_parameter_does_not_disturb_the_step(wrapped_torch):
+    from matrix_fsdp_b200.optim.wrapper import MatrixFSDPOptimizer
+
+    reset_shared_owner_planners()
+    torch.manual_seed(0)
+    model, ref = _PassThrough(), None
+    ref = copy.deepcopy(model)
+    fully_shard(model)
+    opt = MatrixFSDPOptimizer(torch.optim.SGD(model.parameters(), lr=0.1), model) if wrapped_torch \
+        else configure_optimizer(model, "sgd", lr=0.1)
+    ropt = torch.optim.SGD(ref.parameters(), lr=0.1)
+    for seed in range(2):
+        x = torch.randn(4, 8, generator=torch.Generator().manual_seed(seed)).requires_grad_(True)
+        for m in (model, ref):
+            a, b = m(x)
+            # the pass-through output gets its gradient last: after the unit has seen all of its parameters' gradients
+            (a.pow(2).mean() + (b.detach() * 0).sum()).backward(retain_graph=True)
+            b.sum().backward()
+        opt.step(), ropt.step()
+        opt.zero_grad(), ropt.zero_grad()
+    _same_params(model, ref)
+
+
+@pytest.mark.parametrize("wrapped_torch", [False, True])
+def test_a_forward_without_backward_after_a_backward_keeps_the_reduced_gradients(wrapped_torch):
+    from matrix_fsdp_b200.optim.wrapper import MatrixFSDPOptimizer
+
+    model, ref = _pair()
+    opt = MatrixFSDPOptimizer(torch.optim.SGD(model.parameters(), lr=0.1), model) if wrapped_torch \
+        else configure_optimizer(model, "sgd", lr=0.1)
+    ropt = torch.optim.SGD(ref.parameters(), lr=0.1)
+    x = torch.randn(4, 8)
+    model(x).pow(2).mean().backward()
+    ref(x).pow(2).mean().backward()
+    with torch.no_grad():
+        model(x)                                            # e.g. an evaluation batch between backward and step
+    model(x)                                                # and a training-mode forward whose loss is never used
+    opt.step(), ropt.step()
+    _same_params(model, ref)
