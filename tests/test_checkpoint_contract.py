@@ -134,3 +134,60 @@ def test_hsdp_payload_keys_are_shared_by_replicas():
         run_ranks(_hsdp_worker, 4, d)
         files = os.listdir(d)
         assert "matrix_metadata.pt" in files and not [f for f in files if f.startswith("matrix_metadata_rank_")]
+
+
+# ----------------------------------------------------------------------------- mixed precision through every route
+def _bf16_pair(seed, kind, policy):
+    from torch.distributed.fsdp import MixedPrecisionPolicy
+
+    reset_shared_owner_planners()
+    torch.manual_seed(seed)
+    m = nn.Sequential(nn.Linear(4, 6), nn.Tanh(), nn.Linear(6, 4))
+    mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16)
+    fully_shard(m[0], optimizer_policy=policy, mp_policy=mp)
+    fully_shard(m, optimizer_policy=policy, mp_policy=mp)
+    return m, configure_optimizer(m, kind, lr=1e-2)
+
+
+def _bf16_step(m, o, seed):
+    x = torch.randn(3, 4, generator=torch.Generator().manual_seed(seed))
+    y = m(x.bfloat16())
+    y.float().pow(2).mean().backward()
+    o.step()
+    o.zero_grad()
+    return y.detach().float()
+
+
+@pytest.mark.parametrize("kind,policy", [("adamw", None), ("sgd", None), ("mixed_muon_adamw", "mixed_muon_adamw")])
+@pytest.mark.parametrize("route", ["dcp", "in_memory", "facade_sharded", "facade_full"])
+def test_bf16_compute_with_fp32_masters_resumes_exactly_through_every_route(route, kind, policy):
+    """The masters travel, never their bf16 copies: a twin with a history of its own continues bit for bit, and
+    the first forward after the load already runs on the loaded weights."""
+    import copy as _copy
+    import tempfile as _tempfile
+
+    from matrix_fsdp_b200 import load_matrix_state_dict, matrix_state_dict
+    from matrix_fsdp_b200.checkpoint import MatrixStateDictOptions, get_state_dict, set_state_dict
+    from matrix_fsdp_b200.checkpoint.state_dict import iter_optimizer_components
+
+    src, so = _bf16_pair(0, kind, policy)
+    _bf16_step(src, so, 1)
+    _bf16_step(src, so, 2)
+    dst, do = _bf16_pair(7, kind, policy)
+    _bf16_step(dst, do, 5)
+    if route == "dcp":
+        with _tempfile.TemporaryDirectory() as d:
+            save_matrix_dcp(src, d, optimizer=so, no_dist=True)
+            load_matrix_dcp(dst, d, optimizer=do, no_dist=True)
+    elif route == "in_memory":
+        load_matrix_state_dict(dst, matrix_state_dict(src))
+        for (_, a), (_, b) in zip(iter_optimizer_components(so), iter_optimizer_components(do)):
+            b.load_state_dict(_copy.deepcopy(a.state_dict()))
+    else:
+        options = MatrixStateDictOptions(full_state_dict=(route == "facade_full"))
+        model_sd, optim_sd = get_state_dict(src, so, options=options)
+        if route == "facade_full":
+            assert all(v.dtype == torch.float32 for v in model_sd.values())          # masters, not the compute copy
+        set_state_dict(dst, do, model_state_dict=model_sd, optim_state_dict=_copy.deepcopy(optim_sd), options=options)
+    for seed in (3, 4):
+        assert torch.equal(_bf16_step(src, so, seed), _bf16_step(dst, do, seed)), (route, kind, seed)
