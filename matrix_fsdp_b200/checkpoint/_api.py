@@ -18,7 +18,8 @@ import torch
 from torch import nn
 
 from ..parallel.unit_collection import collect_param_groups
-from .state_dict import iter_optimizer_components, load_matrix_state_dict, matrix_state_dict
+from .state_dict import (_full_master_params, iter_optimizer_components, load_matrix_state_dict,
+                         matrix_state_dict)
 
 
 @dataclass
@@ -33,28 +34,6 @@ def _opts(options) -> MatrixStateDictOptions:
         return MatrixStateDictOptions()
     return MatrixStateDictOptions(bool(getattr(options, "full_state_dict", False)),
                                   bool(getattr(options, "cpu_offload", False)), bool(getattr(options, "strict", True)))
-
-
-def _full_master_params(units) -> dict[int, torch.Tensor]:
-    """``id(parameter) -> full tensor`` assembled from the master shards, for units whose compute copy has a lower
-    precision than the master (the unsharded parameters of such a unit are the rounded copy).  Collective."""
-    import torch.distributed as dist
-
-    out: dict[int, torch.Tensor] = {}
-    for u in units:
-        fb = u.flat_buffer
-        if not fb.mixed:
-            continue
-        group = u.groups.shard_group if u.world_size > 1 else None
-        for mp in u.registry:
-            full = torch.zeros(mp.numel, dtype=fb.local_shard.dtype, device=fb.device)
-            piece = fb.pieces.get(mp.fqn)
-            if piece is not None:
-                full[piece.param_start:piece.param_start + piece.numel] = fb.local_shard[piece.local_start:piece.local_end]
-            if group is not None:
-                dist.all_reduce(full, group=group)          # every element has one owner: the sum places the pieces
-            out[id(mp.param)] = full.view(mp.shape)
-    return out
 
 
 def _full_model_state(model: nn.Module, cpu: bool) -> dict[str, torch.Tensor]:

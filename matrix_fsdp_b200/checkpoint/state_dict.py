@@ -548,6 +548,28 @@ def _check_envelope(meta: Mapping[str, Any], *, expect_rank: int | None) -> None
 
 
 # --------------------------------------------------------------------------- save
+def _full_master_params(units) -> dict[int, torch.Tensor]:
+    """``id(parameter) -> full tensor`` assembled from the master shards, for units whose compute copy has a lower
+    precision than the master (the unsharded parameters of such a unit are the rounded copy).  Collective."""
+    import torch.distributed as dist
+
+    out: dict[int, torch.Tensor] = {}
+    for u in units:
+        fb = u.flat_buffer
+        if not fb.mixed:
+            continue
+        group = u.groups.shard_group if u.world_size > 1 else None
+        for mp in u.registry:
+            full = torch.zeros(mp.numel, dtype=fb.local_shard.dtype, device=fb.device)
+            piece = fb.pieces.get(mp.fqn)
+            if piece is not None:
+                full[piece.param_start:piece.param_start + piece.numel] = fb.local_shard[piece.local_start:piece.local_end]
+            if group is not None:
+                dist.all_reduce(full, group=group)          # every element has one owner: the sum places the pieces
+            out[id(mp.param)] = full.view(mp.shape)
+    return out
+
+
 def save_matrix_dcp(model_or_units, directory: str, optimizer=None, *, full_state: bool = False,
                     include_grads: bool = False, dedup_replicates: bool = True, process_group=None,
                     no_dist: bool | None = None) -> dict[str, Any]:
@@ -574,11 +596,15 @@ def save_matrix_dcp(model_or_units, directory: str, optimizer=None, *, full_stat
     if full_state:
         for i, (u, us) in enumerate(zip(units, unit_meta)):
             prefix = f"{us['dcp_payload_rank']}.unit_{i}"
+            masters = _full_master_params([u])           # mixed precision: the masters, not the rounded compute copy
+            if masters:
+                us["full_param_dtype"] = str(u.flat_buffer.local_shard.dtype)
             u.unshard("checkpoint_full_state")
             for mp in u.registry:
                 us["full_param_keys"][mp.fqn] = f"{prefix}.full_param.{mp.fqn}"
                 if dcp_rank == 0 or not use_dist:
-                    tensors[us["full_param_keys"][mp.fqn]] = mp.param.detach().clone()
+                    whole = masters.get(id(mp.param))
+                    tensors[us["full_param_keys"][mp.fqn]] = whole if whole is not None else mp.param.detach().clone()
             u.reshard("checkpoint_full_state")
     opt_meta = None
     if optimizer is not None:
@@ -837,7 +863,7 @@ def load_matrix_dcp_full_state(directory: str, *, no_dist: bool | None = True) -
     for i, su in enumerate(_unit_list(meta, "DCP metadata")):
         for fqn, pm in su["params"].items():
             key = su.get("full_param_keys", {}).get(fqn) or f"{su['dcp_payload_rank']}.unit_{i}.full_param.{fqn}"
-            dtype = _dtype_from_string(su["param_dtype"]) if "param_dtype" in su else _dtype_from_string(pm["dtype"])
+            dtype = _dtype_from_string(su.get("full_param_dtype") or su.get("param_dtype") or pm["dtype"])
             req[key] = torch.empty(tuple(pm["shape"]), dtype=dtype)
             names[key] = param_key(su.get("module_fqn", ""), fqn, i)
     dcp.load(req, checkpoint_id=directory, no_dist=True)

@@ -191,3 +191,21 @@ def test_bf16_compute_with_fp32_masters_resumes_exactly_through_every_route(rout
         set_state_dict(dst, do, model_state_dict=model_sd, optim_state_dict=_copy.deepcopy(optim_sd), options=options)
     for seed in (3, 4):
         assert torch.equal(_bf16_step(src, so, seed), _bf16_step(dst, do, seed)), (route, kind, seed)
+
+
+def test_full_state_files_of_a_bf16_model_hold_the_fp32_masters():
+    from matrix_fsdp_b200 import load_matrix_dcp_full_state
+    from matrix_fsdp_b200.checkpoint import MatrixStateDictOptions, get_model_state_dict
+
+    model, opt = _bf16_pair(0, "adamw", None)
+    _bf16_step(model, opt, 1)
+    with tempfile.TemporaryDirectory() as d:
+        save_matrix_dcp(model, d, optimizer=opt, full_state=True, no_dist=True)
+        whole = load_matrix_dcp_full_state(d)["params"]
+    want = get_model_state_dict(model, options=MatrixStateDictOptions(full_state_dict=True))
+    masters = torch.cat([u.flat_buffer.local_shard for u in (model[0]._matrix_fsdp_param_group, model._matrix_fsdp_param_group)])
+    assert set(whole) == set(want)
+    for k, v in want.items():
+        assert whole[k].dtype == torch.float32 and torch.equal(whole[k], v), k
+    assert torch.equal(torch.cat([want["0.weight"].flatten(), want["0.bias"].flatten(), want["2.weight"].flatten(),
+                                  want["2.bias"].flatten()]), masters)
