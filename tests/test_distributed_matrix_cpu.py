@@ -56,6 +56,18 @@ def _rows(param):
     return Shard(0)
 
 
+def _bf16_everywhere():
+    from torch.distributed.fsdp import MixedPrecisionPolicy
+
+    return MixedPrecisionPolicy(param_dtype=torch.bfloat16)           # gradients are reduced in bf16 as well
+
+
+def _bf16_out_fp32():
+    from torch.distributed.fsdp import MixedPrecisionPolicy
+
+    return MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32, output_dtype=torch.float32)
+
+
 def _planner(name):
     from matrix_fsdp_b200.planning import planner as P
 
@@ -131,6 +143,16 @@ CASES = {
     "units_bf16": ("units", lambda: dict(mp_policy=_bf16()), "adamw", {"bf16": True}),
     "units_bf16_flat_reduce": ("units", lambda: dict(mp_policy=_bf16(), backward_reduce_strategy="flat"), "adamw",
                                {"bf16": True}),
+    "units_bf16_reduce_in_bf16": ("units", lambda: dict(mp_policy=_bf16_everywhere()), "adamw", {"bf16": True}),
+    "units_bf16_reduce_in_bf16_owner_layout": ("units", lambda: dict(mp_policy=_bf16_everywhere(),
+                                                                     group_planner=_planner("parameter_boundary_plan")),
+                                               "sgd", {"bf16": True}),
+    # (one unit: inside a stack every unit would hand fp32 to a sibling whose inputs nobody casts)
+    "root_bf16_fp32_outputs": ("root", lambda: dict(mp_policy=_bf16_out_fp32()), "adamw", {"bf16": True}),
+    "units_bf16_zero_copy_bucket": ("units", lambda: dict(mp_policy=_bf16_everywhere(), use_zero_copy_grad_bucket=True),
+                                    "adamw", {"bf16": True}),
+    "units_bf16_wrapped_torch_adam": ("units", lambda: dict(mp_policy=_bf16()), "torch:Adam",
+                                      {"torch_kw": dict(lr=1e-2), "bf16": True}),
     "root_no_sync": ("root", lambda: {}, "sgd", {"no_sync": True}),
     "units_no_sync": ("units", lambda: {}, "sgd", {"no_sync": True}),
     "units_no_sync_keep_after_forward": ("units", lambda: dict(reshard_after_forward=False), "sgd", {"no_sync": True}),
