@@ -237,6 +237,19 @@ def _detached_prefix(m, x):
     return m.head(m[2](m[1](h)))
 
 
+_ORDERS = ([0, 1, 2], [2, 1, 0], [0, 2], [1], [2, 0], [0, 1, 2])
+
+
+def _changing_order(m, x):
+    """Another order (and another subset) of the blocks at every call: what the scheduler learnt from the last
+    iteration is wrong for this one, prefetched units may go unused."""
+    calls = getattr(m, "_calls", 0)
+    m._calls = calls + 1
+    for j in _ORDERS[calls % len(_ORDERS)]:
+        x = m[j](x)
+    return m.head(x)
+
+
 TOPOLOGIES = {
     "topo_twice_keep": (_twice, dict(reshard_after_forward=False)),
     "topo_branches": (_branches, {}),
@@ -247,8 +260,16 @@ TOPOLOGIES = {
     "topo_reentrant_checkpointed_chain": (_reentrant_checkpointed_chain, {}),
     "topo_detached_prefix": (_detached_prefix, {}),
     "topo_detached_prefix_keep": (_detached_prefix, dict(reshard_after_forward=False)),
+    "topo_changing_order": (_changing_order, {}),
+    "topo_changing_order_keep": (_changing_order, dict(reshard_after_forward=False)),
+    "topo_changing_order_no_prefetch": (_changing_order, dict(forward_prefetch=False, backward_prefetch=False)),
 }
 CASES.update({name: ("units", (lambda kw=kw: dict(kw)), "adamw", {"fn": fn}) for name, (fn, kw) in TOPOLOGIES.items()})
+for _name, _opt_kw in {"three_ahead": dict(max_unsharded_prefetch_units=3), "one_buffer": dict(max_active_full_param_buffers=1),
+                       "post_reshard": dict(backward_prefetch_timing="post_reshard", max_unsharded_prefetch_units=2),
+                       "adaptive": dict(prefetch_policy="adaptive", adaptive_wait_threshold_ms=0.0),
+                       "next_step_prefetch": dict(prefetch_first_unit_after_step=True, next_step_prefetch_units=2)}.items():
+    CASES[f"topo_changing_order_{_name}"] = ("units", lambda: {}, "adamw", {"fn": _changing_order, "opt_kw": _opt_kw})
 
 
 class TopoNet(nn.Sequential):
@@ -368,7 +389,7 @@ def _run_case(rank, world, name):
         y.pow(2).mean().backward(retain_graph=True)
         y.abs().mean().backward()
 
-    for _ in range(2):
+    for _ in range(len(_ORDERS) if o.get("fn") is _changing_order else 2):
         xs = [torch.randn(4, 8, generator=g) for _ in range(2 if o.get("no_sync") else 1)]
         if o.get("no_sync"):
             with model.no_sync():
@@ -415,7 +436,8 @@ THREE_RANK_CASES = ["root_default", "units_default", "policy_default", "units_ke
                     "units_gather_padded", "units_gather_owner_broadcast", "units_gather_all_reduce", "units_rows",
                     "root_rows", "units_zero_copy_bucket", "units_saved_tensor_hooks", "units_bf16", "units_no_sync",
                     "units_activation_checkpoint", "units_layout_flat_reorder", "topo_branches", "topo_twice_keep",
-                    "wrapped_torch_adam", "bare_torch_adamw", "units_two_losses", "root_two_losses"]
+                    "wrapped_torch_adam", "bare_torch_adamw", "units_two_losses", "root_two_losses", "topo_changing_order",
+                    "topo_changing_order_next_step_prefetch"]
 
 
 def _worker(rank, world, out_path, which):
