@@ -207,8 +207,9 @@ def moe_ffn_reference(x, res, router_w, w_gu, w_down, top_k: int, aux_coef: floa
     for el in range(El):
         e = rank * El + el
         tok, kk = (idx_all == e).nonzero(as_tuple=True)
-        if tok.numel() == 0:
-            continue
+        # an expert without tokens still goes through the (empty) products: the result has to hang on ``x_all`` and
+        # ``w_all`` on every rank, or a rank whose experts stay idle would leave out the collectives in the backward
+        # of the gathers while the other ranks run them
         gu = F.linear(x_all[tok], w_gu[el])
         hcur = F.silu(gu[:, :Fd]) * gu[:, Fd:]
         ye = F.linear(hcur, w_down[el]).float() * w_all[tok, kk].unsqueeze(1)

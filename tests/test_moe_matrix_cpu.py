@@ -16,10 +16,10 @@ from dist_utils import run_ranks
 
 # experts, top-k, optimizer
 TRAIN_CASES = ["E4-K1-adamw", "E4-K2-adamw", "E4-K3-adamw", "E8-K2-adamw", "E8-K4-adamw", "E4-K2-sgd", "E8-K3-sgd",
-               "E4-K2-sgdm", "E2-K1-adamw", "E2-K2-adamw"]
+               "E4-K2-sgdm", "E2-K1-adamw", "E2-K2-adamw", "E4-K2-adamw-skewed", "E8-K2-sgd-skewed"]
 CLIP_CASES = ["clip-2", "clip-1", "clip-inf"]
 RESUME_CASES = ["resume-E4-K2-adamw", "resume-E4-K2-sgd", "resume-E4-K2-mixed_muon_adamw", "resume-E8-K3-adamw"]
-TRAIN4_CASES = ["E4-K2-adamw", "E8-K2-adamw", "E8-K3-sgd"]
+TRAIN4_CASES = ["E4-K2-adamw", "E8-K2-adamw", "E8-K3-sgd", "E8-K2-adamw-skewed"]
 RESUME4_CASES = ["resume-E8-K2-mixed_muon_adamw"]
 
 
@@ -44,7 +44,8 @@ def _train_case(rank, world, name):
     from matrix_fsdp_b200.models.moe import MoEModel, configure_moe_optimizer, shard_moe
     from matrix_fsdp_b200.parallel.expert_parallel import reset_contexts
 
-    n_experts, top_k, opt_kind = _parse(name)
+    skewed = name.endswith("-skewed")
+    n_experts, top_k, opt_kind = _parse(name.removesuffix("-skewed"))
     reset_shared_owner_planners()
     reset_contexts()
     cfg = _cfg(n_experts, top_k)
@@ -54,6 +55,15 @@ def _train_case(rank, world, name):
     ref = MoEModel(cfg, ep_group=False)
     el = n_experts // world
     assert model.layers[0].experts.w_down.shape[0] == el
+    if skewed:
+        # tokens whose features sum to a positive number go to the first top_k experts, the others to the next
+        # top_k, nobody to the rest (no ties anywhere): ranks that own only the rest receive no token at all
+        with torch.no_grad():
+            for m in (model, ref):
+                for layer in m.layers:
+                    layer.router.weight.zero_()
+                    layer.router.weight[:top_k] = 50.0
+                    layer.router.weight[top_k:2 * top_k] = -50.0
     shard_moe(model)
     momentum = 0.9 if opt_kind == "sgdm" else 0.0
     hyper = dict(lr=1e-2, betas=(0.9, 0.95)) if opt_kind == "adamw" else dict(lr=0.05, momentum=momentum)
