@@ -69,6 +69,14 @@ def set_model_state_dict(model: nn.Module, model_state_dict, *, options=None) ->
         for u in units:
             for mp in u.registry:
                 by_param[id(mp.param)] = (u, mp)
+        if o.strict:
+            # like nn.Module.load_state_dict(strict=True): nothing the model does not know, checked before anything
+            # is written
+            known = {n for n, _ in model.named_parameters(remove_duplicate=False)} | {n for n, _ in model.named_buffers()}
+            unexpected = sorted(k for k in model_state_dict if k not in known)
+            if unexpected:
+                raise KeyError(f"unexpected key(s) in state dict: {', '.join(map(repr, unexpected))}")
+        shapes = {id(mp.param): tuple(mp.shape) for u in units for mp in u.registry}
         with torch.no_grad():
             for name, p in model.named_parameters(remove_duplicate=False):
                 if name not in model_state_dict:
@@ -76,6 +84,10 @@ def set_model_state_dict(model: nn.Module, model_state_dict, *, options=None) ->
                         raise KeyError(f"missing key {name!r} in state dict")
                     continue
                 full = model_state_dict[name]
+                want = shapes.get(id(p), tuple(p.shape))
+                if tuple(full.shape) != want:
+                    raise RuntimeError(f"size mismatch for {name}: the state dict holds shape {tuple(full.shape)}, "
+                                       f"the model's parameter has shape {want}")
                 hit = by_param.get(id(p))
                 if hit is None:
                     p.data.copy_(full.to(p.device))

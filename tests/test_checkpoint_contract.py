@@ -209,3 +209,35 @@ def test_full_state_files_of_a_bf16_model_hold_the_fp32_masters():
         assert whole[k].dtype == torch.float32 and torch.equal(whole[k], v), k
     assert torch.equal(torch.cat([want["0.weight"].flatten(), want["0.bias"].flatten(), want["2.weight"].flatten(),
                                   want["2.bias"].flatten()]), masters)
+
+
+def test_gathered_state_dict_loading_is_strict_about_names_and_shapes():
+    from matrix_fsdp_b200.checkpoint import MatrixStateDictOptions as O
+    from matrix_fsdp_b200.checkpoint import get_model_state_dict, set_model_state_dict
+
+    def build(seed):
+        reset_shared_owner_planners()
+        torch.manual_seed(seed)
+        m = nn.Sequential(nn.Linear(4, 6), nn.BatchNorm1d(6), nn.Linear(6, 4))
+        fully_shard(m[0])
+        fully_shard(m)
+        return m
+
+    full = get_model_state_dict(build(0), options=O(full_state_dict=True))
+    assert "1.running_mean" in full and "1.num_batches_tracked" in full                 # buffers travel too
+    with pytest.raises(KeyError, match="unexpected"):
+        set_model_state_dict(build(1), dict(full, **{"extra.weight": torch.zeros(2)}), options=O(full_state_dict=True))
+    set_model_state_dict(build(1), dict(full, **{"extra.weight": torch.zeros(2)}), options=O(full_state_dict=True, strict=False))
+    with pytest.raises(KeyError, match="missing key '2.weight'"):
+        set_model_state_dict(build(1), {k: v for k, v in full.items() if not k.startswith("2.")}, options=O(full_state_dict=True))
+    with pytest.raises(RuntimeError, match=r"size mismatch for 0.weight.*\(3, 3\).*\(6, 4\)"):
+        set_model_state_dict(build(1), dict(full, **{"0.weight": torch.zeros(3, 3)}), options=O(full_state_dict=True))
+    target = build(1)
+    before = target._matrix_fsdp_param_group.flat_buffer.local_shard.clone()
+    with pytest.raises(KeyError):                                                        # refused before anything is written
+        set_model_state_dict(target, dict(full, **{"extra.weight": torch.zeros(2)}), options=O(full_state_dict=True))
+    assert torch.equal(target._matrix_fsdp_param_group.flat_buffer.local_shard, before)
+    loaded = build(1)
+    set_model_state_dict(loaded, {k: v.double() for k, v in full.items()}, options=O(full_state_dict=True))
+    again = get_model_state_dict(loaded, options=O(full_state_dict=True))
+    assert all(torch.equal(again[k], full[k]) for k in full) and again["0.weight"].dtype == torch.float32
