@@ -89,19 +89,20 @@ class MatrixFSDPNoSync:
 
     def __init__(self, units) -> None:
         self.units = list(units)
-        self._prev: list[bool] = []
+        self._prev: list[tuple[bool, bool]] = []
 
     def __enter__(self):
-        self._prev = [u.defer_backward_reduce for u in self.units]
+        # both flags are put back as they were found, so contexts nest: leaving an inner one keeps the outer in force
+        self._prev = [(u.defer_backward_reduce, u.in_no_sync) for u in self.units]
         for u in self.units:
             u.defer_backward_reduce = True
             u.in_no_sync = True
         return self
 
     def __exit__(self, *exc):
-        for u, prev in zip(self.units, self._prev):
-            u.defer_backward_reduce = prev
-            u.in_no_sync = False
+        for u, (defer, inside) in zip(self.units, self._prev):
+            u.defer_backward_reduce = defer
+            u.in_no_sync = inside
         return False
 
 

@@ -423,3 +423,30 @@ def test_a_forward_without_backward_after_a_backward_keeps_the_reduced_gradients
     model(x)                                                # and a training-mode forward whose loss is never used
     opt.step(), ropt.step()
     _same_params(model, ref)
+
+
+def test_no_sync_contexts_nest_and_survive_exceptions():
+    model, ref = _pair()
+    opt, ropt = configure_optimizer(model, "sgd", lr=0.1), torch.optim.SGD(ref.parameters(), lr=0.1)
+    units = [b._matrix_fsdp_param_group for b in model]
+    x = torch.randn(4, 8)
+
+    def both():
+        model(x).pow(2).mean().backward()
+        ref(x).pow(2).mean().backward()
+
+    with opt.no_sync():
+        with units[0].no_sync():                                                   # one unit, inside the context of all
+            both()
+        assert all(u.in_no_sync and u.defer_backward_reduce for u in units)      # the outer context is still in force
+        both()
+        assert all(u.flat_buffer.pending_reduce is None and not u.flat_buffer.local_grad_valid for u in units)
+    assert not any(u.in_no_sync or u.defer_backward_reduce for u in units)
+    with pytest.raises(KeyboardInterrupt):
+        with opt.no_sync():
+            both()
+            raise KeyboardInterrupt
+    assert not any(u.in_no_sync or u.defer_backward_reduce for u in units)       # left cleanly
+    both()                                                                        # reduces all four micro-batches
+    opt.step(), ropt.step()
+    _same_params(model, ref)
