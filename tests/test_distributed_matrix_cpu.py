@@ -153,6 +153,10 @@ CASES = {
                                     "adamw", {"bf16": True}),
     "units_bf16_wrapped_torch_adam": ("units", lambda: dict(mp_policy=_bf16()), "torch:Adam",
                                       {"torch_kw": dict(lr=1e-2), "bf16": True}),
+    "units_replicate_only_mesh": ("units", lambda: {}, "adamw", {"mesh": "replicate_only"}),
+    "units_replicate_only_mesh_no_sync": ("units", lambda: {}, "sgd", {"mesh": "replicate_only", "no_sync": True}),
+    "units_replicate_only_mesh_bf16": ("units", lambda: dict(mp_policy=_bf16()), "adamw", {"mesh": "replicate_only", "bf16": True}),
+    "units_one_d_named_mesh": ("units", lambda: {}, "adamw", {"mesh": "one_d_named"}),
     "root_no_sync": ("root", lambda: {}, "sgd", {"no_sync": True}),
     "units_no_sync": ("units", lambda: {}, "sgd", {"no_sync": True}),
     "units_no_sync_keep_after_forward": ("units", lambda: dict(reshard_after_forward=False), "sgd", {"no_sync": True}),
@@ -353,6 +357,20 @@ def _run_case(rank, world, name):
         model.pattern = pattern
     ref = copy.deepcopy(model)
     kw = make_kw()
+    if o.get("mesh") == "replicate_only":                     # a 2 x 1 mesh: nothing to shard, gradients averaged over replicas
+        from torch.distributed.device_mesh import init_device_mesh
+
+        from matrix_fsdp_b200 import DataParallelMeshDims
+
+        if "replicate_only" not in _MESH:
+            _MESH["replicate_only"] = init_device_mesh("cpu", (world, 1), mesh_dim_names=("dp_replicate", "dp_shard"))
+        kw.update(mesh=_MESH["replicate_only"], dp_mesh_dims=DataParallelMeshDims(shard="dp_shard", replicate="dp_replicate"))
+    elif o.get("mesh") == "one_d_named":
+        from torch.distributed.device_mesh import init_device_mesh
+
+        if "one_d" not in _MESH:
+            _MESH["one_d"] = init_device_mesh("cpu", (world,), mesh_dim_names=("dp",))
+        kw.update(mesh=_MESH["one_d"])
     if name.startswith("hsdp_"):
         from matrix_fsdp_b200 import DataParallelMeshDims
 
@@ -425,7 +443,9 @@ def _run_case(rank, world, name):
             assert u.full_param_storage_nbytes() == 0, u.name
         # the optimizer state of a rank is the size of its own shard, never of the whole unit
         assert u.flat_buffer.local_numel <= u.flat_buffer.total_numel
-    if world > 1:
+    if o.get("mesh") == "replicate_only":
+        assert all(u.world_size == 1 and u.replicate_world_size == world for u in units)
+    elif world > 1:
         assert sum(u.flat_buffer.local_numel for u in units) < sum(u.flat_buffer.total_numel for u in units)
 
 
