@@ -1,4 +1,4 @@
-"""matrix_dcp checkpoints cross world sizes: written by 1 process, 2 and 3 flat gloo ranks and 4 gloo ranks (HSDP 2 x 2),
+"""matrix_dcp checkpoints cross world sizes: written by 1 process, 2 and 3 flat gloo ranks, 2 replicas (nothing sharded) and 4 gloo ranks (HSDP 2 x 2),
 each read back, re-sharded, by every OTHER arrangement.  Parameters have to arrive bitwise, and one more training
 step (optimizer state included) has to land where the writer's own next step landed.  Every rank of every
 arrangement trains on the same batch, so the averaged gradient does not depend on the arrangement.
@@ -18,7 +18,7 @@ from torch import nn
 
 from dist_utils import run_ranks
 
-ARRANGEMENTS = ("w1", "w2", "w3", "w4hsdp")
+ARRANGEMENTS = ("w1", "w2", "w2rep", "w3", "w4hsdp")
 OPTIMIZERS = ("adamw", "sgd", "mixed_muon_adamw")
 CASES = [f"{src}->{dst}:{opt}" for src in ARRANGEMENTS for dst in ARRANGEMENTS if src != dst for opt in OPTIMIZERS]
 
@@ -43,6 +43,14 @@ def _build(seed, opt_kind, arrangement):
         if "mesh" not in _CACHE:
             _CACHE["mesh"] = init_device_mesh("cpu", (2, 2), mesh_dim_names=("dp_replicate", "dp_shard"))
         kw = dict(mesh=_CACHE["mesh"], dp_mesh_dims=DataParallelMeshDims(shard="dp_shard", replicate="dp_replicate"))
+    if arrangement == "w2rep":                                # two replicas, nothing sharded: only one of them writes
+        from torch.distributed.device_mesh import init_device_mesh
+
+        from matrix_fsdp_b200 import DataParallelMeshDims
+
+        if "rep" not in _CACHE:
+            _CACHE["rep"] = init_device_mesh("cpu", (2, 1), mesh_dim_names=("dp_replicate", "dp_shard"))
+        kw = dict(mesh=_CACHE["rep"], dp_mesh_dims=DataParallelMeshDims(shard="dp_shard", replicate="dp_replicate"))
     model = _model(seed)
     for m in list(model.children())[:-1] + [model]:
         fully_shard(m, optimizer_policy="mixed_muon_adamw" if opt_kind == "mixed_muon_adamw" else None, **kw)
@@ -140,7 +148,7 @@ def _visit(arrangement, base_dir, sources, save):
     if arrangement == "w1":
         return _stage("w1", base_dir, sources, save=save)
     out_path = os.path.join(base_dir, f"outcomes-{arrangement}-{int(save)}.json")
-    run_ranks(_worker, {"w2": 2, "w3": 3, "w4hsdp": 4}[arrangement], arrangement, base_dir, sources, save, out_path,
+    run_ranks(_worker, {"w2": 2, "w2rep": 2, "w3": 3, "w4hsdp": 4}[arrangement], arrangement, base_dir, sources, save, out_path,
               timeout=600.0)
     with open(out_path) as f:
         return json.load(f)
@@ -152,11 +160,13 @@ def outcomes():
     with tempfile.TemporaryDirectory() as tmp:
         results.update(_visit("w1", tmp, (), True))
         results.update(_visit("w2", tmp, ("w1",), True))
-        results.update(_visit("w3", tmp, ("w1", "w2"), True))
-        results.update(_visit("w4hsdp", tmp, ("w1", "w2", "w3"), True))
+        results.update(_visit("w2rep", tmp, ("w1", "w2"), True))
+        results.update(_visit("w3", tmp, ("w1", "w2", "w2rep"), True))
+        results.update(_visit("w4hsdp", tmp, ("w1", "w2", "w2rep", "w3"), True))
         results.update(_visit("w3", tmp, ("w4hsdp",), False))
-        results.update(_visit("w2", tmp, ("w3", "w4hsdp"), False))
-        results.update(_visit("w1", tmp, ("w2", "w3", "w4hsdp"), False))
+        results.update(_visit("w2rep", tmp, ("w3", "w4hsdp"), False))
+        results.update(_visit("w2", tmp, ("w2rep", "w3", "w4hsdp"), False))
+        results.update(_visit("w1", tmp, ("w2", "w2rep", "w3", "w4hsdp"), False))
     return results
 
 
