@@ -243,3 +243,28 @@ def test_train_step_is_forward_backward_step_and_a_loss_read_back():
         for s, t in zip(sa, [u.flat_buffer.local_shard for u in P.collect_param_groups(other)]):
             assert torch.equal(s, t)
     assert train_step(a, aopt, x, y, "cpu") < loss_a                       # the step went downhill on the same batch
+
+
+# ------------------------------------------------------------------------------------------ kernel library status
+def test_kernel_library_status_says_why_when_it_is_not_available(monkeypatch):
+    from matrix_fsdp_b200.ops import NativeKernelStatus, native_kernel_available, native_kernel_status
+
+    st = native_kernel_status()
+    assert isinstance(st, NativeKernelStatus) and st.library.endswith("libmfsdp_kernels.so")
+    assert native_kernel_available() == st.available
+    if st.available:
+        assert st.reason is None and st.missing_entry_points == () and st.entry_points >= 40
+    else:
+        assert st.reason                                                     # never a bare "no"
+    monkeypatch.setenv("MFSDP_DISABLE_NATIVE_KERNELS", "1")
+    off = native_kernel_status()
+    assert not off.available and off.disabled_by_env and "MFSDP_DISABLE_NATIVE_KERNELS" in off.reason
+
+
+def test_segment_fusion_helpers_merge_per_rank():
+    from matrix_fsdp_b200.core.layout import LayoutSegment as S
+    from matrix_fsdp_b200.ops import coalesce_contiguous_segments, coalesce_rank_segments
+
+    assert coalesce_contiguous_segments([S(0, 3, 0), S(3, 5, 3), S(9, 12, 5)]) == (S(0, 5, 0), S(9, 12, 5))
+    merged = coalesce_rank_segments([[S(0, 3, 0), S(3, 5, 3)], [], [S(5, 6, 0), S(7, 8, 1)]])
+    assert merged == ((S(0, 5, 0),), (), (S(5, 6, 0), S(7, 8, 1)))
