@@ -33,7 +33,7 @@ class MoEConfig:
     rope_theta: float = 10000.0
     eps: float = 1e-5
     init_std: float = 0.02
-    capacity_factor: float = 1.25
+    capacity_factor: float = 0.0          # <= 0: receive buffers sized for the worst case, no row is ever dropped
     max_seq_len: int = 4096
     seed: int = 0
     loss_ignore_index: int | None = None

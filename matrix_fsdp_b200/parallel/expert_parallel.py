@@ -25,7 +25,7 @@ _CONTEXTS: dict[tuple, "ExpertParallelContext"] = {}
 
 class ExpertParallelContext:
     def __init__(self, group, device: torch.device, hidden: int, n_experts: int, top_k: int, max_tokens: int,
-                 capacity_factor: float = 1.25) -> None:
+                 capacity_factor: float = 0.0) -> None:
         self.group, self.device = group, device
         self.world = dist.get_world_size(group) if group is not None else 1
         self.rank = dist.get_rank(group) if group is not None else 0
@@ -81,7 +81,7 @@ class ExpertParallelContext:
 
     @classmethod
     def get(cls, group, device: torch.device, hidden: int, n_experts: int, top_k: int, max_tokens: int,
-            capacity_factor: float = 1.25) -> "ExpertParallelContext":
+            capacity_factor: float = 0.0) -> "ExpertParallelContext":
         key = (id(group) if group is not None else 0, device.index, hidden, n_experts, top_k)
         ctx = _CONTEXTS.get(key)
         if ctx is None or ctx.max_tokens < max_tokens:
