@@ -137,19 +137,26 @@ def _stage(arrangement, base_dir, sources, *, save, rank=0, world=1):
     return results
 
 
-def _worker(rank, world, arrangement, base_dir, sources, save, out_path):
-    results = _stage(arrangement, base_dir, sources, save=save, rank=rank, world=world)
+def _worker(rank, world, jobs, base_dir, save, out_path):
+    results = {}
+    for arrangement, sources in jobs:                       # every arrangement of this world size in one spawn
+        results.update(_stage(arrangement, base_dir, sources, save=save, rank=rank, world=world))
     if rank == 0:
         with open(out_path, "w") as f:
             json.dump(results, f)
 
 
-def _visit(arrangement, base_dir, sources, save):
-    if arrangement == "w1":
-        return _stage("w1", base_dir, sources, save=save)
-    out_path = os.path.join(base_dir, f"outcomes-{arrangement}-{int(save)}.json")
-    run_ranks(_worker, {"w2": 2, "w2rep": 2, "w3": 3, "w4hsdp": 4}[arrangement], arrangement, base_dir, sources, save, out_path,
-              timeout=600.0)
+_WORLD = {"w2": 2, "w2rep": 2, "w3": 3, "w4hsdp": 4}
+
+
+def _visit(jobs, base_dir, save):
+    """``jobs``: [(arrangement, sources), ...] of one world size."""
+    if jobs[0][0] == "w1":
+        return _stage("w1", base_dir, jobs[0][1], save=save)
+    world = _WORLD[jobs[0][0]]
+    assert all(_WORLD[a] == world for a, _ in jobs)
+    out_path = os.path.join(base_dir, f"outcomes-{world}-{int(save)}.json")
+    run_ranks(_worker, world, jobs, base_dir, save, out_path, timeout=600.0)
     with open(out_path) as f:
         return json.load(f)
 
@@ -158,15 +165,13 @@ def _visit(arrangement, base_dir, sources, save):
 def outcomes():
     results = {}
     with tempfile.TemporaryDirectory() as tmp:
-        results.update(_visit("w1", tmp, (), True))
-        results.update(_visit("w2", tmp, ("w1",), True))
-        results.update(_visit("w2rep", tmp, ("w1", "w2"), True))
-        results.update(_visit("w3", tmp, ("w1", "w2", "w2rep"), True))
-        results.update(_visit("w4hsdp", tmp, ("w1", "w2", "w2rep", "w3"), True))
-        results.update(_visit("w3", tmp, ("w4hsdp",), False))
-        results.update(_visit("w2rep", tmp, ("w3", "w4hsdp"), False))
-        results.update(_visit("w2", tmp, ("w2rep", "w3", "w4hsdp"), False))
-        results.update(_visit("w1", tmp, ("w2", "w2rep", "w3", "w4hsdp"), False))
+        results.update(_visit([("w1", ())], tmp, True))
+        results.update(_visit([("w2", ("w1",)), ("w2rep", ("w1", "w2"))], tmp, True))
+        results.update(_visit([("w3", ("w1", "w2", "w2rep"))], tmp, True))
+        results.update(_visit([("w4hsdp", ("w1", "w2", "w2rep", "w3"))], tmp, True))
+        results.update(_visit([("w3", ("w4hsdp",))], tmp, False))
+        results.update(_visit([("w2rep", ("w3", "w4hsdp")), ("w2", ("w2rep", "w3", "w4hsdp"))], tmp, False))
+        results.update(_visit([("w1", ("w2", "w2rep", "w3", "w4hsdp"))], tmp, False))
     return results
 
 
