@@ -321,27 +321,6 @@ def _common_replicate_group(units):
     return next(iter(groups.values()))
 
 
-class _LazyMuonOptimizer:
-    """Placeholder used when this rank owns no Muon matrices (keeps the mixed API uniform)."""
-
-    def __init__(self, **defaults) -> None:
-        self.param_groups: list[dict] = []
-        self.state: dict = {}
-        self.defaults = defaults
-
-    def step(self) -> None:
-        return None
-
-    def zero_grad(self, set_to_none: bool = True) -> None:
-        return None
-
-    def state_dict(self) -> dict:
-        return {"state": {}, "param_groups": []}
-
-    def load_state_dict(self, sd) -> None:
-        return None
-
-
 class MixedMuonAdamWOptimizer:
     """Muon on owned whole matrices + AdamW on the rest, behind one optimizer-like object."""
 
@@ -368,8 +347,10 @@ class MixedMuonAdamWOptimizer:
         if muon_ns_coefficients is not None:
             muon_kw["ns_coefficients"] = tuple(muon_ns_coefficients)
         with _suppress_auto_prepare():
-            self.muon = MatrixMuon(muon_params, low_precision_of=lp_of, **muon_kw) if muon_params \
-                else _LazyMuonOptimizer(**muon_kw)
+            # a rank that owns no matrix still gets a real (empty) Muon optimizer: LR schedulers and state-dict code
+            # written against ``opt.muon`` then run unchanged on every rank
+            self.muon = MatrixMuon(muon_params or [torch.nn.Parameter(torch.zeros(0, 0), requires_grad=False)],
+                                   low_precision_of=lp_of, **muon_kw)
             self.adamw = FlatShardedAdamW(
                 adamw_params or [torch.nn.Parameter(torch.zeros(0))], units=None,
                 lr=lr if adamw_lr is None else adamw_lr, betas=adamw_betas, eps=adamw_eps,

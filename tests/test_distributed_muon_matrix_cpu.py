@@ -178,11 +178,70 @@ def _run_case(rank, world, name):
         assert sum(done) == n_matrices, done                                     # replicas split the work, no repeats
 
 
+def _lonely_rank_case(rank, world):
+    """One matrix, two ranks: one of them owns no matrix at all.  Its ``opt.muon`` is still a torch optimizer (LR
+    schedulers attach on every rank), checkpoints round-trip, and training matches the unsharded optimizers."""
+    import tempfile as _tempfile
+
+    from matrix_fsdp_b200 import configure_optimizer, fully_shard, load_matrix_dcp, save_matrix_dcp
+    from matrix_fsdp_b200.api import reset_shared_owner_planners
+    from matrix_fsdp_b200.optim.muon import MatrixMuon
+
+    def build(seed):
+        reset_shared_owner_planners()
+        torch.manual_seed(seed)
+        m = nn.Sequential(nn.Linear(8, 8))
+        fully_shard(m, optimizer_policy="mixed_muon_adamw")
+        return m, configure_optimizer(m, "mixed_muon_adamw", **dict(_MUON, lr=0.02, weight_decay=0.0))
+
+    model, opt = build(0)
+    torch.manual_seed(0)
+    ref = nn.Sequential(nn.Linear(8, 8))
+    unit = model._matrix_fsdp_param_group
+    owners = [None] * world
+    dist.all_gather_object(owners, unit.owner_ranks("0.weight") == (rank,))
+    assert sum(owners) == 1                                            # exactly one rank owns the matrix
+    assert isinstance(opt.muon, torch.optim.Optimizer) and isinstance(opt.adamw, torch.optim.Optimizer)
+    scheds = [torch.optim.lr_scheduler.StepLR(o, step_size=1, gamma=0.5) for o in (opt.muon, opt.adamw)]
+    rmuon = MatrixMuon([ref[0].weight], lr=0.02, weight_decay=0.0, momentum=_MUON["muon_momentum"], nesterov=True,
+                       ns_steps=_MUON["muon_ns_steps"], adjust_lr_fn="original")
+    radamw = torch.optim.AdamW([ref[0].bias], lr=0.02, weight_decay=0.0)
+    rscheds = [torch.optim.lr_scheduler.StepLR(o, step_size=1, gamma=0.5) for o in (rmuon, radamw)]
+    g = torch.Generator().manual_seed(3 + rank)
+    for _ in range(3):
+        x = torch.randn(4, 8, generator=g)
+        model(x).pow(2).mean().backward()
+        ref(x).pow(2).mean().backward()
+        for p in ref.parameters():
+            dist.all_reduce(p.grad)
+            p.grad /= world
+        opt.step(); rmuon.step(); radamw.step()
+        opt.zero_grad(); rmuon.zero_grad(); radamw.zero_grad()
+        for s in scheds + rscheds:
+            s.step()
+    full = _full_params(model)
+    for n, p in ref.named_parameters():
+        assert torch.allclose(full[n], p.detach(), atol=2e-5), n
+    base = [None]
+    if rank == 0:
+        base[0] = _tempfile.mkdtemp()
+    dist.broadcast_object_list(base, src=0)
+    save_matrix_dcp(model, base[0], optimizer=opt)
+    dist.barrier()
+    twin, topt = build(4)
+    load_matrix_dcp(twin, base[0], optimizer=topt)
+    assert torch.equal(twin._matrix_fsdp_param_group.flat_buffer.local_shard, unit.flat_buffer.local_shard)
+    assert [g_["lr"] for g_ in topt.param_groups] == [g_["lr"] for g_ in opt.param_groups]
+
+
 def _worker(rank, world, out_path, which):
     results = {}
-    for name in (HSDP_CASES if which == "hsdp" else CASES):
+    for name in (HSDP_CASES if which == "hsdp" else list(CASES) + ["lonely_rank"]):
         try:
-            _run_case(rank, world, name)
+            if name == "lonely_rank":
+                _lonely_rank_case(rank, world)
+            else:
+                _run_case(rank, world, name)
             mine = ""
         except Exception:
             mine = traceback.format_exc()
@@ -222,3 +281,8 @@ def test_two_rank_mixed_muon_matches_unsharded_optimizers(outcomes, case):
 def test_four_rank_hsdp_mixed_muon_matches_unsharded_optimizers(hsdp_outcomes, case):
     assert case in hsdp_outcomes, "the worker did not reach this case"
     assert not hsdp_outcomes[case], hsdp_outcomes[case]
+
+
+def test_two_ranks_one_matrix_the_rank_without_it_still_has_a_muon_optimizer(outcomes):
+    assert "lonely_rank" in outcomes, "the worker did not reach this case"
+    assert not outcomes["lonely_rank"], outcomes["lonely_rank"]
