@@ -23,8 +23,21 @@ class LayoutParam(Protocol):
     end: int
 
 
+class _Span:
+    """Interval arithmetic shared by the segment records: ``[global_start, global_end)`` of the flat space, packed
+    at ``local_start`` of the holder's shard."""
+
+    __slots__ = ()
+
+    numel = property(lambda self: self.global_end - self.global_start)
+    local_end = property(lambda self: self.local_start + (self.global_end - self.global_start))
+
+    def intersects(self, start: int, end: int) -> bool:
+        return self.global_start < end and start < self.global_end
+
+
 @dataclass(frozen=True)
-class LayoutSegment:
+class LayoutSegment(_Span):
     global_start: int
     global_end: int
     local_start: int
@@ -35,33 +48,14 @@ class LayoutSegment:
         if self.global_start < 0 or self.local_start < 0:
             raise ValueError("segment offsets must be non-negative")
 
-    @property
-    def numel(self) -> int:
-        return self.global_end - self.global_start
-
-    @property
-    def local_end(self) -> int:
-        return self.local_start + self.numel
-
-    def intersects(self, start: int, end: int) -> bool:
-        return self.global_start < end and start < self.global_end
-
 
 @dataclass(frozen=True)
-class ParamSegment:
+class ParamSegment(_Span):
     fqn: str
     rank: int
     global_start: int
     global_end: int
     local_start: int
-
-    @property
-    def numel(self) -> int:
-        return self.global_end - self.global_start
-
-    @property
-    def local_end(self) -> int:
-        return self.local_start + self.numel
 
     def to_layout_segment(self) -> LayoutSegment:
         return LayoutSegment(self.global_start, self.global_end, self.local_start)
