@@ -128,7 +128,10 @@ def build_ours_moe(cfg: dict, device, mesh, world: int):
 
     mcfg = MoEConfig(vocab_size=cfg["vocab_size"], hidden=cfg["hidden"], n_layers=cfg["n_layers"],
                      n_heads=cfg["n_heads"], head_dim=cfg["head_dim"], n_experts=cfg["n_experts"],
-                     expert_ffn=cfg["expert_ffn"], top_k=cfg["top_k"], max_seq_len=cfg["seq_len"])
+                     expert_ffn=cfg["expert_ffn"], top_k=cfg["top_k"], max_seq_len=cfg["seq_len"],
+                     # 0 (default): receive buffers sized for the worst case, nothing is ever dropped; a positive
+                     # factor caps them at that multiple of the average load and the line reports what was lost
+                     capacity_factor=float(os.environ.get("MFSDP_MOE_CAPACITY_FACTOR", "0")))
     torch.manual_seed(0)
     model = MoEModel(mcfg, ep_group=None if world > 1 else False, device=device, dtype=torch.bfloat16).to(device)
     shard_moe(model, mesh=mesh, mp_policy=MixedPrecisionPolicy(param_dtype=torch.bfloat16),
@@ -342,7 +345,8 @@ def _moe_drop_report(model, device, world: int) -> dict:
     if world > 1:
         dist.all_reduce(lost)
         dist.all_reduce(routed)
-    return {"rows_lost": int(lost.item()), "rows_routed": int(routed.item()), "sized_for_worst_case": dropless}
+    return {"rows_lost": int(lost.item()), "rows_routed": int(routed.item()), "sized_for_worst_case": dropless,
+            "capacity_factor": float(os.environ.get("MFSDP_MOE_CAPACITY_FACTOR", "0"))}
 
 
 def write_timeline(path: str, device_step, sync, rank: int, world: int, device, bench_line: dict) -> dict:
